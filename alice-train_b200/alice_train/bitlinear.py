@@ -1,0 +1,116 @@
+"""Batched BitLinear path on device tensors (torch is used for memory and streams only).
+
+    w = BitLinearWeights(out, in)        # ab_weights handle
+    w.quantize_(latent)                  # kernel (1): gamma + 2-bit codes in every layout
+    xq = act_quant_int8(x)               # kernel (2a)
+    y  = bitlinear_fwd(w, xq)            # kernel (2b): int8 x ternary on tcgen05
+    dx = bitlinear_dx(w, dy)             # kernel (3): bf16 x ternary on tcgen05
+    ste_dw(dy, x, dW, beta=1.0)          # kernel (4): bf16 x bf16 on tcgen05
+
+These stand where the reference runs cuBLAS sgemm on fake-quantised f32 weights
+(src/cuda_matmul.rs:1149-1699,1859-1915) after fused_merge_and_quantize_alpha
+(src/bin/train_qat_70b.rs:2072-2211) / fake_quantize_into (src/qwen35.rs:404).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+
+import torch
+
+from . import _ffi
+from .context import GpuContext
+from .ops import TernaryWeightKernel
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _ffi.AB_F32
+    if t.dtype == torch.bfloat16:
+        return _ffi.AB_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _dp(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _chk2d(t: torch.Tensor, name: str):
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be a 2-D CUDA tensor with unit inner stride")
+
+
+class BitLinearWeights(TernaryWeightKernel):
+    """TernaryWeightKernel plus the absmean quantiser that fills it from latent f32 weights."""
+
+    def quantize_(self, latent: torch.Tensor, fq_out: torch.Tensor | None = None,
+                  guard: int = _ffi.AB_GUARD_INV_ZERO, want_stats: bool = False):
+        if latent.dtype != torch.float32 or not latent.is_cuda or not latent.is_contiguous():
+            raise ValueError("latent weights must be a contiguous float32 CUDA tensor")
+        if latent.numel() != self._out * self._in:
+            raise AssertionError("assertion `left == right` failed: latent.len() == out*in")
+        if fq_out is not None and (fq_out.dtype != torch.float32 or fq_out.numel() != latent.numel()):
+            raise AssertionError("assertion `left == right` failed: src.len() == dst.len()")
+        _ffi.check(self._lib.ab_fq_absmean_pack(self.ctx.handle, _dp(latent), self._h, _dp(fq_out), guard,
+                                                int(want_stats)), self.ctx.handle)
+        return self
+
+
+@dataclasses.dataclass
+class QuantizedActivations:
+    xq: torch.Tensor       # int8 [m, k]
+    scales: torch.Tensor   # f32 [m]  absmax per token
+    rowsums: torch.Tensor  # s32 [m]  sum of xq per token
+
+
+def act_quant_int8(ctx: GpuContext, x: torch.Tensor, out: QuantizedActivations | None = None) -> QuantizedActivations:
+    _chk2d(x, "x")
+    m, k = x.shape
+    if out is None:
+        out = QuantizedActivations(torch.empty((m, k), dtype=torch.int8, device=x.device),
+                                   torch.empty(m, dtype=torch.float32, device=x.device),
+                                   torch.empty(m, dtype=torch.int32, device=x.device))
+    _ffi.check(_ffi.load().ab_act_quant_int8(ctx.handle, _dp(x), _dt(x), m, k, x.stride(0), _dp(out.xq),
+                                             out.xq.stride(0), _dp(out.scales), _dp(out.rowsums)), ctx.handle)
+    return out
+
+
+def bitlinear_fwd(w: BitLinearWeights, a: QuantizedActivations, y: torch.Tensor | None = None,
+                  dtype=torch.bfloat16, acc_out: torch.Tensor | None = None) -> torch.Tensor:
+    m = a.xq.shape[0]
+    if a.xq.shape[1] != w.in_features():
+        raise AssertionError("assertion `left == right` failed: x.cols == in_features")
+    if y is None:
+        y = torch.empty((m, w.out_features()), dtype=dtype, device=a.xq.device)
+    _chk2d(y, "y")
+    _ffi.check(w._lib.ab_bitlinear_fwd(w.ctx.handle, w.handle, _dp(a.xq), a.xq.stride(0), _dp(a.scales),
+                                       _dp(a.rowsums), m, _dp(y), _dt(y), y.stride(0), _dp(acc_out)), w.ctx.handle)
+    return y
+
+
+def bitlinear_dx(w: BitLinearWeights, dy: torch.Tensor, dx: torch.Tensor | None = None, dtype=torch.bfloat16,
+                 beta: float = 0.0) -> torch.Tensor:
+    _chk2d(dy, "dy")
+    if dy.dtype != torch.bfloat16:
+        raise TypeError("dy must be bfloat16")
+    m = dy.shape[0]
+    if dy.shape[1] != w.out_features():
+        raise AssertionError("assertion `left == right` failed: dy.cols == out_features")
+    if dx is None:
+        dx = torch.empty((m, w.in_features()), dtype=dtype, device=dy.device)
+    _chk2d(dx, "dx")
+    _ffi.check(w._lib.ab_bitlinear_dx(w.ctx.handle, w.handle, _dp(dy), dy.stride(0), m, _dp(dx), _dt(dx),
+                                      dx.stride(0), float(beta)), w.ctx.handle)
+    return dx
+
+
+def ste_dw(ctx: GpuContext, dy: torch.Tensor, x: torch.Tensor, dW: torch.Tensor, beta: float = 1.0) -> torch.Tensor:
+    _chk2d(dy, "dy"); _chk2d(x, "x"); _chk2d(dW, "dW")
+    if dy.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or dW.dtype != torch.float32:
+        raise TypeError("dy and x must be bfloat16, dW float32")
+    m, out = dy.shape
+    if x.shape[0] != m or tuple(dW.shape) != (out, x.shape[1]):
+        raise AssertionError("assertion `left == right` failed: grad_weights.len() == out*in")
+    _ffi.check(_ffi.load().ab_ste_dw(ctx.handle, _dp(dy), dy.stride(0), _dp(x), x.stride(0), m, out, x.shape[1],
+                                     _dp(dW), dW.stride(0), float(beta)), ctx.handle)
+    return dW

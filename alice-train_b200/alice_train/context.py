@@ -1,0 +1,73 @@
+"""Device context: the Python face of ab_ctx.
+
+Stands where the reference has GpuContext::new_blocking (src/gpu.rs:37-79), the global
+CUDA_MATMUL installed by init_cuda_blas (src/blas.rs:15-24) and CudaMatmul::new
+(src/cuda_matmul.rs:953).  There is no CPU path: without a B200 creation raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _ffi
+
+
+class GpuContext:
+    def __init__(self, device: int = 0, stream: int | None = None):
+        lib = _ffi.load()
+        h = C.c_void_p()
+        _ffi.check(lib.ab_ctx_create(int(device), C.c_void_p(stream) if stream else None, C.byref(h)))
+        self._lib, self._h, self.device = lib, h, int(device)
+
+    @classmethod
+    def new_blocking(cls, device: int = 0):
+        """Option<GpuContext>: None when no usable device exists (src/gpu.rs:37)."""
+        try:
+            return cls(device)
+        except _ffi.AliceB200Error as e:
+            if e.status == _ffi.AB_ERR_NO_DEVICE:
+                return None
+            raise
+
+    @classmethod
+    def on_torch_stream(cls, device: int = 0):
+        """Context that enqueues on torch's current stream of `device` (so torch events time it)."""
+        import torch
+        return cls(device, torch.cuda.current_stream(device).cuda_stream)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def sync(self):
+        _ffi.check(self._lib.ab_ctx_sync(self._h), self._h)
+
+    def launch_count(self) -> int:
+        return int(self._lib.ab_ctx_launch_count(self._h))
+
+    def close(self):
+        if self._h:
+            self._lib.ab_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_default: GpuContext | None = None
+
+
+def default_context() -> GpuContext:
+    """Process-wide context on device 0, created on first use (the reference keeps one global
+    CudaMatmul behind a OnceLock, src/blas.rs:15)."""
+    global _default
+    if _default is None:
+        _default = GpuContext(0)
+    return _default
+
+
+def set_default_context(ctx: GpuContext | None):
+    global _default
+    _default = ctx

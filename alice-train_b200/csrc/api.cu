@@ -1,0 +1,735 @@
+// extern "C" surface of libalice_b200: argument checks, handle lifetime, host-slice variants.
+// The arithmetic lives in the kernel files; nothing here computes on the CPU.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+float ab_key_to_float(unsigned int k);
+void ab_matvec_bwd_plan(const ab_ctx* ctx, size_t out, size_t in, int* slices, size_t* rows_per_slice,
+                        size_t* partial_stride);
+
+#define AB_REQUIRE(cond, code) \
+    do {                       \
+        if (!(cond)) return (code); \
+    } while (0)
+
+#define AB_TRY(expr)          \
+    do {                      \
+        int _st = (expr);     \
+        if (_st) return _st;  \
+    } while (0)
+
+static int grow(ab_ctx* ctx, void** buf, size_t* cap, size_t bytes) {
+    if (bytes <= *cap && *buf) return AB_OK;
+    if (*buf) {
+        // the old buffer may still be in use by queued work
+        AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+        AB_CUDA_CHECK(ctx, cudaFree(*buf));
+        *buf = nullptr;
+        *cap = 0;
+    }
+    size_t want = bytes < 256 ? 256 : bytes;
+    AB_CUDA_CHECK(ctx, cudaMalloc(buf, want));
+    *cap = want;
+    return AB_OK;
+}
+
+int ab_ctx_scratch(ab_ctx* ctx, size_t bytes, void** out) {
+    AB_TRY(grow(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes));
+    *out = ctx->scratch;
+    return AB_OK;
+}
+
+int ab_ctx_stage(ab_ctx* ctx, int slot, size_t bytes, void** out) {
+    AB_TRY(grow(ctx, &ctx->stage[slot], &ctx->stage_bytes[slot], bytes));
+    *out = ctx->stage[slot];
+    return AB_OK;
+}
+
+static int bind(ab_ctx* ctx) {
+    AB_REQUIRE(ctx, AB_ERR_NULL);
+    AB_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+    return AB_OK;
+}
+
+extern "C" {
+
+const char* ab_status_str(int status) {
+    switch (status) {
+        case AB_OK: return "ok";
+        case AB_ERR_NULL: return "null pointer";
+        case AB_ERR_SHAPE: return "shape or length mismatch";
+        case AB_ERR_ALIGN: return "misaligned pointer or pitch";
+        case AB_ERR_CUDA: return "CUDA error";
+        case AB_ERR_DEVICE_TIMEOUT: return "bounded wait in a kernel ran out";
+        case AB_ERR_UNSUPPORTED: return "unsupported arguments";
+        case AB_ERR_NO_DEVICE: return "no CUDA device";
+        case AB_ERR_STATE: return "handle holds no data";
+        default: return "unknown status";
+    }
+}
+
+int ab_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int ab_ctx_create(int device, void* cuda_stream, ab_ctx** out) {
+    AB_REQUIRE(out, AB_ERR_NULL);
+    *out = nullptr;
+    int n = ab_device_count();
+    if (n <= 0 || device < 0 || device >= n) return AB_ERR_NO_DEVICE;
+    ab_ctx* ctx = new (std::nothrow) ab_ctx();
+    AB_REQUIRE(ctx, AB_ERR_CUDA);
+    ctx->device = device;
+    int st = AB_OK;
+    do {
+        if (cudaSetDevice(device) != cudaSuccess) { st = AB_ERR_NO_DEVICE; break; }
+        int major = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (major != 10) { st = AB_ERR_NO_DEVICE; break; }  // kernels are built for sm_100a only
+        cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (cuda_stream) {
+            ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+        } else {
+            if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { st = AB_ERR_CUDA; break; }
+            ctx->owns_stream = true;
+        }
+        if (cudaMalloc(&ctx->dev_status, 256) != cudaSuccess) { st = AB_ERR_CUDA; break; }
+        if (cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) { st = AB_ERR_CUDA; break; }
+        const char* e = getenv("ALICE_B200_FWD_SIGNED");
+        ctx->fwd_offset_binary = (e && e[0] == '1') ? 0 : 1;
+    } while (0);
+    if (st != AB_OK) {
+        cudaGetLastError();
+        delete ctx;
+        return st;
+    }
+    *out = ctx;
+    return AB_OK;
+}
+
+int ab_ctx_destroy(ab_ctx* ctx) {
+    AB_REQUIRE(ctx, AB_ERR_NULL);
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    for (int i = 0; i < 6; ++i)
+        if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return AB_OK;
+}
+
+int ab_ctx_sync(ab_ctx* ctx) {
+    AB_TRY(bind(ctx));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    int status = 0;
+    AB_CUDA_CHECK(ctx, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        ctx->last_error = "device-side wait timed out, code " + std::to_string(status);
+        cudaMemset(ctx->dev_status, 0, sizeof(int));
+        return AB_ERR_DEVICE_TIMEOUT;
+    }
+    return AB_OK;
+}
+
+void* ab_ctx_stream(ab_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
+const char* ab_ctx_last_error(ab_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+uint64_t ab_ctx_launch_count(ab_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ------------------------------------------------------------------------------ weights
+static int weights_create(ab_ctx* ctx, size_t out, size_t in, bool gemm_copies, ab_weights** wout) {
+    AB_REQUIRE(wout, AB_ERR_NULL);
+    *wout = nullptr;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(out < (1ull << 31) && in < (1ull << 31), AB_ERR_UNSUPPORTED);
+    ab_weights* w = new (std::nothrow) ab_weights();
+    AB_REQUIRE(w, AB_ERR_CUDA);
+    w->ctx = ctx;
+    w->out = out;
+    w->in = in;
+    w->pitch = ab_round_up(in ? in : 1, 128) / 4;
+    w->tpitch = ab_round_up(out ? out : 1, 128) / 4;
+    size_t cbytes = (out ? out : 1) * w->pitch, tbytes = (in ? in : 1) * w->tpitch;
+    cudaError_t e = cudaMalloc(&w->codes, cbytes);
+    if (e == cudaSuccess && gemm_copies) e = cudaMalloc(&w->codes_fwd, cbytes);
+    if (e == cudaSuccess && gemm_copies) e = cudaMalloc(&w->codes_t, tbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&w->gamma_dev, 256);
+    if (e == cudaSuccess) e = cudaMalloc(&w->report_dev, sizeof(ab_fq_dev_report));
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->codes, 0, cbytes, ctx->stream);
+    if (e == cudaSuccess && gemm_copies) e = cudaMemsetAsync(w->codes_fwd, 0, cbytes, ctx->stream);
+    if (e == cudaSuccess && gemm_copies) e = cudaMemsetAsync(w->codes_t, 0, tbytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->report_dev, 0, sizeof(ab_fq_dev_report), ctx->stream);
+    const float one = 1.0f;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->gamma_dev, &one, sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        ctx->last_error = std::string("ab_weights_create: ") + cudaGetErrorString(e);
+        ab_weights_destroy(w);
+        return AB_ERR_CUDA;
+    }
+    *wout = w;
+    return AB_OK;
+}
+
+int ab_weights_create(ab_ctx* ctx, size_t out, size_t in, ab_weights** w) {
+    return weights_create(ctx, out, in, true, w);
+}
+
+int ab_weights_destroy(ab_weights* w) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    if (w->ctx) {
+        cudaSetDevice(w->ctx->device);
+        cudaStreamSynchronize(w->ctx->stream);
+    }
+    if (w->codes) cudaFree(w->codes);
+    if (w->codes_fwd) cudaFree(w->codes_fwd);
+    if (w->codes_t) cudaFree(w->codes_t);
+    if (w->gamma_dev) cudaFree(w->gamma_dev);
+    if (w->report_dev) cudaFree(w->report_dev);
+    delete w;
+    return AB_OK;
+}
+
+size_t ab_weights_out_features(const ab_weights* w) { return w ? w->out : 0; }
+size_t ab_weights_in_features(const ab_weights* w) { return w ? w->in : 0; }
+size_t ab_weights_words_per_row(const ab_weights* w) { return w ? (w->in + 31) / 32 : 0; }
+
+int ab_weights_set_ternary(ab_weights* w, const int8_t* values, size_t len) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(len == w->out * w->in, AB_ERR_SHAPE);
+    if (len) {
+        AB_REQUIRE(values, AB_ERR_NULL);
+        void* d = nullptr;
+        AB_TRY(ab_ctx_stage(ctx, 0, len, &d));
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(d, values, len, cudaMemcpyHostToDevice, ctx->stream));
+        AB_TRY(abk_codes_from_ternary(ctx, w, (const int8_t*)d));
+        AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    w->has_data = true;
+    return AB_OK;
+}
+
+int ab_weights_set_bitplanes(ab_weights* w, const uint32_t* plus, const uint32_t* minus, size_t words) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    const size_t need = w->out * ((w->in + 31) / 32);
+    AB_REQUIRE(words == need, AB_ERR_SHAPE);
+    if (need) {
+        AB_REQUIRE(plus && minus, AB_ERR_NULL);
+        void *dp = nullptr, *dm = nullptr;
+        AB_TRY(ab_ctx_stage(ctx, 0, need * 4, &dp));
+        AB_TRY(ab_ctx_stage(ctx, 1, need * 4, &dm));
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dp, plus, need * 4, cudaMemcpyHostToDevice, ctx->stream));
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dm, minus, need * 4, cudaMemcpyHostToDevice, ctx->stream));
+        AB_TRY(abk_codes_from_bitplanes(ctx, w, (const uint32_t*)dp, (const uint32_t*)dm));
+        AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    w->has_data = true;
+    return AB_OK;
+}
+
+int ab_weights_get_bitplanes(ab_weights* w, uint32_t* plus, uint32_t* minus, size_t words) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w->has_data, AB_ERR_STATE);
+    const size_t need = w->out * ((w->in + 31) / 32);
+    AB_REQUIRE(words == need, AB_ERR_SHAPE);
+    if (!need) return AB_OK;
+    AB_REQUIRE(plus && minus, AB_ERR_NULL);
+    void *dp = nullptr, *dm = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, need * 4, &dp));
+    AB_TRY(ab_ctx_stage(ctx, 1, need * 4, &dm));
+    AB_TRY(abk_codes_to_bitplanes(ctx, w, (uint32_t*)dp, (uint32_t*)dm));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(plus, dp, need * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(minus, dm, need * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_weights_set_packed2b(ab_weights* w, const uint8_t* packed, size_t bytes, float gamma) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    const size_t need = (w->out * w->in + 3) / 4;
+    AB_REQUIRE(bytes == need, AB_ERR_SHAPE);
+    if (need) {
+        AB_REQUIRE(packed, AB_ERR_NULL);
+        void* d = nullptr;
+        AB_TRY(ab_ctx_stage(ctx, 0, need, &d));
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(d, packed, need, cudaMemcpyHostToDevice, ctx->stream));
+        AB_TRY(abk_codes_from_flat(ctx, w, (const uint8_t*)d));
+    }
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(w->gamma_dev, &gamma, sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    w->has_data = true;
+    return AB_OK;
+}
+
+int ab_weights_get_packed2b(ab_weights* w, uint8_t* packed, size_t bytes) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w->has_data, AB_ERR_STATE);
+    const size_t need = (w->out * w->in + 3) / 4;
+    AB_REQUIRE(bytes == need, AB_ERR_SHAPE);
+    if (!need) return AB_OK;
+    AB_REQUIRE(packed, AB_ERR_NULL);
+    void* d = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, need, &d));
+    AB_TRY(abk_codes_to_flat(ctx, w, (uint8_t*)d));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(packed, d, need, cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_weights_get_ternary(ab_weights* w, int8_t* values, size_t len) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w->has_data, AB_ERR_STATE);
+    AB_REQUIRE(len == w->out * w->in, AB_ERR_SHAPE);
+    if (!len) return AB_OK;
+    AB_REQUIRE(values, AB_ERR_NULL);
+    void* d = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, len, &d));
+    AB_TRY(abk_codes_to_ternary(ctx, w, (int8_t*)d));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(values, d, len, cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_weights_set_gamma(ab_weights* w, float gamma) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(w->gamma_dev, &gamma, sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_weights_get_gamma(ab_weights* w, float* gamma) {
+    AB_REQUIRE(w && gamma, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(gamma, w->gamma_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+// ----------------------------------------------------------------------------- quantiser
+int ab_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int guard, int want_stats) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w, AB_ERR_NULL);
+    AB_REQUIRE(w->ctx == ctx, AB_ERR_STATE);
+    AB_REQUIRE(w->codes_fwd && w->codes_t, AB_ERR_STATE);
+    AB_REQUIRE(guard == AB_GUARD_INV_ZERO || guard == AB_GUARD_FLOOR, AB_ERR_UNSUPPORTED);
+    if (w->out * w->in) AB_REQUIRE(w_latent, AB_ERR_NULL);
+    AB_REQUIRE((reinterpret_cast<uintptr_t>(w_latent) & 3) == 0, AB_ERR_ALIGN);
+    return abk_fq_absmean_pack(ctx, w_latent, w, fq_out, guard, want_stats);
+}
+
+int ab_weights_fq_report(ab_weights* w, ab_fq_report* r) {
+    AB_REQUIRE(w && r, AB_ERR_NULL);
+    ab_ctx* ctx = w->ctx;
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w->has_report, AB_ERR_STATE);
+    ab_fq_dev_report d;
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(&d, w->report_dev, sizeof(d), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    memset(r, 0, sizeof(*r));
+    r->gamma = d.gamma;
+    r->sum_abs = d.sum_abs;
+    r->n = (uint64_t)w->out * w->in;
+    r->n_plus = d.n_plus;
+    r->n_minus = d.n_minus;
+    r->n_threshold = d.n_threshold;
+    r->sum_err = d.sum_err;
+    r->dot_wq = d.dot_wq;
+    r->dot_ww = d.dot_ww;
+    r->dot_qq = d.dot_qq;
+    unsigned int kmin, kmax;
+    memcpy(&kmin, &d.w_min, 4);
+    memcpy(&kmax, &d.w_max, 4);
+    r->w_min = ab_key_to_float(kmin);
+    r->w_max = ab_key_to_float(kmax);
+    return AB_OK;
+}
+
+int ab_quantize_and_pack_host(ab_ctx* ctx, const float* weights, size_t n, float* scale, uint8_t* packed) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(scale, AB_ERR_NULL);
+    if (n == 0) {  // (0.0, Vec::new())  src/export.rs:95-97
+        *scale = 0.0f;
+        return AB_OK;
+    }
+    AB_REQUIRE(weights && packed, AB_ERR_NULL);
+    ab_weights* w = nullptr;
+    AB_TRY(weights_create(ctx, 1, n, false, &w));
+    void* d = nullptr;
+    int st = ab_ctx_stage(ctx, 0, n * sizeof(float), &d);
+    if (!st) {
+        cudaError_t e = cudaMemcpyAsync(d, weights, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+    }
+    if (!st) st = abk_fq_absmean_pack(ctx, (const float*)d, w, nullptr, AB_GUARD_INV_ZERO, 0);
+    if (!st) {
+        cudaError_t e = cudaMemcpyAsync(packed, w->codes, (n + 3) / 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(scale, w->gamma_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+    }
+    ab_weights_destroy(w);
+    return st;
+}
+
+int ab_calibrate_scale(ab_ctx* ctx, const float* w, size_t n, float* scale_dev) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(scale_dev, AB_ERR_NULL);
+    if (n) AB_REQUIRE(w, AB_ERR_NULL);
+    return abk_calibrate_scale(ctx, w, n, scale_dev);
+}
+
+int ab_fake_quantize_forward(ab_ctx* ctx, const float* w, float* q, size_t n, const float* scale_dev,
+                             float temperature, int bits) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(scale_dev, AB_ERR_NULL);
+    AB_REQUIRE(bits >= AB_TERNARY && bits <= AB_INT8, AB_ERR_UNSUPPORTED);
+    if (n) AB_REQUIRE(w && q, AB_ERR_NULL);
+    return abk_fake_quantize_forward(ctx, w, q, n, scale_dev, temperature, bits);
+}
+
+int ab_ste_backward(ab_ctx* ctx, const float* g, float* out, size_t n, float clip) {
+    AB_TRY(bind(ctx));
+    if (n) AB_REQUIRE(g && out, AB_ERR_NULL);
+    return abk_ste_backward(ctx, g, out, n, clip);
+}
+
+static int stats_finish(ab_ctx* ctx, double* out7_dev, size_t n, float* out5) {
+    double h[7];
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(h, out7_dev, sizeof(h), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    unsigned long long kmin, kmax;
+    memcpy(&kmin, &h[5], 8);
+    memcpy(&kmax, &h[6], 8);
+    const double dn = (double)n;
+    out5[0] = ab_key_to_float((unsigned int)kmin);
+    out5[1] = ab_key_to_float((unsigned int)kmax);
+    out5[2] = (float)(h[0] / dn);
+    out5[3] = (float)(h[1] / dn);
+    const double denom = sqrt(h[3] * h[4]);
+    out5[4] = denom > 1e-10 ? (float)(h[2] / denom) : 0.0f;
+    return AB_OK;
+}
+
+int ab_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n, float* out5) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(out5, AB_ERR_NULL);
+    if (n == 0) return AB_OK;  // stats untouched (src/qat.rs:266-268)
+    AB_REQUIRE(w && q, AB_ERR_NULL);
+    double* out7 = reinterpret_cast<double*>(reinterpret_cast<char*>(ctx->dev_status) + 64);
+    AB_TRY(abk_calibration_stats(ctx, w, q, n, out7));
+    return stats_finish(ctx, out7, n, out5);
+}
+
+int ab_calibrate_scale_host(ab_ctx* ctx, const float* w, size_t n, float* scale_inout) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(scale_inout, AB_ERR_NULL);
+    if (n == 0) return AB_OK;
+    AB_REQUIRE(w, AB_ERR_NULL);
+    void* d = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, n * sizeof(float), &d));
+    float* sdev = reinterpret_cast<float*>(reinterpret_cast<char*>(ctx->dev_status) + 16);
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(d, w, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(sdev, scale_inout, sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_TRY(abk_calibrate_scale(ctx, (const float*)d, n, sdev));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(scale_inout, sdev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_fake_quantize_forward_host(ab_ctx* ctx, const float* w, size_t w_len, float* q, size_t q_len, float scale,
+                                  float temperature, int bits) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w_len == q_len, AB_ERR_SHAPE);  // assert_eq!(weights.len(), quantized.len())  src/qat.rs:174
+    AB_REQUIRE(bits >= AB_TERNARY && bits <= AB_INT8, AB_ERR_UNSUPPORTED);
+    if (w_len == 0) return AB_OK;
+    AB_REQUIRE(w && q, AB_ERR_NULL);
+    void *dw = nullptr, *dq = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, w_len * sizeof(float), &dw));
+    AB_TRY(ab_ctx_stage(ctx, 1, w_len * sizeof(float), &dq));
+    float* sdev = reinterpret_cast<float*>(reinterpret_cast<char*>(ctx->dev_status) + 16);
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dw, w, w_len * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(sdev, &scale, sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_TRY(abk_fake_quantize_forward(ctx, (const float*)dw, (float*)dq, w_len, sdev, temperature, bits));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(q, dq, w_len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_ste_backward_host(ab_ctx* ctx, const float* go, size_t go_len, float* gi, size_t gi_len, float clip) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(go_len == gi_len, AB_ERR_SHAPE);  // src/qat.rs:212
+    if (go_len == 0) return AB_OK;
+    AB_REQUIRE(go && gi, AB_ERR_NULL);
+    void *a = nullptr, *b = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, go_len * sizeof(float), &a));
+    AB_TRY(ab_ctx_stage(ctx, 1, go_len * sizeof(float), &b));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(a, go, go_len * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_TRY(abk_ste_backward(ctx, (const float*)a, (float*)b, go_len, clip));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(gi, b, go_len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_calibration_stats_host(ab_ctx* ctx, const float* w, const float* q, size_t n, float* out5) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(out5, AB_ERR_NULL);
+    if (n == 0) return AB_OK;
+    AB_REQUIRE(w && q, AB_ERR_NULL);
+    void *a = nullptr, *b = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, n * sizeof(float), &a));
+    AB_TRY(ab_ctx_stage(ctx, 1, n * sizeof(float), &b));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(a, w, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(b, q, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    double* out7 = reinterpret_cast<double*>(reinterpret_cast<char*>(ctx->dev_status) + 64);
+    AB_TRY(abk_calibration_stats(ctx, (const float*)a, (const float*)b, n, out7));
+    return stats_finish(ctx, out7, n, out5);
+}
+
+// -------------------------------------------------------------------------------- matvec
+static int check_w(ab_ctx* ctx, const ab_weights* w) {
+    AB_REQUIRE(w, AB_ERR_NULL);
+    AB_REQUIRE(w->ctx == ctx, AB_ERR_STATE);
+    AB_REQUIRE(w->has_data, AB_ERR_STATE);
+    return AB_OK;
+}
+
+int ab_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (w->out) AB_REQUIRE(y, AB_ERR_NULL);
+    if (w->in) AB_REQUIRE(x, AB_ERR_NULL);
+    return abk_ternary_matvec(ctx, w, x, y);
+}
+
+int ab_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (w->out) AB_REQUIRE(dy, AB_ERR_NULL);
+    if (w->in) AB_REQUIRE(dx, AB_ERR_NULL);
+    return abk_ternary_matvec_backward(ctx, w, dy, dx);
+}
+
+int ab_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy, int pre_norm,
+                          float norm_eps, float* dx, float* d_bias) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (w->out) AB_REQUIRE(dy, AB_ERR_NULL);
+    if (w->in) AB_REQUIRE(dx && x, AB_ERR_NULL);
+    return abk_bitlinear_backward(ctx, w, x, dy, pre_norm, norm_eps, dx, d_bias);
+}
+
+int ab_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in, const float* dy, size_t out, float* dW) {
+    AB_TRY(bind(ctx));
+    if (in * out) AB_REQUIRE(x && dy && dW, AB_ERR_NULL);
+    return abk_ste_weight_grad(ctx, x, in, dy, out, dW);
+}
+
+int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (m * w->out) AB_REQUIRE(a && c, AB_ERR_NULL);
+    return abk_ternary_matmul_bt(ctx, a, w, scale, c, m);
+}
+
+static int h2d(ab_ctx* ctx, int slot, const void* src, size_t bytes, void** dev) {
+    AB_TRY(ab_ctx_stage(ctx, slot, bytes ? bytes : 4, dev));
+    if (bytes) AB_CUDA_CHECK(ctx, cudaMemcpyAsync(*dev, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return AB_OK;
+}
+static int d2h_sync(ab_ctx* ctx, void* dst, const void* dev, size_t bytes) {
+    if (bytes) AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
+int ab_ternary_matvec_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len, float* y, size_t y_len) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(x_len == w->in && y_len == w->out, AB_ERR_SHAPE);
+    if (x_len) AB_REQUIRE(x, AB_ERR_NULL);
+    if (y_len) AB_REQUIRE(y, AB_ERR_NULL);
+    void *dx = nullptr, *dy = nullptr;
+    AB_TRY(h2d(ctx, 0, x, x_len * 4, &dx));
+    AB_TRY(ab_ctx_stage(ctx, 1, y_len * 4 + 4, &dy));
+    AB_TRY(abk_ternary_matvec(ctx, w, (const float*)dx, (float*)dy));
+    return d2h_sync(ctx, y, dy, y_len * 4);
+}
+
+int ab_ternary_matvec_backward_host(ab_ctx* ctx, const ab_weights* w, const float* dy, size_t dy_len, float* dx,
+                                    size_t dx_len) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(dy_len == w->out, AB_ERR_SHAPE);  // assert_eq!(grad_output.len(), out_features)  src/backward.rs:36
+    AB_REQUIRE(dx_len == w->in, AB_ERR_SHAPE);   // assert_eq!(grad_input.len(), in_features)    src/backward.rs:37
+    if (dy_len) AB_REQUIRE(dy, AB_ERR_NULL);
+    if (dx_len) AB_REQUIRE(dx, AB_ERR_NULL);
+    void *ddy = nullptr, *ddx = nullptr;
+    AB_TRY(h2d(ctx, 0, dy, dy_len * 4, &ddy));
+    AB_TRY(ab_ctx_stage(ctx, 1, dx_len * 4 + 4, &ddx));
+    AB_TRY(abk_ternary_matvec_backward(ctx, w, (const float*)ddy, (float*)ddx));
+    return d2h_sync(ctx, dx, ddx, dx_len * 4);
+}
+
+int ab_bitlinear_backward_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len, const float* dy,
+                               size_t dy_len, int pre_norm, float norm_eps, float* dx, size_t dx_len, float* d_bias,
+                               size_t d_bias_len) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(x_len == w->in, AB_ERR_SHAPE);    // src/backward.rs:117
+    AB_REQUIRE(dy_len == w->out, AB_ERR_SHAPE);  // src/backward.rs:118
+    AB_REQUIRE(dx_len == w->in, AB_ERR_SHAPE);   // src/backward.rs:119
+    if (d_bias) AB_REQUIRE(d_bias_len == w->out, AB_ERR_SHAPE);  // src/backward.rs:122
+    if (x_len) AB_REQUIRE(x && dx, AB_ERR_NULL);
+    if (dy_len) AB_REQUIRE(dy, AB_ERR_NULL);
+    void *dxin = nullptr, *ddy = nullptr, *ddx = nullptr, *db = nullptr;
+    AB_TRY(h2d(ctx, 0, x, x_len * 4, &dxin));
+    AB_TRY(h2d(ctx, 1, dy, dy_len * 4, &ddy));
+    AB_TRY(ab_ctx_stage(ctx, 2, dx_len * 4 + 4, &ddx));
+    if (d_bias) AB_TRY(ab_ctx_stage(ctx, 3, dy_len * 4 + 4, &db));
+    AB_TRY(abk_bitlinear_backward(ctx, w, (const float*)dxin, (const float*)ddy, pre_norm, norm_eps, (float*)ddx,
+                                  (float*)db));
+    if (d_bias && dy_len)
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(d_bias, db, dy_len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return d2h_sync(ctx, dx, ddx, dx_len * 4);
+}
+
+int ab_ste_weight_grad_host(ab_ctx* ctx, const float* x, size_t x_len, const float* dy, size_t dy_len, float* dW,
+                            size_t dw_len) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(dw_len == x_len * dy_len, AB_ERR_SHAPE);  // src/backward.rs:176
+    if (dw_len == 0) return AB_OK;
+    AB_REQUIRE(x && dy && dW, AB_ERR_NULL);
+    void *dx = nullptr, *ddy = nullptr, *ddw = nullptr;
+    AB_TRY(h2d(ctx, 0, x, x_len * 4, &dx));
+    AB_TRY(h2d(ctx, 1, dy, dy_len * 4, &ddy));
+    AB_TRY(h2d(ctx, 2, dW, dw_len * 4, &ddw));
+    AB_TRY(abk_ste_weight_grad(ctx, (const float*)dx, x_len, (const float*)ddy, dy_len, (float*)ddw));
+    return d2h_sync(ctx, dW, ddw, dw_len * 4);
+}
+
+int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed_b, float scale, float* c, size_t m,
+                              size_t n, size_t k) {
+    AB_TRY(bind(ctx));
+    if (m * n == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (k) AB_REQUIRE(a && packed_b, AB_ERR_NULL);
+    ab_weights* w = nullptr;
+    AB_TRY(weights_create(ctx, n, k, false, &w));
+    int st = AB_OK;
+    // rows of packed_b have stride ceil(k/4) (src/blas.rs:412); land them at the handle's pitch
+    const size_t pk = (k + 3) / 4;
+    if (pk) {
+        cudaError_t e = cudaMemcpy2DAsync(w->codes, w->pitch, packed_b, pk, pk, n, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+    }
+    w->has_data = true;
+    void *da = nullptr, *dc = nullptr;
+    if (!st) st = h2d(ctx, 0, a, m * k * 4, &da);
+    if (!st) st = h2d(ctx, 1, c, m * n * 4, &dc);
+    if (!st) st = abk_ternary_matmul_bt(ctx, (const float*)da, w, scale, (float*)dc, m);
+    if (!st) st = d2h_sync(ctx, c, dc, m * n * 4);
+    ab_weights_destroy(w);
+    return st;
+}
+
+// ------------------------------------------------------------------------------- batched
+int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x, int8_t* xq,
+                      size_t ld_xq, float* scales, int32_t* rowsums) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(x_dtype == AB_F32 || x_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_x >= k && ld_xq >= k, AB_ERR_SHAPE);
+    if (m) AB_REQUIRE(x && xq && scales, AB_ERR_NULL);
+    return abk_act_quant_int8(ctx, x, x_dtype, m, k, ld_x, xq, ld_xq, scales, rowsums);
+}
+
+int ab_bitlinear_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
+                     const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_fwd, AB_ERR_STATE);
+    AB_REQUIRE(y_dtype == AB_F32 || y_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_xq >= w->in && ld_y >= w->out, AB_ERR_SHAPE);
+    if (m && w->out) AB_REQUIRE(xq && scales && y, AB_ERR_NULL);
+    return abk_gemm_fwd(ctx, w, xq, ld_xq, scales, rowsums, m, y, y_dtype, ld_y, acc_out);
+}
+
+int ab_bitlinear_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx,
+                    int dx_dtype, size_t ld_dx, float beta) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_t, AB_ERR_STATE);
+    AB_REQUIRE(dx_dtype == AB_F32 || dx_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(beta == 0.0f || beta == 1.0f, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_dy >= w->out && ld_dx >= w->in, AB_ERR_SHAPE);
+    if (m && w->in) AB_REQUIRE(dy && dx, AB_ERR_NULL);
+    return abk_gemm_dx(ctx, w, dy, ld_dy, m, dx, dx_dtype, ld_dx, beta);
+}
+
+int ab_ste_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,
+              float* dW, size_t ld_dw, float beta) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(beta == 0.0f || beta == 1.0f, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_dy >= out && ld_x >= in && ld_dw >= in, AB_ERR_SHAPE);
+    AB_REQUIRE(out < (1ull << 31) && in < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (out * in) AB_REQUIRE(dW, AB_ERR_NULL);
+    if (out * in * m) AB_REQUIRE(dy && x, AB_ERR_NULL);
+    return abk_gemm_dw(ctx, dy, ld_dy, x, ld_x, m, out, in, dW, ld_dw, beta);
+}
+
+int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host, const void* dy_host, size_t m,
+                           void* y_host, void* dx_host, float* dW_dev) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_fwd && w->codes_t, AB_ERR_STATE);
+    if (m == 0) return AB_OK;
+    AB_REQUIRE(x_host && dy_host && y_host && dx_host && dW_dev, AB_ERR_NULL);
+    const size_t in = w->in, out = w->out;
+    AB_REQUIRE(in % 16 == 0 && out % 8 == 0, AB_ERR_UNSUPPORTED);
+    void *dx_in = nullptr, *ddy = nullptr, *dxq = nullptr, *dsc = nullptr, *dy_out = nullptr, *ddx = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 0, m * in * 2, &dx_in));
+    AB_TRY(ab_ctx_stage(ctx, 1, m * out * 2, &ddy));
+    AB_TRY(ab_ctx_stage(ctx, 2, m * in, &dxq));
+    AB_TRY(ab_ctx_stage(ctx, 3, m * 8, &dsc));
+    AB_TRY(ab_ctx_stage(ctx, 4, m * out * 2, &dy_out));
+    AB_TRY(ab_ctx_stage(ctx, 5, m * in * 2, &ddx));
+    float* scales = (float*)dsc;
+    int32_t* rowsums = (int32_t*)((char*)dsc + m * 4);
+    cudaStream_t s = ctx->stream;
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_in, x_host, m * in * 2, cudaMemcpyHostToDevice, s));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(ddy, dy_host, m * out * 2, cudaMemcpyHostToDevice, s));
+    AB_TRY(abk_act_quant_int8(ctx, dx_in, AB_BF16, m, in, in, (int8_t*)dxq, in, scales, rowsums));
+    AB_TRY(abk_gemm_fwd(ctx, w, (const int8_t*)dxq, in, scales, rowsums, m, dy_out, AB_BF16, out, nullptr));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(y_host, dy_out, m * out * 2, cudaMemcpyDeviceToHost, s));
+    AB_TRY(abk_gemm_dx(ctx, w, ddy, out, m, ddx, AB_BF16, in, 0.0f));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_host, ddx, m * in * 2, cudaMemcpyDeviceToHost, s));
+    AB_TRY(abk_gemm_dw(ctx, ddy, out, dx_in, in, m, out, in, dW_dev, in, 1.0f));
+    return ab_ctx_sync(ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,286 @@
+// Batch-1 kernels: forward matvec, transposed matvec (dx = W^T dy), the fused BitLinear
+// backward with RMSNorm pre-norm, and the rank-1 STE weight-gradient update.
+//
+// These read the canonical 2-bit codes (0.25 byte per weight) with 128-bit loads and are
+// bound by memory traffic and by the one select+add each weight costs; there are no
+// multiplies by weights anywhere (the reference's "add/sub only" property,
+// src/backward.rs:1-8).
+//
+// Reference semantics:
+//   ternary_matvec_backward  src/backward.rs:28-82   (and shaders/ternary_backward.wgsl:27-61)
+//   bitlinear_backward       src/backward.rs:105-156
+//   ste_weight_grad          src/backward.rs:173-184
+//   ternary_matmul_bt        src/blas.rs:403-457
+#include "common.cuh"
+
+namespace {
+
+// value of element e of a canonical code word applied to v: +v, -v or 0 (code 3 decodes to 0)
+__device__ __forceinline__ float apply_code(uint32_t word, int e, float v) {
+    uint32_t c = (word >> (2 * e)) & 3u;
+    return c == 1u ? v : (c == 2u ? -v : 0.0f);
+}
+
+// ------------------------------------------------------------------------------- forward
+// One warp per output row.  A lane takes 64 consecutive weights (one 128-bit load) per step;
+// x is read through the read-only path and stays in L1 across the rows of a block.
+// y[j] (+)= scale * sum_k W[j][k] x[k]
+constexpr int kFwdWarps = 8;
+
+__global__ void __launch_bounds__(kFwdWarps * 32)
+matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
+                  const float* __restrict__ x, size_t x_stride, float* __restrict__ y, size_t y_stride,
+                  float scale, int accumulate, int use_scale) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const size_t row = (size_t)blockIdx.x * kFwdWarps + wid;
+    if (row >= out) return;
+    const float* xv = x + (size_t)blockIdx.y * x_stride;
+    float* yv = y + (size_t)blockIdx.y * y_stride;
+    const uint4* crow = reinterpret_cast<const uint4*>(codes + row * pitch);
+    const size_t chunks = (in + 63) / 64;  // pitch covers whole 64-element chunks (zero padded)
+    const bool x_vec = (reinterpret_cast<uintptr_t>(xv) & 15) == 0;
+    float acc = 0.0f;
+    for (size_t ch = lane; ch < chunks; ch += 32) {
+        uint4 cw = __ldg(crow + ch);
+        const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
+        const size_t k0 = ch * 64;
+        if (x_vec && k0 + 64 <= in) {
+            const float4* x4 = reinterpret_cast<const float4*>(xv + k0);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                float4 t = __ldg(x4 + q);
+                uint32_t w = w4[q >> 2];
+                int e = (q & 3) * 4;
+                acc += apply_code(w, e, t.x);
+                acc += apply_code(w, e + 1, t.y);
+                acc += apply_code(w, e + 2, t.z);
+                acc += apply_code(w, e + 3, t.w);
+            }
+        } else {
+            for (int e = 0; e < 64; ++e)
+                if (k0 + e < in) acc += apply_code(w4[e >> 4], e & 15, xv[k0 + e]);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        float r = use_scale ? __fmul_rn(acc, scale) : acc;
+        yv[row] = accumulate ? __fadd_rn(yv[row], r) : r;
+    }
+}
+
+// ------------------------------------------------------------------------------ backward
+// dx = W^T dy.  A thread owns one code word = 16 neighbouring columns and walks a slice of
+// rows; a block covers 128 words (2048 columns, 512 contiguous bytes per row).  Row slices
+// (blockIdx.y) give every SM work; their partial sums land in scratch and are added in slice
+// order by a second small kernel, so the result does not depend on scheduling.
+constexpr int kBwdThreads = 128;
+constexpr int kBwdMaxSlice = 2048;  // rows of dy staged in shared memory per block
+
+__global__ void __launch_bounds__(kBwdThreads)
+matvec_bwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t words_per_row,
+                  const float* __restrict__ dy, size_t rows_per_slice, float* __restrict__ partial,
+                  size_t partial_stride /* floats per slice */) {
+    __shared__ float s_dy[kBwdMaxSlice];
+    const size_t word = (size_t)blockIdx.x * kBwdThreads + threadIdx.x;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
+    const size_t r1 = r0 + rows_per_slice < out ? r0 + rows_per_slice : out;
+    for (size_t r = r0 + threadIdx.x; r < r1; r += kBwdThreads) s_dy[r - r0] = dy[r];
+    __syncthreads();
+    if (word >= words_per_row) return;
+    float acc[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
+    const uint32_t* col = reinterpret_cast<const uint32_t*>(codes) + word;
+    const size_t wstride = pitch / 4;
+    size_t r = r0;
+    for (; r + 4 <= r1; r += 4) {  // four independent loads in flight per thread
+        uint32_t w0 = __ldg(col + (r + 0) * wstride), w1 = __ldg(col + (r + 1) * wstride);
+        uint32_t w2 = __ldg(col + (r + 2) * wstride), w3 = __ldg(col + (r + 3) * wstride);
+        float d0 = s_dy[r - r0], d1 = s_dy[r - r0 + 1], d2 = s_dy[r - r0 + 2], d3 = s_dy[r - r0 + 3];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            acc[e] += apply_code(w0, e, d0);
+            acc[e] += apply_code(w1, e, d1);
+            acc[e] += apply_code(w2, e, d2);
+            acc[e] += apply_code(w3, e, d3);
+        }
+    }
+    for (; r < r1; ++r) {
+        uint32_t w0 = __ldg(col + r * wstride);
+        float d0 = s_dy[r - r0];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc[e] += apply_code(w0, e, d0);
+    }
+    float4* dst = reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * partial_stride + word * 16);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+}
+
+__global__ void matvec_bwd_reduce_kernel(const float* __restrict__ partial, size_t partial_stride,
+                                         int slices, size_t in, float* __restrict__ dx) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= in) return;
+    float s = 0.0f;
+    for (int k = 0; k < slices; ++k) s += partial[(size_t)k * partial_stride + i];
+    dx[i] = s;
+}
+
+// pre-norm correction (src/backward.rs:126-150), one block:
+//   rms = sqrt(sum x^2 / n + eps);  dx_i = u_i / rms - (x . u) * x_i / (n * rms^3)
+// where u = W^T dy.  The reference forms sum_j dy_j (W x)_j, which is the same bilinear form
+// dy^T W x = x . (W^T dy); taking it from u saves the second pass over W.
+__global__ void __launch_bounds__(1024)
+prenorm_finish_kernel(const float* __restrict__ x, size_t n, float eps, float* __restrict__ dx) {
+    __shared__ double s_a[32], s_b[32];
+    __shared__ float s_inv, s_coef;
+    double ss = 0.0, dot = 0.0;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        double xv = (double)x[i];
+        ss += xv * xv;
+        dot += xv * (double)dx[i];
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_down_sync(0xffffffffu, ss, o);
+        dot += __shfl_down_sync(0xffffffffu, dot, o);
+    }
+    if ((threadIdx.x & 31) == 0) { s_a[threadIdx.x >> 5] = ss; s_b[threadIdx.x >> 5] = dot; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double a = 0.0, b = 0.0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) { a += s_a[i]; b += s_b[i]; }
+        float sum_sq = (float)a, nf = (float)n;
+        float rms = sqrtf(__fadd_rn(__fdiv_rn(sum_sq, nf), eps));
+        float rms3 = __fmul_rn(__fmul_rn(rms, rms), rms);
+        s_inv = __fdiv_rn(1.0f, rms);
+        s_coef = __fdiv_rn((float)b, __fmul_rn(nf, rms3));
+    }
+    __syncthreads();
+    const float inv = s_inv, coef = s_coef;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x)
+        dx[i] = __fsub_rn(__fmul_rn(dx[i], inv), __fmul_rn(coef, x[i]));
+}
+
+// ------------------------------------------------------------------- STE rank-1 update
+// dW[j][i] += dy_j * x_i with a separate multiply and add (bit-identical to the reference's
+// `+= dy_j * input[i]`).  Pure streaming read-modify-write: 8 bytes of HBM traffic per weight.
+__global__ void __launch_bounds__(256)
+ste_outer_kernel(const float* __restrict__ x, size_t in, const float* __restrict__ dy, size_t out,
+                 float* __restrict__ dW, int vec_ok) {
+    if (vec_ok) {
+        const size_t in4 = in / 4;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        float4* d4 = reinterpret_cast<float4*>(dW);
+        for (size_t j = blockIdx.x; j < out; j += gridDim.x) {
+            const float g = dy[j];
+            float4* row = d4 + j * in4;
+            for (size_t i = threadIdx.x; i < in4; i += blockDim.x) {
+                float4 xv = __ldg(x4 + i), d = row[i];
+                d.x = __fadd_rn(d.x, __fmul_rn(g, xv.x));
+                d.y = __fadd_rn(d.y, __fmul_rn(g, xv.y));
+                d.z = __fadd_rn(d.z, __fmul_rn(g, xv.z));
+                d.w = __fadd_rn(d.w, __fmul_rn(g, xv.w));
+                row[i] = d;
+            }
+        }
+    } else {
+        for (size_t j = blockIdx.x; j < out; j += gridDim.x) {
+            const float g = dy[j];
+            float* row = dW + j * in;
+            for (size_t i = threadIdx.x; i < in; i += blockDim.x)
+                row[i] = __fadd_rn(row[i], __fmul_rn(g, x[i]));
+        }
+    }
+}
+
+}  // namespace
+
+int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y) {
+    if (w->out == 0) return AB_OK;
+    dim3 grid((unsigned)((w->out + kFwdWarps - 1) / kFwdWarps), 1);
+    matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, x, 0, y, 0,
+                                                               1.0f, 0, 0);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
+    if (w->out == 0 || m == 0) return AB_OK;
+    if (m > 65535) return AB_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)((w->out + kFwdWarps - 1) / kFwdWarps), (unsigned)m);
+    matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, a, w->in, c,
+                                                               w->out, scale, 1, 1);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+// Row slicing of the transposed matvec: enough blocks for ~4 per SM, slices no longer than the
+// shared-memory staging of dy allows.
+void ab_matvec_bwd_plan(const ab_ctx* ctx, size_t out, size_t in, int* slices, size_t* rows_per_slice,
+                        size_t* partial_stride) {
+    const size_t wpr = ab_round_up(in, 128) / 16;
+    const size_t col_blocks = (wpr + kBwdThreads - 1) / kBwdThreads;
+    size_t s = ((size_t)ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
+    size_t max_s = (out + 31) / 32;  // at least 32 rows per slice
+    if (s > max_s) s = max_s;
+    if (s > 128) s = 128;
+    if (s < 1) s = 1;
+    size_t rps = (out + s - 1) / s;
+    if (rps > (size_t)kBwdMaxSlice) { rps = kBwdMaxSlice; }
+    if (rps < 1) rps = 1;
+    s = (out + rps - 1) / rps;
+    if (s < 1) s = 1;
+    *slices = (int)s;
+    *rows_per_slice = rps;
+    *partial_stride = wpr * 16;
+}
+
+int abk_matvec_backward_with_scratch(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx,
+                                     float* partial, int slices, size_t rps, size_t pstride) {
+    const size_t wpr = w->pitch / 4;
+    dim3 grid((unsigned)((wpr + kBwdThreads - 1) / kBwdThreads), (unsigned)slices);
+    matvec_bwd_kernel<<<grid, kBwdThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, wpr, dy, rps, partial,
+                                                            pstride);
+    AB_LAUNCH_CHECK(ctx);
+    matvec_bwd_reduce_kernel<<<(unsigned)((w->in + 255) / 256), 256, 0, ctx->stream>>>(partial, pstride, slices,
+                                                                                      w->in, dx);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx) {
+    if (w->in == 0) return AB_OK;
+    if (w->out == 0) {
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(dx, 0, w->in * sizeof(float), ctx->stream));
+        return AB_OK;
+    }
+    int slices;
+    size_t rps, pstride;
+    ab_matvec_bwd_plan(ctx, w->out, w->in, &slices, &rps, &pstride);
+    void* partial = nullptr;
+    int st = ab_ctx_scratch(ctx, (size_t)slices * pstride * sizeof(float), &partial);
+    if (st) return st;
+    return abk_matvec_backward_with_scratch(ctx, w, dy, dx, (float*)partial, slices, rps, pstride);
+}
+
+int abk_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy, int pre_norm,
+                           float norm_eps, float* dx, float* d_bias) {
+    if (d_bias && w->out)
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(d_bias, dy, w->out * sizeof(float), cudaMemcpyDeviceToDevice,
+                                           ctx->stream));
+    int st = abk_ternary_matvec_backward(ctx, w, dy, dx);
+    if (st || !pre_norm || w->in == 0) return st;
+    prenorm_finish_kernel<<<1, 1024, 0, ctx->stream>>>(x, w->in, norm_eps, dx);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in, const float* dy, size_t out, float* dW) {
+    if (in == 0 || out == 0) return AB_OK;
+    int vec_ok = (in % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                 ((reinterpret_cast<uintptr_t>(dW) & 15) == 0);
+    size_t blocks = (size_t)ctx->sm_count * 8;
+    if (blocks > out) blocks = out;
+    ste_outer_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, in, dy, out, dW, vec_ok);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}

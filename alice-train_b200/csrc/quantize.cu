@@ -1,0 +1,606 @@
+// Kernel (1): absmean FakeQuantize + 2-bit pack, and the conversions between the packed
+// layouts.  All of this is HBM-bound streaming work: 128-bit loads, one 32-bit store of 16
+// codes per thread, grids sized from the SM count.
+//
+// Reference semantics (file:line in the alice-train crate):
+//   gamma  = f32(sum_f64 |w| / n)                                  src/qwen35.rs:226-227
+//   code   = clamp(round_half_away(w * inv_gamma), -1, 1)          src/qwen35.rs:230, src/export.rs:107
+//   pack   = element i -> byte i/4, shift 2*(i%4); 01=+1 10=-1     src/export.rs:117-133
+//   planes = word j*wpr + k/32, bit k%32                           shaders/ternary_backward.wgsl:5-7
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ double warp_sum(double v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sums `v` over the block in a fixed order (lane tree, then warp 0 over the warp partials).
+// Result valid in thread 0.
+__device__ __forceinline__ double block_sum(double v, double* smem /*[32]*/) {
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    v = warp_sum(v);
+    if (lane == 0) smem[wid] = v;
+    __syncthreads();
+    double r = 0.0;
+    if (wid == 0) {
+        r = lane < (blockDim.x >> 5) ? smem[lane] : 0.0;
+        r = warp_sum(r);
+    }
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ unsigned int float_key(float f) {  // order-preserving uint key
+    unsigned int b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__host__ __device__ __forceinline__ float key_float(unsigned int k) {
+    unsigned int b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(b);
+#else
+    float f;
+    memcpy(&f, &b, 4);
+    return f;
+#endif
+}
+
+// ---------------------------------------------------------------------------- pass A: gamma
+// Every block writes one f64 partial; the last block to finish adds the partials in block
+// order, derives gamma / inv_gamma under the requested guard and clears the counters that
+// pass B accumulates into.  The result does not depend on scheduling.
+__global__ void __launch_bounds__(kThreads)
+absmean_reduce_kernel(const float* __restrict__ w, size_t n, double* __restrict__ partials,
+                      ab_fq_dev_report* __restrict__ rep, float* __restrict__ gamma_out, int guard,
+                      int keep_when_empty) {
+    __shared__ double sm[32];
+    __shared__ bool is_last;
+    double acc = 0.0;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        size_t n4 = n / 4;
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        for (size_t i = tid; i < n4; i += stride) {
+            float4 v = __ldg(w4 + i);
+            acc += (double)fabsf(v.x);
+            acc += (double)fabsf(v.y);
+            acc += (double)fabsf(v.z);
+            acc += (double)fabsf(v.w);
+        }
+        for (size_t i = n4 * 4 + tid; i < n; i += stride) acc += (double)fabsf(w[i]);
+    } else {
+        for (size_t i = tid; i < n; i += stride) acc += (double)fabsf(w[i]);
+    }
+    double bs = block_sum(acc, sm);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = bs;
+        __threadfence();
+        unsigned int done = atomicAdd(&rep->blocks_done, 1u);
+        is_last = (done == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // fixed-order final sum: thread t adds partials t, t+256, ... then the block tree
+    double s = 0.0;
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x) s += partials[i];
+    s = block_sum(s, sm);
+    if (threadIdx.x == 0) {
+        float gamma, inv;
+        if (n == 0) {
+            gamma = keep_when_empty ? *gamma_out : 0.0f;
+            inv = 0.0f;
+        } else {
+            gamma = (float)(s / (double)n);
+            if (guard == AB_GUARD_FLOOR) {
+                if (gamma < 1e-10f) gamma = 1e-10f;
+                inv = 1.0f / gamma;
+            } else {
+                inv = gamma > 1e-10f ? 1.0f / gamma : 0.0f;
+            }
+        }
+        rep->sum_abs = s;
+        rep->gamma = gamma;
+        rep->inv_gamma = inv;
+        rep->sum_err = rep->dot_wq = rep->dot_ww = rep->dot_qq = 0.0;
+        rep->n_plus = rep->n_minus = rep->n_threshold = 0ull;
+        rep->w_min = __uint_as_float(0xffffffffu);  // holds keys until read back
+        rep->w_max = __uint_as_float(0u);
+        rep->blocks_done = 0u;
+        *gamma_out = gamma;
+    }
+}
+
+// ------------------------------------------------------------------------ pass B: codes
+// One thread owns 16 consecutive elements of one row: 64 bytes in, one canonical word and one
+// forward-operand word out.  Words are visited from the END of the tensor so that the tail
+// pass A left in L2 is consumed first.
+template <bool WANT_FQ, bool WANT_STATS>
+__global__ void __launch_bounds__(kThreads)
+quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row,
+                     uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd,
+                     float* fq_out, ab_fq_dev_report* __restrict__ rep, int offset_binary) {
+    const size_t total = out * words_per_row;
+    size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const float gamma = rep->gamma, inv = rep->inv_gamma;
+    unsigned int n_plus = 0, n_minus = 0, n_thr = 0;
+    double s_err = 0, s_wq = 0, s_ww = 0, s_qq = 0;
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    if (gi < total) {
+        size_t wi = total - 1 - gi;
+        size_t row = wi / words_per_row, cw = wi % words_per_row;
+        size_t col0 = cw * 16;
+        float v[16];
+        const float* src = w + row * in + col0;
+        int valid = col0 >= in ? 0 : (int)((in - col0) < 16 ? (in - col0) : 16);
+        if (valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            const float4* s4 = reinterpret_cast<const float4*>(src);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 t = WANT_FQ ? s4[q] : __ldg(s4 + q);  // fq_out may alias w
+                v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = e < valid ? src[e] : 0.0f;
+        }
+        uint32_t cword = 0, fword = 0;
+        float qv[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            float scaled = __fmul_rn(v[e], inv);
+            float r = roundf(scaled);              // half away from zero, as f32::round
+            r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
+            int c = (r != r) ? 0 : (int)r;         // NaN -> 0 like `as i8`
+            if (e >= valid) c = 0;
+            uint32_t canon = c > 0 ? 1u : (c < 0 ? 2u : 0u);
+            uint32_t fenc = offset_binary ? (uint32_t)(c + 1) : (c > 0 ? 1u : (c < 0 ? 3u : 0u));
+            cword |= canon << (2 * e);
+            fword |= fenc << ab_perm_bit(e);
+            qv[e] = __fmul_rn(r, gamma);
+            if (e < valid) {
+                n_plus += c > 0;
+                n_minus += c < 0;
+                float a = fabsf(scaled);
+                n_thr += (a >= 0.49999997f && a <= 0.50000006f);
+                if (WANT_STATS) {
+                    double wd = (double)v[e], qd = (double)qv[e];
+                    s_err += fabs(wd - qd);
+                    s_wq += wd * qd;
+                    s_ww += wd * wd;
+                    s_qq += qd * qd;
+                    vmin = fminf(vmin, v[e]);
+                    vmax = fmaxf(vmax, v[e]);
+                }
+            }
+        }
+        codes[wi] = cword;
+        if (codes_fwd) codes_fwd[wi] = fword;
+        if (WANT_FQ) {
+            float* dst = fq_out + row * in + col0;
+            if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    d4[q] = make_float4(qv[4 * q], qv[4 * q + 1], qv[4 * q + 2], qv[4 * q + 3]);
+            } else {
+                for (int e = 0; e < valid; ++e) dst[e] = qv[e];
+            }
+        }
+    }
+    // block-level reduction of the counters, one atomic per block per counter
+    __shared__ unsigned int sc[3];
+    __shared__ double sd[32];
+    if (threadIdx.x < 3) sc[threadIdx.x] = 0;
+    __syncthreads();
+    n_plus = __reduce_add_sync(0xffffffffu, n_plus);
+    n_minus = __reduce_add_sync(0xffffffffu, n_minus);
+    n_thr = __reduce_add_sync(0xffffffffu, n_thr);
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&sc[0], n_plus);
+        atomicAdd(&sc[1], n_minus);
+        atomicAdd(&sc[2], n_thr);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (sc[0]) atomicAdd(&rep->n_plus, (unsigned long long)sc[0]);
+        if (sc[1]) atomicAdd(&rep->n_minus, (unsigned long long)sc[1]);
+        if (sc[2]) atomicAdd(&rep->n_threshold, (unsigned long long)sc[2]);
+    }
+    if (WANT_STATS) {
+        double b;
+        b = block_sum(s_err, sd); if (threadIdx.x == 0) atomicAdd(&rep->sum_err, b);
+        b = block_sum(s_wq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_wq, b);
+        b = block_sum(s_ww, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_ww, b);
+        b = block_sum(s_qq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_qq, b);
+        unsigned int kmin = __reduce_min_sync(0xffffffffu, float_key(vmin));
+        unsigned int kmax = __reduce_max_sync(0xffffffffu, float_key(vmax));
+        if ((threadIdx.x & 31) == 0) {
+            atomicMin(reinterpret_cast<unsigned int*>(&rep->w_min), kmin);
+            atomicMax(reinterpret_cast<unsigned int*>(&rep->w_max), kmax);
+        }
+    }
+}
+
+// --------------------------------------------------------- operand copies from canonical
+__global__ void __launch_bounds__(kThreads)
+repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, size_t words,
+                  int offset_binary) {
+    size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= words) return;
+    uint32_t cw = codes[wi], f = 0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        uint32_t c = (cw >> (2 * e)) & 3u;
+        uint32_t enc = offset_binary ? (c == 1u ? 2u : (c == 2u ? 0u : 1u))
+                                     : (c == 1u ? 1u : (c == 2u ? 3u : 0u));
+        f |= enc << ab_perm_bit(e);
+    }
+    codes_fwd[wi] = f;
+}
+
+// codes_t[i][jg] gathers column i of 16 consecutive rows j = 16*jg + e.  A warp covers 32
+// consecutive output words of one input feature (coalesced 128-byte stores); the strided
+// byte reads are served from L1/L2 because neighbouring blocks share the same sectors.
+__global__ void __launch_bounds__(kThreads)
+transpose_codes_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
+                       uint32_t* __restrict__ codes_t, size_t twords_per_row) {
+    size_t jg = (size_t)blockIdx.x * 32 + (threadIdx.x & 31);
+    size_t i = (size_t)blockIdx.y * (kThreads / 32) + (threadIdx.x >> 5);
+    if (i >= in || jg >= twords_per_row) return;
+    uint32_t t = 0;
+    const uint8_t* col = codes + (i >> 2);
+    int sh = 2 * (int)(i & 3);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        size_t j = jg * 16 + e;
+        uint32_t c = j < out ? ((uint32_t)col[j * pitch] >> sh) & 3u : 0u;
+        if (c == 3u) c = 0u;
+        t |= c << ab_perm_bit(e);
+    }
+    codes_t[i * twords_per_row + jg] = t;
+}
+
+// ------------------------------------------------------------------ boundary conversions
+__global__ void codes_from_ternary_kernel(const int8_t* __restrict__ vals, size_t out, size_t in,
+                                          size_t wpr, uint32_t* __restrict__ codes) {
+    size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= out * wpr) return;
+    size_t row = wi / wpr, col0 = (wi % wpr) * 16;
+    uint32_t cw = 0;
+    for (int e = 0; e < 16; ++e) {
+        size_t k = col0 + e;
+        if (k < in) {
+            int v = vals[row * in + k];
+            cw |= (v == 1 ? 1u : (v == -1 ? 2u : 0u)) << (2 * e);
+        }
+    }
+    codes[wi] = cw;
+}
+
+__global__ void codes_from_bitplanes_kernel(const uint32_t* __restrict__ plus,
+                                            const uint32_t* __restrict__ minus, size_t out, size_t in,
+                                            size_t wpr, size_t planes_wpr, uint32_t* __restrict__ codes) {
+    size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= out * wpr) return;
+    size_t row = wi / wpr, cw_i = wi % wpr, col0 = cw_i * 16;
+    uint32_t cw = 0;
+    if (col0 < in) {
+        size_t pw = row * planes_wpr + col0 / 32;
+        uint32_t p = plus[pw] >> (col0 % 32), m = minus[pw] >> (col0 % 32);
+        for (int e = 0; e < 16; ++e) {
+            if (col0 + e < in) {
+                uint32_t c = ((p >> e) & 1u) ? 1u : (((m >> e) & 1u) ? 2u : 0u);
+                cw |= c << (2 * e);
+            }
+        }
+    }
+    codes[wi] = cw;
+}
+
+__global__ void codes_from_flat_kernel(const uint8_t* __restrict__ flat, size_t out, size_t in,
+                                       size_t wpr, uint32_t* __restrict__ codes) {
+    size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= out * wpr) return;
+    size_t row = wi / wpr, col0 = (wi % wpr) * 16;
+    uint32_t cw = 0;
+    for (int e = 0; e < 16; ++e) {
+        size_t k = col0 + e;
+        if (k < in) {
+            size_t g = row * in + k;
+            uint32_t c = ((uint32_t)flat[g >> 2] >> (2 * (g & 3))) & 3u;
+            if (c == 3u) c = 0u;  // 0b11 decodes to 0 (src/export.rs:143-148)
+            cw |= c << (2 * e);
+        }
+    }
+    codes[wi] = cw;
+}
+
+__device__ __forceinline__ uint32_t code_at(const uint8_t* codes, size_t pitch, size_t row, size_t k) {
+    return ((uint32_t)codes[row * pitch + (k >> 2)] >> (2 * (k & 3))) & 3u;
+}
+
+__global__ void codes_to_bitplanes_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out,
+                                          size_t in, size_t planes_wpr, uint32_t* __restrict__ plus,
+                                          uint32_t* __restrict__ minus) {
+    size_t pi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pi >= out * planes_wpr) return;
+    size_t row = pi / planes_wpr, col0 = (pi % planes_wpr) * 32;
+    uint32_t p = 0, m = 0;
+    for (int b = 0; b < 32; ++b) {
+        size_t k = col0 + b;
+        if (k < in) {
+            uint32_t c = code_at(codes, pitch, row, k);
+            p |= (uint32_t)(c == 1u) << b;
+            m |= (uint32_t)(c == 2u) << b;
+        }
+    }
+    plus[pi] = p;
+    minus[pi] = m;
+}
+
+__global__ void codes_to_flat_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out,
+                                     size_t in, uint8_t* __restrict__ flat, size_t flat_bytes) {
+    size_t bi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (bi >= flat_bytes) return;
+    uint32_t byte = 0;
+    for (int q = 0; q < 4; ++q) {
+        size_t g = bi * 4 + q;
+        if (g < out * in) byte |= code_at(codes, pitch, g / in, g % in) << (2 * q);
+    }
+    flat[bi] = (uint8_t)byte;
+}
+
+__global__ void codes_to_ternary_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out,
+                                        size_t in, int8_t* __restrict__ vals) {
+    size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= out * in) return;
+    uint32_t c = code_at(codes, pitch, g / in, g % in);
+    vals[g] = c == 1u ? 1 : (c == 2u ? -1 : 0);
+}
+
+// --------------------------------------------------------------- FakeQuantize, flat API
+// src/qat.rs:173-206.  bits: 0/1 ternary, 2 int4 (+-7), 3 int8 (+-127).
+__global__ void __launch_bounds__(kThreads)
+fake_quantize_kernel(const float* __restrict__ w, float* __restrict__ q, size_t n,
+                     const float* __restrict__ scale_dev, float temperature, int bits) {
+    const float scale = *scale_dev;
+    const float inv_scale = __fdiv_rn(1.0f, fmaxf(scale, 1e-10f));
+    const float inv_temp = __fdiv_rn(1.0f, fmaxf(temperature, 1e-10f));
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float wv = w[i], r;
+        if (bits == AB_TERNARY || bits == AB_BINARY2) {
+            float scaled = __fmul_rn(__fmul_rn(wv, inv_scale), inv_temp);
+            r = roundf(scaled);
+            r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
+            q[i] = __fmul_rn(r, scale);
+        } else {
+            const float half = bits == AB_INT4 ? 7.0f : 127.0f;
+            float scaled = __fmul_rn(__fmul_rn(__fmul_rn(wv, inv_scale), half), inv_temp);
+            r = roundf(scaled);
+            r = r < -half ? -half : (r > half ? half : r);
+            q[i] = __fdiv_rn(__fmul_rn(r, scale), half);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+ste_backward_kernel(const float* __restrict__ g, float* __restrict__ out, size_t n, float clip) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = g[i];
+        if (clip > 0.0f) v = v < -clip ? -clip : (v > clip ? clip : v);
+        out[i] = v;
+    }
+}
+
+// out7 = {sum_abs, sum_err, dot_wq, dot_ww, dot_qq, min_key, max_key}; must be pre-initialised.
+__global__ void __launch_bounds__(kThreads)
+calibration_stats_kernel(const float* __restrict__ w, const float* __restrict__ q, size_t n,
+                         double* __restrict__ out7) {
+    __shared__ double sd[32];
+    double a = 0, e = 0, wq = 0, ww = 0, qq = 0;
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float wv = w[i], qv = q[i];
+        a += (double)fabsf(wv);
+        e += (double)fabsf(wv - qv);
+        wq += (double)wv * (double)qv;
+        ww += (double)wv * (double)wv;
+        qq += (double)qv * (double)qv;
+        vmin = fminf(vmin, wv);
+        vmax = fmaxf(vmax, wv);
+    }
+    double b;
+    b = block_sum(a, sd);  if (threadIdx.x == 0) atomicAdd(out7 + 0, b);
+    b = block_sum(e, sd);  if (threadIdx.x == 0) atomicAdd(out7 + 1, b);
+    b = block_sum(wq, sd); if (threadIdx.x == 0) atomicAdd(out7 + 2, b);
+    b = block_sum(ww, sd); if (threadIdx.x == 0) atomicAdd(out7 + 3, b);
+    b = block_sum(qq, sd); if (threadIdx.x == 0) atomicAdd(out7 + 4, b);
+    unsigned int kmin = __reduce_min_sync(0xffffffffu, float_key(vmin));
+    unsigned int kmax = __reduce_max_sync(0xffffffffu, float_key(vmax));
+    if ((threadIdx.x & 31) == 0) {
+        atomicMin(reinterpret_cast<unsigned int*>(out7 + 5), kmin);
+        atomicMax(reinterpret_cast<unsigned int*>(out7 + 6), kmax);
+    }
+}
+
+__global__ void init_stats_kernel(double* out7) {
+    for (int i = 0; i < 5; ++i) out7[i] = 0.0;
+    *reinterpret_cast<unsigned long long*>(out7 + 5) = 0xffffffffull;
+    *reinterpret_cast<unsigned long long*>(out7 + 6) = 0ull;
+}
+
+inline unsigned int grid_for(size_t items, int per_block) {
+    size_t g = (items + per_block - 1) / per_block;
+    return (unsigned int)(g == 0 ? 1 : g);
+}
+
+}  // namespace
+
+float ab_key_to_float(unsigned int k) { return key_float(k); }
+
+static int reduce_launch(ab_ctx* ctx, const float* w, size_t n, ab_fq_dev_report* rep, float* gamma_out,
+                         int guard, int keep_when_empty) {
+    // a few resident blocks per SM keep enough 128-bit loads in flight to saturate HBM
+    unsigned int blocks = (unsigned int)(ctx->sm_count * 8);
+    size_t need = (n / 4 + kThreads - 1) / kThreads;
+    if (need < blocks) blocks = (unsigned int)(need ? need : 1);
+    void* part = nullptr;
+    int st = ab_ctx_scratch(ctx, sizeof(double) * blocks, &part);
+    if (st) return st;
+    absmean_reduce_kernel<<<blocks, kThreads, 0, ctx->stream>>>(w, n, (double*)part, rep, gamma_out,
+                                                                guard, keep_when_empty);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int guard,
+                        int want_stats) {
+    const size_t n = w->out * w->in;
+    int st = reduce_launch(ctx, w_latent, n, w->report_dev, w->gamma_dev, guard, 0);
+    if (st) return st;
+    const size_t wpr = w->pitch / 4;
+    const size_t words = w->out * wpr;
+    if (words) {
+        unsigned int grid = grid_for(words, kThreads);
+        uint32_t* c = reinterpret_cast<uint32_t*>(w->codes);
+        uint32_t* f = reinterpret_cast<uint32_t*>(w->codes_fwd);
+        const int ob = ctx->fwd_offset_binary;
+        if (fq_out && want_stats)
+            quantize_pack_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+        else if (fq_out)
+            quantize_pack_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+        else if (want_stats)
+            quantize_pack_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+        else
+            quantize_pack_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+        AB_LAUNCH_CHECK(ctx);
+        if (w->codes_t) {
+            const size_t twpr = w->tpitch / 4;
+            dim3 tg(grid_for(twpr, 32), grid_for(w->in, kThreads / 32));
+            transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
+                                                                    reinterpret_cast<uint32_t*>(w->codes_t), twpr);
+            AB_LAUNCH_CHECK(ctx);
+        }
+    }
+    w->has_data = true;
+    w->has_report = true;
+    return AB_OK;
+}
+
+int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w) {
+    const size_t wpr = w->pitch / 4, words = w->out * wpr;
+    if (!words || !w->codes_fwd || !w->codes_t) return AB_OK;
+    repack_fwd_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(
+        reinterpret_cast<const uint32_t*>(w->codes), reinterpret_cast<uint32_t*>(w->codes_fwd), words,
+        ctx->fwd_offset_binary);
+    AB_LAUNCH_CHECK(ctx);
+    const size_t twpr = w->tpitch / 4;
+    dim3 tg(grid_for(twpr, 32), grid_for(w->in, kThreads / 32));
+    transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
+                                                            reinterpret_cast<uint32_t*>(w->codes_t), twpr);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_codes_from_ternary(ab_ctx* ctx, ab_weights* w, const int8_t* vals_dev) {
+    const size_t wpr = w->pitch / 4, words = w->out * wpr;
+    if (!words) return AB_OK;
+    codes_from_ternary_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(
+        vals_dev, w->out, w->in, wpr, reinterpret_cast<uint32_t*>(w->codes));
+    AB_LAUNCH_CHECK(ctx);
+    return abk_rebuild_operand_copies(ctx, w);
+}
+
+int abk_codes_from_bitplanes(ab_ctx* ctx, ab_weights* w, const uint32_t* plus_dev, const uint32_t* minus_dev) {
+    const size_t wpr = w->pitch / 4, words = w->out * wpr;
+    if (!words) return AB_OK;
+    codes_from_bitplanes_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(
+        plus_dev, minus_dev, w->out, w->in, wpr, (w->in + 31) / 32, reinterpret_cast<uint32_t*>(w->codes));
+    AB_LAUNCH_CHECK(ctx);
+    return abk_rebuild_operand_copies(ctx, w);
+}
+
+int abk_codes_from_flat(ab_ctx* ctx, ab_weights* w, const uint8_t* flat_dev) {
+    const size_t wpr = w->pitch / 4, words = w->out * wpr;
+    if (!words) return AB_OK;
+    codes_from_flat_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(
+        flat_dev, w->out, w->in, wpr, reinterpret_cast<uint32_t*>(w->codes));
+    AB_LAUNCH_CHECK(ctx);
+    return abk_rebuild_operand_copies(ctx, w);
+}
+
+int abk_codes_to_bitplanes(ab_ctx* ctx, const ab_weights* w, uint32_t* plus_dev, uint32_t* minus_dev) {
+    const size_t pw = (w->in + 31) / 32, total = w->out * pw;
+    if (!total) return AB_OK;
+    codes_to_bitplanes_kernel<<<grid_for(total, kThreads), kThreads, 0, ctx->stream>>>(
+        w->codes, w->pitch, w->out, w->in, pw, plus_dev, minus_dev);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_codes_to_flat(ab_ctx* ctx, const ab_weights* w, uint8_t* flat_dev) {
+    const size_t bytes = (w->out * w->in + 3) / 4;
+    if (!bytes) return AB_OK;
+    codes_to_flat_kernel<<<grid_for(bytes, kThreads), kThreads, 0, ctx->stream>>>(
+        w->codes, w->pitch, w->out, w->in, flat_dev, bytes);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_codes_to_ternary(ab_ctx* ctx, const ab_weights* w, int8_t* vals_dev) {
+    const size_t n = w->out * w->in;
+    if (!n) return AB_OK;
+    codes_to_ternary_kernel<<<grid_for(n, kThreads), kThreads, 0, ctx->stream>>>(
+        w->codes, w->pitch, w->out, w->in, vals_dev);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_calibrate_scale(ab_ctx* ctx, const float* w, size_t n, float* scale_dev) {
+    if (n == 0) return AB_OK;  // unchanged (src/qat.rs:156-158)
+    void* rep = nullptr;
+    int st = ab_ctx_stage(ctx, 5, sizeof(ab_fq_dev_report), &rep);
+    if (st) return st;
+    AB_CUDA_CHECK(ctx, cudaMemsetAsync(rep, 0, sizeof(ab_fq_dev_report), ctx->stream));
+    return reduce_launch(ctx, w, n, (ab_fq_dev_report*)rep, scale_dev, AB_GUARD_FLOOR, 1);
+}
+
+int abk_fake_quantize_forward(ab_ctx* ctx, const float* w, float* q, size_t n, const float* scale_dev,
+                              float temperature, int bits) {
+    if (n == 0) return AB_OK;
+    unsigned int blocks = (unsigned int)(ctx->sm_count * 8);
+    unsigned int need = grid_for(n, kThreads);
+    fake_quantize_kernel<<<need < blocks ? need : blocks, kThreads, 0, ctx->stream>>>(w, q, n, scale_dev,
+                                                                                     temperature, bits);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_ste_backward(ab_ctx* ctx, const float* g, float* out, size_t n, float clip) {
+    if (n == 0) return AB_OK;
+    unsigned int blocks = (unsigned int)(ctx->sm_count * 8);
+    unsigned int need = grid_for(n, kThreads);
+    ste_backward_kernel<<<need < blocks ? need : blocks, kThreads, 0, ctx->stream>>>(g, out, n, clip);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n, double* out7_dev) {
+    init_stats_kernel<<<1, 1, 0, ctx->stream>>>(out7_dev);
+    AB_LAUNCH_CHECK(ctx);
+    if (n == 0) return AB_OK;
+    unsigned int blocks = (unsigned int)(ctx->sm_count * 4);
+    unsigned int need = grid_for(n, kThreads);
+    calibration_stats_kernel<<<need < blocks ? need : blocks, kThreads, 0, ctx->stream>>>(w, q, n, out7_dev);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}

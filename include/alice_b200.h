@@ -1,0 +1,241 @@
+/*
+ * alice_b200 — C ABI of the B200 (sm_100a) ternary BitLinear kernels.
+ *
+ * This is the drop-in boundary for the linear-layer hot path of ALICE-Train (Rust crate
+ * alice-train 0.2.0).  Every entry point names the reference interface it stands in for
+ * (file:line inside that crate).  Plain pointers and sizes only; no allocation is returned to
+ * the caller except the two opaque handles below, which the caller frees.
+ *
+ * Conventions
+ *   - every function returns an ab_status (0 = AB_OK) and never aborts the process;
+ *   - "_host" entry points take HOST pointers, copy in, run, copy out and block until done
+ *     (these mirror the reference's slice API one to one);
+ *   - all other entry points take DEVICE pointers and are asynchronous on the context's
+ *     stream; call ab_ctx_sync() before reading results on the host;
+ *   - matrices are row-major; W is [out_features x in_features] as in the reference
+ *     (src/llama.rs:183-203); `ld*` arguments are row pitches in ELEMENTS;
+ *   - there is no CPU fallback: without a CUDA device ab_ctx_create() fails with
+ *     AB_ERR_NO_DEVICE and nothing else can be called.
+ */
+#ifndef ALICE_B200_H
+#define ALICE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AB_API __attribute__((visibility("default")))
+#else
+#define AB_API
+#endif
+
+typedef struct ab_ctx ab_ctx;         /* one per (host thread, device); owns a stream + scratch */
+typedef struct ab_weights ab_weights; /* device-resident ternary weight matrix (+ gamma)        */
+
+typedef enum ab_status {
+    AB_OK = 0,
+    AB_ERR_NULL = 1,           /* a required pointer was NULL                                  */
+    AB_ERR_SHAPE = 2,          /* length / shape mismatch (the reference's assert_eq! panics)  */
+    AB_ERR_ALIGN = 3,          /* pointer or pitch not aligned as documented                   */
+    AB_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed; see ab_ctx_last_error()   */
+    AB_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside a kernel ran out                       */
+    AB_ERR_UNSUPPORTED = 6,    /* argument combination not implemented                         */
+    AB_ERR_NO_DEVICE = 7,      /* no usable CUDA device (GpuContext::new_blocking -> None)     */
+    AB_ERR_STATE = 8           /* handle used before it holds data                             */
+} ab_status;
+
+typedef enum ab_dtype { AB_F32 = 0, AB_BF16 = 1 } ab_dtype;
+
+/* QuantBits of the reference (src/qat.rs:22-50) */
+typedef enum ab_quant_bits { AB_TERNARY = 0, AB_BINARY2 = 1, AB_INT4 = 2, AB_INT8 = 3 } ab_quant_bits;
+
+/* How gamma guards against a zero tensor.
+ * AB_GUARD_INV_ZERO : inv = gamma > 1e-10 ? 1/gamma : 0   (src/qwen35.rs:226-228, src/export.rs:100-102)
+ * AB_GUARD_FLOOR    : gamma = max(gamma, 1e-10)           (src/qat.rs:163-166, src/bin/train_qat_70b.rs:2129) */
+typedef enum ab_gamma_guard { AB_GUARD_INV_ZERO = 0, AB_GUARD_FLOOR = 1 } ab_gamma_guard;
+
+/* Result of the absmean quantiser, read back with ab_weights_fq_report(). */
+typedef struct ab_fq_report {
+    float gamma;            /* f32( sum|w| / n ), after the guard                               */
+    double sum_abs;         /* f64 sum of |w|                                                   */
+    uint64_t n;             /* elements quantised                                               */
+    uint64_t n_plus;        /* codes equal to +1                                                */
+    uint64_t n_minus;       /* codes equal to -1                                                */
+    uint64_t n_threshold;   /* elements with |w*inv_gamma| within 1 ulp of 0.5 (could flip
+                               under a differently rounded gamma); reported, not an error      */
+    /* CalibrationStats inputs (src/qat.rs:270-310), f64; zero unless stats were requested     */
+    double sum_err, dot_wq, dot_ww, dot_qq;
+    float w_min, w_max;
+} ab_fq_report;
+
+/* ------------------------------------------------------------------------------ context */
+
+/* Creates a context on `device`.  `cuda_stream` may be NULL (the context creates its own
+ * stream) or an existing cudaStream_t to run on.
+ * Replaces GpuContext::new_blocking (src/gpu.rs:37-79), GpuBackwardEngine::new
+ * (src/gpu_backward.rs:59), CudaMatmul::new (src/cuda_matmul.rs:953) and init_cuda_blas
+ * (src/blas.rs:19-24). */
+AB_API int ab_ctx_create(int device, void* cuda_stream, ab_ctx** ctx);
+AB_API int ab_ctx_destroy(ab_ctx* ctx);
+/* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
+AB_API int ab_ctx_sync(ab_ctx* ctx);
+AB_API void* ab_ctx_stream(ab_ctx* ctx);
+AB_API const char* ab_ctx_last_error(ab_ctx* ctx);
+/* Number of kernels this context has launched so far. */
+AB_API uint64_t ab_ctx_launch_count(ab_ctx* ctx);
+AB_API const char* ab_status_str(int status);
+AB_API int ab_device_count(void);
+
+/* --------------------------------------------------------- ternary weights (the handle) */
+
+/* Replaces alice_ml::ops::TernaryWeightKernel as used by src/backward.rs:33-45 and
+ * src/gpu_backward.rs:176-220 (out_features, in_features, words_per_row, plus_bits,
+ * minus_bits, from_ternary).  The handle owns device copies of the codes in the layouts the
+ * kernels consume, plus the scale gamma (1.0 until set). */
+AB_API int ab_weights_create(ab_ctx* ctx, size_t out_features, size_t in_features, ab_weights** w);
+AB_API int ab_weights_destroy(ab_weights* w);
+AB_API size_t ab_weights_out_features(const ab_weights* w);
+AB_API size_t ab_weights_in_features(const ab_weights* w);
+AB_API size_t ab_weights_words_per_row(const ab_weights* w); /* ceil(in/32) */
+
+/* TernaryWeightKernel::from_ternary(&[i8], out, in): row-major values in {-1,0,+1}. (host) */
+AB_API int ab_weights_set_ternary(ab_weights* w, const int8_t* values, size_t len);
+/* Bit-planes, word j*wpr + k/32, bit k%32, LSB first (shaders/ternary_backward.wgsl:5-7). (host) */
+AB_API int ab_weights_set_bitplanes(ab_weights* w, const uint32_t* plus_bits,
+                                    const uint32_t* minus_bits, size_t words);
+AB_API int ab_weights_get_bitplanes(ab_weights* w, uint32_t* plus_bits, uint32_t* minus_bits,
+                                    size_t words);
+/* 2-bit codes, 4 per byte, flat over the tensor, 01=+1 10=-1 00=0 (src/export.rs:117-153). (host) */
+AB_API int ab_weights_set_packed2b(ab_weights* w, const uint8_t* packed, size_t bytes, float gamma);
+AB_API int ab_weights_get_packed2b(ab_weights* w, uint8_t* packed, size_t bytes);
+AB_API int ab_weights_get_ternary(ab_weights* w, int8_t* values, size_t len);
+AB_API int ab_weights_set_gamma(ab_weights* w, float gamma);
+AB_API int ab_weights_get_gamma(ab_weights* w, float* gamma);
+
+/* ---------------------------------------------------------- (1) absmean FakeQuantize + pack */
+
+/* gamma = f32(sum_f64|w| / n); codes = clamp(round_half_away(w * inv_gamma), -1, 1), written
+ * into the handle in every layout the other kernels read.  Optionally also writes the f32
+ * fake-quantised tensor codes*gamma to `fq_out` (may alias `w_latent`), and the
+ * CalibrationStats sums when `want_stats` != 0.  `w_latent` is [out x in] f32, row pitch =
+ * in_features, device memory.
+ * Replaces fq_vec / fq_vec_inplace (src/qwen35.rs:221-251), quantize_and_pack
+ * (src/export.rs:94-113), FakeQuantize::calibrate_scale + fake_quantize_forward for Ternary
+ * (src/qat.rs:155-186) and LayerDeltaCache::fused_merge_and_quantize_alpha with alpha = 1,
+ * T = 1 (src/bin/train_qat_70b.rs:2109-2172). */
+AB_API int ab_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out,
+                              int guard, int want_stats);
+/* Waits for the stream and copies the report of the last ab_fq_absmean_pack on `w`. */
+AB_API int ab_weights_fq_report(ab_weights* w, ab_fq_report* report);
+
+/* quantize_and_pack(&[f32]) -> (f32, Vec<u8>)  (src/export.rs:94-113). Host buffers;
+ * `packed` must hold ceil(n/4) bytes.  n == 0 returns scale 0 and writes nothing. */
+AB_API int ab_quantize_and_pack_host(ab_ctx* ctx, const float* weights, size_t n, float* scale,
+                                     uint8_t* packed);
+
+/* FakeQuantize (src/qat.rs:116-230), flat tensors.  Device pointers. */
+/* calibrate_scale: *scale_dev = max(f32(sum|w|/n), 1e-10); unchanged when n == 0.            */
+AB_API int ab_calibrate_scale(ab_ctx* ctx, const float* w, size_t n, float* scale_dev);
+/* fake_quantize_forward for any QuantBits; `scale_dev` is a device scalar.                   */
+AB_API int ab_fake_quantize_forward(ab_ctx* ctx, const float* w, float* q, size_t n,
+                                    const float* scale_dev, float temperature, int bits);
+/* ste_backward: copy, or clamp to +-grad_clip when grad_clip > 0.                            */
+AB_API int ab_ste_backward(ab_ctx* ctx, const float* grad_output, float* grad_input, size_t n,
+                           float grad_clip);
+/* CalibrationStats::update_weights (src/qat.rs:264-310): out5 (HOST) = min, max, mean|w|,
+ * MAE, cosine.  Blocks. */
+AB_API int ab_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n, float* out5);
+/* Host-slice forms of the same four calls (FakeQuantize keeps `scale` on the host). */
+AB_API int ab_calibrate_scale_host(ab_ctx* ctx, const float* w, size_t n, float* scale_inout);
+AB_API int ab_fake_quantize_forward_host(ab_ctx* ctx, const float* w, size_t w_len, float* q,
+                                         size_t q_len, float scale, float temperature, int bits);
+AB_API int ab_ste_backward_host(ab_ctx* ctx, const float* grad_output, size_t go_len,
+                                float* grad_input, size_t gi_len, float grad_clip);
+AB_API int ab_calibration_stats_host(ab_ctx* ctx, const float* w, const float* q, size_t n,
+                                     float* out5);
+
+/* ----------------------------------------------------------------- batch-1 (matvec) path */
+
+/* y = W x, add/sub only.  Replaces alice_ml::ops::ternary_matvec_kernel as called at
+ * src/backward.rs:138. */
+AB_API int ab_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y);
+/* dx = W^T dy (dx overwritten).  Replaces ternary_matvec_backward (src/backward.rs:28-82),
+ * GpuBackwardEngine::ternary_matvec_backward (src/gpu_backward.rs:170-306) and the shader
+ * shaders/ternary_backward.wgsl:27-61. */
+AB_API int ab_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx);
+/* bitlinear_backward (src/backward.rs:105-156); `d_bias` may be NULL. */
+AB_API int ab_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy,
+                                 int pre_norm, float norm_eps, float* dx, float* d_bias);
+/* dW[j*in+i] += dy_j * x_i.  Replaces ste_weight_grad (src/backward.rs:173-184). */
+AB_API int ab_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in_features, const float* dy,
+                              size_t out_features, float* dW);
+/* C[m x out] += gamma * A[m x in] * W^T straight off the packed codes, f32.
+ * Replaces blas::ternary_matmul_bt (src/blas.rs:403-457). */
+AB_API int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale,
+                                float* c, size_t m);
+
+/* Host-slice forms with the reference's length checks (AB_ERR_SHAPE where it would panic). */
+AB_API int ab_ternary_matvec_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len,
+                                  float* y, size_t y_len);
+AB_API int ab_ternary_matvec_backward_host(ab_ctx* ctx, const ab_weights* w, const float* dy,
+                                           size_t dy_len, float* dx, size_t dx_len);
+AB_API int ab_bitlinear_backward_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len,
+                                      const float* dy, size_t dy_len, int pre_norm, float norm_eps,
+                                      float* dx, size_t dx_len, float* d_bias, size_t d_bias_len);
+AB_API int ab_ste_weight_grad_host(ab_ctx* ctx, const float* x, size_t x_len, const float* dy,
+                                   size_t dy_len, float* dW, size_t dw_len);
+AB_API int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed_b,
+                                     float scale, float* c, size_t m, size_t n, size_t k);
+
+/* -------------------------------------------------------------------- batched (GEMM) path */
+
+/* (2a) Per-token int8 absmax quantisation.  x is [m x k] (f32 or bf16), xq is [m x ld_xq] int8,
+ * scales[m] = max|x_t|, rowsums[m] = sum_k xq_tk (s32).  xq_tk = clamp(round_half_away(
+ * x_tk * (127/s_t)), +-127); a zero row gives xq = 0.  No reference counterpart (the reference
+ * has no activation quantisation); defined by the target specification. */
+AB_API int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x,
+                             int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
+
+/* (2b) y[m x out] = ((float)acc * (s_t/127)) * gamma with acc = xq . codes^T in s32 (exact).
+ * `acc_out` (s32 [m x out], pitch out) may be NULL.  Stands where the reference runs
+ * CudaMatmul::matmul_bt / matmul_bt_with_gpu_b / matmul_bt_inplace / gemm_gpu_bt
+ * (src/cuda_matmul.rs:1149-1199,1262-1318,1516-1575,5746-5777),
+ * GpuMatmul::matmul_bt (src/gpu_matmul.rs:405-535) and blas_matmul_bt (src/blas.rs:71-109) on
+ * fake-quantised f32 weights. */
+AB_API int ab_bitlinear_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq,
+                            const float* scales, const int32_t* rowsums, size_t m, void* y,
+                            int y_dtype, size_t ld_y, int32_t* acc_out);
+
+/* (3) dx[m x in] = beta*dx + gamma * dy[m x out] . codes, dy bf16, f32 accumulation.
+ * Replaces CudaMatmul::matmul_nn / matmul_nn_with_gpu_b / matmul_nn_inplace
+ * (src/cuda_matmul.rs:1204-1258,1459-1513,1578-1637, called at 4125-4287) and the
+ * dA half of matmul_bt_backward (src/llama_backward.rs:118-126).  beta is 0 or 1. */
+AB_API int ab_bitlinear_dx(ab_ctx* ctx, const ab_weights* w, const void* dy_bf16, size_t ld_dy,
+                           size_t m, void* dx, int dx_dtype, size_t ld_dx, float beta);
+
+/* (4) dW[out x in] = beta*dW + dy^T[out x m] . x[m x in], bf16 operands, f32 result.
+ * Replaces CudaMatmul::matmul_tn / matmul_tn_inplace (src/cuda_matmul.rs:1640-1699,1859-1915,
+ * called at 4180-4347) and the
+ * dB half of matmul_bt_backward (src/llama_backward.rs:129-137).  beta is 0 or 1. */
+AB_API int ab_ste_dw(ab_ctx* ctx, const void* dy_bf16, size_t ld_dy, const void* x_bf16, size_t ld_x,
+                     size_t m, size_t out_features, size_t in_features, float* dW, size_t ld_dw,
+                     float beta);
+
+/* One forward+backward pass of a BitLinear layer on HOST buffers (pinned memory makes the
+ * copies asynchronous): H2D x and dy (bf16), act-quant, forward, dx, dW += , D2H y and dx
+ * (bf16).  dW stays on the device in `dW_dev` (f32 [out x in], accumulated) as a gradient
+ * buffer does between micro-batches.  Blocks until y and dx are on the host.
+ * This is the reference's per-projection sequence matmul_bt -> matmul_nn -> matmul_tn
+ * (src/cuda_matmul.rs:3643-3666,4125-4200) behind one call. */
+AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_bf16_host,
+                                  const void* dy_bf16_host, size_t m, void* y_bf16_host,
+                                  void* dx_bf16_host, float* dW_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALICE_B200_H */

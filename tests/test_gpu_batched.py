@@ -1,0 +1,198 @@
+"""GPU parity of the batched path through the C ABI: per-token int8 activation quantisation,
+the int8 x ternary forward (s32 accumulators bit-exact), dx = dy.W off the packed codes and the
+STE gradient dW = dy^T.x on the tensor cores, against the CPU oracle.
+
+Tolerances (max |err| over max |ref|): f32 outputs of the bf16-operand GEMMs 1e-5 (products
+are exact, only the f32 summation order differs); bf16 outputs 1e-2.  Small problems are
+compared in full; the Llama-3-8B MLP shapes are compared on seeded samples of output elements
+(a full CPU product at that size would take hours) plus exact integer checks."""
+import numpy as np
+import pytest
+
+from helpers import normal_f32, rel_err, rng, to_bf16_tensor
+
+pytestmark = pytest.mark.gpu
+RTOL_F32 = 1e-5
+RTOL_BF16 = 1e-2
+
+
+@pytest.fixture(scope="module")
+def env():
+    import alice_train
+    import torch
+    from alice_train import bitlinear
+    assert torch.cuda.is_available()
+    ctx = alice_train.GpuContext.on_torch_stream(0)
+    alice_train.set_default_context(ctx)
+    return alice_train, bitlinear, ctx, torch
+
+
+def _weights(env, orc, out, inn, seed, std=0.02):
+    at, bl, ctx, torch = env
+    w_lat = normal_f32(seed, (out, inn), std)
+    h = bl.BitLinearWeights(out, inn, ctx).quantize_(torch.from_numpy(w_lat).cuda())
+    g, codes, _ = orc.quantize_and_pack(w_lat)
+    ctx.sync()
+    assert h.gamma == g
+    return h, g, codes.reshape(out, inn)
+
+
+@pytest.mark.parametrize("m,k,dtype", [(64, 4096, "bf16"), (5, 37, "f32"), (3, 14336, "bf16"), (17, 1000, "f32"),
+                                       (2, 20000, "bf16")])
+def test_act_quant_bit_exact(env, orc, m, k, dtype):
+    at, bl, ctx, torch = env
+    x = normal_f32(30, (m, k))
+    x[1] = 0.0  # zero row: scale 0, xq 0
+    if dtype == "bf16":
+        xt, xr = to_bf16_tensor(orc, x, "cuda")
+    else:
+        xt, xr = torch.from_numpy(x).cuda(), x
+    qa = bl.act_quant_int8(ctx, xt)
+    ctx.sync()
+    xq_ref, s_ref = orc.act_quant_int8(xr)
+    assert np.array_equal(qa.xq.cpu().numpy(), xq_ref)
+    assert np.array_equal(qa.scales.cpu().numpy(), s_ref)
+    assert np.array_equal(qa.rowsums.cpu().numpy(), xq_ref.astype(np.int32).sum(axis=1))
+
+
+@pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 256, 128), (100, 300, 272), (1, 256, 4096),
+                                       (130, 8, 48), (257, 1000, 2000), (4, 4, 4), (3, 5, 7)])
+def test_forward_accumulators_bit_exact(env, orc, m, out, inn):
+    at, bl, ctx, torch = env
+    h, g, codes = _weights(env, orc, out, inn, 40)
+    x = normal_f32(41, (m, inn))
+    xt, xr = to_bf16_tensor(orc, x, "cuda")
+    qa = bl.act_quant_int8(ctx, xt)
+    acc = torch.empty((m, out), dtype=torch.int32, device="cuda")
+    y32 = bl.bitlinear_fwd(h, qa, dtype=torch.float32, acc_out=acc)
+    y16 = bl.bitlinear_fwd(h, qa, dtype=torch.bfloat16)
+    ctx.sync()
+    xq_ref, s_ref = orc.act_quant_int8(xr)
+    acc_ref = orc.int8_ternary_acc(xq_ref, codes)
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    y_ref = orc.bitlinear_fwd_scale(acc_ref, s_ref, g)
+    assert np.array_equal(y32.cpu().numpy(), y_ref)  # same three f32 operations, same order
+    assert rel_err(y16.float().cpu().numpy(), y_ref) <= RTOL_BF16
+    h.close()
+
+
+@pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 64, 256), (100, 304, 264), (1, 4096, 256),
+                                       (130, 48, 8), (257, 2000, 1000), (4, 4, 4), (3, 7, 5)])
+def test_dx_vs_oracle(env, orc, m, out, inn):
+    at, bl, ctx, torch = env
+    h, g, codes = _weights(env, orc, out, inn, 50)
+    dy = normal_f32(51, (m, out), 1e-2)
+    dyt, dyr = to_bf16_tensor(orc, dy, "cuda")
+    dx32 = bl.bitlinear_dx(h, dyt, dtype=torch.float32)
+    dx16 = bl.bitlinear_dx(h, dyt, dtype=torch.bfloat16)
+    ctx.sync()
+    wq = codes.astype(np.float32) * np.float32(g)
+    ref, _ = orc.matmul_bt_backward(dyr, np.zeros((m, inn), np.float32), wq, m, out, inn, want=("da",))
+    e32, e16 = rel_err(dx32.cpu().numpy(), ref), rel_err(dx16.float().cpu().numpy(), ref)
+    print(f"[dx] {m}x{out}x{inn}: rel err f32 {e32:.2e}, bf16 {e16:.2e}")
+    assert e32 <= RTOL_F32 and e16 <= RTOL_BF16
+    # accumulate form (beta = 1): dA += dC.B  (src/llama_backward.rs:118-126)
+    base = normal_f32(52, (m, inn), 1e-2)
+    acc = torch.from_numpy(base.copy()).cuda()
+    bl.bitlinear_dx(h, dyt, dx=acc, beta=1.0)
+    ctx.sync()
+    assert rel_err(acc.cpu().numpy(), ref + base) <= RTOL_F32
+    h.close()
+
+
+@pytest.mark.parametrize("m,out,inn", [(256, 128, 256), (64, 128, 256), (1000, 136, 264), (70, 8, 16), (512, 300, 520),
+                                       (4, 4, 4), (5, 3, 7)])
+def test_dw_vs_oracle(env, orc, m, out, inn):
+    at, bl, ctx, torch = env
+    dy, x = normal_f32(60, (m, out), 1e-2), normal_f32(61, (m, inn))
+    dyt, dyr = to_bf16_tensor(orc, dy, "cuda")
+    xt, xr = to_bf16_tensor(orc, x, "cuda")
+    dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
+    bl.ste_dw(ctx, dyt, xt, dw, beta=0.0)
+    ctx.sync()
+    _, ref = orc.matmul_bt_backward(dyr, xr, np.zeros((out, inn), np.float32), m, out, inn, want=("db",))
+    e = rel_err(dw.cpu().numpy(), ref)
+    print(f"[dW] {m}x{out}x{inn}: rel err {e:.2e}")
+    assert e <= RTOL_F32
+    bl.ste_dw(ctx, dyt, xt, dw, beta=1.0)  # += (src/backward.rs:181, src/llama_backward.rs:135)
+    ctx.sync()
+    assert rel_err(dw.cpu().numpy(), 2 * ref) <= RTOL_F32
+
+
+def test_llama8b_mlp_shapes_sampled(env, orc):
+    """configs[1]: hidden 4096, intermediate 14336, 4096 tokens; x bf16 ~ N(0,1), dy bf16 ~ N(0,1e-4),
+    W ~ N(0, 0.02^2).  Codes and gamma are checked in full, GEMM outputs on 400 seeded samples each,
+    plus a linearity property of the integer forward over the whole output."""
+    at, bl, ctx, torch = env
+    m = 4096
+    r = rng(70)
+    for name, out, inn, seed in [("gate", 14336, 4096, 10), ("down", 4096, 14336, 12)]:
+        w_lat = normal_f32(seed, (out, inn), 0.02)
+        h = bl.BitLinearWeights(out, inn, ctx).quantize_(torch.from_numpy(w_lat).cuda())
+        g, codes, packed = orc.quantize_and_pack(w_lat)
+        codes = codes.reshape(out, inn)
+        ctx.sync()
+        assert h.gamma == g and np.array_equal(h.to_packed(), packed)
+        x, dy = normal_f32(seed + 100, (m, inn)), normal_f32(seed + 200, (m, out), 1e-2)
+        xt, xr = to_bf16_tensor(orc, x, "cuda")
+        dyt, dyr = to_bf16_tensor(orc, dy, "cuda")
+        qa = bl.act_quant_int8(ctx, xt)
+        acc = torch.empty((m, out), dtype=torch.int32, device="cuda")
+        y = bl.bitlinear_fwd(h, qa, dtype=torch.float32, acc_out=acc)
+        dx = bl.bitlinear_dx(h, dyt, dtype=torch.float32)
+        dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
+        bl.ste_dw(ctx, dyt, xt, dw, beta=0.0)
+        ctx.sync()
+        xq_ref, s_ref = orc.act_quant_int8(xr)
+        assert np.array_equal(qa.xq.cpu().numpy(), xq_ref)
+        acc_h, y_h, dx_h, dw_h = acc.cpu().numpy(), y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy()
+        wq = codes.astype(np.float32) * np.float32(g)
+        ts, js, is_ = r.integers(0, m, 400), r.integers(0, out, 400), r.integers(0, inn, 400)
+        e_dx = e_dw = 0.0
+        for t, j, i in zip(ts, js, is_):
+            a_ref = orc.lib.orc_int8_ternary_acc_element(xq_ref.reshape(-1), codes.reshape(-1), out, inn, t, j)
+            assert acc_h[t, j] == a_ref
+            assert y_h[t, j] == orc.lib.orc_bitlinear_fwd_scale(int(a_ref), float(s_ref[t]), g)
+            e_dx = max(e_dx, abs(dx_h[t, i] - orc.dx_element(dyr.reshape(-1), wq.reshape(-1), out, inn, t, i)))
+            e_dw = max(e_dw, abs(dw_h[j, i] - orc.dw_element(dyr.reshape(-1), xr.reshape(-1), m, out, inn, j, i)))
+        e_dx /= np.abs(dx_h).max()
+        e_dw /= np.abs(dw_h).max()
+        print(f"[{name}] sampled rel err dx {e_dx:.2e} dW {e_dw:.2e}")
+        assert e_dx <= RTOL_F32 and e_dw <= RTOL_F32
+        # size-independent property over the WHOLE output: the integer forward is linear in xq, so
+        # sum_t acc[t, :] equals (sum_t xq[t, :]) . codes^T computed exactly on the CPU in int64
+        colsum = xq_ref.astype(np.int64).sum(axis=0)
+        assert np.array_equal(acc_h.astype(np.int64).sum(axis=0), codes.astype(np.int64) @ colsum)
+        # dx and dW are two contractions of the same trilinear form: <dx, x> == <dW, W> * gamma
+        lhs = float(np.sum(dx_h.astype(np.float64) * xr.astype(np.float64)))
+        rhs = float(np.sum(dw_h.astype(np.float64) * wq.astype(np.float64)))
+        assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1e-12), (lhs, rhs)
+        h.close()
+
+
+def test_bitlinear_step_host(env, orc):
+    """The host-buffer entry point (H2D, act-quant, fwd, dx, dW +=, D2H) against its parts."""
+    import ctypes as C
+    at, bl, ctx, torch = env
+    from alice_train import _ffi
+    m, out, inn = 256, 512, 1024
+    h, g, codes = _weights(env, orc, out, inn, 80)
+    x, dy = normal_f32(81, (m, inn)), normal_f32(82, (m, out), 1e-2)
+    xb = torch.from_numpy(orc.bf16_round(x).view(np.int16)).view(torch.bfloat16).pin_memory()
+    dyb = torch.from_numpy(orc.bf16_round(dy).view(np.int16)).view(torch.bfloat16).pin_memory()
+    y_h = torch.empty((m, out), dtype=torch.bfloat16).pin_memory()
+    dx_h = torch.empty((m, inn), dtype=torch.bfloat16).pin_memory()
+    dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
+    for _ in range(2):  # dW accumulates across calls
+        _ffi.check(_ffi.load().ab_bitlinear_step_host(ctx.handle, h.handle, C.c_void_p(xb.data_ptr()),
+                                                      C.c_void_p(dyb.data_ptr()), m, C.c_void_p(y_h.data_ptr()),
+                                                      C.c_void_p(dx_h.data_ptr()), C.c_void_p(dw.data_ptr())), ctx.handle)
+    qa = bl.act_quant_int8(ctx, xb.cuda())
+    y_ref = bl.bitlinear_fwd(h, qa, dtype=torch.bfloat16)
+    dx_ref = bl.bitlinear_dx(h, dyb.cuda(), dtype=torch.bfloat16)
+    dw_ref = torch.zeros_like(dw)
+    bl.ste_dw(ctx, dyb.cuda(), xb.cuda(), dw_ref, beta=0.0)
+    ctx.sync()
+    assert torch.equal(y_h.cuda(), y_ref) and torch.equal(dx_h.cuda(), dx_ref)
+    assert rel_err(dw.cpu().numpy(), 2 * dw_ref.cpu().numpy()) <= 1e-6
+    h.close()

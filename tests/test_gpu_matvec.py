@@ -1,0 +1,157 @@
+"""GPU parity of the batch-1 path (ternary_matvec_backward, bitlinear_backward, ste_weight_grad,
+ternary_matmul_bt) through the C ABI: the reference's own test vectors, then the CPU-runnable
+configuration of the target specification (2048x2048, seeds fixed) against the CPU oracle.
+Floating-point tolerance: 1e-5 of the largest reference magnitude (f32 sums in another order);
+ste_weight_grad is bit-exact (separate multiply and add, as in src/backward.rs:181)."""
+import numpy as np
+import pytest
+
+from helpers import normal_f32, rel_err
+
+pytestmark = pytest.mark.gpu
+RTOL_F32 = 1e-5
+
+
+@pytest.fixture(scope="module")
+def at():
+    import alice_train
+    import torch
+    assert torch.cuda.is_available()
+    alice_train.set_default_context(alice_train.GpuContext.on_torch_stream(0))
+    return alice_train
+
+
+def test_ternary_matvec_backward_golden(at, golden):
+    for c in golden["ternary_matvec_backward"]:
+        w = at.TernaryWeightKernel.from_ternary(c["w"], c["out"], c["in"])
+        dx = np.full(c["in"], 123.0, np.float32)  # must be overwritten, not accumulated
+        at.ternary_matvec_backward(np.array(c["dy"], np.float32), w, dx)
+        for got, want in zip(dx, c["dx"]):
+            if want is not None:
+                assert abs(got - want) <= c["tol"], c["cite"]
+    for c in golden["ternary_matvec_forward"]:
+        w = at.TernaryWeightKernel.from_ternary(c["w"], c["out"], c["in"])
+        y = np.zeros(c["out"], np.float32)
+        at.ternary_matvec_kernel(np.array(c["x"], np.float32), w, y)
+        assert np.allclose(y, c["y"], atol=c["tol"]), c["cite"]
+
+
+def test_bitlinear_backward_golden(at, orc, golden):
+    for c in golden["bitlinear_backward"]:
+        w = at.TernaryWeightKernel.from_ternary(c["w"], c["out"], c["in"])
+        dx, db = np.zeros(c["in"], np.float32), np.zeros(c["out"], np.float32)
+        at.bitlinear_backward(np.array(c["x"], np.float32), np.array(c["dy"], np.float32), w, c["pre_norm"],
+                              c["norm_eps"], dx, db)
+        ow = orc.TernaryWeightKernel.from_ternary(c["w"], c["out"], c["in"])
+        ref = orc.bitlinear_backward(c["x"], c["dy"], ow, c["pre_norm"], c["norm_eps"])
+        assert np.allclose(dx, ref, rtol=1e-5, atol=1e-6), c["cite"]
+        if "dx" in c:
+            assert np.allclose(dx, c["dx"], atol=c["tol"]), c["cite"]
+        if "d_bias" in c:
+            assert np.allclose(db, c["d_bias"], atol=c["tol"]), c["cite"]
+        if c.get("finite"):
+            assert np.all(np.isfinite(dx))
+        if c.get("nonzero"):
+            assert np.any(np.abs(dx) > 1e-8)
+    # analytic gradient against central differences through the GPU forward (src/backward.rs:424-495)
+    for c in golden["backward_numerical"]:
+        w = at.TernaryWeightKernel.from_ternary(c["w"], c["out"], c["in"])
+        x = np.array(c["x"], np.float32)
+
+        def fwd(inp):
+            y = np.zeros(c["out"], np.float32)
+            at.ternary_matvec_kernel(inp, w, y)
+            if c["pre_norm"]:
+                rms = np.sqrt(np.float32(np.sum(inp * inp, dtype=np.float32) / np.float32(len(inp)) + np.float32(c["norm_eps"])))
+                y = y / rms
+            return float(y.sum(dtype=np.float32))
+
+        dx = np.zeros(c["in"], np.float32)
+        if c["pre_norm"]:
+            at.bitlinear_backward(x, np.array(c["dy"], np.float32), w, True, c["norm_eps"], dx)
+        else:
+            at.ternary_matvec_backward(np.array(c["dy"], np.float32), w, dx)
+        eps = np.float32(c["eps"])
+        for i in range(len(x)):
+            xp, xm = x.copy(), x.copy()
+            xp[i] += eps
+            xm[i] -= eps
+            assert abs(dx[i] - (fwd(xp) - fwd(xm)) / (2 * float(eps))) < c["tol"], (c["cite"], i)
+
+
+def test_ste_weight_grad_golden(at, golden):
+    for c in golden["ste_weight_grad"]:
+        dw = np.array(c["dw0"], np.float32)
+        at.ste_weight_grad(np.array(c["x"], np.float32), np.array(c["dy"], np.float32), dw)
+        assert np.allclose(dw, c["dw"], atol=c["tol"]), c["cite"]
+    for c in golden["ste_weight_grad_multi"]:
+        dw = np.zeros(len(c["dw"]), np.float32)
+        for s in c["steps"]:
+            at.ste_weight_grad(np.array(s["x"], np.float32), np.array(s["dy"], np.float32), dw)
+        assert np.allclose(dw, c["dw"], atol=c["tol"]), c["cite"]
+
+
+def test_length_mismatch_raises_assertion(at, golden):
+    for c in golden["length_mismatch"]:
+        with pytest.raises(AssertionError, match="assertion"):
+            if c["fn"] == "ternary_matvec_backward":
+                w = at.TernaryWeightKernel.from_ternary([1, -1, 0, 1], c["out"], c["in"])
+                at.ternary_matvec_backward(np.ones(c["dy_len"], np.float32), w, np.zeros(c["dx_len"], np.float32))
+            elif c["fn"] == "bitlinear_backward":
+                w = at.TernaryWeightKernel.from_ternary([1, -1, 0, 1], c["out"], c["in"])
+                at.bitlinear_backward(np.ones(c["x_len"], np.float32), np.ones(c["dy_len"], np.float32), w, False,
+                                      1e-5, np.zeros(c["dx_len"], np.float32))
+            else:
+                at.ste_weight_grad(np.ones(c["x_len"], np.float32), np.ones(c["dy_len"], np.float32),
+                                   np.zeros(c["dw_len"], np.float32))
+
+
+@pytest.mark.parametrize("out,inn", [(2048, 2048), (1, 3), (3, 1), (7, 130), (257, 33), (4096, 14336), (100, 2049)])
+def test_matvec_path_vs_oracle(at, orc, out, inn):
+    """configs[0] of the target specification is (2048, 2048): W ~ N(0, 0.02^2) seed 1 ternarised
+    by absmean, x ~ N(0,1) seed 2, dy ~ N(0,1) seed 3, eps 1e-6."""
+    w_lat = normal_f32(1, (out, inn), 0.02)
+    _, codes, _ = orc.quantize_and_pack(w_lat)
+    x, dy = normal_f32(2, (inn,)), normal_f32(3, (out,))
+    dy[::17] = 0.0  # rows the reference skips (src/backward.rs:48)
+    ow = orc.TernaryWeightKernel.from_ternary(codes, out, inn)
+    w = at.TernaryWeightKernel.from_ternary(codes, out, inn)
+
+    dx = np.zeros(inn, np.float32)
+    at.ternary_matvec_backward(dy, w, dx)
+    e = rel_err(dx, orc.ternary_matvec_backward(dy, ow))
+    assert e <= RTOL_F32, e
+
+    y = np.zeros(out, np.float32)
+    at.ternary_matvec_kernel(x, w, y)
+    assert rel_err(y, orc.ternary_matvec(x, ow)) <= RTOL_F32
+
+    for pre_norm in (False, True):
+        dxb, db = np.zeros(inn, np.float32), np.zeros(out, np.float32)
+        at.bitlinear_backward(x, dy, w, pre_norm, 1e-6, dxb, db)
+        ref, refb = orc.bitlinear_backward(x, dy, ow, pre_norm, 1e-6, True)
+        e = rel_err(dxb, ref)
+        assert e <= RTOL_F32, (pre_norm, e)
+        assert np.array_equal(db, refb)
+    w.close()
+
+
+@pytest.mark.parametrize("out,inn", [(2048, 2048), (5, 3), (33, 130)])
+def test_ste_weight_grad_bit_exact(at, orc, out, inn):
+    x, dy = normal_f32(2, (inn,)), normal_f32(3, (out,))
+    for start in (np.zeros(out * inn, np.float32), normal_f32(4, (out * inn,))):
+        dw = start.copy()
+        at.ste_weight_grad(x, dy, dw)
+        assert np.array_equal(dw, orc.ste_weight_grad(x, dy, start))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 256), (3, 17, 37), (2, 128, 4096), (1, 5, 3)])
+def test_ternary_matmul_bt(at, orc, m, n, k):
+    w_lat = normal_f32(8, (n, k), 0.02)
+    g, codes, _ = orc.quantize_and_pack(w_lat)
+    rows = np.concatenate([orc.pack_ternary(codes.reshape(n, k)[j]) for j in range(n)])
+    a = normal_f32(9, (m, k))
+    c0 = normal_f32(10, (m, n))
+    c = c0.copy()
+    at.blas.ternary_matmul_bt(a, rows, g, c, m, n, k)
+    assert rel_err(c, orc.ternary_matmul_bt(a, rows, g, c0, m, n, k)) <= RTOL_F32
