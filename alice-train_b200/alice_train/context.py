@@ -32,7 +32,10 @@ class GpuContext:
     def on_torch_stream(cls, device: int = 0):
         """Context that enqueues on torch's current stream of `device` (so torch events time it)."""
         import torch
-        return cls(device, torch.cuda.current_stream(device).cuda_stream)
+        handle = torch.cuda.current_stream(device).cuda_stream
+        # torch reports the legacy default stream as 0, which the C ABI reads as "create a stream";
+        # cudaStreamLegacy (0x1) names that same stream explicitly
+        return cls(device, handle if handle else 1)
 
     @property
     def handle(self):

@@ -75,7 +75,8 @@ typedef struct ab_fq_report {
 /* ------------------------------------------------------------------------------ context */
 
 /* Creates a context on `device`.  `cuda_stream` may be NULL (the context creates its own
- * stream) or an existing cudaStream_t to run on.
+ * stream) or an existing cudaStream_t to run on (pass cudaStreamLegacy, (void*)1, for the
+ * legacy default stream, whose own handle is the null pointer).
  * Replaces GpuContext::new_blocking (src/gpu.rs:37-79), GpuBackwardEngine::new
  * (src/gpu_backward.rs:59), CudaMatmul::new (src/cuda_matmul.rs:953) and init_cuda_blas
  * (src/blas.rs:19-24). */
