@@ -1,0 +1,78 @@
+"""Partitioning of the BitLinear path across the GPUs of one box (one process per GPU).
+
+The reference has no multi-GPU code at all (single CudaContext::new(0), src/cuda_matmul.rs:954);
+the two partitionings here are the ones the target specification names:
+
+  * data parallel over tokens: forward and dx are independent per token; dW = dy^T.x is a sum
+    over tokens, so the only exchange is one all-reduce(sum) of dW per projection;
+  * output-row shards of W: forward and dW are independent per row; gamma needs the global
+    sum |w| (one f64 all-reduce of 8 bytes) and dx is a sum over row shards (all-reduce or
+    reduce-scatter of [tokens x in]).
+
+torch.distributed is the plumbing (NCCL on GPUs, gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def token_shard(tokens: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous, balanced split of `tokens` (earlier ranks take the remainder)."""
+    base, rem = divmod(tokens, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def row_shard(out_features: int, world: int, rank: int, align: int = 1) -> tuple[int, int]:
+    """Contiguous split of W's output rows in multiples of `align` (last rank takes the tail)."""
+    blocks = (out_features + align - 1) // align
+    b0, b1 = token_shard(blocks, world, rank)
+    return min(b0 * align, out_features), min(b1 * align, out_features)
+
+
+class DwAllReducer:
+    """One asynchronous all-reduce(sum) per projection, issued as soon as its dW is ready and
+    waited for at the end of the step, so the exchange overlaps the remaining GEMMs."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self._pending = []
+
+    def submit(self, dW: torch.Tensor):
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            self._pending.append(dist.all_reduce(dW, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def wait(self):
+        for h in self._pending:
+            h.wait()
+        self._pending.clear()
+
+
+def global_gamma(sum_abs_local: torch.Tensor, n_total: int, group=None, floor: bool = False) -> torch.Tensor:
+    """gamma of a row-sharded tensor: all-reduce the f64 shard sums of |w|, divide by the global
+    element count, round to f32 (src/qwen35.rs:226-227).  Every rank gets the same bits."""
+    assert sum_abs_local.dtype == torch.float64
+    total = sum_abs_local.clone()
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
+    gamma = (total / float(n_total)).to(torch.float32)
+    if floor:
+        gamma = torch.clamp_min(gamma, 1e-10)
+    return gamma
+
+
+def gather_rows(y_local: torch.Tensor, group=None) -> torch.Tensor:
+    """Forward of a row-sharded layer: concatenate the [tokens x out/g] shards along features."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return y_local
+    parts = [torch.empty_like(y_local) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, y_local.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
+
+
+def reduce_dx(dx_partial: torch.Tensor, group=None) -> torch.Tensor:
+    """Backward of a row-sharded layer: dx = sum over shards of dy[:, shard] . W_shard."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(dx_partial, op=dist.ReduceOp.SUM, group=group)
+    return dx_partial

@@ -125,6 +125,10 @@ int ab_ctx_destroy(ab_ctx* ctx) {
     for (int i = 0; i < 6; ++i)
         if (ctx->stage[i]) cudaFree(ctx->stage[i]);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
+    for (int i = 0; i < 6; ++i)
+        if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return AB_OK;
@@ -720,15 +724,37 @@ int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host,
     AB_TRY(ab_ctx_stage(ctx, 5, m * in * 2, &ddx));
     float* scales = (float*)dsc;
     int32_t* rowsums = (int32_t*)((char*)dsc + m * 4);
-    cudaStream_t s = ctx->stream;
-    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_in, x_host, m * in * 2, cudaMemcpyHostToDevice, s));
-    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(ddy, dy_host, m * out * 2, cudaMemcpyHostToDevice, s));
+    // Three streams so that PCIe runs in both directions while the tensor cores work:
+    //   copy_in : H2D x, H2D dy            compute: act-quant, fwd | dx | dW            copy_out: D2H y, D2H dx
+    if (!ctx->copy_in) {
+        AB_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+        AB_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 6; ++i) AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->ev[i], cudaEventDisableTiming));
+    }
+    cudaStream_t s = ctx->stream, si = ctx->copy_in, so = ctx->copy_out;
+    cudaEvent_t e_start = ctx->ev[0], e_x = ctx->ev[1], e_dy = ctx->ev[2], e_y = ctx->ev[3], e_dx = ctx->ev[4],
+                e_out = ctx->ev[5];
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_start, s));  // staging buffers are free once earlier work on s is done
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(si, e_start, 0));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(so, e_start, 0));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_in, x_host, m * in * 2, cudaMemcpyHostToDevice, si));
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_x, si));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(ddy, dy_host, m * out * 2, cudaMemcpyHostToDevice, si));
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_dy, si));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(s, e_x, 0));
     AB_TRY(abk_act_quant_int8(ctx, dx_in, AB_BF16, m, in, in, (int8_t*)dxq, in, scales, rowsums));
     AB_TRY(abk_gemm_fwd(ctx, w, (const int8_t*)dxq, in, scales, rowsums, m, dy_out, AB_BF16, out, nullptr));
-    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(y_host, dy_out, m * out * 2, cudaMemcpyDeviceToHost, s));
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_y, s));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(so, e_y, 0));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(y_host, dy_out, m * out * 2, cudaMemcpyDeviceToHost, so));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(s, e_dy, 0));
     AB_TRY(abk_gemm_dx(ctx, w, ddy, out, m, ddx, AB_BF16, in, 0.0f));
-    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_host, ddx, m * in * 2, cudaMemcpyDeviceToHost, s));
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_dx, s));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(so, e_dx, 0));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_host, ddx, m * in * 2, cudaMemcpyDeviceToHost, so));
+    AB_CUDA_CHECK(ctx, cudaEventRecord(e_out, so));
     AB_TRY(abk_gemm_dw(ctx, ddy, out, dx_in, in, m, out, in, dW_dev, in, 1.0f));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(s, e_out, 0));  // the context stream now also covers the copies out
     return ab_ctx_sync(ctx);
 }
 

@@ -45,6 +45,9 @@ struct ab_ctx {
     size_t stage_bytes[6] = {0, 0, 0, 0, 0, 0};
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
     int* dev_status = nullptr;
+    // copy streams + events of the host-buffer step (created on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint64_t launches = 0;
     int fwd_offset_binary = 1;  // encoding of codes_fwd, fixed for the life of the context
     std::string last_error;
