@@ -77,6 +77,7 @@ SIGNATURES = {
     "ab_bitlinear_dx": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _i, _sz, _f]),
     "ab_ste_dw": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _f]),
     "ab_bitlinear_step_host": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "ab_tensor_peak_probe": (_i, [_vp, _i, _i, C.POINTER(C.c_double)]),
 }
 
 _lib = None

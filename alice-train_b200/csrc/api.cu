@@ -706,6 +706,28 @@ int ab_ste_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t l
     return abk_gemm_dw(ctx, dy, ld_dy, x, ld_x, m, out, in, dW, ld_dw, beta);
 }
 
+#ifdef AB_GEMM_TRACE
+// Trace builds only (never part of the shipped library): reserve / read back the timestamp buffer.
+__attribute__((visibility("default"))) int ab_debug_trace(ab_ctx* ctx, long long* host, size_t n, int reset) {
+    void* d = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 5, 128 * 8 * sizeof(long long), &d));
+    if (reset) {
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(d, 0, 128 * 8 * sizeof(long long), ctx->stream));
+        return AB_OK;
+    }
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemcpy(host, d, n * sizeof(long long), cudaMemcpyDeviceToHost));
+    return AB_OK;
+}
+#endif
+
+int ab_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(ops_out, AB_ERR_NULL);
+    AB_REQUIRE(iters > 0 && iters <= (1 << 20), AB_ERR_UNSUPPORTED);
+    return abk_tensor_peak_probe(ctx, kind_i8, iters, ops_out);
+}
+
 int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host, const void* dy_host, size_t m,
                            void* y_host, void* dx_host, float* dW_dev) {
     AB_TRY(bind(ctx));

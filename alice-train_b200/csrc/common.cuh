@@ -138,6 +138,8 @@ int abk_gemm_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, 
 int abk_gemm_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m,
                 size_t out, size_t in, float* dW, size_t ld_dw, float beta);
 
+int abk_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out);
+
 // gemm_simt.cu : any-shape kernels for operands the tensor-core path cannot take (unaligned
 // pitches, dimensions that are not multiples of 8).  Same arithmetic definition.
 int abk_simt_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,

@@ -11,7 +11,7 @@
 //               accumulating in TMEM (two 256-column accumulators, so the epilogue of tile i
 //               overlaps the main loop of tile i+1); owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, apply scales, store to global memory
-//   warps 6-13  (FWD/DX) expanders: turn the staged 2-bit codes into the 128B-swizzled K-major
+//   warps 6-21  (FWD/DX) expanders: turn the staged 2-bit codes into the 128B-swizzled K-major
 //               int8 / bf16 operand tile the tensor core reads.  The weights therefore cross
 //               HBM/L2 at 0.25 byte each and are never materialised wider than that off-chip.
 // For DW both operands are token-major in memory, i.e. MN-major for the tensor core: TMA lands
@@ -32,9 +32,10 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * 128;  // one stage of A: 128 rows x 128 bytes of K
 constexpr int B_BYTES = BN * 128;
 constexpr int P_BYTES = BN * 32;   // staged codes (FWD: 32 B per row; DX uses the first half)
-constexpr int NUM_EXPANDER_WARPS = 8;
+constexpr int NUM_EXPANDER_WARPS = 16;
 constexpr int TMEM_COLS = 512;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // ~2 s at B200 clocks
+constexpr uint32_t WAIT_HINT_NS = 20000;   // one hardware suspension
+constexpr int WAIT_LIMIT_TRIES = 100000;    // x 20 us = 2 s, then the kernel gives up
 
 enum Mode { FWD = 0, DX = 1, DW = 2 };
 
@@ -45,13 +46,24 @@ struct Params {
     const float* scales;     // FWD: per-token absmax
     const int32_t* rowsums;  // FWD: per-token sum of xq (offset-binary weights)
     int offset_binary;
+    int n_fast;              // tile order, see tile_coords()
     void* out;
     int out_dtype;
     long long ld_out;
     int32_t* acc_out;        // FWD: raw accumulators, pitch N, may be null
     float beta;
     int* status;
+    long long* trace;        // AB_GEMM_TRACE builds only: per-stage timestamps of CTA 0
 };
+
+#ifdef AB_GEMM_TRACE
+#define AB_TRACE(it, slot)                                                          \
+    do {                                                                            \
+        if (blockIdx.x == 0 && (it) < 128 && p.trace) p.trace[(it) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define AB_TRACE(it, slot)
+#endif
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -66,30 +78,29 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+// One try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes
+// or roughly `hint_ns` pass, so waiting warps do not compete for issue slots with working ones.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag) when the limit is hit or another
-// role already gave up.
+// Bounded wait: at most WAIT_LIMIT_TRIES suspensions of WAIT_HINT_NS each (~2 s).  Returns false
+// (and raises the CTA's abort flag) when the limit is hit or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+    for (int tries = 0; tries < WAIT_LIMIT_TRIES; ++tries) {
+        if (mbar_try(bar, parity, WAIT_HINT_NS)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = code;
-            return false;
-        }
     }
+    *abort_flag = code;
+    return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1) {
     asm volatile(
@@ -175,8 +186,24 @@ __device__ __forceinline__ void expand_bf16(uint32_t w, uint32_t* o /*[8]*/) {
 }
 
 // ------------------------------------------------------------------------------- kernel
+constexpr int kThreadsDW = 6 * 32;                             // producer, MMA, 4 epilogue warps
+constexpr int kThreadsExp = (6 + NUM_EXPANDER_WARPS) * 32;     // + expanders
+
+// Tile order.  The operand indexed by the FAST tile coordinate is touched in full by every wave
+// of CTAs (and so must live in L2); the other operand streams through once.  The host picks the
+// fast coordinate so that the re-read operand is the small one (always N for packed weights).
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0) {
+    if (p.n_fast) {
+        n0 = (tile % p.tiles_n) * BN;
+        m0 = (tile / p.tiles_n) * BM;
+    } else {
+        m0 = (tile % p.tiles_m) * BM;
+        n0 = (tile / p.tiles_m) * BN;
+    }
+}
+
 template <int MODE>
-__global__ void __launch_bounds__(MODE == DW ? 192 : 448, 1)
+__global__ void __launch_bounds__(MODE == DW ? kThreadsDW : kThreadsExp, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -220,7 +247,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_tiles = p.tiles_m * p.tiles_n;
-    constexpr int KB_ELEMS = MODE == FWD ? 128 : 64;  // K elements per stage
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -229,10 +255,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t phase = 0;
             constexpr uint32_t TX = MODE == FWD ? A_BYTES + BN * 32 : (MODE == DX ? A_BYTES + BN * 16 : A_BYTES + B_BYTES);
             bool ok = true;
+            int gi = 0;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                int m0, n0;
+                tile_coords(p, tile, m0, n0);
+                for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                     if (!(ok = mbar_wait(smem_u32(empty + stage), phase ^ 1, abort_flag, 1))) break;
+                    AB_TRACE(gi, 0);
                     const uint32_t bar = smem_u32(full_a + stage);
                     mbar_expect_tx(bar, TX);
                     if (MODE == FWD) {
@@ -260,9 +289,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             constexpr uint32_t idesc_dx = make_idesc(1, 1, 1, 0, 0), idesc_dw = make_idesc(1, 1, 1, 1, 1);
             const uint32_t idesc = MODE == FWD ? (p.offset_binary ? idesc_fwd_u8 : idesc_fwd_s8)
                                                : (MODE == DX ? idesc_dx : idesc_dw);
+            // Descriptors of stage 0, k-step 0; every other one differs only in the 14-bit start
+            // address field (16-byte units), which never carries: all tiles sit below 256 KB.
+            //   K-major  (FWD, DX): SBO = next 8 rows (1024 B); 32 bytes of K per MMA
+            //   MN-major (DW)     : LBO = next 64-feature block (8192 B), SBO = next 8 tokens (1024 B);
+            //                       16 tokens = 2048 B per MMA
+            const uint64_t da0 = MODE == DW ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
+            const uint64_t db0 = MODE == DW ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
+            constexpr uint64_t KSTEP = (MODE == DW ? 2048 : 32) >> 4;
             int stage = 0;
             uint32_t phase = 0;
-            int it = 0;
+            int it = 0, gi = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
                 const int acc = it & 1;
@@ -270,25 +307,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (!(ok = mbar_wait(smem_u32(tmem_empty + acc), acc_phase ^ 1, abort_flag, 2))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                     if (!(ok = mbar_wait(smem_u32(full_a + stage), phase, abort_flag, 3))) break;
+                    AB_TRACE(gi, 1);
                     if (MODE != DW)
                         if (!(ok = mbar_wait(smem_u32(full_b + stage), phase, abort_flag, 4))) break;
+                    AB_TRACE(gi, 2);
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(s_a + stage * A_BYTES), b_addr = smem_u32(s_b + stage * B_BYTES);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint64_t da, db;
-                        if (MODE == DW) {  // MN-major: LBO = next 64-feature block, SBO = next 8 tokens
-                            da = make_desc(a_addr + k * 2048, 8192, 1024);
-                            db = make_desc(b_addr + k * 2048, 8192, 1024);
-                        } else {           // K-major: SBO = next 8 rows, 32 bytes of K per MMA
-                            da = make_desc(a_addr + k * 32, 16, 1024);
-                            db = make_desc(b_addr + k * 32, 16, 1024);
-                        }
-                        umma<MODE>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-                    }
+                    const uint64_t da = da0 + (uint64_t)(stage * (A_BYTES >> 4));
+                    const uint64_t db = db0 + (uint64_t)(stage * (B_BYTES >> 4));
+                    umma<MODE>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
+                    umma<MODE>(d_tmem, da + KSTEP, db + KSTEP, idesc, 1u);
+                    umma<MODE>(d_tmem, da + 2 * KSTEP, db + 2 * KSTEP, idesc, 1u);
+                    umma<MODE>(d_tmem, da + 3 * KSTEP, db + 3 * KSTEP, idesc, 1u);
                     umma_commit(smem_u32(empty + stage));
+                    AB_TRACE(gi, 3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) umma_commit(smem_u32(tmem_full + acc));
@@ -301,7 +334,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         bool ok = true;
         const float gamma = MODE == DW ? 1.0f : *p.gamma;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
-            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            int m0, n0;
+            tile_coords(p, tile, m0, n0);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!(ok = mbar_wait(smem_u32(tmem_full + acc), acc_phase, abort_flag, 5))) break;
@@ -317,20 +351,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                __syncwarp();  // lanes that skipped the previous chunk's stores rejoin before the aligned load
+                uint32_t v[32];  // accumulators, converted in place to the f32 results
+                __syncwarp();    // lanes that skipped the previous chunk's stores rejoin before the aligned load
                 tmem_ld32(taddr + c * 32, v);
                 const int col0 = n0 + c * 32;
                 if (!row_ok || col0 >= p.N) continue;
                 const int ncols = p.N - col0 < 32 ? p.N - col0 : 32;
-                float f[32];
                 if (MODE == FWD) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        int a = (int)v[i] - row_sum;
-                        v[i] = (uint32_t)a;
-                        f[i] = __fmul_rn(__fmul_rn((float)a, row_scale), gamma);
-                    }
+                    for (int i = 0; i < 32; ++i) v[i] = (uint32_t)((int)v[i] - row_sum);
                     if (p.acc_out) {
                         int32_t* dst = p.acc_out + (long long)row * p.N + col0;
                         if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -343,12 +372,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                 if (i < ncols) dst[i] = (int32_t)v[i];
                         }
                     }
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float a = __uint_as_float(v[i]);
-                        f[i] = MODE == DX ? __fmul_rn(a, gamma) : a;
-                    }
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)(int)v[i], row_scale), gamma));
+                } else if (MODE == DX) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__fmul_rn(__uint_as_float(v[i]), gamma));
                 }
                 if (p.out_dtype == AB_F32) {
                     float* dst = reinterpret_cast<float*>(p.out) + (long long)row * p.ld_out + col0;
@@ -356,7 +385,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
-                            float4 o = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                            float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                   __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
                             if (p.beta != 0.0f) {
                                 float4 old = d4[q];
                                 o.x = __fadd_rn(o.x, old.x); o.y = __fadd_rn(o.y, old.y);
@@ -367,14 +397,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (i < ncols) dst[i] = p.beta != 0.0f ? __fadd_rn(f[i], dst[i]) : f[i];
+                            if (i < ncols)
+                                dst[i] = p.beta != 0.0f ? __fadd_rn(__uint_as_float(v[i]), dst[i]) : __uint_as_float(v[i]);
                     }
                 } else {
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ld_out + col0;
                     if (p.beta != 0.0f) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (i < ncols) f[i] = __fadd_rn(f[i], __bfloat162float(dst[i]));
+                            if (i < ncols) v[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), __bfloat162float(dst[i])));
                     }
                     if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                         uint4* d4 = reinterpret_cast<uint4*>(dst);
@@ -383,7 +414,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             uint32_t h[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(f[8 * q + 2 * j], f[8 * q + 2 * j + 1]);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * j]),
+                                                                          __uint_as_float(v[8 * q + 2 * j + 1]));
                                 h[j] = *reinterpret_cast<uint32_t*>(&b2);
                             }
                             d4[q] = make_uint4(h[0], h[1], h[2], h[3]);
@@ -391,7 +423,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (i < ncols) dst[i] = __float2bfloat16_rn(f[i]);
+                            if (i < ncols) dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
                     }
                 }
             }
@@ -401,36 +433,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (MODE != DW) {
         // --------------------------------------------------------------------- expanders
-        const int r = (warp - 6) * 32 + lane;  // row of the B tile owned by this thread
+        // Two threads per row of the B tile: thread e owns row e/2, K-half e%2 (four 16-byte chunks).
+        const int e = (warp - 6) * 32 + lane;
+        const int r = e >> 1, half = e & 1;
+        const int sw = r & 7;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        int gi = 0;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            for (int kb = 0; kb < p.num_kb; ++kb) {
+            for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                 if (!(ok = mbar_wait(smem_u32(full_a + stage), phase, abort_flag, 6))) break;
+                if (threadIdx.x == 6 * 32) AB_TRACE(gi, 4);
                 uint8_t* brow = s_b + stage * B_BYTES + r * 128;
-                const int sw = r & 7;
                 if (MODE == FWD) {
-                    const uint4* src = reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + r * 32);
-                    uint4 lo = src[0], hi = src[1];
-                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(brow + ((c ^ sw) << 4)) = expand_i8(w[c], p.offset_binary);
-                } else {
-                    uint4 pk = *reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + r * 16);
+                    const uint4 pk = *reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + e * 16);
                     const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-                    for (int wi = 0; wi < 4; ++wi) {
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4*>(brow + (((half * 4 + c) ^ sw) << 4)) = expand_i8(w[c], p.offset_binary);
+                } else {
+                    const uint2 pk = *reinterpret_cast<const uint2*>(s_p + stage * P_BYTES + e * 8);
+                    const uint32_t w[2] = {pk.x, pk.y};
+#pragma unroll
+                    for (int wi = 0; wi < 2; ++wi) {
                         uint32_t o[8];
                         expand_bf16(w[wi], o);
-                        *reinterpret_cast<uint4*>(brow + (((2 * wi) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                        *reinterpret_cast<uint4*>(brow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                        *reinterpret_cast<uint4*>(brow + (((half * 4 + 2 * wi) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(brow + (((half * 4 + 2 * wi + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
                     }
                 }
+                if (threadIdx.x == 6 * 32) AB_TRACE(gi, 5);
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(full_b + stage));
+                if (threadIdx.x == 6 * 32) AB_TRACE(gi, 6);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
@@ -446,6 +483,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------- peak probe
+// Issues `iters` x 4 MMAs of the production shape (128x256, 32 bytes of K each) per CTA on
+// zero-filled shared-memory tiles, with no loads and no epilogue: the time of this kernel is the
+// tensor pipe's own ceiling for that instruction kind at the clocks the GPU actually holds.
+template <int MODE>
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + A_BYTES + B_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    for (int i = threadIdx.x; i < (A_BYTES + B_BYTES) / 16; i += blockDim.x)
+        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(bar), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_async_smem();
+    if ((threadIdx.x >> 5) == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {
+        constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0) : make_idesc(1, 1, 1, 0, 0);
+        const uint32_t a_addr = smem_u32(smem), b_addr = smem_u32(smem + A_BYTES);
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma<MODE>(tmem_base, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc,
+                           (it | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(bar));
+        mbar_wait(smem_u32(bar), 0, abort_flag, 9);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(status, 0, 100 + *abort_flag);
+    if ((threadIdx.x >> 5) == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
     }
 }
 
@@ -500,14 +585,32 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     constexpr int KB = MODE == FWD ? 128 : 64;
     p.num_kb = (p.K + KB - 1) / KB;
     p.status = ctx->dev_status;
+#ifdef AB_GEMM_TRACE
+    p.trace = reinterpret_cast<long long*>(ctx->stage[5]);  // trace builds: the caller sized stage 5
+#endif
     long long tiles = (long long)p.tiles_m * p.tiles_n;
     int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    gemm_kernel<MODE><<<grid, MODE == DW ? 192 : 448, smem, ctx->stream>>>(ta, tb, p);
+    gemm_kernel<MODE><<<grid, MODE == DW ? kThreadsDW : kThreadsExp, smem, ctx->stream>>>(ta, tb, p);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }
 
 }  // namespace tc
+
+int abk_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
+    constexpr size_t smem = 1024 + tc::A_BYTES + tc::B_BYTES + 64;
+    if (kind_i8) {
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc::mma_peak_kernel<tc::FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tc::mma_peak_kernel<tc::FWD><<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
+    } else {
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc::mma_peak_kernel<tc::DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tc::mma_peak_kernel<tc::DX><<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
+    }
+    AB_LAUNCH_CHECK(ctx);
+    // operations issued by the launch: 2 * M * N * K per MMA, 4 MMAs per iteration, one CTA per SM
+    *ops_out = 2.0 * tc::BM * tc::BN * (kind_i8 ? 32.0 : 16.0) * 4.0 * (double)iters * ctx->sm_count;
+    return AB_OK;
+}
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -527,6 +630,7 @@ int abk_gemm_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_x
     p.M = (int)m; p.N = (int)w->out; p.K = (int)w->in;
     p.gamma = w->gamma_dev; p.scales = scales; p.rowsums = rowsums; p.offset_binary = ctx->fwd_offset_binary;
     p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.acc_out = acc_out; p.beta = 0.0f;
+    p.n_fast = 1;  // the packed weights are the small operand
     return tc::launch<tc::FWD>(ctx, ta, tb, p);
 }
 
@@ -545,6 +649,7 @@ int abk_gemm_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, 
     tc::Params p{};
     p.M = (int)m; p.N = (int)w->in; p.K = (int)w->out;
     p.gamma = w->gamma_dev; p.out = dx; p.out_dtype = dx_dtype; p.ld_out = (long long)ld_dx; p.beta = beta;
+    p.n_fast = 1;
     return tc::launch<tc::DX>(ctx, ta, tb, p);
 }
 
@@ -563,5 +668,6 @@ int abk_gemm_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t
     tc::Params p{};
     p.M = (int)out; p.N = (int)in; p.K = (int)m;
     p.out = dW; p.out_dtype = AB_F32; p.ld_out = (long long)ld_dw; p.beta = beta;
+    p.n_fast = in <= out ? 1 : 0;  // re-read the smaller of x and dy
     return tc::launch<tc::DW>(ctx, ta, tb, p);
 }

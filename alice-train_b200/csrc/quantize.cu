@@ -227,6 +227,124 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
     }
 }
 
+// Fast path of pass B (rows that are multiples of 16 elements, 16-byte aligned tensors): every
+// lane loads ONE float4 so that a warp reads 512 contiguous bytes per instruction, four loads
+// in flight per lane; the four lanes that share a 16-element group merge their 2-bit fields
+// with two shuffles and one of them stores the canonical word, another the forward-operand
+// word.  Chunks are walked from the end of the tensor (see above).
+template <bool WANT_FQ, bool WANT_STATS>
+__global__ void __launch_bounds__(kThreads)
+quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per_row, int dense_rows,
+                         uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, float* fq_out,
+                         ab_fq_dev_report* __restrict__ rep, int offset_binary) {
+    const int lane = threadIdx.x & 31, sub = lane & 3;
+    const size_t total_warps = (size_t)gridDim.x * (kThreads / 32);
+    const size_t warp_global = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const size_t nchunks = (n4 + 31) / 32;
+    const float gamma = rep->gamma, inv = rep->inv_gamma;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4* q4 = reinterpret_cast<float4*>(fq_out);
+    unsigned int n_plus = 0, n_minus = 0, n_thr = 0;
+    double s_err = 0, s_wq = 0, s_ww = 0, s_qq = 0;
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    constexpr int U = 4;
+    for (size_t c0 = warp_global; c0 < nchunks; c0 += U * total_warps) {
+        float4 v[U];
+        size_t g[U];
+        bool act[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            size_t c = c0 + (size_t)u * total_warps;
+            g[u] = c < nchunks ? (nchunks - 1 - c) * 32 + lane : n4;
+            act[u] = g[u] < n4;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (act[u]) v[u] = WANT_FQ ? w4[g[u]] : __ldg(w4 + g[u]);  // fq_out may alias w
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c0 + (size_t)u * total_warps >= nchunks) break;  // warp-uniform
+            const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            float qv[4];
+            uint32_t cpart = 0, fpart = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float scaled = __fmul_rn(x[i], inv);
+                float r = roundf(scaled);
+                r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
+                int cc = (r != r) ? 0 : (int)r;
+                uint32_t canon = cc > 0 ? 1u : (cc < 0 ? 2u : 0u);
+                uint32_t fenc = offset_binary ? (uint32_t)(cc + 1) : (cc > 0 ? 1u : (cc < 0 ? 3u : 0u));
+                if (!act[u]) { canon = 0; fenc = 0; }
+                cpart |= canon << (8 * sub + 2 * i);   // element e = 4*sub + i sits at bit 2e
+                fpart |= fenc << (8 * i + 2 * sub);    // and at bit 8*(e%4) + 2*(e/4) in the operand copy
+                qv[i] = __fmul_rn(r, gamma);
+                if (act[u]) {
+                    n_plus += cc > 0;
+                    n_minus += cc < 0;
+                    float a = fabsf(scaled);
+                    n_thr += (a >= 0.49999997f && a <= 0.50000006f);
+                    if (WANT_STATS) {
+                        double wd = (double)x[i], qd = (double)qv[i];
+                        s_err += fabs(wd - qd);
+                        s_wq += wd * qd;
+                        s_ww += wd * wd;
+                        s_qq += qd * qd;
+                        vmin = fminf(vmin, x[i]);
+                        vmax = fmaxf(vmax, x[i]);
+                    }
+                }
+            }
+            cpart |= __shfl_xor_sync(0xffffffffu, cpart, 1);
+            fpart |= __shfl_xor_sync(0xffffffffu, fpart, 1);
+            cpart |= __shfl_xor_sync(0xffffffffu, cpart, 2);
+            fpart |= __shfl_xor_sync(0xffffffffu, fpart, 2);
+            if (act[u]) {
+                size_t grp = g[u] >> 2, word;
+                if (dense_rows) {
+                    word = grp;
+                } else {
+                    size_t row = g[u] / in4, col4 = g[u] - row * in4;
+                    word = row * words_per_row + (col4 >> 2);
+                }
+                if (sub == 0) codes[word] = cpart;
+                if (sub == 1 && codes_fwd) codes_fwd[word] = fpart;
+                if (WANT_FQ) q4[g[u]] = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            }
+        }
+    }
+    __shared__ unsigned int sc[3];
+    __shared__ double sd[32];
+    if (threadIdx.x < 3) sc[threadIdx.x] = 0;
+    __syncthreads();
+    n_plus = __reduce_add_sync(0xffffffffu, n_plus);
+    n_minus = __reduce_add_sync(0xffffffffu, n_minus);
+    n_thr = __reduce_add_sync(0xffffffffu, n_thr);
+    if (lane == 0) {
+        atomicAdd(&sc[0], n_plus);
+        atomicAdd(&sc[1], n_minus);
+        atomicAdd(&sc[2], n_thr);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (sc[0]) atomicAdd(&rep->n_plus, (unsigned long long)sc[0]);
+        if (sc[1]) atomicAdd(&rep->n_minus, (unsigned long long)sc[1]);
+        if (sc[2]) atomicAdd(&rep->n_threshold, (unsigned long long)sc[2]);
+    }
+    if (WANT_STATS) {
+        double b;
+        b = block_sum(s_err, sd); if (threadIdx.x == 0) atomicAdd(&rep->sum_err, b);
+        b = block_sum(s_wq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_wq, b);
+        b = block_sum(s_ww, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_ww, b);
+        b = block_sum(s_qq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_qq, b);
+        unsigned int kmin = __reduce_min_sync(0xffffffffu, float_key(vmin));
+        unsigned int kmax = __reduce_max_sync(0xffffffffu, float_key(vmax));
+        if (lane == 0) {
+            atomicMin(reinterpret_cast<unsigned int*>(&rep->w_min), kmin);
+            atomicMax(reinterpret_cast<unsigned int*>(&rep->w_max), kmax);
+        }
+    }
+}
+
 // --------------------------------------------------------- operand copies from canonical
 __global__ void __launch_bounds__(kThreads)
 repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, size_t words,
@@ -244,26 +362,47 @@ repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ cod
     codes_fwd[wi] = f;
 }
 
-// codes_t[i][jg] gathers column i of 16 consecutive rows j = 16*jg + e.  A warp covers 32
-// consecutive output words of one input feature (coalesced 128-byte stores); the strided
-// byte reads are served from L1/L2 because neighbouring blocks share the same sectors.
+// codes_t[i][jg] gathers column i of the 16 rows j = 16*jg + e.  A block transposes a tile of
+// 128 rows x 128 columns through shared memory: 32-byte row segments in (coalesced), 32-byte
+// segments of the transposed rows out (coalesced), the 2-bit shuffle in between.
+constexpr int kTT = 128;
 __global__ void __launch_bounds__(kThreads)
 transpose_codes_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
                        uint32_t* __restrict__ codes_t, size_t twords_per_row) {
-    size_t jg = (size_t)blockIdx.x * 32 + (threadIdx.x & 31);
-    size_t i = (size_t)blockIdx.y * (kThreads / 32) + (threadIdx.x >> 5);
-    if (i >= in || jg >= twords_per_row) return;
-    uint32_t t = 0;
-    const uint8_t* col = codes + (i >> 2);
-    int sh = 2 * (int)(i & 3);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-        size_t j = jg * 16 + e;
-        uint32_t c = j < out ? ((uint32_t)col[j * pitch] >> sh) & 3u : 0u;
-        if (c == 3u) c = 0u;
-        t |= c << ab_perm_bit(e);
+    __shared__ uint4 s_in[kTT][2];        // [row j][32 bytes = 128 columns]
+    __shared__ uint32_t s_out[kTT][9];    // [column i][8 words = 128 rows], padded against bank conflicts
+    const size_t i0 = (size_t)blockIdx.x * kTT, j0 = (size_t)blockIdx.y * kTT;
+    const int t = threadIdx.x;
+    {
+        const size_t row = j0 + (t >> 1);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < out) v = __ldg(reinterpret_cast<const uint4*>(codes + row * pitch + i0 / 4) + (t & 1));
+        s_in[t >> 1][t & 1] = v;
     }
-    codes_t[i * twords_per_row + jg] = t;
+    __syncthreads();
+    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&s_in[0][0]);
+    const int il = t & (kTT - 1), sh = 2 * (il & 3);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int jgl = (t >> 7) + 2 * k;  // word of 16 rows inside the tile
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            uint32_t c = ((uint32_t)sb[(jgl * 16 + e) * 32 + (il >> 2)] >> sh) & 3u;
+            if (c == 3u) c = 0u;
+            word |= c << ab_perm_bit(e);
+        }
+        s_out[il][jgl] = word;
+    }
+    __syncthreads();
+    {
+        const size_t i = i0 + (t >> 1);
+        const int h = (t & 1) * 4;
+        if (i < in) {
+            uint4 v = make_uint4(s_out[t >> 1][h], s_out[t >> 1][h + 1], s_out[t >> 1][h + 2], s_out[t >> 1][h + 3]);
+            *reinterpret_cast<uint4*>(codes_t + i * twords_per_row + j0 / 16 + h) = v;
+        }
+    }
 }
 
 // ------------------------------------------------------------------ boundary conversions
@@ -470,22 +609,40 @@ int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float
     const size_t wpr = w->pitch / 4;
     const size_t words = w->out * wpr;
     if (words) {
-        unsigned int grid = grid_for(words, kThreads);
         uint32_t* c = reinterpret_cast<uint32_t*>(w->codes);
         uint32_t* f = reinterpret_cast<uint32_t*>(w->codes_fwd);
         const int ob = ctx->fwd_offset_binary;
-        if (fq_out && want_stats)
-            quantize_pack_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
-        else if (fq_out)
-            quantize_pack_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
-        else if (want_stats)
-            quantize_pack_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
-        else
-            quantize_pack_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+        const bool vec = (w->in % 16 == 0) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
+                         (!fq_out || (reinterpret_cast<uintptr_t>(fq_out) & 15) == 0);
+        if (vec) {
+            const size_t n4 = n / 4, in4 = w->in / 4;
+            const int dense = (wpr == w->in / 16) ? 1 : 0;
+            size_t chunks = (n4 + 31) / 32;
+            size_t want = (chunks + (kThreads / 32) * 4 - 1) / ((kThreads / 32) * 4);
+            unsigned int grid = (unsigned int)(want < (size_t)ctx->sm_count * 8 ? (want ? want : 1) : (size_t)ctx->sm_count * 8);
+            if (fq_out && want_stats)
+                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev, ob);
+            else if (fq_out)
+                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev, ob);
+            else if (want_stats)
+                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev, ob);
+            else
+                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev, ob);
+        } else {
+            unsigned int grid = grid_for(words, kThreads);
+            if (fq_out && want_stats)
+                quantize_pack_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+            else if (fq_out)
+                quantize_pack_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+            else if (want_stats)
+                quantize_pack_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+            else
+                quantize_pack_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+        }
         AB_LAUNCH_CHECK(ctx);
         if (w->codes_t) {
             const size_t twpr = w->tpitch / 4;
-            dim3 tg(grid_for(twpr, 32), grid_for(w->in, kThreads / 32));
+            dim3 tg(grid_for(w->in, kTT), grid_for(w->out, kTT));
             transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
                                                                     reinterpret_cast<uint32_t*>(w->codes_t), twpr);
             AB_LAUNCH_CHECK(ctx);
@@ -504,7 +661,7 @@ int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w) {
         ctx->fwd_offset_binary);
     AB_LAUNCH_CHECK(ctx);
     const size_t twpr = w->tpitch / 4;
-    dim3 tg(grid_for(twpr, 32), grid_for(w->in, kThreads / 32));
+    dim3 tg(grid_for(w->in, kTT), grid_for(w->out, kTT));
     transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
                                                             reinterpret_cast<uint32_t*>(w->codes_t), twpr);
     AB_LAUNCH_CHECK(ctx);

@@ -66,7 +66,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu), "-f", self.path],
+                                          "-lms", "50", "-i", str(self.gpu), "-f", self.path],
                                          stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -265,16 +265,32 @@ def run_native(args):
         per[c]["tops_avg"] = ops_per_launch / (per[c]["ms_avg"] * 1e-3) / 1e12 if per[c]["ms_avg"] > 0 else None
     aq_bytes = sum(tokens * i * 3 + tokens * 8 for _, _, i in projs) / len(projs)
     per["act_quant"]["gbs_avg"] = aq_bytes / (per["act_quant"]["ms_avg"] * 1e-3) / 1e9 if per["act_quant"]["ms_avg"] > 0 else None
+    # tensor-pipe ceilings at the clocks this GPU holds: MMA-only kernels of the production tile shape
+    probe = {}
+    for kind, key in ((1, "int8_tops"), (0, "bf16_tflops")):
+        ops = C.c_double(0.0)
+        best = None
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _ffi.check(_ffi.load().ab_tensor_peak_probe(ctx.handle, kind, 4000, C.byref(ops)), ctx.handle)
+            b.record()
+            torch.cuda.synchronize()
+            t = a.elapsed_time(b)
+            best = t if best is None else min(best, t)
+        probe[key] = ops.value / (best * 1e-3) / 1e12
+    ctx.sync()
     dom = max(("fwd", "dx", "dw"), key=lambda c: per[c]["ms_total"])
-    # denominators: measured bf16 dense throughput for the bf16 kernels; the int8 pipe is twice as
-    # wide and has no measured entry, so 2x the measured bf16 figure is used and said so
+    # denominators: the measured cuBLAS bf16 figure for the bf16 kernels; the peaks file has no int8
+    # entry, so the int8 kernel is set against the MMA-only probe measured just above
     peak_bf16 = pk["bf16_tflops_sustained"]
-    peak = peak_bf16 * (2.0 if dom == "fwd" else 1.0)
+    peak = probe["int8_tops"] if dom == "fwd" else peak_bf16
     roofline = {"bound": "tensor", "kernel": {"fwd": "gemm_kernel<FWD> int8 x ternary", "dx": "gemm_kernel<DX> bf16 x ternary",
                                               "dw": "gemm_kernel<DW> bf16 x bf16"}[dom],
                 "achieved": per[dom]["tops_avg"], "peak": peak, "unit": "TFLOP/s",
                 "frac": per[dom]["tops_avg"] / peak if per[dom]["tops_avg"] else None, "traffic": None,
-                "peak_source": f"{pk['source']} bf16 sustained {peak_bf16} TFLOP/s" + (" x2 for the int8 pipe" if dom == "fwd" else ""),
+                "peak_source": ("int8 MMA-only probe (ab_tensor_peak_probe) in this run" if dom == "fwd"
+                                else f"{pk['source']} bf16 sustained {peak_bf16} TFLOP/s"),
                 "algorithmic_ops_per_launch": ops_per_launch}
 
     value = world * tokens * args.steps / (ms_total * 1e-3)
@@ -333,7 +349,10 @@ def run_native(args):
                                ("; NCCL all-reduce of dW overlapped" if world > 1 else ""),
                        "l2": "working set per step exceeds the 126 MB L2 (dW alone is 3 x 235 MB); no explicit flush"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
-            "clocks": clocks, "kernels": per,
+            "clocks": clocks, "kernels": per, "tensor_pipe_probe": probe,
+            "fractions": {"fwd_of_int8_probe": per["fwd"]["tops_avg"] / probe["int8_tops"],
+                          "dx_of_bf16_measured": per["dx"]["tops_avg"] / peak_bf16,
+                          "dw_of_bf16_measured": per["dw"]["tops_avg"] / peak_bf16},
             "tops_total": 6.0 * tokens * sum(o * i for _, o, i in projs) * args.steps / (ms_total * 1e-3) / 1e12,
         }
         print(json.dumps(line), flush=True)
@@ -345,7 +364,7 @@ def run_native(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS))

@@ -236,6 +236,14 @@ AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* 
                                   const void* dy_bf16_host, size_t m, void* y_bf16_host,
                                   void* dx_bf16_host, float* dW_dev);
 
+/* Measurement aid (no counterpart in the reference): launches, on the context's stream, a kernel
+ * that only issues tensor-core instructions of the production tile shape (no loads, no
+ * epilogue) — `iters` x 4 MMAs per SM, int8 (kind_i8 != 0) or bf16.  *ops_out receives the
+ * number of operations the launch performs; time it with events to obtain the tensor pipe's
+ * ceiling for that kind at the clocks the device holds, the denominator the benchmark's
+ * int8 roofline uses. */
+AB_API int ab_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out);
+
 #ifdef __cplusplus
 }
 #endif
