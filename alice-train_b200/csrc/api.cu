@@ -105,8 +105,6 @@ int ab_ctx_create(int device, void* cuda_stream, ab_ctx** out) {
         }
         if (cudaMalloc(&ctx->dev_status, 256) != cudaSuccess) { st = AB_ERR_CUDA; break; }
         if (cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) { st = AB_ERR_CUDA; break; }
-        const char* e = getenv("ALICE_B200_FWD_SIGNED");
-        ctx->fwd_offset_binary = (e && e[0] == '1') ? 0 : 1;
     } while (0);
     if (st != AB_OK) {
         cudaGetLastError();

@@ -22,10 +22,10 @@
 //                                 within each group of 16 elements, element e sits at bit
 //                                 8*(e%4) + 2*(e/4) so that `(word >> 2q) & 0x03030303` yields
 //                                 the four int8 lanes of output word q.  Encoding is offset
-//                                 binary (w+1 in {0,1,2}; the int8 MMA then takes B as
-//                                 unsigned and the epilogue subtracts the per-token sum of
-//                                 xq) or two's complement (01=+1, 11=-1, 00=0; signed B),
-//                                 per ab_ctx::fwd_offset_binary.
+//                                 binary, w+1 in {0,1,2}: the int8 MMA takes B as unsigned
+//                                 and the epilogue subtracts the per-token sum of xq, which
+//                                 keeps the s32 result exact and the expansion one shift and
+//                                 one mask per four weights.
 //   codes_t   [in][tpitch]        the TRANSPOSE (row = input feature, column = output
 //                                 feature) for dx = dy.W, canonical encoding, same in-group
 //                                 permutation.  tpitch = round_up(out,128)/4 bytes.
@@ -49,7 +49,6 @@ struct ab_ctx {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint64_t launches = 0;
-    int fwd_offset_binary = 1;  // encoding of codes_fwd, fixed for the life of the context
     std::string last_error;
 };
 

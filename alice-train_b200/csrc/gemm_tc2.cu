@@ -1,0 +1,560 @@
+// Batched BitLinear products on CTA PAIRS (tcgen05 cta_group::2): one MMA instruction spans two
+// SMs and a 256x256 output tile; each CTA of the pair stages its own 128 rows of A and its own
+// half (128 rows) of B, so per SM the shared-memory traffic of a k-step is two thirds of the
+// single-CTA 128x256 tile and the weight expansion per SM is halved.
+//
+//   FWD  y  = (xq . Wc^T) * s_t/127 * gamma     int8 x ternary (unsigned w+1), s32 in TMEM
+//   DX   dx = gamma * dy . Wc                   bf16 x ternary, f32 in TMEM
+//   DW   dW = dy^T . x                          bf16 x bf16 (both MN-major), f32 in TMEM
+//
+// A cluster of two CTAs walks 256x256 tiles persistently.  Per CTA:
+//   warp 0   TMA producer.  A (and for DW the B half) is loaded with the cta_group::2 form so
+//            that its bytes are counted on the LEADER's barrier; the 2-bit codes go to a local
+//            barrier for this CTA's expanders.
+//   warp 1   leader CTA only: one lane issues tcgen05.mma.cta_group::2 and commits (multicast to
+//            both CTAs' barriers).  Both CTAs: TMEM allocation (512 columns = two accumulators).
+//   warps 2-5 epilogue of this CTA's 128 rows: tcgen05.ld, scale, store.
+//   expander warps (FWD/DX): 2-bit codes -> 128B-swizzled K-major operand rows of this CTA's B
+//            half; they sit on warp slots that do not share a scheduler with the MMA warp.
+// Barriers that gate the MMA (operands ready, accumulator drained) live in the leader and are
+// arrived on remotely by the peer; barriers released by the MMA live in both CTAs.
+// Every wait is bounded; a wait that runs out raises the CTA's abort flag, which ends every
+// role's loop, and both CTAs still meet at the final cluster barrier before freeing TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace tc2 {
+
+using namespace tc;
+
+constexpr int BM = 256;            // tile rows of the pair (128 per CTA)
+constexpr int BN = 256;            // tile columns (each CTA stages 128 rows of B)
+constexpr int A_BYTES = 128 * 128; // per CTA, per stage
+constexpr int B_BYTES = 128 * 128;
+constexpr int P_BYTES = 128 * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_EXP_WARPS = 8;
+constexpr int kWarpsDW = 6;
+constexpr int kWarpsExp = 16;      // ids 0..15; 9 and 13 stay idle (they share the MMA warp's scheduler)
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's leader
+
+template <int MODE> struct Cfg { static constexpr int STAGES = MODE == DW ? 7 : 6; };
+
+struct Params {
+    int M, N, K;
+    int tiles_m, tiles_n, num_kb;
+    const float* gamma;
+    const float* scales;
+    const int32_t* rowsums;
+    int n_fast;
+    void* out;
+    int out_dtype;
+    long long ld_out;
+    int32_t* acc_out;
+    float beta;
+    int* status;
+    long long* trace;
+};
+
+#ifdef AB_GEMM_TRACE
+#define AB_TRACE2(it, slot)                                                         \
+    do {                                                                            \
+        if (blockIdx.x == 0 && (it) < 128 && p.trace) p.trace[(it) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define AB_TRACE2(it, slot)
+#endif
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on a barrier that may live in the other CTA of the pair
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    // default semantics (release at CTA scope): what was written before it is consumed by this
+    // CTA's own tensor core, after the proxy fence; a cluster-scope release costs ~1000 cycles
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// raise the pending byte count of a barrier without arriving on it
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// The MMA thread's wait: no suspend hint (it is the critical path).  Bounded like every other wait.
+__device__ __forceinline__ bool mbar_wait_mma(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+#pragma unroll 1
+    for (int tries = 0; tries < 20000000; ++tries) {
+        if (mbar_try_cluster(bar, parity)) return true;
+        if ((tries & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = code;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t leader_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((unsigned short)3)
+        : "memory");
+}
+template <int MODE>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    if (MODE == FWD) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    }
+}
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0) {
+    if (p.n_fast) {
+        n0 = (tile % p.tiles_n) * BN;
+        m0 = (tile / p.tiles_n) * BM;
+    } else {
+        m0 = (tile % p.tiles_m) * BM;
+        n0 = (tile / p.tiles_m) * BN;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__((MODE == DW ? kWarpsDW : kWarpsExp) * 32, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
+    constexpr int STAGES = Cfg<MODE>::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_a = smem;
+    uint8_t* s_b = s_a + STAGES * A_BYTES;
+    uint8_t* s_p = s_b + STAGES * B_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + (MODE == DW ? 0 : STAGES * P_BYTES));
+    // LEADER: "operands of the stage are ready in both CTAs".  FWD/DX: 16 expander-warp arrivals
+    // (B halves written) plus the bytes of both A tiles; DW: one arrival plus the bytes of both
+    // CTAs' A and B boxes.  One barrier, so the MMA thread waits once per stage.
+    uint64_t* full = bars;
+    uint64_t* unused_slot = bars + STAGES;    // (keeps the layout of the barrier block fixed)
+    uint64_t* full_p = bars + 2 * STAGES;     // local : this CTA's codes landed
+    uint64_t* empty = bars + 3 * STAGES;      // local : MMAs reading the stage retired (multicast commit)
+    uint64_t* tmem_full = bars + 4 * STAGES;  // local : accumulator complete (multicast commit)
+    uint64_t* tmem_empty = tmem_full + 2;     // LEADER: both CTAs' epilogues drained the accumulator
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(full + s), MODE == DW ? 1 : 2 * NUM_EXP_WARPS);
+            mbar_init(smem_u32(unused_slot + s), 1);
+            mbar_init(smem_u32(full_p + s), 1);
+            mbar_init(smem_u32(empty + s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(tmem_full + a), 1);
+            mbar_init(smem_u32(tmem_empty + a), 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            // bytes counted on the leader's barrier per stage: both CTAs' A tiles (+ DW: both B halves)
+            constexpr uint32_t TX_LEADER = MODE == DW ? 2 * (A_BYTES + B_BYTES) : 2 * A_BYTES;
+            constexpr uint32_t TX_P = MODE == FWD ? 128 * 32 : 128 * 16;
+            bool ok = true;
+            int gi = 0;
+            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+                int m0, n0;
+                tile_coords(p, tile, m0, n0);
+                m0 += 128 * (int)rank;  // this CTA's rows of A
+                n0 += 128 * (int)rank;  // and its half of B
+                for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
+                    if (!(ok = mbar_wait(smem_u32(empty + stage), phase ^ 1, abort_flag, 1))) break;
+                    AB_TRACE2(gi, 0);
+                    const uint32_t lbar = smem_u32(full + stage) & PEER_MASK;
+                    // The leader announces the bytes BEFORE it issues its own loads: its expanders
+                    // (FWD/DX) can only arrive after its codes landed, so the phase cannot complete
+                    // on arrivals alone while the byte count is still unannounced.
+                    if (rank == 0) {
+                        if (MODE == DW) mbar_expect_tx(smem_u32(full + stage), TX_LEADER);
+                        else mbar_expect_tx_only(smem_u32(full + stage), TX_LEADER);
+                    }
+                    if (MODE == FWD) {
+                        mbar_expect_tx(smem_u32(full_p + stage), TX_P);
+                        tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 32, n0);
+                        tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 128, m0);
+                    } else if (MODE == DX) {
+                        mbar_expect_tx(smem_u32(full_p + stage), TX_P);
+                        tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 16, n0);
+                        tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < 2; ++b)
+                            tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES + b * 8192), &tm_a, lbar, m0 + 64 * b, kb * 64);
+#pragma unroll
+                        for (int b = 0; b < 2; ++b)
+                            tma_load_2d_pair(smem_u32(s_b + stage * B_BYTES + b * 8192), &tm_b, lbar, n0 + 64 * b, kb * 64);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN)
+                                                   : (MODE == DX ? make_idesc(1, 1, 1, 0, 0, BM, BN)
+                                                                 : make_idesc(1, 1, 1, 1, 1, BM, BN));
+            const uint64_t da0 = MODE == DW ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
+            const uint64_t db0 = MODE == DW ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
+            constexpr uint64_t KSTEP = (MODE == DW ? 2048 : 32) >> 4;
+            // Flat loop over (tile, k-block) with the NEXT stage's barrier polled before this stage's
+            // MMAs are issued: the poll's shared-memory round trip (slow while the tensor core and
+            // TMA saturate shared memory) overlaps the issue instead of preceding it.
+            const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+            const long long total = (long long)my_tiles * p.num_kb;
+            int stage = 0, kb = 0, it = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            bool ready = total > 0 ? mbar_try_cluster(smem_u32(full + stage), phase) : false;
+            uint32_t d_tmem = tmem_base;
+            for (long long gi = 0; ok && gi < total; ++gi) {
+                if (kb == 0) {
+                    const int acc = it & 1;
+                    if (!(ok = mbar_wait_mma(smem_u32(tmem_empty + acc), ((it >> 1) & 1) ^ 1, abort_flag, 2))) break;
+                    d_tmem = tmem_base + acc * BN;
+                }
+                if (!ready)
+                    if (!(ok = mbar_wait_mma(smem_u32(full + stage), phase, abort_flag, 3))) break;
+                AB_TRACE2(gi, 2);
+                tc_fence_after();
+                const uint64_t da = da0 + (uint64_t)(stage * (A_BYTES >> 4));
+                const uint64_t db = db0 + (uint64_t)(stage * (B_BYTES >> 4));
+                const uint32_t cur_empty = smem_u32(empty + stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                ready = gi + 1 < total ? mbar_try_cluster(smem_u32(full + stage), phase) : false;
+                AB_TRACE2(gi, 1);
+                umma_pair<MODE>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
+                umma_pair<MODE>(d_tmem, da + KSTEP, db + KSTEP, idesc, 1u);
+                umma_pair<MODE>(d_tmem, da + 2 * KSTEP, db + 2 * KSTEP, idesc, 1u);
+                umma_pair<MODE>(d_tmem, da + 3 * KSTEP, db + 3 * KSTEP, idesc, 1u);
+                AB_TRACE2(gi, 7);
+                umma_commit_pair(cur_empty);
+                AB_TRACE2(gi, 3);
+                if (++kb == p.num_kb) {
+                    umma_commit_pair(smem_u32(tmem_full + (it & 1)));
+                    kb = 0;
+                    ++it;
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------------- epilogue
+        const int quad = warp & 3;
+        int it = 0;
+        bool ok = true;
+        const float gamma = MODE == DW ? 1.0f : *p.gamma;
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++it) {
+            int m0, n0;
+            tile_coords(p, tile, m0, n0);
+            m0 += 128 * (int)rank;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!(ok = mbar_wait(smem_u32(tmem_full + acc), acc_phase, abort_flag, 5))) break;
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const bool row_ok = row < p.M;
+            float row_scale = 0.0f;
+            int row_sum = 0;
+            if (MODE == FWD && row_ok) {
+                row_scale = __fdiv_rn(p.scales[row], 127.0f);
+                row_sum = p.rowsums[row];
+            }
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                __syncwarp();
+                tmem_ld32(taddr + c * 32, v);
+                const int col0 = n0 + c * 32;
+                if (!row_ok || col0 >= p.N) continue;
+                const int ncols = p.N - col0 < 32 ? p.N - col0 : 32;
+                if (MODE == FWD) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = (uint32_t)((int)v[i] - row_sum);
+                    if (p.acc_out) {
+                        int32_t* dst = p.acc_out + (long long)row * p.N + col0;
+                        if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < ncols) dst[i] = (int32_t)v[i];
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)(int)v[i], row_scale), gamma));
+                } else if (MODE == DX) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__fmul_rn(__uint_as_float(v[i]), gamma));
+                }
+                if (p.out_dtype == AB_F32) {
+                    float* dst = reinterpret_cast<float*>(p.out) + (long long)row * p.ld_out + col0;
+                    if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                   __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                            if (p.beta != 0.0f) {
+                                float4 old = d4[q];
+                                o.x = __fadd_rn(o.x, old.x); o.y = __fadd_rn(o.y, old.y);
+                                o.z = __fadd_rn(o.z, old.z); o.w = __fadd_rn(o.w, old.w);
+                            }
+                            d4[q] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < ncols)
+                                dst[i] = p.beta != 0.0f ? __fadd_rn(__uint_as_float(v[i]), dst[i]) : __uint_as_float(v[i]);
+                    }
+                } else {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ld_out + col0;
+                    if (p.beta != 0.0f) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < ncols) v[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), __bfloat162float(dst[i])));
+                    }
+                    if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * j]),
+                                                                          __uint_as_float(v[8 * q + 2 * j + 1]));
+                                h[j] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                            d4[q] = make_uint4(h[0], h[1], h[2], h[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < ncols) dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + acc) & PEER_MASK);
+        }
+    } else if (MODE != DW && (warp & 3) != 1) {
+        // --------------------------------------------------------------------- expanders
+        // Warp slots 6,7,8,10,11,12,14,15 -> expander index 0..7; two threads per row of this CTA's
+        // 128-row B half, four 16-byte chunks each.
+        const int xw = warp - 6 - (warp > 9) - (warp > 13);
+        if (xw < NUM_EXP_WARPS) {
+            const int e = xw * 32 + lane;
+            const int r = e >> 1, half = e & 1;
+            const int sw = r & 7;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int gi = 0;
+            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+                for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
+                    if (!(ok = mbar_wait(smem_u32(full_p + stage), phase, abort_flag, 6))) break;
+                    if (threadIdx.x == 6 * 32) AB_TRACE2(gi, 4);
+                    uint8_t* brow = s_b + stage * B_BYTES + r * 128;
+                    if (MODE == FWD) {
+                        const uint4 pk = *reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + e * 16);
+                        const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            *reinterpret_cast<uint4*>(brow + (((half * 4 + c) ^ sw) << 4)) = expand_u8(w[c]);
+                    } else {
+                        const uint2 pk = *reinterpret_cast<const uint2*>(s_p + stage * P_BYTES + e * 8);
+                        const uint32_t w[2] = {pk.x, pk.y};
+#pragma unroll
+                        for (int wi = 0; wi < 2; ++wi) {
+                            uint32_t o[8];
+                            expand_bf16(w[wi], o);
+                            *reinterpret_cast<uint4*>(brow + (((half * 4 + 2 * wi) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                            *reinterpret_cast<uint4*>(brow + (((half * 4 + 2 * wi + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
+                    }
+                    if (threadIdx.x == 6 * 32) AB_TRACE2(gi, 5);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(smem_u32(full + stage) & PEER_MASK);
+                    if (threadIdx.x == 6 * 32) AB_TRACE2(gi, 6);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------ common exit
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 200 + *abort_flag);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    cluster_sync_all();  // neither CTA retires while the other may still address its barriers / TMEM
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int MODE>
+static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
+    constexpr int STAGES = Cfg<MODE>::STAGES;
+    constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (MODE == DW ? 0 : P_BYTES)) + 512;
+    static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    if (!attr_set[ctx->device & 7]) {
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[ctx->device & 7] = true;
+    }
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.N + BN - 1) / BN;
+    constexpr int KB = MODE == FWD ? 128 : 64;
+    p.num_kb = (p.K + KB - 1) / KB;
+    p.status = ctx->dev_status;
+#ifdef AB_GEMM_TRACE
+    p.trace = reinterpret_cast<long long*>(ctx->stage[5]);
+#endif
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3((MODE == DW ? kWarpsDW : kWarpsExp) * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // one resident CTA pair per two SMs; ask the runtime how many pairs the device can co-schedule
+    static int max_clusters[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (max_clusters[ctx->device & 7] == 0) {
+        cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1), 1, 1);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = ctx->sm_count / 2;
+        }
+        max_clusters[ctx->device & 7] = n < ctx->sm_count / 2 ? n : ctx->sm_count / 2;
+    }
+    long long tiles = (long long)p.tiles_m * p.tiles_n;
+    int clusters = (int)(tiles < max_clusters[ctx->device & 7] ? tiles : max_clusters[ctx->device & 7]);
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+    AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, ta, tb, p));
+    ctx->launches++;
+    return AB_OK;
+}
+
+}  // namespace tc2
+
+int ab_make_tmap(ab_ctx* ctx, CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1,
+                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle sw);
+
+int abk_gemm2_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
+                  const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, w->in, m, ld_xq, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_fwd, w->pitch, w->out, w->pitch, 32, 128,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)m; p.N = (int)w->out; p.K = (int)w->in;
+    p.gamma = w->gamma_dev; p.scales = scales; p.rowsums = rowsums;
+    p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.acc_out = acc_out; p.beta = 0.0f;
+    p.n_fast = 1;
+    return tc2::launch<tc::FWD>(ctx, ta, tb, p);
+}
+
+int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx, int dx_dtype,
+                 size_t ld_dx, float beta) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dy, w->out, m, ld_dy * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_t, w->tpitch, w->in, w->tpitch, 16, 128,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)m; p.N = (int)w->in; p.K = (int)w->out;
+    p.gamma = w->gamma_dev; p.out = dx; p.out_dtype = dx_dtype; p.ld_out = (long long)ld_dx; p.beta = beta;
+    p.n_fast = 1;
+    return tc2::launch<tc::DX>(ctx, ta, tb, p);
+}
+
+int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,
+                 float* dW, size_t ld_dw, float beta) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dy, out, m, ld_dy * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, in, m, ld_x * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)out; p.N = (int)in; p.K = (int)m;
+    p.out = dW; p.out_dtype = AB_F32; p.ld_out = (long long)ld_dw; p.beta = beta;
+    p.n_fast = in <= out ? 1 : 0;
+    return tc2::launch<tc::DW>(ctx, ta, tb, p);
+}

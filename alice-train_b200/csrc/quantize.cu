@@ -124,7 +124,7 @@ template <bool WANT_FQ, bool WANT_STATS>
 __global__ void __launch_bounds__(kThreads)
 quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row,
                      uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd,
-                     float* fq_out, ab_fq_dev_report* __restrict__ rep, int offset_binary) {
+                     float* fq_out, ab_fq_dev_report* __restrict__ rep) {
     const size_t total = out * words_per_row;
     size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const float gamma = rep->gamma, inv = rep->inv_gamma;
@@ -159,7 +159,7 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
             int c = (r != r) ? 0 : (int)r;         // NaN -> 0 like `as i8`
             if (e >= valid) c = 0;
             uint32_t canon = c > 0 ? 1u : (c < 0 ? 2u : 0u);
-            uint32_t fenc = offset_binary ? (uint32_t)(c + 1) : (c > 0 ? 1u : (c < 0 ? 3u : 0u));
+            uint32_t fenc = (uint32_t)(c + 1);  // offset binary
             cword |= canon << (2 * e);
             fword |= fenc << ab_perm_bit(e);
             qv[e] = __fmul_rn(r, gamma);
@@ -236,7 +236,7 @@ template <bool WANT_FQ, bool WANT_STATS>
 __global__ void __launch_bounds__(kThreads)
 quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per_row, int dense_rows,
                          uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, float* fq_out,
-                         ab_fq_dev_report* __restrict__ rep, int offset_binary) {
+                         ab_fq_dev_report* __restrict__ rep) {
     const int lane = threadIdx.x & 31, sub = lane & 3;
     const size_t total_warps = (size_t)gridDim.x * (kThreads / 32);
     const size_t warp_global = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
@@ -273,7 +273,7 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
                 r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
                 int cc = (r != r) ? 0 : (int)r;
                 uint32_t canon = cc > 0 ? 1u : (cc < 0 ? 2u : 0u);
-                uint32_t fenc = offset_binary ? (uint32_t)(cc + 1) : (cc > 0 ? 1u : (cc < 0 ? 3u : 0u));
+                uint32_t fenc = (uint32_t)(cc + 1);  // offset binary
                 if (!act[u]) { canon = 0; fenc = 0; }
                 cpart |= canon << (8 * sub + 2 * i);   // element e = 4*sub + i sits at bit 2e
                 fpart |= fenc << (8 * i + 2 * sub);    // and at bit 8*(e%4) + 2*(e/4) in the operand copy
@@ -347,16 +347,14 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
 
 // --------------------------------------------------------- operand copies from canonical
 __global__ void __launch_bounds__(kThreads)
-repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, size_t words,
-                  int offset_binary) {
+repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, size_t words) {
     size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (wi >= words) return;
     uint32_t cw = codes[wi], f = 0;
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
         uint32_t c = (cw >> (2 * e)) & 3u;
-        uint32_t enc = offset_binary ? (c == 1u ? 2u : (c == 2u ? 0u : 1u))
-                                     : (c == 1u ? 1u : (c == 2u ? 3u : 0u));
+        uint32_t enc = c == 1u ? 2u : (c == 2u ? 0u : 1u);  // w + 1
         f |= enc << ab_perm_bit(e);
     }
     codes_fwd[wi] = f;
@@ -611,7 +609,6 @@ int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float
     if (words) {
         uint32_t* c = reinterpret_cast<uint32_t*>(w->codes);
         uint32_t* f = reinterpret_cast<uint32_t*>(w->codes_fwd);
-        const int ob = ctx->fwd_offset_binary;
         const bool vec = (w->in % 16 == 0) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
                          (!fq_out || (reinterpret_cast<uintptr_t>(fq_out) & 15) == 0);
         if (vec) {
@@ -621,23 +618,23 @@ int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float
             size_t want = (chunks + (kThreads / 32) * 4 - 1) / ((kThreads / 32) * 4);
             unsigned int grid = (unsigned int)(want < (size_t)ctx->sm_count * 8 ? (want ? want : 1) : (size_t)ctx->sm_count * 8);
             if (fq_out && want_stats)
-                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev, ob);
+                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev);
             else if (fq_out)
-                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev, ob);
+                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev);
             else if (want_stats)
-                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev, ob);
+                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev);
             else
-                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev, ob);
+                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev);
         } else {
             unsigned int grid = grid_for(words, kThreads);
             if (fq_out && want_stats)
-                quantize_pack_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+                quantize_pack_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev);
             else if (fq_out)
-                quantize_pack_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev, ob);
+                quantize_pack_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, fq_out, w->report_dev);
             else if (want_stats)
-                quantize_pack_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+                quantize_pack_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev);
             else
-                quantize_pack_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev, ob);
+                quantize_pack_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, w->out, w->in, wpr, c, f, nullptr, w->report_dev);
         }
         AB_LAUNCH_CHECK(ctx);
         if (w->codes_t) {
@@ -657,8 +654,7 @@ int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w) {
     const size_t wpr = w->pitch / 4, words = w->out * wpr;
     if (!words || !w->codes_fwd || !w->codes_t) return AB_OK;
     repack_fwd_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(
-        reinterpret_cast<const uint32_t*>(w->codes), reinterpret_cast<uint32_t*>(w->codes_fwd), words,
-        ctx->fwd_offset_binary);
+        reinterpret_cast<const uint32_t*>(w->codes), reinterpret_cast<uint32_t*>(w->codes_fwd), words);
     AB_LAUNCH_CHECK(ctx);
     const size_t twpr = w->tpitch / 4;
     dim3 tg(grid_for(w->in, kTT), grid_for(w->out, kTT));
