@@ -1,6 +1,5 @@
-// Host side of the tensor-core path: TMA tensor-map construction, dispatch between the CTA-pair
-// kernels (gemm_tc2.cu) and the any-shape CUDA-core kernels (gemm_simt.cu), and the MMA-only probe
-// that measures the tensor pipe's ceiling.
+// Host side of the tensor-core path: TMA tensor-map construction and the dispatch between the
+// CTA-pair kernels (gemm_tc2.cu) and the any-shape CUDA-core kernels (gemm_simt.cu).
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -8,59 +7,6 @@
 #include "tc_ptx.cuh"
 
 namespace tc {
-
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int A_BYTES = BM * 128;
-constexpr int B_BYTES = BN * 128;
-
-// ------------------------------------------------------------------------- peak probe
-// Issues `iters` x 4 MMAs of the production shape (128x256, 32 bytes of K each) per CTA on
-// zero-filled shared-memory tiles, with no loads and no epilogue: the time of this kernel is the
-// tensor pipe's own ceiling for that instruction kind at the clocks the GPU actually holds.
-template <int MODE>
-__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + A_BYTES + B_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    for (int i = threadIdx.x; i < (A_BYTES + B_BYTES) / 16; i += blockDim.x)
-        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (threadIdx.x == 0) {
-        mbar_init(smem_u32(bar), 1);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    fence_async_smem();
-    if ((threadIdx.x >> 5) == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) {
-        constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0) : make_idesc(1, 1, 1, 0, 0);
-        const uint32_t a_addr = smem_u32(smem), b_addr = smem_u32(smem + A_BYTES);
-        for (int it = 0; it < iters; ++it) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                umma<MODE>(tmem_base, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc,
-                           (it | k) != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(bar));
-        mbar_wait(smem_u32(bar), 0, abort_flag, 9);
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(status, 0, 100 + *abort_flag);
-    if ((threadIdx.x >> 5) == 0) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
-    }
-}
 
 // -------------------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -101,21 +47,6 @@ int make_tmap(ab_ctx* ctx, CUtensorMap* tm, CUtensorMapDataType dt, const void* 
 }
 
 }  // namespace tc
-
-int abk_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
-    constexpr size_t smem = 1024 + tc::A_BYTES + tc::B_BYTES + 64;
-    if (kind_i8) {
-        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc::mma_peak_kernel<tc::FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        tc::mma_peak_kernel<tc::FWD><<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
-    } else {
-        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc::mma_peak_kernel<tc::DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        tc::mma_peak_kernel<tc::DX><<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
-    }
-    AB_LAUNCH_CHECK(ctx);
-    // operations issued by the launch: 2 * M * N * K per MMA, 4 MMAs per iteration, one CTA per SM
-    *ops_out = 2.0 * tc::BM * tc::BN * (kind_i8 ? 32.0 : 16.0) * 4.0 * (double)iters * ctx->sm_count;
-    return AB_OK;
-}
 
 int ab_make_tmap(ab_ctx* ctx, CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1,
                  uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle sw) {

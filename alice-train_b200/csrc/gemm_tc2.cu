@@ -22,6 +22,7 @@
 // role's loop, and both CTAs still meet at the final cluster barrier before freeing TMEM.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -57,6 +58,7 @@ struct Params {
     float beta;
     int* status;
     long long* trace;
+    int debug_flags;         // trace builds only: 1 = producer skips the loads (timing experiments)
 };
 
 #ifdef AB_GEMM_TRACE
@@ -91,14 +93,15 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) 
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
-// The MMA thread's wait: no suspend hint (it is the critical path).  Bounded like every other wait.
+// The MMA thread polls with the non-blocking test_wait: try_wait, even on a completed phase, costs
+// several hundred cycles here, which is most of a stage.  Bounded like every other wait.
 __device__ __forceinline__ bool mbar_wait_mma(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
 #pragma unroll 1
     for (int tries = 0; tries < 20000000; ++tries) {
@@ -135,6 +138,32 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint
             ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
             : "memory");
     }
+}
+
+// The four MMAs of one pipeline stage in a single block of PTX.  Only the low word of a
+// shared-memory descriptor (start address, in 16-byte units) changes between them.  `first_acc`
+// is the accumulate flag of the first MMA (0 on the first k-block of a tile); the rest accumulate.
+template <int MODE, int KSTEP16>
+__device__ __forceinline__ void umma_pair_x4(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t first_acc) {
+#define AB_MMA4(KIND)                                                                              \
+    asm volatile(                                                                                  \
+        "{\n\t.reg .pred p, pt;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"                     \
+        "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 pt, %6, %6;\n\t"                                     \
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"                                       \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, p;\n\t"                         \
+        "add.u32 al, %1, %7;\n\tadd.u32 bl, %3, %7;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t"                        \
+        "add.u32 al, %1, %8;\n\tadd.u32 bl, %3, %8;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t"                        \
+        "add.u32 al, %1, %9;\n\tadd.u32 bl, %3, %9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t}"                       \
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first_acc),     \
+          "n"(KSTEP16), "n"(2 * KSTEP16), "n"(3 * KSTEP16)                                         \
+        : "memory")
+    if (MODE == FWD) AB_MMA4("i8");
+    else AB_MMA4("f16");
+#undef AB_MMA4
 }
 
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0) {
@@ -237,6 +266,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 16, n0);
                         tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
                     } else {
+#ifdef AB_GEMM_TRACE
+                        if (p.debug_flags & 1) {  // no loads: complete the byte count by hand
+                            if (rank == 0) asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + stage)), "r"(TX_LEADER) : "memory");
+                            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                            continue;
+                        }
+#endif
 #pragma unroll
                         for (int b = 0; b < 2; ++b)
                             tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES + b * 8192), &tm_a, lbar, m0 + 64 * b, kb * 64);
@@ -256,45 +292,48 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                                                  : make_idesc(1, 1, 1, 1, 1, BM, BN));
             const uint64_t da0 = MODE == DW ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
             const uint64_t db0 = MODE == DW ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
-            constexpr uint64_t KSTEP = (MODE == DW ? 2048 : 32) >> 4;
-            // Flat loop over (tile, k-block) with the NEXT stage's barrier polled before this stage's
-            // MMAs are issued: the poll's shared-memory round trip (slow while the tensor core and
-            // TMA saturate shared memory) overlaps the issue instead of preceding it.
-            const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
-            const long long total = (long long)my_tiles * p.num_kb;
-            int stage = 0, kb = 0, it = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            bool ready = total > 0 ? mbar_try_cluster(smem_u32(full + stage), phase) : false;
-            uint32_t d_tmem = tmem_base;
-            for (long long gi = 0; ok && gi < total; ++gi) {
-                if (kb == 0) {
-                    const int acc = it & 1;
-                    if (!(ok = mbar_wait_mma(smem_u32(tmem_empty + acc), ((it >> 1) & 1) ^ 1, abort_flag, 2))) break;
-                    d_tmem = tmem_base + acc * BN;
+            constexpr int KSTEP = (MODE == DW ? 2048 : 32) >> 4;
+            // This single thread paces the whole pair: everything it executes per stage beyond the
+            // MMAs themselves is tensor-pipe idle time.  So the ring is walked with the stage index
+            // unrolled (barrier and descriptor addresses are immediates), the NEXT stage's barrier is
+            // polled before this stage's MMAs are issued (the poll's round trip overlaps the issue),
+            // and the four MMAs of a stage go out as one block of PTX.
+            const uint32_t a_lo = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32);
+            const uint32_t b_lo = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
+            const uint32_t full0 = smem_u32(full), empty0 = smem_u32(empty);
+            const uint32_t tfull0 = smem_u32(tmem_full), tempty0 = smem_u32(tmem_empty);
+            int tiles_left = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+            int kb_left = p.num_kb, it = 0;
+            uint32_t phase = 0, first_acc = 0, d_tmem = tmem_base;
+            bool ok = tiles_left > 0;
+            if (ok) ok = mbar_wait_mma(tempty0, 1, abort_flag, 2);
+            bool ready = ok ? mbar_try_cluster(full0, 0) : false;
+            int gi = 0;
+            while (ok) {
+#pragma unroll
+                for (int s = 0; s < STAGES; ++s) {
+                    if (!ready)
+                        if (!(ok = mbar_wait_mma(full0 + 8 * s, phase, abort_flag, 3))) break;
+                    AB_TRACE2(gi, 2);
+                    tc_fence_after();
+                    ready = mbar_try_cluster(full0 + 8 * ((s + 1) % STAGES), s + 1 == STAGES ? phase ^ 1 : phase);
+                    umma_pair_x4<MODE, KSTEP>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
+                                              first_acc);
+                    umma_commit_pair(empty0 + 8 * s);
+                    AB_TRACE2(gi, 3);
+                    ++gi;
+                    first_acc = 1;
+                    if (--kb_left == 0) {
+                        umma_commit_pair(tfull0 + 8 * (it & 1));
+                        if (--tiles_left == 0) { ok = false; break; }
+                        ++it;
+                        kb_left = p.num_kb;
+                        first_acc = 0;
+                        if (!(ok = mbar_wait_mma(tempty0 + 8 * (it & 1), ((it >> 1) & 1) ^ 1, abort_flag, 2))) break;
+                        d_tmem = tmem_base + (it & 1) * BN;
+                    }
                 }
-                if (!ready)
-                    if (!(ok = mbar_wait_mma(smem_u32(full + stage), phase, abort_flag, 3))) break;
-                AB_TRACE2(gi, 2);
-                tc_fence_after();
-                const uint64_t da = da0 + (uint64_t)(stage * (A_BYTES >> 4));
-                const uint64_t db = db0 + (uint64_t)(stage * (B_BYTES >> 4));
-                const uint32_t cur_empty = smem_u32(empty + stage);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                ready = gi + 1 < total ? mbar_try_cluster(smem_u32(full + stage), phase) : false;
-                AB_TRACE2(gi, 1);
-                umma_pair<MODE>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
-                umma_pair<MODE>(d_tmem, da + KSTEP, db + KSTEP, idesc, 1u);
-                umma_pair<MODE>(d_tmem, da + 2 * KSTEP, db + 2 * KSTEP, idesc, 1u);
-                umma_pair<MODE>(d_tmem, da + 3 * KSTEP, db + 3 * KSTEP, idesc, 1u);
-                AB_TRACE2(gi, 7);
-                umma_commit_pair(cur_empty);
-                AB_TRACE2(gi, 3);
-                if (++kb == p.num_kb) {
-                    umma_commit_pair(smem_u32(tmem_full + (it & 1)));
-                    kb = 0;
-                    ++it;
-                }
+                phase ^= 1;
             }
         }
     } else if (warp < 6) {
@@ -462,6 +501,59 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
+// MMA-only probe: `iters` x 4 cta_group::2 MMAs (256x256 tile) per CTA pair on operand tiles that
+// sit in shared memory for the whole launch (pseudo-random finite values), no loads, no epilogue.
+// Its time is the ceiling of the tensor pipes for the instruction shape the kernels above issue.
+template <int MODE>
+__global__ void __launch_bounds__(128, 1) mma_pair_peak_kernel(int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + A_BYTES + B_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t rank = cluster_ctarank();
+    for (int i = threadIdx.x; i < (A_BYTES + B_BYTES) / 16; i += blockDim.x) {
+        uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u, w[4];
+        for (int j = 0; j < 4; ++j) {
+            h = h * 1664525u + 1013904223u;
+            w[j] = MODE == FWD ? (h & 0x3F3F3F3Fu) : ((h & 0x007F007Fu) | 0x3F803F80u);  // small int8 / bf16 in [1,2)
+        }
+        reinterpret_cast<uint4*>(smem)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(bar), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_async_smem();
+    if ((threadIdx.x >> 5) == 0) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0 && rank == 0) {
+        constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN) : make_idesc(1, 1, 1, 0, 0, BM, BN);
+        const uint64_t da = make_desc(smem_u32(smem), 16, 1024), db = make_desc(smem_u32(smem + A_BYTES), 16, 1024);
+        for (int it = 0; it < iters; ++it)
+            umma_pair_x4<MODE, 2>(tmem_base, (uint32_t)da, (uint32_t)(da >> 32), (uint32_t)db, (uint32_t)(db >> 32), idesc,
+                                  it != 0 ? 1u : 0u);
+        umma_commit_pair(smem_u32(bar));
+    }
+    if (threadIdx.x == 0) mbar_wait(smem_u32(bar), 0, abort_flag, 9);
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(status, 0, 200 + *abort_flag);
+    cluster_sync_all();
+    if ((threadIdx.x >> 5) == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+    }
+}
+
 template <int MODE>
 static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
@@ -478,6 +570,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     p.status = ctx->dev_status;
 #ifdef AB_GEMM_TRACE
     p.trace = reinterpret_cast<long long*>(ctx->stage[5]);
+    p.debug_flags = getenv("AB_TRACE_NOLOAD") ? 1 : 0;
 #endif
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3((MODE == DW ? kWarpsDW : kWarpsExp) * 32, 1, 1);
@@ -510,6 +603,33 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
 }
 
 }  // namespace tc2
+
+int abk_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
+    constexpr size_t smem = 1024 + tc2::A_BYTES + tc2::B_BYTES + 64;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (kind_i8) {
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc2::mma_pair_peak_kernel<tc::FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, tc2::mma_pair_peak_kernel<tc::FWD>, iters, ctx->dev_status));
+    } else {
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc2::mma_pair_peak_kernel<tc::DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, tc2::mma_pair_peak_kernel<tc::DX>, iters, ctx->dev_status));
+    }
+    ctx->launches++;
+    // operations of the launch: 2 * M * N * K per MMA, 4 MMAs per iteration, one CTA pair per two SMs
+    *ops_out = 2.0 * tc2::BM * tc2::BN * (kind_i8 ? 32.0 : 16.0) * 4.0 * (double)iters * (ctx->sm_count / 2);
+    return AB_OK;
+}
 
 int ab_make_tmap(ab_ctx* ctx, CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1,
                  uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle sw);

@@ -237,11 +237,11 @@ AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* 
                                   void* dx_bf16_host, float* dW_dev);
 
 /* Measurement aid (no counterpart in the reference): launches, on the context's stream, a kernel
- * that only issues tensor-core instructions of the production tile shape (no loads, no
- * epilogue) — `iters` x 4 MMAs per SM, int8 (kind_i8 != 0) or bf16.  *ops_out receives the
- * number of operations the launch performs; time it with events to obtain the tensor pipe's
- * ceiling for that kind at the clocks the device holds, the denominator the benchmark's
- * int8 roofline uses. */
+ * that only issues the tensor-core instruction of the production kernels (256x256 tile on a CTA
+ * pair, operands resident in shared memory, no loads, no epilogue) — `iters` x 4 MMAs per SM
+ * pair, int8 (kind_i8 != 0) or bf16.  *ops_out receives the number of operations the launch
+ * performs; time it with events to obtain the tensor pipe's ceiling for that kind at the clocks
+ * the device holds, the denominator the benchmark's int8 roofline uses. */
 AB_API int ab_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out);
 
 #ifdef __cplusplus
