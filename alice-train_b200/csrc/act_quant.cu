@@ -8,8 +8,8 @@
 //
 // The reference has no activation quantiser; this is the definition fixed by the target
 // specification.  HBM-bound: 2 (bf16) or 4 (f32) bytes read and 1 byte written per element.
-// One block per token; the row is read with 128-bit loads, kept in registers when it fits and
-// re-read (from L1/L2) otherwise.
+// 32 to 256 threads per token (several tokens per block for short rows); the row is read with
+// 128-bit loads, kept in registers when it fits and re-read (from L1/L2) otherwise.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -47,47 +47,56 @@ __device__ __forceinline__ int quant1(float x, float inv) {
     return (int)r;
 }
 
-template <typename T>
+// TPR threads share one token row; a block of 256 threads holds 256/TPR rows, so short rows still
+// put whole 128-bit loads of many rows in flight per SM instead of one small row per block.
+template <typename T, int TPR>
 __global__ void __launch_bounds__(kThreads)
-act_quant_kernel(const T* __restrict__ x, size_t k, size_t ld_x, int8_t* __restrict__ xq, size_t ld_xq,
+act_quant_kernel(const T* __restrict__ x, size_t m, size_t k, size_t ld_x, int8_t* __restrict__ xq, size_t ld_xq,
                  float* __restrict__ scales, int32_t* __restrict__ rowsums, int vec_ok) {
+    constexpr int ROWS = kThreads / TPR;          // rows per block
+    constexpr int WPR = TPR / 32;                  // warps per row
     __shared__ float s_max[kThreads / 32];
     __shared__ int s_sum[kThreads / 32];
-    const size_t t = blockIdx.x;
-    const T* row = x + t * ld_x;
-    int8_t* orow = xq + t * ld_xq;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int rl = threadIdx.x / TPR, tr = threadIdx.x % TPR;  // row in block, thread in row
+    const size_t t = (size_t)blockIdx.x * ROWS + rl;
+    const bool row_ok = t < m;
+    const T* row = x + (row_ok ? t : 0) * ld_x;
+    int8_t* orow = xq + (row_ok ? t : 0) * ld_xq;
     const size_t k8 = vec_ok ? k / 8 : 0;  // 8-element groups handled with vector accesses
-    const bool in_regs = k8 <= (size_t)kRegChunks * kThreads;
+    const bool in_regs = k8 <= (size_t)kRegChunks * TPR;
 
     float cache[kRegChunks][8];
     float amax = 0.0f;
-    if (in_regs) {
+    if (row_ok) {
+        if (in_regs) {
 #pragma unroll
-        for (int c = 0; c < kRegChunks; ++c) {
-            size_t g = (size_t)c * kThreads + threadIdx.x;
-            if (g < k8) {
-                Vec8<T>::load(row + g * 8, cache[c]);
+            for (int c = 0; c < kRegChunks; ++c) {
+                size_t g = (size_t)c * TPR + tr;
+                if (g < k8) {
+                    Vec8<T>::load(row + g * 8, cache[c]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(cache[c][i]));
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(cache[c][i]));
+                }
+            }
+        } else {
+            for (size_t g = tr; g < k8; g += TPR) {
+                float v[8];
+                Vec8<T>::load(row + g * 8, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
             }
         }
-    } else {
-        for (size_t g = threadIdx.x; g < k8; g += kThreads) {
-            float v[8];
-            Vec8<T>::load(row + g * 8, v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        }
+        for (size_t i = k8 * 8 + tr; i < k; i += TPR) amax = fmaxf(amax, fabsf(Vec8<T>::one(row + i)));
     }
-    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += kThreads) amax = fmaxf(amax, fabsf(Vec8<T>::one(row + i)));
-
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) s_max[wid] = amax;
-    __syncthreads();
-    amax = s_max[0];
+    if (WPR > 1) {
+        if (lane == 0) s_max[wid] = amax;
+        __syncthreads();
+        amax = s_max[rl * WPR];
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) amax = fmaxf(amax, s_max[i]);
+        for (int i = 1; i < WPR; ++i) amax = fmaxf(amax, s_max[rl * WPR + i]);
+    }
 
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     int sum = 0;
@@ -100,37 +109,55 @@ act_quant_kernel(const T* __restrict__ x, size_t k, size_t ld_x, int8_t* __restr
         pk.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
         *reinterpret_cast<uint2*>(orow + g * 8) = pk;
     };
-    if (in_regs) {
+    if (row_ok) {
+        if (in_regs) {
 #pragma unroll
-        for (int c = 0; c < kRegChunks; ++c) {
-            size_t g = (size_t)c * kThreads + threadIdx.x;
-            if (g < k8) emit8(cache[c], g);
+            for (int c = 0; c < kRegChunks; ++c) {
+                size_t g = (size_t)c * TPR + tr;
+                if (g < k8) emit8(cache[c], g);
+            }
+        } else {
+            for (size_t g = tr; g < k8; g += TPR) {
+                float v[8];
+                Vec8<T>::load(row + g * 8, v);
+                emit8(v, g);
+            }
         }
-    } else {
-        for (size_t g = threadIdx.x; g < k8; g += kThreads) {
-            float v[8];
-            Vec8<T>::load(row + g * 8, v);
-            emit8(v, g);
+        for (size_t i = k8 * 8 + tr; i < k; i += TPR) {
+            int q = quant1(Vec8<T>::one(row + i), inv);
+            sum += q;
+            orow[i] = (int8_t)q;
         }
+        // columns k..ld_xq are zeroed so that padded pitches never feed garbage to the GEMM
+        for (size_t i = k + tr; i < ld_xq; i += TPR) orow[i] = 0;
     }
-    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += kThreads) {
-        int q = quant1(Vec8<T>::one(row + i), inv);
-        sum += q;
-        orow[i] = (int8_t)q;
-    }
-    // columns k..ld_xq are zeroed so that padded pitches never feed garbage to the GEMM
-    for (size_t i = k + threadIdx.x; i < ld_xq; i += kThreads) orow[i] = 0;
-
     sum = __reduce_add_sync(0xffffffffu, sum);
-    if (lane == 0) s_sum[wid] = sum;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int tot = 0;
+    if (WPR > 1) {
+        if (lane == 0) s_sum[wid] = sum;
+        __syncthreads();
+        sum = 0;
 #pragma unroll
-        for (int i = 0; i < kThreads / 32; ++i) tot += s_sum[i];
-        scales[t] = amax;
-        if (rowsums) rowsums[t] = tot;
+        for (int i = 0; i < WPR; ++i) sum += s_sum[rl * WPR + i];
     }
+    if (row_ok && tr == 0) {
+        scales[t] = amax;
+        if (rowsums) rowsums[t] = sum;
+    }
+}
+
+template <typename T>
+static void launch_act_quant(ab_ctx* ctx, const T* x, size_t m, size_t k, size_t ld_x, int8_t* xq, size_t ld_xq,
+                             float* scales, int32_t* rowsums, int vec_ok) {
+    // fewest threads per row that still keep the row in registers (8 chunks of 8 elements each)
+    const size_t per_thread_cap = (size_t)kRegChunks * 8;
+#define AB_AQ(TPR)                                                                                          \
+    act_quant_kernel<T, TPR><<<(unsigned)((m + (kThreads / TPR) - 1) / (kThreads / TPR)), kThreads, 0, ctx->stream>>>( \
+        x, m, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok)
+    if (k <= per_thread_cap * 32) AB_AQ(32);
+    else if (k <= per_thread_cap * 64) AB_AQ(64);
+    else if (k <= per_thread_cap * 128) AB_AQ(128);
+    else AB_AQ(256);
+#undef AB_AQ
 }
 
 }  // namespace
@@ -143,11 +170,9 @@ int abk_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t
     int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ld_x * esz) % 16 == 0) &&
                  ((reinterpret_cast<uintptr_t>(xq) & 7) == 0) && (ld_xq % 8 == 0);
     if (x_dtype == AB_BF16)
-        act_quant_kernel<__nv_bfloat16><<<(unsigned)m, kThreads, 0, ctx->stream>>>(
-            (const __nv_bfloat16*)x, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok);
+        launch_act_quant<__nv_bfloat16>(ctx, (const __nv_bfloat16*)x, m, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok);
     else
-        act_quant_kernel<float><<<(unsigned)m, kThreads, 0, ctx->stream>>>((const float*)x, k, ld_x, xq,
-                                                                         ld_xq, scales, rowsums, vec_ok);
+        launch_act_quant<float>(ctx, (const float*)x, m, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }

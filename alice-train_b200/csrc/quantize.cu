@@ -268,30 +268,27 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
             uint32_t cpart = 0, fpart = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float scaled = __fmul_rn(x[i], inv);
-                float r = roundf(scaled);
-                r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
-                int cc = (r != r) ? 0 : (int)r;
-                uint32_t canon = cc > 0 ? 1u : (cc < 0 ? 2u : 0u);
-                uint32_t fenc = (uint32_t)(cc + 1);  // offset binary
-                if (!act[u]) { canon = 0; fenc = 0; }
-                cpart |= canon << (8 * sub + 2 * i);   // element e = 4*sub + i sits at bit 2e
-                fpart |= fenc << (8 * i + 2 * sub);    // and at bit 8*(e%4) + 2*(e/4) in the operand copy
-                qv[i] = __fmul_rn(r, gamma);
-                if (act[u]) {
-                    n_plus += cc > 0;
-                    n_minus += cc < 0;
-                    float a = fabsf(scaled);
-                    n_thr += (a >= 0.49999997f && a <= 0.50000006f);
-                    if (WANT_STATS) {
-                        double wd = (double)x[i], qd = (double)qv[i];
-                        s_err += fabs(wd - qd);
-                        s_wq += wd * qd;
-                        s_ww += wd * wd;
-                        s_qq += qd * qd;
-                        vmin = fminf(vmin, x[i]);
-                        vmax = fmaxf(vmax, x[i]);
-                    }
+                // clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff s <= -0.5, else 0 (NaN -> 0):
+                // two compares instead of a software roundf
+                const float scaled = __fmul_rn(x[i], inv);
+                const uint32_t pl = act[u] && scaled >= 0.5f, mi = act[u] && scaled <= -0.5f;
+                cpart |= (pl | (mi << 1)) << (8 * sub + 2 * i);                      // element e = 4*sub + i at bit 2e
+                fpart |= (act[u] ? (1u + pl - mi) : 0u) << (8 * i + 2 * sub);        // w+1 at bit 8*(e%4) + 2*(e/4)
+                const uint32_t mag = __float_as_uint(scaled) & 0x7fffffffu;          // |s| within 1 ulp of 0.5
+                n_thr += act[u] && (mag - 0x3EFFFFFFu) <= 2u;
+                if (WANT_FQ || WANT_STATS) {
+                    // c * gamma as the reference forms it: NaN stays NaN, a rounded-to-zero value keeps its sign
+                    qv[i] = scaled != scaled ? scaled
+                                            : (pl ? gamma : (mi ? -gamma : __uint_as_float(__float_as_uint(scaled) & 0x80000000u)));
+                }
+                if (WANT_STATS && act[u]) {
+                    double wd = (double)x[i], qd = (double)qv[i];
+                    s_err += fabs(wd - qd);
+                    s_wq += wd * qd;
+                    s_ww += wd * wd;
+                    s_qq += qd * qd;
+                    vmin = fminf(vmin, x[i]);
+                    vmax = fmaxf(vmax, x[i]);
                 }
             }
             cpart |= __shfl_xor_sync(0xffffffffu, cpart, 1);
@@ -306,7 +303,11 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
                     size_t row = g[u] / in4, col4 = g[u] - row * in4;
                     word = row * words_per_row + (col4 >> 2);
                 }
-                if (sub == 0) codes[word] = cpart;
+                if (sub == 0) {
+                    codes[word] = cpart;
+                    n_plus += __popc(cpart & 0x55555555u);
+                    n_minus += __popc(cpart & 0xAAAAAAAAu);
+                }
                 if (sub == 1 && codes_fwd) codes_fwd[word] = fpart;
                 if (WANT_FQ) q4[g[u]] = make_float4(qv[0], qv[1], qv[2], qv[3]);
             }
