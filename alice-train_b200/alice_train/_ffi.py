@@ -64,6 +64,7 @@ SIGNATURES = {
     "ab_calibration_stats_host": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "ab_ternary_matvec": (_i, [_vp, _vp, _vp, _vp]),
     "ab_ternary_matvec_backward": (_i, [_vp, _vp, _vp, _vp]),
+    "ab_ternary_matvec_backward_static": (_i, [_vp, _vp, _vp, _vp]),
     "ab_bitlinear_backward": (_i, [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp]),
     "ab_ste_weight_grad": (_i, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "ab_ternary_matmul_bt": (_i, [_vp, _vp, _vp, _f, _vp, _sz]),

@@ -537,6 +537,14 @@ int ab_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy
     return abk_ternary_matvec_backward(ctx, w, dy, dx);
 }
 
+int ab_ternary_matvec_backward_static(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (w->out) AB_REQUIRE(dy, AB_ERR_NULL);
+    if (w->in) AB_REQUIRE(dx, AB_ERR_NULL);
+    return abk_ternary_matvec_backward_static(ctx, w, dy, dx);
+}
+
 int ab_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy, int pre_norm,
                           float norm_eps, float* dx, float* d_bias) {
     AB_TRY(bind(ctx));

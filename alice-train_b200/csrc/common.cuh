@@ -123,6 +123,7 @@ int abk_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t
 // matvec.cu
 int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y);
 int abk_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx);
+int abk_ternary_matvec_backward_static(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx);
 int abk_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy,
                            int pre_norm, float norm_eps, float* dx, float* d_bias);
 int abk_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in, const float* dy, size_t out, float* dW);

@@ -262,6 +262,65 @@ int abk_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* d
     return abk_matvec_backward_with_scratch(ctx, w, dy, dx, (float*)partial, slices, rps, pstride);
 }
 
+// ------------------------------------------------------- allocation-free transposed matvec
+// Partial sums of the variant below live in this fixed array instead of context scratch, so
+// the call never asks the CUDA allocator for anything.  Every GPU that loads the library holds
+// these 4 MiB until the process exits.
+constexpr size_t kStaticScratchFloats = size_t(1) << 20;
+static __device__ __align__(256) float g_matvec_bwd_scratch[kStaticScratchFloats];
+
+// The array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static float* static_scratch_ptr(ab_ctx* ctx) {
+    static std::mutex mu;
+    static float* ptr[64] = {};
+    if (ctx->device < 0 || ctx->device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptr[ctx->device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_matvec_bwd_scratch);  // ab_* entry points bind the device first
+        if (e != cudaSuccess) {
+            ctx->last_error = std::string("cudaGetSymbolAddress(g_matvec_bwd_scratch): ") + cudaGetErrorString(e);
+            cudaGetLastError();
+            return nullptr;
+        }
+        ptr[ctx->device] = static_cast<float*>(p);
+    }
+    return ptr[ctx->device];
+}
+
+int abk_ternary_matvec_backward_static(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx) {
+    if (w->in == 0) return AB_OK;
+    if (w->out == 0) {
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(dx, 0, w->in * sizeof(float), ctx->stream));
+        return AB_OK;
+    }
+    int slices;
+    size_t rps, pstride;
+    ab_matvec_bwd_plan(ctx, w->out, w->in, &slices, &rps, &pstride);
+    if (pstride > kStaticScratchFloats) {
+        ctx->last_error = "ab_ternary_matvec_backward_static: in_features " + std::to_string(w->in) +
+                          " needs " + std::to_string(pstride) + " scratch floats per row slice; the fixed array holds " +
+                          std::to_string(kStaticScratchFloats) + " (use ab_ternary_matvec_backward)";
+        return AB_ERR_UNSUPPORTED;
+    }
+    // fewer, longer row slices until the partial sums fit the fixed array
+    while ((size_t)slices * pstride > kStaticScratchFloats) {
+        slices = (slices + 1) / 2;
+        rps = (w->out + slices - 1) / slices;
+        slices = (int)((w->out + rps - 1) / rps);
+    }
+    if (rps > (size_t)kBwdMaxSlice) {
+        ctx->last_error = "ab_ternary_matvec_backward_static: out_features " + std::to_string(w->out) + " x in_features " +
+                          std::to_string(w->in) + " exceeds what the fixed scratch array can slice (use ab_ternary_matvec_backward)";
+        return AB_ERR_UNSUPPORTED;
+    }
+    float* scratch = static_scratch_ptr(ctx);
+    if (!scratch) return AB_ERR_CUDA;
+    // every partial sum the reduction reads is written by the first kernel: nothing needs clearing
+    return abk_matvec_backward_with_scratch(ctx, w, dy, dx, scratch, slices, rps, pstride);
+}
+
 int abk_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy, int pre_norm,
                            float norm_eps, float* dx, float* d_bias) {
     if (d_bias && w->out)

@@ -168,6 +168,22 @@ AB_API int ab_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, f
  * GpuBackwardEngine::ternary_matvec_backward (src/gpu_backward.rs:170-306) and the shader
  * shaders/ternary_backward.wgsl:27-61. */
 AB_API int ab_ternary_matvec_backward(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx);
+/* Same result as ab_ternary_matvec_backward, for callers that must not touch the CUDA allocator.
+ * It has no counterpart in the reference.  The plain entry point keeps its partial sums in
+ * scratch memory that the context allocates (and grows) with cudaMalloc on demand.  That is
+ * unwelcome in a trainer that has already handed the whole device to its own arena — the
+ * reference's 70B runs size their layer buffers to fill VRAM, so a late cudaMalloc can simply
+ * fail — and in a step loop that may not stall, since cudaMalloc and cudaFree synchronise the
+ * device.  This variant keeps the partial sums in a fixed 4 MiB array inside the library (each
+ * GPU that loads the library holds it until the process ends) and calls no allocating routine.
+ *   - limit: round_up(in_features, 128) * row_slices <= 2^20 floats, at most 2048 rows per
+ *     slice; larger matrices return AB_ERR_UNSUPPORTED with the reason in ab_ctx_last_error();
+ *   - the first call on a device looks up the array's device address; make that call before
+ *     any stream capture begins;
+ *   - all calls on a device share the one array: calls that can overlap on the GPU (different
+ *     streams or contexts) race on it — keep them stream-ordered.  Nothing in it needs clearing
+ *     between calls. */
+AB_API int ab_ternary_matvec_backward_static(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx);
 /* bitlinear_backward (src/backward.rs:105-156); `d_bias` may be NULL. */
 AB_API int ab_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, const float* dy,
                                  int pre_norm, float norm_eps, float* dx, float* d_bias);
