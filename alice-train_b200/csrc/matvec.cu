@@ -15,57 +15,97 @@
 
 namespace {
 
-// value of element e of a canonical code word applied to v: +v, -v or 0 (code 3 decodes to 0)
-__device__ __forceinline__ float apply_code(uint32_t word, int e, float v) {
-    uint32_t c = (word >> (2 * e)) & 3u;
-    return c == 1u ? v : (c == 2u ? -v : 0.0f);
+// A canonical code word (16 x 2 bits; 01 = +1, 10 = -1) is turned into 16 f32 coefficients
+// +-2.0 / 0.0 with two instructions each and no table: `u` carries, per element, bit 2e = "non
+// zero" and bit 2e+1 = "minus"; shifted so that those two bits land on bits 30 and 31 and masked,
+// they ARE the floats 2.0 (0x40000000), -2.0 (0xC0000000) and 0.0.  The other factor is halved
+// beforehand (exact), so one FFMA per weight adds +v, -v or nothing.
+__device__ __forceinline__ uint32_t code_flags(uint32_t w) {
+    return ((w | (w >> 1)) & 0x55555555u) | (w & 0xAAAAAAAAu);
+}
+__device__ __forceinline__ float coef2(uint32_t u, int e) {  // +-2.0 or 0.0 for element e
+    return __uint_as_float((e == 15 ? u : (u << (30 - 2 * e))) & 0xC0000000u);
 }
 
 // ------------------------------------------------------------------------------- forward
-// One warp per output row.  A lane takes 64 consecutive weights (one 128-bit load) per step;
-// x is read through the read-only path and stays in L1 across the rows of a block.
-// y[j] (+)= scale * sum_k W[j][k] x[k]
-constexpr int kFwdWarps = 8;
+// y[j] = sum_k W[j][k] x[k].  A warp owns a tile of 2048 columns: every lane keeps its 64 values
+// of x (halved) in registers and walks the rows of the block's row group, one 128-bit load of
+// codes and 64 FFMAs per row, then a shuffle reduction.  x is therefore read once per row GROUP
+// instead of once per row.  Column tiles (blockIdx.y) write partial sums that a second small
+// kernel adds in tile order.
+constexpr int kFwdWarps = 4;     // warps per block, each on its own rows
+constexpr int kFwdRows = 8;      // rows per warp per step of the grid-stride loop
+constexpr int kFwdTile = 2048;   // columns per warp pass
 
 __global__ void __launch_bounds__(kFwdWarps * 32)
 matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
-                  const float* __restrict__ x, size_t x_stride, float* __restrict__ y, size_t y_stride,
-                  float scale, int accumulate, int use_scale) {
+                  const float* __restrict__ x, size_t x_stride, float* __restrict__ partial,
+                  size_t partial_stride /* floats per (batch row, column tile) */, size_t tiles) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const size_t row = (size_t)blockIdx.x * kFwdWarps + wid;
-    if (row >= out) return;
-    const float* xv = x + (size_t)blockIdx.y * x_stride;
-    float* yv = y + (size_t)blockIdx.y * y_stride;
-    const uint4* crow = reinterpret_cast<const uint4*>(codes + row * pitch);
-    const size_t chunks = (in + 63) / 64;  // pitch covers whole 64-element chunks (zero padded)
-    const bool x_vec = (reinterpret_cast<uintptr_t>(xv) & 15) == 0;
-    float acc = 0.0f;
-    for (size_t ch = lane; ch < chunks; ch += 32) {
-        uint4 cw = __ldg(crow + ch);
-        const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-        const size_t k0 = ch * 64;
-        if (x_vec && k0 + 64 <= in) {
-            const float4* x4 = reinterpret_cast<const float4*>(xv + k0);
+    const size_t tile = blockIdx.y, b = blockIdx.z;
+    const float* xv = x + b * x_stride;
+    const size_t k0 = tile * kFwdTile + (size_t)lane * 64;
+    float xh[64];
+    if (k0 + 64 <= in && (reinterpret_cast<uintptr_t>(xv + k0) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(xv + k0);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                float4 t = __ldg(x4 + q);
-                uint32_t w = w4[q >> 2];
-                int e = (q & 3) * 4;
-                acc += apply_code(w, e, t.x);
-                acc += apply_code(w, e + 1, t.y);
-                acc += apply_code(w, e + 2, t.z);
-                acc += apply_code(w, e + 3, t.w);
+        for (int q = 0; q < 16; ++q) {
+            float4 t = __ldg(x4 + q);
+            xh[4 * q] = 0.5f * t.x; xh[4 * q + 1] = 0.5f * t.y; xh[4 * q + 2] = 0.5f * t.z; xh[4 * q + 3] = 0.5f * t.w;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) xh[e] = k0 + e < in ? 0.5f * xv[k0 + e] : 0.0f;
+    }
+    const bool have = k0 / 4 < pitch;  // inside the (zero padded) row pitch
+    const uint8_t* cbase = codes + k0 / 4;
+    float* pdst = partial + (b * tiles + tile) * partial_stride;
+    // row groups are dealt round-robin to the warps of the grid, so x stays in registers for all of them
+    for (size_t row0 = ((size_t)blockIdx.x * kFwdWarps + wid) * kFwdRows; row0 < out;
+         row0 += (size_t)gridDim.x * kFwdWarps * kFwdRows) {
+    const size_t row1 = row0 + kFwdRows < out ? row0 + kFwdRows : out;
+    for (size_t r = row0; r < row1; r += 2) {
+        const bool two = r + 1 < row1;
+        uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
+        if (have) {
+            c0 = __ldg(reinterpret_cast<const uint4*>(cbase + r * pitch));
+            if (two) c1 = __ldg(reinterpret_cast<const uint4*>(cbase + (r + 1) * pitch));
+        }
+        const uint32_t w0[4] = {code_flags(c0.x), code_flags(c0.y), code_flags(c0.z), code_flags(c0.w)};
+        const uint32_t w1[4] = {code_flags(c1.x), code_flags(c1.y), code_flags(c1.z), code_flags(c1.w)};
+        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                a0[e & 3] = fmaf(coef2(w0[q], e), xh[16 * q + e], a0[e & 3]);
+                a1[e & 3] = fmaf(coef2(w1[q], e), xh[16 * q + e], a1[e & 3]);
             }
-        } else {
-            for (int e = 0; e < 64; ++e)
-                if (k0 + e < in) acc += apply_code(w4[e >> 4], e & 15, xv[k0 + e]);
+        }
+        float s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]), s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
+        for (int o = 16; o > 0; o >>= 1) {
+            s0 += __shfl_down_sync(0xffffffffu, s0, o);
+            s1 += __shfl_down_sync(0xffffffffu, s1, o);
+        }
+        if (lane == 0) {
+            pdst[r] = s0;
+            if (two) pdst[r + 1] = s1;
         }
     }
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-        float r = use_scale ? __fmul_rn(acc, scale) : acc;
-        yv[row] = accumulate ? __fadd_rn(yv[row], r) : r;
     }
+}
+
+// y[b][j] (+)= scale * sum over column tiles, in tile order
+__global__ void matvec_fwd_reduce_kernel(const float* __restrict__ partial, size_t partial_stride, size_t tiles,
+                                         size_t out, float* __restrict__ y, size_t y_stride, float scale,
+                                         int accumulate, int use_scale) {
+    const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (j >= out) return;
+    float s = 0.0f;
+    for (size_t t = 0; t < tiles; ++t) s += partial[(b * tiles + t) * partial_stride + j];
+    float r = use_scale ? __fmul_rn(s, scale) : s;
+    float* dst = y + b * y_stride + j;
+    *dst = accumulate ? __fadd_rn(*dst, r) : r;
 }
 
 // ------------------------------------------------------------------------------ backward
@@ -73,47 +113,64 @@ matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
 // rows; a block covers 128 words (2048 columns, 512 contiguous bytes per row).  Row slices
 // (blockIdx.y) give every SM work; their partial sums land in scratch and are added in slice
 // order by a second small kernel, so the result does not depend on scheduling.
-constexpr int kBwdThreads = 128;
+constexpr int kBwdWarps = 8;
+constexpr int kBwdThreads = kBwdWarps * 32;
 constexpr int kBwdMaxSlice = 2048;  // rows of dy staged in shared memory per block
 
+// Block = 8 warps over the same 32 code words (512 columns): lane l owns word l, warp w takes rows
+// r0+w, r0+w+8, ... of the block's row slice (each warp load is 128 contiguous bytes of one row).
+// The eight partial sums per column meet in shared memory, so one slice costs one row of partials.
 __global__ void __launch_bounds__(kBwdThreads)
 matvec_bwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t words_per_row,
                   const float* __restrict__ dy, size_t rows_per_slice, float* __restrict__ partial,
                   size_t partial_stride /* floats per slice */) {
-    __shared__ float s_dy[kBwdMaxSlice];
-    const size_t word = (size_t)blockIdx.x * kBwdThreads + threadIdx.x;
+    __shared__ float s_dy[kBwdMaxSlice];              // halved, see coef2()
+    __shared__ float s_red[kBwdWarps][32 * 16 + 4];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const size_t word = (size_t)blockIdx.x * 32 + lane;
     const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
     const size_t r1 = r0 + rows_per_slice < out ? r0 + rows_per_slice : out;
-    for (size_t r = r0 + threadIdx.x; r < r1; r += kBwdThreads) s_dy[r - r0] = dy[r];
+    for (size_t r = r0 + threadIdx.x; r < r1; r += kBwdThreads) s_dy[r - r0] = 0.5f * dy[r];
     __syncthreads();
-    if (word >= words_per_row) return;
     float acc[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
-    const uint32_t* col = reinterpret_cast<const uint32_t*>(codes) + word;
-    const size_t wstride = pitch / 4;
-    size_t r = r0;
-    for (; r + 4 <= r1; r += 4) {  // four independent loads in flight per thread
-        uint32_t w0 = __ldg(col + (r + 0) * wstride), w1 = __ldg(col + (r + 1) * wstride);
-        uint32_t w2 = __ldg(col + (r + 2) * wstride), w3 = __ldg(col + (r + 3) * wstride);
-        float d0 = s_dy[r - r0], d1 = s_dy[r - r0 + 1], d2 = s_dy[r - r0 + 2], d3 = s_dy[r - r0 + 3];
+    if (word < words_per_row) {
+        const uint32_t* col = reinterpret_cast<const uint32_t*>(codes) + word;
+        const size_t wstride = pitch / 4;
+        constexpr int U = 4;  // independent loads in flight per thread
+        size_t r = r0 + wid;
+        for (; r + (U - 1) * kBwdWarps < r1; r += U * kBwdWarps) {
+            uint32_t w[U];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            acc[e] += apply_code(w0, e, d0);
-            acc[e] += apply_code(w1, e, d1);
-            acc[e] += apply_code(w2, e, d2);
-            acc[e] += apply_code(w3, e, d3);
+            for (int u = 0; u < U; ++u) w[u] = __ldg(col + (r + u * kBwdWarps) * wstride);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t f = code_flags(w[u]);
+                const float d = s_dy[r - r0 + u * kBwdWarps];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
+            }
+        }
+        for (; r < r1; r += kBwdWarps) {
+            const uint32_t f = code_flags(__ldg(col + r * wstride));
+            const float d = s_dy[r - r0];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
         }
     }
-    for (; r < r1; ++r) {
-        uint32_t w0 = __ldg(col + r * wstride);
-        float d0 = s_dy[r - r0];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) acc[e] += apply_code(w0, e, d0);
+    for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<float4*>(&s_red[wid][lane * 16 + 4 * q]) = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    __syncthreads();
+    // 512 columns, 256 threads: two columns each, summed over the warps in warp order
+    for (int c = threadIdx.x; c < 32 * 16; c += kBwdThreads) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kBwdWarps; ++w) sum += s_red[w][c];
+        const size_t colw = (size_t)blockIdx.x * 32 + (c >> 4);
+        if (colw < words_per_row) partial[(size_t)blockIdx.y * partial_stride + colw * 16 + (c & 15)] = sum;
     }
-    float4* dst = reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * partial_stride + word * 16);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
 }
 
 __global__ void matvec_bwd_reduce_kernel(const float* __restrict__ partial, size_t partial_stride,
@@ -194,35 +251,52 @@ ste_outer_kernel(const float* __restrict__ x, size_t in, const float* __restrict
 
 }  // namespace
 
-int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y) {
-    if (w->out == 0) return AB_OK;
-    dim3 grid((unsigned)((w->out + kFwdWarps - 1) / kFwdWarps), 1);
-    matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, x, 0, y, 0,
-                                                               1.0f, 0, 0);
+static int matvec_fwd_launch(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_stride, float* y,
+                             size_t y_stride, size_t m, float scale, int accumulate, int use_scale) {
+    const size_t tiles = (w->in + kFwdTile - 1) / kFwdTile;
+    const size_t pstride = ab_round_up(w->out, 32);
+    void* partial = nullptr;
+    int st = ab_ctx_scratch(ctx, m * (tiles ? tiles : 1) * pstride * sizeof(float), &partial);
+    if (st) return st;
+    if (tiles) {
+        // about one resident wave: 5 blocks of 4 warps per SM at this kernel's register count
+        size_t groups = (w->out + kFwdWarps * kFwdRows - 1) / (kFwdWarps * kFwdRows);
+        size_t gx = ((size_t)ctx->sm_count * 5 + tiles * m - 1) / (tiles * m);
+        if (gx > groups) gx = groups;
+        if (gx < 1) gx = 1;
+        dim3 grid((unsigned)gx, (unsigned)tiles, (unsigned)m);
+        matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, x, x_stride,
+                                                                  (float*)partial, pstride, tiles);
+        AB_LAUNCH_CHECK(ctx);
+    }
+    dim3 rgrid((unsigned)((w->out + 255) / 256), (unsigned)m);
+    matvec_fwd_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>((const float*)partial, pstride, tiles, w->out, y, y_stride,
+                                                            scale, accumulate, use_scale);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
+}
+
+int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y) {
+    if (w->out == 0) return AB_OK;
+    return matvec_fwd_launch(ctx, w, x, 0, y, 0, 1, 1.0f, 0, 0);
 }
 
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
     if (w->out == 0 || m == 0) return AB_OK;
     if (m > 65535) return AB_ERR_UNSUPPORTED;
-    dim3 grid((unsigned)((w->out + kFwdWarps - 1) / kFwdWarps), (unsigned)m);
-    matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, a, w->in, c,
-                                                               w->out, scale, 1, 1);
-    AB_LAUNCH_CHECK(ctx);
-    return AB_OK;
+    return matvec_fwd_launch(ctx, w, a, w->in, c, w->out, m, scale, 1, 1);
 }
 
-// Row slicing of the transposed matvec: enough blocks for ~4 per SM, slices no longer than the
+// Row slicing of the transposed matvec: enough blocks for ~6 per SM, slices no longer than the
 // shared-memory staging of dy allows.
 void ab_matvec_bwd_plan(const ab_ctx* ctx, size_t out, size_t in, int* slices, size_t* rows_per_slice,
                         size_t* partial_stride) {
     const size_t wpr = ab_round_up(in, 128) / 16;
-    const size_t col_blocks = (wpr + kBwdThreads - 1) / kBwdThreads;
-    size_t s = ((size_t)ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
-    size_t max_s = (out + 31) / 32;  // at least 32 rows per slice
+    const size_t col_blocks = (wpr + 31) / 32;
+    size_t s = ((size_t)ctx->sm_count * 6 + col_blocks - 1) / col_blocks;  // ~6 blocks of 8 warps per SM
+    size_t max_s = (out + 63) / 64;  // at least 64 rows (8 per warp) per slice
     if (s > max_s) s = max_s;
-    if (s > 128) s = 128;
+    if (s > 256) s = 256;
     if (s < 1) s = 1;
     size_t rps = (out + s - 1) / s;
     if (rps > (size_t)kBwdMaxSlice) { rps = kBwdMaxSlice; }
@@ -237,7 +311,7 @@ void ab_matvec_bwd_plan(const ab_ctx* ctx, size_t out, size_t in, int* slices, s
 int abk_matvec_backward_with_scratch(ab_ctx* ctx, const ab_weights* w, const float* dy, float* dx,
                                      float* partial, int slices, size_t rps, size_t pstride) {
     const size_t wpr = w->pitch / 4;
-    dim3 grid((unsigned)((wpr + kBwdThreads - 1) / kBwdThreads), (unsigned)slices);
+    dim3 grid((unsigned)((wpr + 31) / 32), (unsigned)slices);
     matvec_bwd_kernel<<<grid, kBwdThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, wpr, dy, rps, partial,
                                                             pstride);
     AB_LAUNCH_CHECK(ctx);
