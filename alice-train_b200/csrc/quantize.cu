@@ -227,20 +227,21 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
     }
 }
 
-// Fast path of pass B (rows that are multiples of 16 elements, 16-byte aligned tensors): every
-// lane loads ONE float4 so that a warp reads 512 contiguous bytes per instruction, four loads
-// in flight per lane; the four lanes that share a 16-element group merge their 2-bit fields
-// with two shuffles and one of them stores the canonical word, another the forward-operand
-// word.  Chunks are walked from the end of the tensor (see above).
+// Fast path of pass B (rows that are multiples of 128 elements, 16-byte aligned tensors, fewer
+// than 2^33 elements): every lane loads ONE float4 so that a warp reads 512 contiguous bytes per
+// instruction, four loads in flight per lane; the four lanes that share a 16-element group merge
+// their 2-bit fields with two shuffles and one of them stores the canonical word, another the
+// forward-operand word.  Row pitch equals the row length here, so code word i simply holds
+// elements 16i..16i+15 of the flat tensor.  512-byte chunks are walked from the end of the
+// tensor (see above).  clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff s <= -0.5 and
+// 0 otherwise (NaN -> 0), so the codes take two compares per element instead of a software roundf.
 template <bool WANT_FQ, bool WANT_STATS>
 __global__ void __launch_bounds__(kThreads)
-quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per_row, int dense_rows,
-                         uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, float* fq_out,
-                         ab_fq_dev_report* __restrict__ rep) {
+quantize_pack_vec_kernel(const float* w, uint32_t nchunks /* of 32 float4 */, uint32_t* __restrict__ codes,
+                         uint32_t* __restrict__ codes_fwd, float* fq_out, ab_fq_dev_report* __restrict__ rep) {
     const int lane = threadIdx.x & 31, sub = lane & 3;
-    const size_t total_warps = (size_t)gridDim.x * (kThreads / 32);
-    const size_t warp_global = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-    const size_t nchunks = (n4 + 31) / 32;
+    const uint32_t total_warps = gridDim.x * (kThreads / 32);
+    const uint32_t warp_global = (blockIdx.x * kThreads + threadIdx.x) >> 5;
     const float gamma = rep->gamma, inv = rep->inv_gamma;
     const float4* w4 = reinterpret_cast<const float4*>(w);
     float4* q4 = reinterpret_cast<float4*>(fq_out);
@@ -248,40 +249,34 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
     double s_err = 0, s_wq = 0, s_ww = 0, s_qq = 0;
     float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
     constexpr int U = 4;
-    for (size_t c0 = warp_global; c0 < nchunks; c0 += U * total_warps) {
+    for (uint32_t c0 = warp_global; c0 < nchunks; c0 += U * total_warps) {
         float4 v[U];
-        size_t g[U];
-        bool act[U];
+        uint32_t g[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            size_t c = c0 + (size_t)u * total_warps;
-            g[u] = c < nchunks ? (nchunks - 1 - c) * 32 + lane : n4;
-            act[u] = g[u] < n4;
-            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (act[u]) v[u] = WANT_FQ ? w4[g[u]] : __ldg(w4 + g[u]);  // fq_out may alias w
+            const uint32_t c = c0 + u * total_warps;
+            g[u] = (nchunks - 1 - (c < nchunks ? c : c0)) * 32 + lane;  // an out-of-range slot re-reads chunk c0
+            v[u] = WANT_FQ ? w4[g[u]] : __ldg(w4 + g[u]);               // fq_out may alias w
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (c0 + (size_t)u * total_warps >= nchunks) break;  // warp-uniform
+            if (c0 + u * total_warps >= nchunks) break;  // warp-uniform
             const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
             float qv[4];
-            uint32_t cpart = 0, fpart = 0;
+            uint32_t cbits = 0, fbits = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                // clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff s <= -0.5, else 0 (NaN -> 0):
-                // two compares instead of a software roundf
                 const float scaled = __fmul_rn(x[i], inv);
-                const uint32_t pl = act[u] && scaled >= 0.5f, mi = act[u] && scaled <= -0.5f;
-                cpart |= (pl | (mi << 1)) << (8 * sub + 2 * i);                      // element e = 4*sub + i at bit 2e
-                fpart |= (act[u] ? (1u + pl - mi) : 0u) << (8 * i + 2 * sub);        // w+1 at bit 8*(e%4) + 2*(e/4)
-                const uint32_t mag = __float_as_uint(scaled) & 0x7fffffffu;          // |s| within 1 ulp of 0.5
-                n_thr += act[u] && (mag - 0x3EFFFFFFu) <= 2u;
+                const uint32_t pl = scaled >= 0.5f, mi = scaled <= -0.5f;
+                cbits |= (pl | (mi << 1)) << (2 * i);
+                fbits |= (1u + pl - mi) << (8 * i);  // offset binary w+1
+                n_thr += ((__float_as_uint(scaled) & 0x7fffffffu) - 0x3EFFFFFFu) <= 2u;  // |s| within 1 ulp of 0.5
                 if (WANT_FQ || WANT_STATS) {
                     // c * gamma as the reference forms it: NaN stays NaN, a rounded-to-zero value keeps its sign
                     qv[i] = scaled != scaled ? scaled
-                                            : (pl ? gamma : (mi ? -gamma : __uint_as_float(__float_as_uint(scaled) & 0x80000000u)));
+                                             : (pl ? gamma : (mi ? -gamma : __uint_as_float(__float_as_uint(scaled) & 0x80000000u)));
                 }
-                if (WANT_STATS && act[u]) {
+                if (WANT_STATS) {
                     double wd = (double)x[i], qd = (double)qv[i];
                     s_err += fabs(wd - qd);
                     s_wq += wd * qd;
@@ -291,26 +286,20 @@ quantize_pack_vec_kernel(const float* w, size_t n4, size_t in4, size_t words_per
                     vmax = fmaxf(vmax, x[i]);
                 }
             }
+            // element e = 4*sub + i of the group: bit 2e in the canonical word, bit 8*(e%4) + 2*(e/4) in the operand copy
+            uint32_t cpart = cbits << (8 * sub), fpart = fbits << (2 * sub);
             cpart |= __shfl_xor_sync(0xffffffffu, cpart, 1);
             fpart |= __shfl_xor_sync(0xffffffffu, fpart, 1);
             cpart |= __shfl_xor_sync(0xffffffffu, cpart, 2);
             fpart |= __shfl_xor_sync(0xffffffffu, fpart, 2);
-            if (act[u]) {
-                size_t grp = g[u] >> 2, word;
-                if (dense_rows) {
-                    word = grp;
-                } else {
-                    size_t row = g[u] / in4, col4 = g[u] - row * in4;
-                    word = row * words_per_row + (col4 >> 2);
-                }
-                if (sub == 0) {
-                    codes[word] = cpart;
-                    n_plus += __popc(cpart & 0x55555555u);
-                    n_minus += __popc(cpart & 0xAAAAAAAAu);
-                }
-                if (sub == 1 && codes_fwd) codes_fwd[word] = fpart;
-                if (WANT_FQ) q4[g[u]] = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            const uint32_t word = g[u] >> 2;
+            if (sub == 0) {
+                codes[word] = cpart;
+                n_plus += __popc(cpart & 0x55555555u);
+                n_minus += __popc(cpart & 0xAAAAAAAAu);
             }
+            if (sub == 1 && codes_fwd) codes_fwd[word] = fpart;
+            if (WANT_FQ) q4[g[u]] = make_float4(qv[0], qv[1], qv[2], qv[3]);
         }
     }
     __shared__ unsigned int sc[3];
@@ -610,22 +599,20 @@ int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float
     if (words) {
         uint32_t* c = reinterpret_cast<uint32_t*>(w->codes);
         uint32_t* f = reinterpret_cast<uint32_t*>(w->codes_fwd);
-        const bool vec = (w->in % 16 == 0) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
+        const bool vec = (w->in % 128 == 0) && n < (size_t(1) << 33) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
                          (!fq_out || (reinterpret_cast<uintptr_t>(fq_out) & 15) == 0);
         if (vec) {
-            const size_t n4 = n / 4, in4 = w->in / 4;
-            const int dense = (wpr == w->in / 16) ? 1 : 0;
-            size_t chunks = (n4 + 31) / 32;
-            size_t want = (chunks + (kThreads / 32) * 4 - 1) / ((kThreads / 32) * 4);
+            const uint32_t chunks = (uint32_t)(n / 128);
+            size_t want = ((size_t)chunks + (kThreads / 32) * 4 - 1) / ((kThreads / 32) * 4);
             unsigned int grid = (unsigned int)(want < (size_t)ctx->sm_count * 8 ? (want ? want : 1) : (size_t)ctx->sm_count * 8);
             if (fq_out && want_stats)
-                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev);
+                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, fq_out, w->report_dev);
             else if (fq_out)
-                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, fq_out, w->report_dev);
+                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, fq_out, w->report_dev);
             else if (want_stats)
-                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev);
+                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, nullptr, w->report_dev);
             else
-                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, n4, in4, wpr, dense, c, f, nullptr, w->report_dev);
+                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, nullptr, w->report_dev);
         } else {
             unsigned int grid = grid_for(words, kThreads);
             if (fq_out && want_stats)

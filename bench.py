@@ -285,10 +285,13 @@ def run_native(args):
     # entry, so the int8 kernel is set against the MMA-only probe measured just above
     peak_bf16 = pk["bf16_tflops_sustained"]
     peak = probe["int8_tops"] if dom == "fwd" else peak_bf16
-    roofline = {"bound": "tensor", "kernel": {"fwd": "gemm_kernel<FWD> int8 x ternary", "dx": "gemm_kernel<DX> bf16 x ternary",
-                                              "dw": "gemm_kernel<DW> bf16 x bf16"}[dom],
+    roofline = {"bound": "tensor", "kernel": {"fwd": "gemm_pair_kernel<FWD> int8 x ternary", "dx": "gemm_pair_kernel<DX> bf16 x ternary",
+                                              "dw": "gemm_pair_kernel<DW> bf16 x bf16"}[dom],
                 "achieved": per[dom]["tops_avg"], "peak": peak, "unit": "TFLOP/s",
-                "frac": per[dom]["tops_avg"] / peak if per[dom]["tops_avg"] else None, "traffic": None,
+                "frac": per[dom]["tops_avg"] / peak if per[dom]["tops_avg"] else None,
+                # DRAM read + write bytes of one launch from the ncu capture summarised in
+                # profiles/gemm_pair_kernel_llama8b_mlp.md (gate projection; llama3-8b-mlp workload only)
+                "traffic": ({"fwd": 95.4e6, "dx": 171.0e6, "dw": 392.4e6}[dom] if args.workload == "llama3-8b-mlp" else None),
                 "peak_source": ("int8 MMA-only probe (ab_tensor_peak_probe) in this run" if dom == "fwd"
                                 else f"{pk['source']} bf16 sustained {peak_bf16} TFLOP/s"),
                 "algorithmic_ops_per_launch": ops_per_launch}
