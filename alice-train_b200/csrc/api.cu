@@ -139,7 +139,7 @@ int ab_ctx_sync(ab_ctx* ctx) {
     AB_CUDA_CHECK(ctx, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != 0) {
         ctx->last_error = "device-side wait timed out, code " + std::to_string(status);
-        cudaMemset(ctx->dev_status, 0, sizeof(int));
+        cudaMemset(ctx->dev_status, 0, 64);  // status word and the GEMM tile counter (left mid-count by an aborted launch)
         return AB_ERR_DEVICE_TIMEOUT;
     }
     return AB_OK;

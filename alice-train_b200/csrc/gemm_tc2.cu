@@ -57,6 +57,7 @@ struct Params {
     int32_t* acc_out;
     float beta;
     int* status;
+    int* tile_counter;       // global work counter of the launch (0 on entry, reset to 0 by the last CTA pair)
     long long* trace;
     int debug_flags;         // trace builds only: 1 = producer skips the loads (timing experiments)
 };
@@ -85,6 +86,52 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     // CTA's own tensor core, after the proxy fence; a cluster-scope release costs ~1000 cycles
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// --------------------------------------------------------------------------------- tile feed
+// Tiles are handed out dynamically: the leader's producer thread draws the next tile index from a
+// global counter and publishes it to a 4-entry ring in BOTH CTAs' shared memory; every other role
+// consumes the ring in order.  A pair that starts late (SMs busy with another kernel, e.g. the
+// collective that overlaps this GEMM) simply draws fewer tiles instead of stretching the launch.
+constexpr int SCHED_SLOTS = 4;
+constexpr uint32_t PEER_BIT = 0x01000000u;
+
+struct TileFeed {
+    uint32_t full0, empty0_leader;  // shared addresses: local sched_full[0]; the LEADER's sched_empty[0]
+    volatile int* tiles;            // local sched_tile[]
+    int slot;
+    uint32_t phase;
+};
+__device__ __forceinline__ bool mbar_try_acq_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS)
+        : "memory");
+    return ok != 0;
+}
+// Next tile index for a consumer.  `lead_lane` is true for the one thread of the caller (a single
+// thread, or lane 0 of a converged warp) that reports the slot as read.  Returns INT_MAX on abort.
+__device__ __forceinline__ int feed_next(TileFeed& f, bool whole_warp, bool lead_lane, volatile int* abort_flag) {
+    const uint32_t bar = f.full0 + 8 * f.slot;
+    bool ok = false;
+#pragma unroll 1
+    for (int tries = 0; tries < WAIT_LIMIT_TRIES; ++tries) {
+        if (mbar_try_acq_cluster(bar, f.phase)) { ok = true; break; }
+        if (*abort_flag) break;
+    }
+    if (!ok) {
+        if (!*abort_flag) *abort_flag = 7;
+        return 0x7fffffff;
+    }
+    const int tile = f.tiles[f.slot];
+    if (whole_warp) __syncwarp();
+    if (lead_lane) mbar_arrive_cluster(f.empty0_leader + 8 * f.slot);
+    if (++f.slot == SCHED_SLOTS) { f.slot = 0; f.phase ^= 1; }
+    return tile;
+}
+
 // raise the pending byte count of a barrier without arriving on it
 __device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -197,10 +244,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint64_t* tmem_empty = tmem_full + 2;     // LEADER: both CTAs' epilogues drained the accumulator
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint64_t* sched_full = tmem_empty + 4;               // local : a tile index was published to this slot
+    uint64_t* sched_empty = sched_full + SCHED_SLOTS;    // LEADER: every consumer of both CTAs has read the slot
+    volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + SCHED_SLOTS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();  // 0 = leader
-    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    // consumers of a published tile: the peer's producer, the MMA thread, 2 x 4 epilogue warps, 2 x 8 expander warps
+    constexpr uint32_t SCHED_CONSUMERS = MODE == DW ? 10 : 10 + 2 * NUM_EXP_WARPS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -212,6 +264,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(tmem_full + a), 1);
             mbar_init(smem_u32(tmem_empty + a), 8);
+        }
+        for (int q = 0; q < SCHED_SLOTS; ++q) {
+            mbar_init(smem_u32(sched_full + q), 1);
+            mbar_init(smem_u32(sched_empty + q), SCHED_CONSUMERS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -230,10 +286,39 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_tiles = p.tiles_m * p.tiles_n;
+    TileFeed feed;
+    feed.full0 = smem_u32(sched_full);
+    feed.empty0_leader = smem_u32(sched_empty) & PEER_MASK;
+    feed.tiles = sched_tile;
+    feed.slot = 0;
+    feed.phase = 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            // The leader's producer is also the scheduler: it draws tile indices from the global
+            // counter, two ahead of the loads, and publishes each to both CTAs.
+            int pub_slot = 0;
+            uint32_t pub_phase = 0;
+            auto publish = [&]() -> int {
+                const int t = atomicAdd(p.tile_counter, 1);
+                if (t == num_tiles + num_clusters - 1) atomicExch(p.tile_counter, 0);  // last draw of the launch
+                if (!mbar_wait(smem_u32(sched_empty + pub_slot), pub_phase ^ 1, abort_flag, 8)) return 0x7fffffff;
+                sched_tile[pub_slot] = t;
+                const uint32_t peer_tile = smem_u32(const_cast<int*>(sched_tile + pub_slot)) | PEER_BIT;
+                asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_tile), "r"(t) : "memory");
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(sched_full + pub_slot)) : "memory");
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(sched_full + pub_slot) | PEER_BIT) : "memory");
+                if (++pub_slot == SCHED_SLOTS) { pub_slot = 0; pub_phase ^= 1; }
+                return t;
+            };
+            int tile, next_tile = 0x7fffffff;
+            if (rank == 0) {
+                tile = publish();
+                next_tile = tile < num_tiles ? publish() : tile;
+            } else {
+                tile = feed_next(feed, false, true, abort_flag);
+            }
             int stage = 0;
             uint32_t phase = 0;
             // bytes counted on the leader's barrier per stage: both CTAs' A tiles (+ DW: both B halves)
@@ -241,7 +326,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t TX_P = MODE == FWD ? 128 * 32 : 128 * 16;
             bool ok = true;
             int gi = 0;
-            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+            while (ok && tile < num_tiles) {
                 int m0, n0;
                 tile_coords(p, tile, m0, n0);
                 m0 += 128 * (int)rank;  // this CTA's rows of A
@@ -282,6 +367,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
+                if (rank == 0) {
+                    tile = next_tile;
+                    if (next_tile < num_tiles) next_tile = publish();
+                } else {
+                    tile = feed_next(feed, false, true, abort_flag);
+                }
             }
         }
     } else if (warp == 1) {
@@ -302,10 +393,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint32_t b_lo = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
             const uint32_t full0 = smem_u32(full), empty0 = smem_u32(empty);
             const uint32_t tfull0 = smem_u32(tmem_full), tempty0 = smem_u32(tmem_empty);
-            int tiles_left = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
             int kb_left = p.num_kb, it = 0;
             uint32_t phase = 0, first_acc = 0, d_tmem = tmem_base;
-            bool ok = tiles_left > 0;
+            bool ok = feed_next(feed, false, true, abort_flag) < num_tiles;  // the tile's coordinates do not matter here
             if (ok) ok = mbar_wait_mma(tempty0, 1, abort_flag, 2);
             bool ready = ok ? mbar_try_cluster(full0, 0) : false;
             int gi = 0;
@@ -325,7 +415,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     first_acc = 1;
                     if (--kb_left == 0) {
                         umma_commit_pair(tfull0 + 8 * (it & 1));
-                        if (--tiles_left == 0) { ok = false; break; }
+                        if (feed_next(feed, false, true, abort_flag) >= num_tiles) { ok = false; break; }
                         ++it;
                         kb_left = p.num_kb;
                         first_acc = 0;
@@ -342,7 +432,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int it = 0;
         bool ok = true;
         const float gamma = MODE == DW ? 1.0f : *p.gamma;
-        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++it) {
+        for (int tile = feed_next(feed, true, lane == 0, abort_flag); ok && tile < num_tiles;
+             tile = feed_next(feed, true, lane == 0, abort_flag), ++it) {
             int m0, n0;
             tile_coords(p, tile, m0, n0);
             m0 += 128 * (int)rank;
@@ -454,7 +545,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             bool ok = true;
             int gi = 0;
-            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+            for (int tile = feed_next(feed, true, lane == 0, abort_flag); ok && tile < num_tiles;
+                 tile = feed_next(feed, true, lane == 0, abort_flag)) {
                 for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                     if (!(ok = mbar_wait(smem_u32(full_p + stage), phase, abort_flag, 6))) break;
                     if (threadIdx.x == 6 * 32) AB_TRACE2(gi, 4);
@@ -558,6 +650,7 @@ template <int MODE>
 static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
     constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (MODE == DW ? 0 : P_BYTES)) + 512;
+    static_assert((4 * STAGES + 4 + 2 * SCHED_SLOTS) * 8 + 16 + 4 * SCHED_SLOTS <= 512, "barrier block");
     static bool attr_set[8] = {false, false, false, false, false, false, false, false};
     if (!attr_set[ctx->device & 7]) {
         AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -568,6 +661,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     constexpr int KB = MODE == FWD ? 128 : 64;
     p.num_kb = (p.K + KB - 1) / KB;
     p.status = ctx->dev_status;
+    p.tile_counter = ctx->dev_status + 8;  // zero between launches: the last CTA pair of a launch resets it
 #ifdef AB_GEMM_TRACE
     p.trace = reinterpret_cast<long long*>(ctx->stage[5]);
     p.debug_flags = getenv("AB_TRACE_NOLOAD") ? 1 : 0;
