@@ -52,6 +52,8 @@ SIGNATURES = {
     "ab_weights_set_gamma": (_i, [_vp, _f]),
     "ab_weights_get_gamma": (_i, [_vp, C.POINTER(_f)]),
     "ab_fq_absmean_pack": (_i, [_vp, _vp, _vp, _vp, _i, _i]),
+    "ab_fq_shard_abs_sum": (_i, [_vp, _vp, _vp, _vp]),
+    "ab_fq_shard_pack": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i, _i]),
     "ab_weights_fq_report": (_i, [_vp, C.POINTER(FqReport)]),
     "ab_quantize_and_pack_host": (_i, [_vp, _vp, _sz, C.POINTER(_f), _vp]),
     "ab_calibrate_scale": (_i, [_vp, _vp, _sz, _vp]),

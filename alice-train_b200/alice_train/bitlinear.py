@@ -55,6 +55,29 @@ class BitLinearWeights(TernaryWeightKernel):
                                                 int(want_stats)), self.ctx.handle)
         return self
 
+    def shard_abs_sum(self, latent_shard: torch.Tensor, sum_abs: torch.Tensor | None = None) -> torch.Tensor:
+        """Step (a) of the row-sharded quantiser: f64 sum of |w| over this GPU's rows, as a 1-element CUDA
+        tensor the caller all-reduces (parallel.global_abs_sum)."""
+        if latent_shard.dtype != torch.float32 or not latent_shard.is_cuda or not latent_shard.is_contiguous():
+            raise ValueError("latent weights must be a contiguous float32 CUDA tensor")
+        if latent_shard.numel() != self._out * self._in:
+            raise AssertionError("assertion `left == right` failed: latent.len() == out*in")
+        if sum_abs is None:
+            sum_abs = torch.zeros(1, dtype=torch.float64, device=latent_shard.device)
+        _ffi.check(self._lib.ab_fq_shard_abs_sum(self.ctx.handle, _dp(latent_shard), self._h, _dp(sum_abs)), self.ctx.handle)
+        return sum_abs
+
+    def quantize_shard_(self, latent_shard: torch.Tensor, sum_abs_total: torch.Tensor, n_total: int,
+                        fq_out: torch.Tensor | None = None, guard: int = _ffi.AB_GUARD_INV_ZERO, want_stats: bool = False):
+        """Step (b): codes of this GPU's rows with gamma = f32(sum_abs_total / n_total) of the whole tensor."""
+        if sum_abs_total.dtype != torch.float64 or not sum_abs_total.is_cuda:
+            raise ValueError("sum_abs_total must be a float64 CUDA tensor")
+        if latent_shard.numel() != self._out * self._in:
+            raise AssertionError("assertion `left == right` failed: latent.len() == out*in")
+        _ffi.check(self._lib.ab_fq_shard_pack(self.ctx.handle, _dp(latent_shard), self._h, _dp(sum_abs_total), n_total,
+                                              _dp(fq_out), guard, int(want_stats)), self.ctx.handle)
+        return self
+
 
 @dataclasses.dataclass
 class QuantizedActivations:

@@ -62,6 +62,14 @@ def global_gamma(sum_abs_local: torch.Tensor, n_total: int, group=None, floor: b
     return gamma
 
 
+def global_abs_sum(sum_abs_local: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place all-reduce of the 8-byte f64 shard sums of |w| (the only exchange the row-sharded quantiser needs)."""
+    assert sum_abs_local.dtype == torch.float64
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(sum_abs_local, op=dist.ReduceOp.SUM, group=group)
+    return sum_abs_local
+
+
 def gather_rows(y_local: torch.Tensor, group=None) -> torch.Tensor:
     """Forward of a row-sharded layer: concatenate the [tokens x out/g] shards along features."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:

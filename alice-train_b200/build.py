@@ -66,5 +66,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+def build_cpp_test() -> str:
+    """Compiles tests/cpp/host_mirror_test.cpp (the C++ host mirror's own test) with g++ against the library."""
+    src = os.path.join(ROOT, "tests", "cpp", "host_mirror_test.cpp")
+    hdr = os.path.join(HERE, "cpp", "alice_train.hpp")
+    exe = os.path.join(ROOT, "tests", "cpp", "_build", "host_mirror_test")
+    os.makedirs(os.path.dirname(exe), exist_ok=True)
+    deps = [src, hdr, os.path.join(ROOT, "include", "alice_b200.h"), OUT]
+    if os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
+        return exe
+    subprocess.check_call(["/usr/bin/g++", "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"),
+                           "-I", os.path.join(HERE, "cpp"), src, "-o", exe, "-L", HERE, "-lalice_b200",
+                           "-Wl,-rpath," + HERE, "-Wl,-rpath,$ORIGIN/../../../alice-train_b200"])
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -345,6 +345,29 @@ int ab_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float*
     return abk_fq_absmean_pack(ctx, w_latent, w, fq_out, guard, want_stats);
 }
 
+int ab_fq_shard_abs_sum(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_shard, double* sum_abs_dev) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w_shard && sum_abs_dev, AB_ERR_NULL);
+    AB_REQUIRE(w_shard->ctx == ctx, AB_ERR_STATE);
+    if (w_shard->out * w_shard->in) AB_REQUIRE(w_latent_shard, AB_ERR_NULL);
+    AB_REQUIRE((reinterpret_cast<uintptr_t>(w_latent_shard) & 3) == 0 && (reinterpret_cast<uintptr_t>(sum_abs_dev) & 7) == 0, AB_ERR_ALIGN);
+    return abk_fq_shard_abs_sum(ctx, w_latent_shard, w_shard, sum_abs_dev);
+}
+
+int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_shard, const double* sum_abs_total_dev,
+                     size_t n_total, float* fq_out, int guard, int want_stats) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(w_shard && sum_abs_total_dev, AB_ERR_NULL);
+    AB_REQUIRE(w_shard->ctx == ctx, AB_ERR_STATE);
+    AB_REQUIRE(w_shard->codes_fwd && w_shard->codes_t, AB_ERR_STATE);
+    AB_REQUIRE(guard == AB_GUARD_INV_ZERO || guard == AB_GUARD_FLOOR, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(n_total >= w_shard->out * w_shard->in, AB_ERR_SHAPE);
+    if (w_shard->out * w_shard->in) AB_REQUIRE(w_latent_shard, AB_ERR_NULL);
+    AB_REQUIRE((reinterpret_cast<uintptr_t>(w_latent_shard) & 3) == 0 && (reinterpret_cast<uintptr_t>(sum_abs_total_dev) & 7) == 0,
+               AB_ERR_ALIGN);
+    return abk_fq_shard_pack(ctx, w_latent_shard, w_shard, sum_abs_total_dev, n_total, fq_out, guard, want_stats);
+}
+
 int ab_weights_fq_report(ab_weights* w, ab_fq_report* r) {
     AB_REQUIRE(w && r, AB_ERR_NULL);
     ab_ctx* ctx = w->ctx;

@@ -589,11 +589,54 @@ static int reduce_launch(ab_ctx* ctx, const float* w, size_t n, ab_fq_dev_report
     return AB_OK;
 }
 
+// gamma of a row shard from the sum of |w| over ALL shards (a device double the caller has all-reduced)
+// and the element count of the whole tensor; same f64 -> f32 arithmetic and guards as pass A.
+__global__ void shard_gamma_kernel(ab_fq_dev_report* rep, float* gamma_out, const double* total, unsigned long long n_total,
+                                   int guard) {
+    float gamma = 0.0f, inv = 0.0f;
+    if (n_total) {
+        gamma = (float)(*total / (double)n_total);
+        if (guard == AB_GUARD_FLOOR) {
+            if (gamma < 1e-10f) gamma = 1e-10f;
+            inv = 1.0f / gamma;
+        } else {
+            inv = gamma > 1e-10f ? 1.0f / gamma : 0.0f;
+        }
+    }
+    rep->gamma = gamma;
+    rep->inv_gamma = inv;
+    rep->sum_err = rep->dot_wq = rep->dot_ww = rep->dot_qq = 0.0;
+    rep->n_plus = rep->n_minus = rep->n_threshold = 0ull;
+    rep->w_min = __uint_as_float(0xffffffffu);
+    rep->w_max = __uint_as_float(0u);
+    *gamma_out = gamma;
+}
+
+static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int want_stats);
+
 int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int guard,
                         int want_stats) {
-    const size_t n = w->out * w->in;
-    int st = reduce_launch(ctx, w_latent, n, w->report_dev, w->gamma_dev, guard, 0);
+    int st = reduce_launch(ctx, w_latent, w->out * w->in, w->report_dev, w->gamma_dev, guard, 0);
     if (st) return st;
+    return pack_launch(ctx, w_latent, w, fq_out, want_stats);
+}
+
+int abk_fq_shard_abs_sum(ab_ctx* ctx, const float* w_latent, ab_weights* w, double* sum_abs_dev) {
+    int st = reduce_launch(ctx, w_latent, w->out * w->in, w->report_dev, w->gamma_dev, AB_GUARD_INV_ZERO, 0);
+    if (st) return st;
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(sum_abs_dev, &w->report_dev->sum_abs, sizeof(double), cudaMemcpyDeviceToDevice, ctx->stream));
+    return AB_OK;
+}
+
+int abk_fq_shard_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, const double* total_dev, size_t n_total,
+                      float* fq_out, int guard, int want_stats) {
+    shard_gamma_kernel<<<1, 1, 0, ctx->stream>>>(w->report_dev, w->gamma_dev, total_dev, (unsigned long long)n_total, guard);
+    AB_LAUNCH_CHECK(ctx);
+    return pack_launch(ctx, w_latent, w, fq_out, want_stats);
+}
+
+static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int want_stats) {
+    const size_t n = w->out * w->in;
     const size_t wpr = w->pitch / 4;
     const size_t words = w->out * wpr;
     if (words) {

@@ -37,6 +37,9 @@ WORKLOADS = {
     # name: (tokens per GPU, [(projection, out_features, in_features)])
     "llama3-8b-mlp": (4096, [("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]),
     "small": (1024, [("gate", 2048, 1024), ("down", 1024, 2048)]),
+    # one Llama-3-70B-shaped decoder layer, 8192 tokens per STEP (rows of W sharded over the GPUs; run_rowshard)
+    "llama3-70b-layer": (8192, [("q", 8192, 8192), ("k", 1024, 8192), ("v", 1024, 8192), ("o", 8192, 8192),
+                                ("gate", 28672, 8192), ("up", 28672, 8192), ("down", 8192, 28672)]),
 }
 METRIC = "BitLinear fwd+bwd tokens/s at Llama-8B shape"
 UNIT = "tokens/s"
@@ -450,6 +453,152 @@ def run_hbm(args):
     print(json.dumps(line), flush=True)
     return 0
 
+# ------------------------------------------- one Llama-3-70B-shaped layer, output rows sharded
+ROWSHARD_TOKENS, ROWSHARD_LINEARS = WORKLOADS["llama3-70b-layer"]
+
+
+def run_rowshard(args):
+    """--workload llama3-70b-layer: the seven ternary linears of one Llama-3-70B decoder layer (hidden 8192,
+    intermediate 28672, 8 KV heads x 128), 8192 tokens per step, W ~ N(0, 0.015^2).  Every GPU holds out/N rows of
+    each latent and packed matrix (strong scaling: the step's work is fixed).  One step, per linear: the two-call
+    quantiser with its 8-byte all-reduce of sum|w|, act-quant (replicated), forward of the local rows followed by
+    an all-gather of y, the dx partial product followed by a reduce-scatter over tokens, and the local rows of dW
+    (no exchange).  Both exchanges are issued asynchronously and waited for at the end of the step."""
+    import torch
+    import torch.distributed as dist
+
+    import alice_train
+    from alice_train import bitlinear as bl, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a B200: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = alice_train.GpuContext.on_torch_stream(local)
+    tokens = ROWSHARD_TOKENS
+    assert tokens % world == 0
+    pk = peaks()
+    gen = torch.Generator(device=dev)
+    layers = []
+    for li, (name, out, inn) in enumerate(ROWSHARD_LINEARS):
+        r0, r1 = parallel.row_shard(out, world, rank, align=128)
+        rows = r1 - r0
+        gen.manual_seed(7000 + 131 * li + rank)     # this GPU's rows of the latent matrix
+        w_lat = torch.randn((rows, inn), generator=gen, device=dev, dtype=torch.float32) * 0.015
+        gen.manual_seed(8000 + li)                  # x and dy are the same on every GPU (replicated activations)
+        x = torch.randn((tokens, inn), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        dy = (torch.randn((tokens, out), generator=gen, device=dev, dtype=torch.float32) * 1e-2).to(torch.bfloat16)
+        layers.append(dict(
+            name=name, out=out, inn=inn, rows=rows, w=bl.BitLinearWeights(rows, inn, ctx), w_lat=w_lat, x=x,
+            dy=dy[:, r0:r1].contiguous(), sum_abs=torch.zeros(1, dtype=torch.float64, device=dev),
+            qa=bl.QuantizedActivations(torch.empty((tokens, inn), dtype=torch.int8, device=dev),
+                                       torch.empty(tokens, dtype=torch.float32, device=dev),
+                                       torch.empty(tokens, dtype=torch.int32, device=dev)),
+            y=torch.empty((tokens, rows), dtype=torch.bfloat16, device=dev),
+            y_all=torch.empty((world, tokens, rows), dtype=torch.bfloat16, device=dev) if world > 1 else None,
+            dx=torch.empty((tokens, inn), dtype=torch.bfloat16, device=dev),
+            dx_mine=torch.empty((tokens // world, inn), dtype=torch.bfloat16, device=dev) if world > 1 else None,
+            dW=torch.zeros((rows, inn), dtype=torch.float32, device=dev)))
+        del dy
+    ctx.sync()
+    classes = ("fq", "act_quant", "fwd", "dx", "dw")
+    ev = {c: [] for c in classes}
+
+    def step(record: bool):
+        handles = []
+        for L in layers:
+            def timed(cls, fn):
+                if record:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    fn()
+                    b.record()
+                    ev[cls].append((a, b))
+                else:
+                    fn()
+
+            def quantise():
+                L["w"].shard_abs_sum(L["w_lat"], L["sum_abs"])
+                parallel.global_abs_sum(L["sum_abs"])          # 8 bytes; every GPU derives the same gamma
+                L["w"].quantize_shard_(L["w_lat"], L["sum_abs"], L["out"] * L["inn"])
+            timed("fq", quantise)
+            timed("act_quant", lambda: bl.act_quant_int8(ctx, L["x"], L["qa"]))
+            timed("fwd", lambda: bl.bitlinear_fwd(L["w"], L["qa"], y=L["y"]))
+            if world > 1:
+                handles.append(dist.all_gather_into_tensor(L["y_all"], L["y"], async_op=True))
+            timed("dx", lambda: bl.bitlinear_dx(L["w"], L["dy"], dx=L["dx"]))
+            if world > 1:
+                handles.append(dist.reduce_scatter_tensor(L["dx_mine"], L["dx"], op=dist.ReduceOp.SUM, async_op=True))
+            timed("dw", lambda: bl.ste_dw(ctx, L["dy"], L["x"], L["dW"], beta=0.0))
+        for hnd in handles:
+            hnd.wait()
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(False)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    fence()
+    launches0 = ctx.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step(True)
+    t1.record()
+    fence()
+    launches = ctx.launch_count() - launches0
+    ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+    per = {}
+    for c in classes:
+        ts = [a.elapsed_time(b) for a, b in ev[c]]
+        per[c] = {"launches": len(ts), "ms_per_step": sum(ts) / args.steps}
+    ops_rank = 2.0 * tokens * sum(L["rows"] * L["inn"] for L in layers)       # per GEMM class, this GPU, one step
+    for c in ("fwd", "dx", "dw"):
+        per[c]["tops"] = ops_rank / (per[c]["ms_per_step"] * 1e-3) / 1e12
+    fq_bytes = 4.25 * sum(L["rows"] * L["inn"] for L in layers)
+    per["fq"]["gbs"] = fq_bytes / (per["fq"]["ms_per_step"] * 1e-3) / 1e9
+    dom = max(("fwd", "dx", "dw"), key=lambda c: per[c]["ms_per_step"])
+    peak_bf16 = pk["bf16_tflops_sustained"]
+    gather_bytes = sum(tokens * L["out"] * 2 for L in layers) if world > 1 else 0
+    rs_bytes = sum(tokens * L["inn"] * 2 for L in layers) if world > 1 else 0
+    if rank == 0:
+        line = {
+            "metric": "BitLinear fwd+bwd tokens/s, one Llama-3-70B-shaped layer, output rows sharded", "value": tokens * args.steps / (ms_total * 1e-3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 forward (s32 accumulate), bf16 backward (f32 accumulate)", "data": "synthetic",
+            "config": {"workload": "llama3-70b-layer", "tokens_per_step": tokens, "linears": {n: [o, i] for n, o, i in ROWSHARD_LINEARS},
+                       "parallelism": f"rows/{world}" if world > 1 else "single",
+                       "step": "per linear: quantise the local rows (8-byte all-reduce of sum|w|), act-quant, fwd -> all-gather y (bf16), "
+                               "dx partial -> reduce-scatter over tokens (bf16), dW rows (local)",
+                       "exchange_bytes_per_step": {"all_gather_y_total": gather_bytes, "reduce_scatter_dx_input_per_gpu": rs_bytes},
+                       "l2": "latent shards, dW and activations exceed the 126 MB L2 at every N; no explicit flush"},
+            "roofline": {"bound": "tensor", "kernel": f"gemm_pair_kernel<{dom.upper()}>", "achieved": per[dom]["tops"], "peak": peak_bf16,
+                         "unit": "TFLOP/s", "frac": per[dom]["tops"] / peak_bf16, "traffic": None,
+                         "peak_source": f"{pk['source']} bf16 sustained"},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks, "kernels": per,
+            "tops_total": 6.0 * tokens * sum(o * i for _, o, i in ROWSHARD_LINEARS) * args.steps / (ms_total * 1e-3) / 1e12,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -468,6 +617,8 @@ def main():
         return run_reference(args)
     if args.workload == "hbm-kernels":
         return run_hbm(args)
+    if args.workload == "llama3-70b-layer":
+        return run_rowshard(args)
     return run_native(args)
 
 

@@ -130,6 +130,18 @@ AB_API int ab_weights_get_gamma(ab_weights* w, float* gamma);
  * T = 1 (src/bin/train_qat_70b.rs:2109-2172). */
 AB_API int ab_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out,
                               int guard, int want_stats);
+/* The same quantiser for a tensor whose output rows are split over several GPUs: gamma is a property of the
+ * WHOLE tensor, so each GPU (a) reduces sum|w| of its rows in f64 into the device double `sum_abs_dev`, the
+ * caller sums those 8-byte values over the GPUs (ncclAllReduce, f64, sum), and (b) packs its rows with
+ * gamma = f32(total / n_total), n_total = elements of the whole tensor.  `w_shard` is a handle created with
+ * this GPU's row count; report counters (n_plus, n_minus, n_threshold, stats) then cover the shard, gamma the
+ * whole tensor.  The reference quantises on one host (fq_vec, src/qwen35.rs:221-251; the gamma pass of
+ * fused_merge_and_quantize_alpha, src/bin/train_qat_70b.rs:2109-2131): these two calls are that function cut
+ * at the point where the sum becomes gamma. */
+AB_API int ab_fq_shard_abs_sum(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_shard, double* sum_abs_dev);
+AB_API int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_shard,
+                            const double* sum_abs_total_dev, size_t n_total, float* fq_out, int guard,
+                            int want_stats);
 /* Waits for the stream and copies the report of the last ab_fq_absmean_pack on `w`. */
 AB_API int ab_weights_fq_report(ab_weights* w, ab_fq_report* report);
 

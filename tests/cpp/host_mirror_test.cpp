@@ -1,0 +1,275 @@
+// Replays the reference crate's unit-test vectors through the C++ host mirror (alice_train.hpp).
+// Each case names the reference test it restates (file:line within the reference project).
+// Usage: host_mirror_test            full run on device 0 (exit 0 when every case passes)
+//        host_mirror_test --no-device   expects no usable device: new_blocking() must be empty
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "alice_train.hpp"
+
+using namespace alice_train;
+using F = std::vector<float>;
+using T = std::vector<int8_t>;
+
+static int g_fail = 0, g_run = 0;
+static void expect(bool ok, const char* cite, const char* what) {
+    ++g_run;
+    if (!ok) {
+        ++g_fail;
+        std::printf("FAIL %s: %s\n", cite, what);
+    }
+}
+static bool close_to(const F& a, const F& b, float tol) {
+    if (a.size() != b.size()) return false;
+    for (size_t i = 0; i < a.size(); ++i)
+        if (!(std::fabs(a[i] - b[i]) <= tol)) return false;
+    return true;
+}
+template <class Fn>
+static bool panics(Fn&& f) {
+    try {
+        f();
+    } catch (const AssertionError&) {
+        return true;
+    }
+    return false;
+}
+
+static void backward_cases() {
+    struct Case { const char* cite; T w; size_t out, in; F dy, dx; };
+    const Case cases[] = {
+        {"src/backward.rs:199-206", {1, 0, 0, 1}, 2, 2, {3, 7}, {3, 7}},
+        {"src/backward.rs:209-216", {1, -1, 0, 1}, 2, 2, {2, 3}, {2, 1}},
+        {"src/backward.rs:219-227", {1, -1, 0, 1, 1, -1, 0, -1, 1}, 3, 3, {1, 1, 1}, {2, -1, 0}},
+        {"src/backward.rs:230-236", {0, 0, 0, 0}, 2, 2, {5, 3}, {0, 0}},
+    };
+    for (const Case& c : cases) {
+        auto w = TernaryWeightKernel::from_ternary(c.w, c.out, c.in);
+        F dx(c.in, 99.0f);
+        ternary_matvec_backward(c.dy, w, dx);
+        expect(close_to(dx, c.dx, 1e-6f), c.cite, "ternary_matvec_backward");
+    }
+    // adjoint identity <Wx, dy> == <x, W^T dy>, the property behind src/backward.rs:239-300
+    {
+        const size_t out = 37, in = 131;
+        T w(out * in);
+        F x(in), dy(out), y(out), dx(in);
+        uint32_t s = 12345;
+        auto next = [&] { s = s * 1664525u + 1013904223u; return s >> 8; };
+        for (auto& v : w) v = static_cast<int8_t>(next() % 3) - 1;
+        for (auto& v : x) v = static_cast<float>(next() % 2001) / 1000.0f - 1.0f;
+        for (auto& v : dy) v = static_cast<float>(next() % 2001) / 1000.0f - 1.0f;
+        auto k = TernaryWeightKernel::from_ternary(w, out, in);
+        ternary_matvec_kernel(x, k, y);
+        ternary_matvec_backward(dy, k, dx);
+        double lhs = 0, rhs = 0;
+        for (size_t j = 0; j < out; ++j) lhs += double(y[j]) * dy[j];
+        for (size_t i = 0; i < in; ++i) rhs += double(x[i]) * dx[i];
+        expect(std::fabs(lhs - rhs) <= 1e-3 * (1.0 + std::fabs(lhs)), "src/backward.rs:239-300", "adjoint identity");
+        expect(k.words_per_row() == (in + 31) / 32 && k.plus_bits().size() == out * k.words_per_row(), "alice_ml::ops", "bit-plane shape");
+    }
+}
+
+static void bitlinear_cases() {
+    auto w = TernaryWeightKernel::from_ternary(T{1, -1, 0, 1}, 2, 2);
+    {
+        F dx(2);
+        bitlinear_backward({2, 3}, {1, 1}, w, false, 1e-5f, dx);
+        expect(close_to(dx, {1, 0}, 1e-6f), "src/backward.rs:368-376", "grad_input without pre_norm");
+    }
+    {
+        F dx(2), db(2);
+        bitlinear_backward({2, 3}, {0.5f, 1.5f}, w, false, 1e-5f, dx, &db);
+        expect(close_to(db, {0.5f, 1.5f}, 1e-6f), "src/backward.rs:379-396", "grad_bias == grad_output");
+    }
+    {
+        auto w3 = TernaryWeightKernel::from_ternary(T{1, 0, -1, 1, 0, -1, 1, 0, -1}, 3, 3);
+        F dx(3), db(3);
+        bitlinear_backward({1, 2, 3}, {7, -3, 0.5f}, w3, false, 1e-5f, dx, &db);
+        expect(close_to(db, {7, -3, 0.5f}, 1e-6f), "src/backward.rs:399-421", "grad_bias 3x3");
+    }
+    {
+        // pre_norm: dx = (g - x_hat * mean(g * x_hat)) / rms with g = W^T dy (src/backward.rs:118-150)
+        F x{2, 3}, dy{1, 1}, dx(2), db(2);
+        bitlinear_backward(x, dy, w, true, 1e-5f, dx, &db);
+        const float rms = std::sqrt((4.0f + 9.0f) / 2.0f + 1e-5f);
+        const float g0 = 1.0f, g1 = 0.0f, h0 = 2.0f / rms, h1 = 3.0f / rms;
+        const float dot = (g0 * h0 + g1 * h1) / 2.0f;
+        expect(close_to(dx, {(g0 - h0 * dot) / rms, (g1 - h1 * dot) / rms}, 1e-5f), "src/backward.rs:498-519", "pre_norm grad_input");
+        expect(close_to(db, {1, 1}, 1e-6f), "src/backward.rs:498-519", "pre_norm grad_bias");
+    }
+}
+
+static void ste_cases() {
+    struct Case { const char* cite; F x, dy, dw0, dw; };
+    const Case cases[] = {
+        {"src/backward.rs:536-545", {1, 2}, {3, 5}, {0, 0, 0, 0}, {3, 6, 5, 10}},
+        {"src/backward.rs:548-554", {1}, {2}, {1}, {3}},
+        {"src/backward.rs:557-569", {1, 2}, {1, 2, 3}, {0, 0, 0, 0, 0, 0}, {1, 2, 2, 4, 3, 6}},
+        {"src/backward.rs:572-578", {1, 2}, {0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}},
+    };
+    for (const Case& c : cases) {
+        F dw = c.dw0;
+        ste_weight_grad(c.x, c.dy, dw);
+        expect(close_to(dw, c.dw, 1e-6f), c.cite, "ste_weight_grad");
+    }
+}
+
+static void mismatch_cases() {
+    auto w = TernaryWeightKernel::from_ternary(T{1, 0, 0, 1}, 2, 2);
+    expect(panics([&] { F dy(1), dx(2); ternary_matvec_backward(dy, w, dx); }), "src/backward.rs:611-617", "short grad_output panics");
+    expect(panics([&] { F dy(2), dx(3); ternary_matvec_backward(dy, w, dx); }), "src/backward.rs:619-625", "long grad_input panics");
+    expect(panics([&] { F x(1), dy(2), dx(2); bitlinear_backward(x, dy, w, false, 1e-5f, dx); }), "src/backward.rs:627-641", "short input panics");
+    expect(panics([&] { F x(2), dy(1), dw(3); ste_weight_grad(x, dy, dw); }), "src/backward.rs:643-646", "wrong grad_weights length panics");
+    expect(panics([&] { TernaryWeightKernel::from_ternary(T{1, 0, 1}, 2, 2); }), "alice_ml::ops", "from_ternary length");
+}
+
+static void qat_cases() {
+    {
+        FakeQuantize fq(QatConfig::ternary());
+        fq.calibrate_scale({1.0f, -1.0f, 0.5f, -0.5f});
+        expect(std::fabs(fq.scale() - 0.75f) <= 1e-6f, "src/qat.rs:558-564", "calibrate_scale mean|w|");
+        FakeQuantize e(QatConfig::ternary());
+        e.calibrate_scale({});
+        expect(std::fabs(e.scale() - 1.0f) <= 1e-6f, "src/qat.rs:567-571", "empty keeps scale 1");
+    }
+    {
+        FakeQuantize fq(QatConfig::ternary());
+        F w{0.9f, -0.8f, 0.05f, 0.4f, -0.45f, 2.5f}, q(w.size());
+        fq.calibrate_scale(w);
+        fq.fake_quantize_forward(w, q);
+        bool in_set = true;
+        for (float v : q) {
+            const float t = v / fq.scale();
+            in_set = in_set && (std::fabs(t) < 1e-5f || std::fabs(std::fabs(t) - 1.0f) < 1e-5f);
+        }
+        expect(in_set, "src/qat.rs:532-555", "ternary forward stays in {-s,0,+s}");
+        expect(panics([&] { F q2(3); fq.fake_quantize_forward(w, q2); }), "src/qat.rs:171", "length mismatch panics");
+    }
+    {
+        FakeQuantize fq(QatConfig::ternary());
+        F gi(3);
+        fq.ste_backward({1, -2, 3}, gi);
+        expect(close_to(gi, {1, -2, 3}, 0.0f), "src/qat.rs:583-589", "ste identity");
+        QatConfig c = QatConfig::ternary();
+        c.grad_clip = 1.5f;
+        FakeQuantize fc(c);
+        fc.ste_backward({3, -2, 0.5f}, gi);
+        expect(close_to(gi, {1.5f, -1.5f, 0.5f}, 1e-6f), "src/qat.rs:592-604", "ste clip");
+    }
+    {
+        QatConfig c = QatConfig::ternary();
+        c.temperature_decay = 0.9f;
+        FakeQuantize fq(c);
+        fq.step_temperature();
+        const float t1 = fq.temperature();
+        fq.step_temperature();
+        expect(std::fabs(t1 - 0.9f) < 1e-4f && std::fabs(fq.temperature() - 0.81f) < 1e-4f, "src/qat.rs:609-621", "temperature decay");
+        QatConfig f = QatConfig::ternary();
+        f.temperature = 0.02f;
+        f.temperature_decay = 0.1f;
+        FakeQuantize ff(f);
+        ff.step_temperature();
+        expect(std::fabs(ff.temperature() - 0.01f) < 1e-6f, "src/qat.rs:624-633", "temperature floor");
+        expect(levels(QuantBits::Ternary) == 3 && levels(QuantBits::Int4) == 16 && levels(QuantBits::Int8) == 256 &&
+                   std::fabs(effective_bits(QuantBits::Ternary) - 1.58f) < 0.01f, "src/qat.rs:452-465", "QuantBits levels");
+    }
+    {
+        // one-weight regression y = w*x, MSE loss; the loss after 100 steps is not above the first (src/qat.rs:683-733)
+        QatTrainer trainer(1, 0.1f, QatConfig::ternary());
+        FakeQuantize fq(QatConfig::ternary());
+        F latent{0.0f}, qbuf(1), input{1.0f}, target{0.5f}, out(1), go(1), gw(1);
+        auto forward = [](const F& w, const F& x, F& y) { y[0] = w[0] * x[0]; };
+        auto loss = [](const F& y, const F& t, F& g) { const float d = y[0] - t[0]; g[0] = 2.0f * d; return d * d; };
+        float first = 0, last = 0;
+        for (int s = 0; s < 100; ++s) {
+            auto r = trainer.qat_step(latent, qbuf, input, target, out, go, gw, fq, forward, loss);
+            if (s == 0) first = r.first;
+            last = r.first;
+        }
+        expect(last <= first + 1e-6f, "src/qat.rs:683-733", "qat_step loss does not grow");
+        expect(trainer.stats().quantization_mae >= 0.0f, "src/qat.rs:683-733", "stats updated");
+        trainer.step_epoch(fq);
+        expect(fq.temperature() < 1.0f, "src/qat.rs:436-439", "step_epoch decays temperature");
+    }
+}
+
+static void export_cases() {
+    const T cases[] = {{1, -1, 0, 1, -1, 0, 0, 1, -1}, {}, {-1}, {0}, {1}, {1, 1, 1, 1, -1}};
+    for (const T& v : cases) {
+        auto packed = pack_ternary(v);
+        expect(packed.size() == (v.size() + 3) / 4 && unpack_ternary(packed, v.size()) == v, "src/export.rs:763-785", "pack/unpack round trip");
+    }
+    {
+        // encoding 00 = 0, 01 = +1, 10 = -1, element i at bits 2*(i%4) (src/export.rs:118-141)
+        auto p = pack_ternary(T{1, -1, 0, 1});
+        expect(p.size() == 1 && p[0] == (0x1 | (0x2 << 2) | (0x0 << 4) | (0x1 << 6)), "src/export.rs:118-141", "2-bit encoding");
+    }
+    {
+        auto r = quantize_and_pack({1.0f, -1.0f, 0.5f, -0.5f, 0.0f});
+        expect(std::fabs(r.first - 0.6f) <= 1e-5f && r.second.size() == 2, "src/export.rs:825-830", "quantize_and_pack scale");
+        auto e = quantize_and_pack({});
+        expect(e.first == 0.0f && e.second.empty(), "src/export.rs:818-822", "empty quantize_and_pack");
+        auto t = quantize_and_pack({0.5f, -0.3f, 0.01f, 0.8f, -0.9f});
+        auto u = unpack_ternary(t.second, 5);
+        expect(u == T({1, -1, 0, 1, -1}), "src/export.rs:798-815", "codes of a small tensor");
+    }
+    {
+        auto p = pack_ternary(T{1, -1, 0, 1});
+        expect(close_to(dequantize(p, 4, 0.5f), {0.5f, -0.5f, 0.0f, 0.5f}, 1e-6f), "src/export.rs:833-842", "dequantize");
+    }
+    {
+        // C += scale * A B^T against a direct sum (src/blas.rs:403-457)
+        const size_t m = 3, n = 5, k = 9;
+        T b(n * k);
+        F a(m * k), c(m * n, 1.0f), want(m * n, 1.0f);
+        for (size_t i = 0; i < b.size(); ++i) b[i] = static_cast<int8_t>((i * 7 + 1) % 3) - 1;
+        for (size_t i = 0; i < a.size(); ++i) a[i] = 0.25f * static_cast<float>(static_cast<int>(i % 11) - 5);
+        std::vector<uint8_t> packed;
+        for (size_t r = 0; r < n; ++r) {
+            auto row = pack_ternary(T(b.begin() + r * k, b.begin() + (r + 1) * k));
+            packed.insert(packed.end(), row.begin(), row.end());
+        }
+        for (size_t i = 0; i < m; ++i)
+            for (size_t j = 0; j < n; ++j) {
+                float s = 0;
+                for (size_t p = 0; p < k; ++p) s += a[i * k + p] * b[j * k + p];
+                want[i * n + j] += 0.5f * s;
+            }
+        blas::ternary_matmul_bt(a, packed, 0.5f, c, m, n, k);
+        expect(close_to(c, want, 1e-5f), "src/blas.rs:403-457", "ternary_matmul_bt");
+    }
+}
+
+int main(int argc, char** argv) {
+    if (argc > 1 && std::strcmp(argv[1], "--no-device") == 0) {
+        auto c = GpuContext::new_blocking(0);
+        if (c) {
+            std::printf("a device is present; --no-device expects none\n");
+            return 2;
+        }
+        bool threw = false;
+        try {
+            GpuContext::global();
+        } catch (const Error& e) {
+            threw = e.status == AB_ERR_NO_DEVICE;
+        }
+        std::printf(threw ? "no-device ok\n" : "global() did not fail without a device\n");
+        return threw ? 0 : 1;
+    }
+    try {
+        backward_cases();
+        bitlinear_cases();
+        ste_cases();
+        mismatch_cases();
+        qat_cases();
+        export_cases();
+    } catch (const std::exception& e) {
+        std::printf("unexpected exception: %s\n", e.what());
+        return 3;
+    }
+    std::printf("%d checks, %d failed\n", g_run, g_fail);
+    return g_fail ? 1 : 0;
+}

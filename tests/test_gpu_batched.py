@@ -119,55 +119,85 @@ def test_dw_vs_oracle(env, orc, m, out, inn):
     assert rel_err(dw.cpu().numpy(), 2 * ref) <= RTOL_F32
 
 
+def _check_linear_sampled(env, orc, r, name, m, out, inn, seed, std, samples=400):
+    """One linear at full size: codes, gamma and act-quant compared in full; forward accumulators (exact),
+    forward output (exact), dx and dW (RTOL_F32) on seeded samples; two whole-output properties."""
+    at, bl, ctx, torch = env
+    w_lat = normal_f32(seed, (out, inn), std)
+    h = bl.BitLinearWeights(out, inn, ctx).quantize_(torch.from_numpy(w_lat).cuda())
+    g, codes, packed = orc.quantize_and_pack(w_lat)
+    codes = codes.reshape(out, inn)
+    ctx.sync()
+    assert h.gamma == g and np.array_equal(h.to_packed(), packed)
+    del w_lat, packed
+    x, dy = normal_f32(seed + 100, (m, inn)), normal_f32(seed + 200, (m, out), 1e-2)
+    xt, xr = to_bf16_tensor(orc, x, "cuda")
+    dyt, dyr = to_bf16_tensor(orc, dy, "cuda")
+    del x, dy
+    qa = bl.act_quant_int8(ctx, xt)
+    acc = torch.empty((m, out), dtype=torch.int32, device="cuda")
+    y = bl.bitlinear_fwd(h, qa, dtype=torch.float32, acc_out=acc)
+    dx = bl.bitlinear_dx(h, dyt, dtype=torch.float32)
+    dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
+    bl.ste_dw(ctx, dyt, xt, dw, beta=0.0)
+    ctx.sync()
+    xq_ref, s_ref = orc.act_quant_int8(xr)
+    assert np.array_equal(qa.xq.cpu().numpy(), xq_ref)
+    wq = codes.astype(np.float32) * np.float32(g)
+    ts, js, is_ = r.integers(0, m, samples), r.integers(0, out, samples), r.integers(0, inn, samples)
+    idx_tj = torch.from_numpy(ts * out + js).cuda()
+    acc_s = acc.reshape(-1)[idx_tj].cpu().numpy()
+    y_s = y.reshape(-1)[idx_tj].cpu().numpy()
+    dx_s = dx.reshape(-1)[torch.from_numpy(ts * inn + is_).cuda()].cpu().numpy()
+    dw_s = dw.reshape(-1)[torch.from_numpy(js * inn + is_).cuda()].cpu().numpy()
+    e_dx = e_dw = 0.0
+    for n, (t, j, i) in enumerate(zip(ts, js, is_)):
+        a_ref = orc.lib.orc_int8_ternary_acc_element(xq_ref.reshape(-1), codes.reshape(-1), out, inn, t, j)
+        assert acc_s[n] == a_ref
+        assert y_s[n] == orc.lib.orc_bitlinear_fwd_scale(int(a_ref), float(s_ref[t]), g)
+        e_dx = max(e_dx, abs(dx_s[n] - orc.dx_element(dyr.reshape(-1), wq.reshape(-1), out, inn, t, i)))
+        e_dw = max(e_dw, abs(dw_s[n] - orc.dw_element(dyr.reshape(-1), xr.reshape(-1), m, out, inn, j, i)))
+    e_dx /= float(dx.abs().max())
+    e_dw /= float(dw.abs().max())
+    print(f"[{name} {out}x{inn}, {m} tokens] sampled rel err dx {e_dx:.2e} dW {e_dw:.2e}")
+    assert e_dx <= RTOL_F32 and e_dw <= RTOL_F32
+    # size-independent property over the WHOLE output: the integer forward is linear in xq, so
+    # sum_t acc[t, :] equals (sum_t xq[t, :]) . codes^T; every term is an integer below 2^53, exact in f64
+    colsum = xq_ref.astype(np.int64).sum(axis=0).astype(np.float64)
+    want = np.concatenate([codes[a:a + 1024].astype(np.float64) @ colsum for a in range(0, out, 1024)])
+    assert np.array_equal(acc.sum(dim=0, dtype=torch.int64).cpu().numpy(), want.astype(np.int64))
+    # dx and dW are two contractions of the same trilinear form: <dx, x> == <dW, W> * gamma
+    # (the terms have random signs, so the error is set against the sum of their magnitudes)
+    prod = dx.double() * xt.double()
+    lhs, mag = float(prod.sum()), float(prod.abs().sum())
+    rhs = float((dw.double() * torch.from_numpy(wq).cuda().double()).sum())
+    assert abs(lhs - rhs) <= 1e-6 * mag, (lhs, rhs, mag)
+    h.close()
+
+
 def test_llama8b_mlp_shapes_sampled(env, orc):
     """configs[1]: hidden 4096, intermediate 14336, 4096 tokens; x bf16 ~ N(0,1), dy bf16 ~ N(0,1e-4),
-    W ~ N(0, 0.02^2).  Codes and gamma are checked in full, GEMM outputs on 400 seeded samples each,
-    plus a linearity property of the integer forward over the whole output."""
-    at, bl, ctx, torch = env
-    m = 4096
+    W ~ N(0, 0.02^2)."""
     r = rng(70)
     for name, out, inn, seed in [("gate", 14336, 4096, 10), ("down", 4096, 14336, 12)]:
-        w_lat = normal_f32(seed, (out, inn), 0.02)
-        h = bl.BitLinearWeights(out, inn, ctx).quantize_(torch.from_numpy(w_lat).cuda())
-        g, codes, packed = orc.quantize_and_pack(w_lat)
-        codes = codes.reshape(out, inn)
-        ctx.sync()
-        assert h.gamma == g and np.array_equal(h.to_packed(), packed)
-        x, dy = normal_f32(seed + 100, (m, inn)), normal_f32(seed + 200, (m, out), 1e-2)
-        xt, xr = to_bf16_tensor(orc, x, "cuda")
-        dyt, dyr = to_bf16_tensor(orc, dy, "cuda")
-        qa = bl.act_quant_int8(ctx, xt)
-        acc = torch.empty((m, out), dtype=torch.int32, device="cuda")
-        y = bl.bitlinear_fwd(h, qa, dtype=torch.float32, acc_out=acc)
-        dx = bl.bitlinear_dx(h, dyt, dtype=torch.float32)
-        dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
-        bl.ste_dw(ctx, dyt, xt, dw, beta=0.0)
-        ctx.sync()
-        xq_ref, s_ref = orc.act_quant_int8(xr)
-        assert np.array_equal(qa.xq.cpu().numpy(), xq_ref)
-        acc_h, y_h, dx_h, dw_h = acc.cpu().numpy(), y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy()
-        wq = codes.astype(np.float32) * np.float32(g)
-        ts, js, is_ = r.integers(0, m, 400), r.integers(0, out, 400), r.integers(0, inn, 400)
-        e_dx = e_dw = 0.0
-        for t, j, i in zip(ts, js, is_):
-            a_ref = orc.lib.orc_int8_ternary_acc_element(xq_ref.reshape(-1), codes.reshape(-1), out, inn, t, j)
-            assert acc_h[t, j] == a_ref
-            assert y_h[t, j] == orc.lib.orc_bitlinear_fwd_scale(int(a_ref), float(s_ref[t]), g)
-            e_dx = max(e_dx, abs(dx_h[t, i] - orc.dx_element(dyr.reshape(-1), wq.reshape(-1), out, inn, t, i)))
-            e_dw = max(e_dw, abs(dw_h[j, i] - orc.dw_element(dyr.reshape(-1), xr.reshape(-1), m, out, inn, j, i)))
-        e_dx /= np.abs(dx_h).max()
-        e_dw /= np.abs(dw_h).max()
-        print(f"[{name}] sampled rel err dx {e_dx:.2e} dW {e_dw:.2e}")
-        assert e_dx <= RTOL_F32 and e_dw <= RTOL_F32
-        # size-independent property over the WHOLE output: the integer forward is linear in xq, so
-        # sum_t acc[t, :] equals (sum_t xq[t, :]) . codes^T computed exactly on the CPU in int64
-        colsum = xq_ref.astype(np.int64).sum(axis=0)
-        assert np.array_equal(acc_h.astype(np.int64).sum(axis=0), codes.astype(np.int64) @ colsum)
-        # dx and dW are two contractions of the same trilinear form: <dx, x> == <dW, W> * gamma
-        lhs = float(np.sum(dx_h.astype(np.float64) * xr.astype(np.float64)))
-        rhs = float(np.sum(dw_h.astype(np.float64) * wq.astype(np.float64)))
-        assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1e-12), (lhs, rhs)
-        h.close()
+        _check_linear_sampled(env, orc, r, name, 4096, out, inn, seed, 0.02)
+
+
+# The distinct ternary linears of the other benchmark configurations, each at its full shape with 8192 tokens:
+# Llama-3.2-1B (src/llama.rs:64-80), the Qwen3.5-9B-like hybrid (src/qwen35.rs:154-164, 183-191; in_proj_b/a have
+# 32 output rows) and one Llama-3-70B layer (src/llama.rs:100-116, W ~ N(0, 0.015^2)).
+MODEL_LINEARS = [
+    ("1b-q/o", 2048, 2048, 0.02), ("1b-k/v", 512, 2048, 0.02), ("1b-gate/up", 8192, 2048, 0.02), ("1b-down", 2048, 8192, 0.02),
+    ("q35-in_proj_qkv", 8192, 4096, 0.02), ("q35-in_proj_z/out/q/o", 4096, 4096, 0.02), ("q35-in_proj_b/a", 32, 4096, 0.02),
+    ("q35-k/v", 1024, 4096, 0.02), ("q35-gate/up", 12288, 4096, 0.02), ("q35-down", 4096, 12288, 0.02),
+    ("70b-q/o", 8192, 8192, 0.015), ("70b-k/v", 1024, 8192, 0.015), ("70b-gate/up", 28672, 8192, 0.015),
+    ("70b-down", 8192, 28672, 0.015),
+]
+
+
+@pytest.mark.parametrize("name,out,inn,std", MODEL_LINEARS, ids=[c[0] for c in MODEL_LINEARS])
+def test_model_linear_shapes_sampled(env, orc, name, out, inn, std):
+    _check_linear_sampled(env, orc, rng(out * 31 + inn), name, 8192, out, inn, 300 + out % 97, std, samples=200)
 
 
 def test_bitlinear_step_host(env, orc):
