@@ -17,6 +17,7 @@ AB_ERR_DEVICE_TIMEOUT, AB_ERR_UNSUPPORTED, AB_ERR_NO_DEVICE, AB_ERR_STATE = 5, 6
 AB_F32, AB_BF16 = 0, 1
 AB_TERNARY, AB_BINARY2, AB_INT4, AB_INT8 = 0, 1, 2, 3
 AB_GUARD_INV_ZERO, AB_GUARD_FLOOR = 0, 1
+AB_OPT_EXACT_MATVEC = 1
 
 
 class FqReport(C.Structure):
@@ -31,6 +32,7 @@ _vp, _sz, _i, _f = C.c_void_p, C.c_size_t, C.c_int, C.c_float
 # name -> (restype, argtypes); every symbol include/alice_b200.h declares
 SIGNATURES = {
     "ab_ctx_create": (_i, [_i, _vp, C.POINTER(_vp)]),
+    "ab_ctx_set_option": (_i, [_vp, _i, _i]),
     "ab_ctx_destroy": (_i, [_vp]),
     "ab_ctx_sync": (_i, [_vp]),
     "ab_ctx_stream": (_vp, [_vp]),
@@ -55,6 +57,8 @@ SIGNATURES = {
     "ab_fq_shard_abs_sum": (_i, [_vp, _vp, _vp, _vp]),
     "ab_fq_shard_pack": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i, _i]),
     "ab_weights_fq_report": (_i, [_vp, C.POINTER(FqReport)]),
+    "ab_dp_allreduce_start": (_i, [_vp, _vp, _sz, _vp, _vp, _i, _i, C.c_uint32, _i]),
+    "ab_dp_allreduce_wait": (_i, [_vp]),
     "ab_quantize_and_pack_host": (_i, [_vp, _vp, _sz, C.POINTER(_f), _vp]),
     "ab_calibrate_scale": (_i, [_vp, _vp, _sz, _vp]),
     "ab_fake_quantize_forward": (_i, [_vp, _vp, _vp, _sz, _vp, _f, _i]),

@@ -44,6 +44,11 @@ class GpuContext:
     def sync(self):
         _ffi.check(self._lib.ab_ctx_sync(self._h), self._h)
 
+    def set_exact_matvec(self, on: bool):
+        """True: the batch-1 kernels add in f32 as the reference's loops do; False (default): matrices of at
+        least 64 x 512 use the integer tensor-core path (vector rounded to 32-bit fixed point, sums exact)."""
+        _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_EXACT_MATVEC, int(bool(on))), self._h)
+
     def launch_count(self) -> int:
         return int(self._lib.ab_ctx_launch_count(self._h))
 

@@ -49,6 +49,56 @@ class DwAllReducer:
         self._pending.clear()
 
 
+class SwitchDwAllReducer:
+    """dW buffers in symmetric memory, summed over the GPUs inside NVSwitch by the library's own kernel
+    (ab_dp_allreduce_start / _wait) instead of NCCL: no staging copies and 8 CTAs per exchange, so the GEMMs that
+    overlap it keep their SMs.  torch's symmetric-memory allocator provides the mapping (each GPU's buffer plus the
+    group's multicast address); the arithmetic and the inter-GPU barriers are in the CUDA library.
+
+        red = SwitchDwAllReducer(ctx, [(out, inn), ...], device)   # collective: every rank, same shapes
+        ste_dw(ctx, dy, x, red.dW[i], beta=0.0); red.submit(i); ...; red.wait()
+    """
+
+    FLAG_FLOATS = 64
+
+    def __init__(self, ctx, shapes, device, group=None, ctas: int = 0):
+        import math
+
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _ffi
+        self._ffi, self.ctx, self.ctas = _ffi, ctx, int(ctas)
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world < 2:
+            raise ValueError("SwitchDwAllReducer needs at least two GPUs")
+        self.dW, self._bufs, self._epoch = [], [], []
+        for shape in shapes:
+            n = math.prod(shape)
+            n_pad = (n + 4 * self.world - 1) // (4 * self.world) * (4 * self.world)
+            t = symm_mem.empty(n_pad + self.FLAG_FLOATS, dtype=torch.float32, device=device)
+            hdl = symm_mem.rendezvous(t, self.group)
+            if not hdl.multicast_ptr:
+                raise RuntimeError("this group of GPUs has no NVSwitch multicast mapping")
+            t[n:].zero_()  # padding and the barrier counters
+            mc = hdl.multicast_ptr + (t.data_ptr() - hdl.buffer_ptrs[hdl.rank])
+            self._bufs.append((t, hdl, mc, n_pad))
+            self._epoch.append(0)
+            self.dW.append(t[:n].view(shape))
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)
+        torch.cuda.synchronize(device)
+
+    def submit(self, i: int):
+        t, _, mc, n_pad = self._bufs[i]
+        self._epoch[i] += 1
+        self._ffi.check(self._ffi.load().ab_dp_allreduce_start(
+            self.ctx.handle, mc, n_pad, t.data_ptr() + 4 * n_pad, mc + 4 * n_pad, self.rank, self.world, self._epoch[i],
+            self.ctas), self.ctx.handle)
+
+    def wait(self):
+        self._ffi.check(self._ffi.load().ab_dp_allreduce_wait(self.ctx.handle), self.ctx.handle)
+
+
 def global_gamma(sum_abs_local: torch.Tensor, n_total: int, group=None, floor: bool = False) -> torch.Tensor:
     """gamma of a row-sharded tensor: all-reduce the f64 shard sums of |w|, divide by the global
     element count, round to f32 (src/qwen35.rs:226-227).  Every rank gets the same bits."""

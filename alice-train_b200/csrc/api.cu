@@ -127,9 +127,24 @@ int ab_ctx_destroy(ab_ctx* ctx) {
     if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     for (int i = 0; i < 6; ++i)
         if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
+    if (ctx->comm_stream) {
+        cudaStreamSynchronize(ctx->comm_stream);
+        cudaStreamDestroy(ctx->comm_stream);
+    }
+    if (ctx->comm_ready) cudaEventDestroy(ctx->comm_ready);
+    if (ctx->comm_done) cudaEventDestroy(ctx->comm_done);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return AB_OK;
+}
+
+int ab_ctx_set_option(ab_ctx* ctx, int option, int value) {
+    AB_REQUIRE(ctx, AB_ERR_NULL);
+    if (option == AB_OPT_EXACT_MATVEC) {
+        ctx->exact_matvec = value != 0;
+        return AB_OK;
+    }
+    return AB_ERR_UNSUPPORTED;
 }
 
 int ab_ctx_sync(ab_ctx* ctx) {
@@ -366,6 +381,26 @@ int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_sha
     AB_REQUIRE((reinterpret_cast<uintptr_t>(w_latent_shard) & 3) == 0 && (reinterpret_cast<uintptr_t>(sum_abs_total_dev) & 7) == 0,
                AB_ERR_ALIGN);
     return abk_fq_shard_pack(ctx, w_latent_shard, w_shard, sum_abs_total_dev, n_total, fq_out, guard, want_stats);
+}
+
+int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, uint32_t* flags_local, uint32_t* flags_multicast,
+                          int rank, int world, uint32_t epoch, int ctas) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(multicast_buf && flags_local && flags_multicast, AB_ERR_NULL);
+    AB_REQUIRE(world >= 2 && world <= 64 && rank >= 0 && rank < world && epoch >= 1, AB_ERR_SHAPE);
+    AB_REQUIRE(n > 0 && n % (4 * (size_t)world) == 0, AB_ERR_SHAPE);
+    AB_REQUIRE((reinterpret_cast<uintptr_t>(multicast_buf) & 15) == 0 && (reinterpret_cast<uintptr_t>(flags_local) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(flags_multicast) & 15) == 0, AB_ERR_ALIGN);
+    AB_REQUIRE(ctas >= 0 && ctas <= 148, AB_ERR_UNSUPPORTED);
+    // default CTA count: each GPU reduces 1/world of the buffer, and a CTA sustains about 6.5 GB/s (one ld_reduce
+    // round trip is ~5 us); more CTAs than the step needs only add contention for the GEMMs that run beside them
+    if (ctas == 0) ctas = world <= 2 ? 16 : (world <= 4 ? 12 : 8);
+    return abk_dp_allreduce_start(ctx, multicast_buf, n, flags_local, flags_multicast, rank, world, epoch, ctas);
+}
+
+int ab_dp_allreduce_wait(ab_ctx* ctx) {
+    AB_TRY(bind(ctx));
+    return abk_dp_allreduce_wait(ctx);
 }
 
 int ab_weights_fq_report(ab_weights* w, ab_fq_report* r) {

@@ -27,8 +27,8 @@
 //                                 keeps the s32 result exact and the expansion one shift and
 //                                 one mask per four weights.
 //   codes_t   [in][tpitch]        the TRANSPOSE (row = input feature, column = output
-//                                 feature) for dx = dy.W, canonical encoding, same in-group
-//                                 permutation.  tpitch = round_up(out,128)/4 bytes.
+//                                 feature) for dx = dy.W and dx = W^T dy, offset binary, same
+//                                 in-group permutation.  tpitch = round_up(out,128)/4 bytes.
 // ------------------------------------------------------------------------------------------
 
 static inline size_t ab_round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
@@ -48,6 +48,11 @@ struct ab_ctx {
     // copy streams + events of the host-buffer step (created on first use)
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // high-priority stream + events of the data-parallel dW exchange (created on first use)
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t comm_ready = nullptr, comm_done = nullptr;
+    bool comm_pending = false;
+    bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     uint64_t launches = 0;
     std::string last_error;
 };
@@ -132,6 +137,15 @@ int abk_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, con
 int abk_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in, const float* dy, size_t out, float* dW);
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c,
                           size_t m);
+
+// matvec_mma.cu
+int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows, size_t k, const float* v, float* y, float scale,
+                   int accumulate, int use_scale);
+
+// dp_allreduce.cu
+int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* flags_local, unsigned int* flags_mc, int rank,
+                           int world, unsigned int epoch, int ctas);
+int abk_dp_allreduce_wait(ab_ctx* ctx);
 
 // gemm_tc.cu
 int abk_gemm_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,

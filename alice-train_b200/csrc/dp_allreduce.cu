@@ -1,0 +1,130 @@
+// Data-parallel exchange of the latent-weight gradient: dW summed over the GPUs of one NVSwitch domain, in place,
+// by the switch itself.
+//
+// The buffer lives in memory that every GPU of the group has mapped twice: its own copy (plain pointer) and the
+// group's multicast address.  GPU r owns the r-th slice of the buffer: one `multimem.ld_reduce.add.v4.f32` returns
+// the sum of that address over all GPUs (the addition happens inside NVSwitch), one `multimem.st.v4.f32` writes the
+// sum back to all of them.  Per GPU and call n*4 bytes leave and n*4 bytes arrive over NVLink, nothing is staged,
+// and a handful of small CTAs keep enough requests in flight: the GEMMs that run beside it keep their SMs.  The
+// reference has no counterpart: it trains on one device (CudaContext::new(0), src/cuda_matmul.rs:954).
+//
+// Two device-side barriers bracket the transfer, each a counter in the same multicast mapping that every GPU
+// increments with `multimem.red` and polls on its own copy: before the first read every GPU's gradient kernel must
+// have finished, after the last write nobody may still be reading.  Every poll is bounded; a wait that runs out
+// records AB_ERR_DEVICE_TIMEOUT in the context's status word and the kernel returns without touching the data.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kArThreads = 256;
+constexpr unsigned long long kSpinNs = 4000000000ull;  // 4 s: far beyond any skew between the GPUs' launches
+
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mc_signal(unsigned int* mc_flag) {
+    asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_flag), "r"(1u) : "memory");
+}
+// true once *flag has reached `target` (wrap-safe), false when the time limit passed first
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int target) {
+    const unsigned long long t0 = now_ns();
+    for (;;) {
+        if ((int)(ld_acquire_sys(flag) - target) >= 0) return true;
+        if (now_ns() - t0 > kSpinNs) return false;
+        __nanosleep(200);
+    }
+}
+__device__ __forceinline__ float4 mc_ld_reduce(const float* mc) {
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void mc_st(float* mc, float4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+// flags (u32, in the multicast-mapped allocation): [0] start barrier, [1] end barrier, [2] CTAs of this GPU done.
+// The CTA is small on purpose (256 threads, no shared memory of its own, at most 64 registers a thread): it fits on
+// an SM beside a resident CTA of the pair GEMMs, so the exchange takes issue slots from them, not SMs.
+__global__ void __launch_bounds__(kArThreads, 4)
+nvls_allreduce_kernel(float* __restrict__ mc_buf, size_t n_vec4, unsigned int* __restrict__ flags_local,
+                      unsigned int* __restrict__ flags_mc, int rank, int world, unsigned int target, int* __restrict__ status) {
+    int go = 0;
+    if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) mc_signal(flags_mc + 0);
+        go = wait_flag(flags_local + 0, target) ? 1 : 0;
+        if (!go) atomicExch(status, 0x4152);
+    }
+    go = __syncthreads_or(go);
+    if (go) {
+        const size_t per = n_vec4 / (size_t)world;       // the host checked divisibility
+        float* mine = mc_buf + (size_t)rank * per * 4;
+        const size_t stride = (size_t)gridDim.x * kArThreads;
+        size_t i = (size_t)blockIdx.x * kArThreads + threadIdx.x;
+        constexpr int U = 8;                             // independent round trips in flight per thread
+        for (; i + (U - 1) * stride < per; i += U * stride) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = mc_ld_reduce(mine + 4 * (i + u * stride));
+#pragma unroll
+            for (int u = 0; u < U; ++u) mc_st(mine + 4 * (i + u * stride), v[u]);
+        }
+        for (; i < per; i += stride) mc_st(mine + 4 * i, mc_ld_reduce(mine + 4 * i));
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(flags_local + 2, 1u);
+        if (prev == gridDim.x - 1) {  // last CTA of this GPU: everything this GPU wrote is ordered before the signal
+            __threadfence_system();
+            flags_local[2] = 0u;
+            mc_signal(flags_mc + 1);
+            if (!wait_flag(flags_local + 1, target)) atomicExch(status, 0x4153);
+        }
+    }
+}
+
+}  // namespace
+
+int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* flags_local, unsigned int* flags_mc, int rank,
+                           int world, unsigned int epoch, int ctas) {
+    if (!ctx->comm_stream) {
+        int lo = 0, hi = 0;
+        AB_CUDA_CHECK(ctx, cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        AB_CUDA_CHECK(ctx, cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, hi));
+        AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming));
+        AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+        // ask for the same L1 / shared-memory split the GEMMs run with: an SM only changes its split when it is
+        // idle, so a CTA of this kernel that arrived first would otherwise keep the GEMM's CTA off that SM
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(nvls_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                cudaSharedmemCarveoutMaxShared));
+    }
+    // the exchange starts once everything queued on the context's stream so far (the dW GEMM) has finished
+    AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
+    nvls_allreduce_kernel<<<ctas, kArThreads, 0, ctx->comm_stream>>>(mc_buf, n / 4, flags_local, flags_mc, rank, world,
+                                                                      epoch * (unsigned int)world, ctx->dev_status);
+    AB_LAUNCH_CHECK(ctx);
+    AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+    ctx->comm_pending = true;
+    return AB_OK;
+}
+
+int abk_dp_allreduce_wait(ab_ctx* ctx) {
+    if (ctx->comm_pending) {  // the comm stream is in order: its latest event covers every exchange started so far
+        AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
+        ctx->comm_pending = false;
+    }
+    return AB_OK;
+}

@@ -350,7 +350,7 @@ repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ cod
     codes_fwd[wi] = f;
 }
 
-// codes_t[i][jg] gathers column i of the 16 rows j = 16*jg + e.  A block transposes a tile of
+// codes_t[i][jg] gathers column i of the 16 rows j = 16*jg + e, re-encoded as w+1.  A block transposes a tile of
 // 128 rows x 128 columns through shared memory: 32-byte row segments in (coalesced), 32-byte
 // segments of the transposed rows out (coalesced), the 2-bit shuffle in between.
 constexpr int kTT = 128;
@@ -380,7 +380,9 @@ transpose_codes_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t o
             if (c == 3u) c = 0u;
             word |= c << ab_perm_bit(e);
         }
-        s_out[il][jgl] = word;
+        // canonical (01 = +1, 10 = -1) -> offset binary w+1 (10, 00; zero = 01), all 16 fields at once
+        const uint32_t plus = word & 0x55555555u, minus = (word >> 1) & 0x55555555u;
+        s_out[il][jgl] = (plus << 1) | (~(plus | minus) & 0x55555555u);
     }
     __syncthreads();
     {

@@ -114,15 +114,15 @@ __device__ __forceinline__ uint4 expand_u8(uint32_t w) {
     // the 2-bit fields hold w+1 in {0,1,2}: already the unsigned byte the MMA takes
     return make_uint4(w & 0x03030303u, (w >> 2) & 0x03030303u, (w >> 4) & 0x03030303u, (w >> 6) & 0x03030303u);
 }
-// DX: canonical codes (1 = +1, 2 = -1) -> bf16 bit patterns through a byte permute: the code of
-// each element selects its high byte from {00, 3F, BF, 00} and its low byte from {00, 80, 80, 00}.
+// DX: offset-binary codes (w+1: 0 = -1, 1 = 0, 2 = +1) -> bf16 bit patterns through a byte permute: the code
+// of each element selects its high byte from {BF, 00, 3F, 00} and its low byte from {80, 00, 80, 00}.
 __device__ __forceinline__ void expand_bf16(uint32_t w, uint32_t* o /*[8]*/) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         uint32_t t = (w >> (2 * q)) & 0x03030303u;
         uint32_t sel = t * 0x11u + 0x04040404u;
-        o[2 * q] = __byte_perm(0x00BF3F00u, 0x00808000u, sel);
-        o[2 * q + 1] = __byte_perm(0x00BF3F00u, 0x00808000u, sel >> 16);
+        o[2 * q] = __byte_perm(0x003F00BFu, 0x00800080u, sel);
+        o[2 * q + 1] = __byte_perm(0x003F00BFu, 0x00800080u, sel >> 16);
     }
 }
 

@@ -206,13 +206,28 @@ def run_native(args):
             dx=torch.empty((tokens, inn), dtype=torch.bfloat16, device=dev),
             dW=torch.zeros((out, inn), dtype=torch.float32, device=dev)))
     ctx.sync()
+    # data parallel: dW lives in symmetric memory and is summed inside NVSwitch by the library's own kernel;
+    # NCCL remains the exchange where the GPUs have no multicast mapping (or on request)
+    switch, exchange = None, "none"
+    if world > 1:
+        exchange = "nccl"
+        if args.dw_exchange == "switch":
+            try:
+                from alice_train import parallel
+                switch = parallel.SwitchDwAllReducer(ctx, [(L["out"], L["inn"]) for L in layers], dev, ctas=args.exchange_ctas)
+                for L, buf in zip(layers, switch.dW):
+                    L["dW"] = buf
+                exchange = "switch"
+            except RuntimeError as e:
+                if rank == 0:
+                    print(f"[bench] in-switch exchange unavailable ({e}); using NCCL", file=sys.stderr)
 
     classes = ("act_quant", "fwd", "dx", "dw")
     ev = {c: [] for c in classes}
 
     def step(record: bool):
         handles = []
-        for L in layers:
+        for li, L in enumerate(layers):
             def timed(cls, fn):
                 if record:
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -224,13 +239,17 @@ def run_native(args):
                     fn()
             # dW first: its all-reduce (data parallel runs) then overlaps this projection's other kernels
             timed("dw", lambda: bl.ste_dw(ctx, L["dy"], L["x"], L["dW"], beta=0.0))
-            if world > 1:  # data parallel over tokens: the one exchange step is the sum of dW
+            if switch is not None:  # data parallel over tokens: the one exchange step is the sum of dW
+                switch.submit(li)
+            elif world > 1:
                 handles.append(dist.all_reduce(L["dW"], op=dist.ReduceOp.SUM, async_op=True))
             timed("act_quant", lambda: bl.act_quant_int8(ctx, L["x"], L["qa"]))
             timed("fwd", lambda: bl.bitlinear_fwd(L["w"], L["qa"], y=L["y"]))
             timed("dx", lambda: bl.bitlinear_dx(L["w"], L["dy"], dx=L["dx"]))
         for hnd in handles:
             hnd.wait()
+        if switch is not None:
+            switch.wait()
 
     def fence():
         if world > 1:
@@ -313,11 +332,20 @@ def run_native(args):
         lib = _ffi.load()
 
         def e2e_step():
-            for L, Hh in zip(layers, host):
+            pending = []
+            for li, (L, Hh) in enumerate(zip(layers, host)):
                 _ffi.check(lib.ab_bitlinear_step_host(ctx.handle, L["w"].handle, C.c_void_p(Hh["x"].data_ptr()),
                                                       C.c_void_p(Hh["dy"].data_ptr()), tokens,
                                                       C.c_void_p(Hh["y"].data_ptr()), C.c_void_p(Hh["dx"].data_ptr()),
                                                       C.c_void_p(L["dW"].data_ptr())), ctx.handle)
+                if switch is not None:      # the data-parallel sum of dW belongs to the step end to end as well
+                    switch.submit(li)
+                elif world > 1:
+                    pending.append(dist.all_reduce(L["dW"], op=dist.ReduceOp.SUM, async_op=True))
+            for hnd in pending:
+                hnd.wait()
+            if switch is not None:
+                switch.wait()
         e2e_steps = max(2, min(args.steps, 5))
         e2e_step()
         fence()
@@ -353,7 +381,9 @@ def run_native(args):
                        "projections": {n: [o, i] for n, o, i in projs},
                        "parallelism": f"dp{world}" if world > 1 else "single",
                        "step": "per projection: dW (overwrite), act-quant int8, fwd, dx" +
-                               ("; NCCL all-reduce of each dW issued right after its GEMM, overlapping the rest" if world > 1 else ""),
+                               {"switch": "; each dW summed over the GPUs inside NVSwitch (multimem kernel of the library) right after its GEMM, overlapping the rest",
+                                "nccl": "; NCCL all-reduce of each dW issued right after its GEMM, overlapping the rest", "none": ""}[exchange],
+                       "dw_exchange": exchange,
                        "l2": "working set per step exceeds the 126 MB L2 (dW alone is 3 x 235 MB); no explicit flush"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks, "kernels": per, "tensor_pipe_probe": probe,
@@ -460,10 +490,11 @@ ROWSHARD_TOKENS, ROWSHARD_LINEARS = WORKLOADS["llama3-70b-layer"]
 def run_rowshard(args):
     """--workload llama3-70b-layer: the seven ternary linears of one Llama-3-70B decoder layer (hidden 8192,
     intermediate 28672, 8 KV heads x 128), 8192 tokens per step, W ~ N(0, 0.015^2).  Every GPU holds out/N rows of
-    each latent and packed matrix (strong scaling: the step's work is fixed).  One step, per linear: the two-call
-    quantiser with its 8-byte all-reduce of sum|w|, act-quant (replicated), forward of the local rows followed by
-    an all-gather of y, the dx partial product followed by a reduce-scatter over tokens, and the local rows of dW
-    (no exchange).  Both exchanges are issued asynchronously and waited for at the end of the step."""
+    each latent and packed matrix (strong scaling: the step's work is fixed).  One step: the two-call quantiser over
+    all seven linears with ONE all-reduce of their seven f64 sums of |w| between the calls; then per linear act-quant
+    (replicated), forward of the local rows followed by an all-gather of y, the dx partial product followed by a
+    reduce-scatter over tokens, and the local rows of dW (no exchange).  The two big exchanges are issued
+    asynchronously and waited for at the end of the step."""
     import torch
     import torch.distributed as dist
 
@@ -495,7 +526,7 @@ def run_rowshard(args):
         dy = (torch.randn((tokens, out), generator=gen, device=dev, dtype=torch.float32) * 1e-2).to(torch.bfloat16)
         layers.append(dict(
             name=name, out=out, inn=inn, rows=rows, w=bl.BitLinearWeights(rows, inn, ctx), w_lat=w_lat, x=x,
-            dy=dy[:, r0:r1].contiguous(), sum_abs=torch.zeros(1, dtype=torch.float64, device=dev),
+            dy=dy[:, r0:r1].contiguous(),
             qa=bl.QuantizedActivations(torch.empty((tokens, inn), dtype=torch.int8, device=dev),
                                        torch.empty(tokens, dtype=torch.float32, device=dev),
                                        torch.empty(tokens, dtype=torch.int32, device=dev)),
@@ -509,24 +540,30 @@ def run_rowshard(args):
     classes = ("fq", "act_quant", "fwd", "dx", "dw")
     ev = {c: [] for c in classes}
 
+    sums = torch.zeros(len(layers), dtype=torch.float64, device=dev)
+
     def step(record: bool):
         handles = []
-        for L in layers:
-            def timed(cls, fn):
-                if record:
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    fn()
-                    b.record()
-                    ev[cls].append((a, b))
-                else:
-                    fn()
 
-            def quantise():
-                L["w"].shard_abs_sum(L["w_lat"], L["sum_abs"])
-                parallel.global_abs_sum(L["sum_abs"])          # 8 bytes; every GPU derives the same gamma
-                L["w"].quantize_shard_(L["w_lat"], L["sum_abs"], L["out"] * L["inn"])
-            timed("fq", quantise)
+        def timed(cls, fn):
+            if record:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                ev[cls].append((a, b))
+            else:
+                fn()
+
+        def quantise():   # all seven sums of |w| travel in ONE 56-byte all-reduce, ahead of the step's big exchanges
+            for i, L in enumerate(layers):
+                L["w"].shard_abs_sum(L["w_lat"], sums[i:i + 1])
+            parallel.global_abs_sum(sums)
+            for i, L in enumerate(layers):
+                L["w"].quantize_shard_(L["w_lat"], sums[i:i + 1], L["out"] * L["inn"])
+        timed("fq", quantise)
+        for L in layers:
+
             timed("act_quant", lambda: bl.act_quant_int8(ctx, L["x"], L["qa"]))
             timed("fwd", lambda: bl.bitlinear_fwd(L["w"], L["qa"], y=L["y"]))
             if world > 1:
@@ -584,7 +621,7 @@ def run_rowshard(args):
             "dtype": "int8 forward (s32 accumulate), bf16 backward (f32 accumulate)", "data": "synthetic",
             "config": {"workload": "llama3-70b-layer", "tokens_per_step": tokens, "linears": {n: [o, i] for n, o, i in ROWSHARD_LINEARS},
                        "parallelism": f"rows/{world}" if world > 1 else "single",
-                       "step": "per linear: quantise the local rows (8-byte all-reduce of sum|w|), act-quant, fwd -> all-gather y (bf16), "
+                       "step": "quantise the local rows of all linears (one all-reduce of the 7 sums of |w|); then per linear: act-quant, fwd -> all-gather y (bf16), "
                                "dx partial -> reduce-scatter over tokens (bf16), dW rows (local)",
                        "exchange_bytes_per_step": {"all_gather_y_total": gather_bytes, "reduce_scatter_dx_input_per_gpu": rs_bytes},
                        "l2": "latent shards, dW and activations exceed the 126 MB L2 at every N; no explicit flush"},
@@ -608,6 +645,9 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS) + ["hbm-kernels"])
     ap.add_argument("--cpu-tokens", type=int, default=4, help="tokens per CPU-baseline sample")
+    ap.add_argument("--dw-exchange", default="switch", choices=["switch", "nccl"],
+                    help="data-parallel sum of dW: the library's in-switch kernel (default) or NCCL")
+    ap.add_argument("--exchange-ctas", type=int, default=0, help="CTAs of the in-switch exchange kernel (0 = library default)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -82,6 +82,15 @@ typedef struct ab_fq_report {
  * (src/blas.rs:19-24). */
 AB_API int ab_ctx_create(int device, void* cuda_stream, ab_ctx** ctx);
 AB_API int ab_ctx_destroy(ab_ctx* ctx);
+/* Context options.  AB_OPT_EXACT_MATVEC (default 0): when 1, ab_ternary_matvec, ab_ternary_matvec_backward and
+ * ab_bitlinear_backward add the selected elements in f32 as the reference's loops do (src/backward.rs:45-80).
+ * By default, matrices of at least 64 x 512 go through an integer path instead: the vector is rounded to 32-bit
+ * fixed point with one shared power-of-two scale (error at most 2^-31 of its largest magnitude per element), the
+ * sums are then exact integers on the tensor cores and are rounded to f32 once.  That path reaches the HBM
+ * roofline; it differs from f32 accumulation only in rounding, except that elements below 2^-31 of the vector's
+ * largest magnitude drop out. */
+typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1 } ab_option;
+AB_API int ab_ctx_set_option(ab_ctx* ctx, int option, int value);
 /* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
 AB_API int ab_ctx_sync(ab_ctx* ctx);
 AB_API void* ab_ctx_stream(ab_ctx* ctx);
@@ -263,6 +272,29 @@ AB_API int ab_ste_dw(ab_ctx* ctx, const void* dy_bf16, size_t ld_dy, const void*
 AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_bf16_host,
                                   const void* dy_bf16_host, size_t m, void* y_bf16_host,
                                   void* dx_bf16_host, float* dW_dev);
+
+/* ------------------------------------------------- data-parallel exchange of dW (NVSwitch) */
+
+/* Sums a f32 buffer over the GPUs of one NVSwitch domain, in place, inside the switch (multimem.ld_reduce /
+ * multimem.st on the group's multicast mapping): the data-parallel all-reduce of dW, with no staging copy and
+ * small CTAs that fit beside a resident GEMM CTA, so the GEMMs of the same step keep their SMs.  The reference trains on one device
+ * (CudaContext::new(0), src/cuda_matmul.rs:954) and has no counterpart; this is the exchange the token-parallel
+ * partition of STE dW (src/backward.rs:173-184 summed over tokens) needs.
+ *   multicast_buf    the buffer's address in the multicast mapping (every GPU passes the same logical buffer)
+ *   n                floats; a multiple of 4*world
+ *   flags_local      16 bytes inside the same allocation, this GPU's own mapping; zeroed once, before the first
+ *                    call, on every GPU (then synchronise the GPUs)
+ *   flags_multicast  the same 16 bytes in the multicast mapping
+ *   epoch            1 for the first call on this buffer, then 2, 3, ...; equal on all GPUs
+ *   ctas             CTAs to launch (256 threads each, small enough to share an SM with a GEMM CTA), 0 = default
+ *                    (16 for 2 GPUs, 12 for up to 4, 8 beyond: sized for a gradient exchange that overlaps GEMMs)
+ * _start queues the exchange on a high-priority stream of the context behind the work already queued on the
+ * context's stream and returns; _wait makes the context's stream wait for every exchange started so far.  Every
+ * GPU of the group must make the same calls in the same order.  Waits on the other GPUs are bounded (4 s): when
+ * one runs out the buffer is left as it was and ab_ctx_sync() returns AB_ERR_DEVICE_TIMEOUT. */
+AB_API int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, uint32_t* flags_local,
+                                 uint32_t* flags_multicast, int rank, int world, uint32_t epoch, int ctas);
+AB_API int ab_dp_allreduce_wait(ab_ctx* ctx);
 
 /* Measurement aid (no counterpart in the reference): launches, on the context's stream, a kernel
  * that only issues the tensor-core instruction of the production kernels (256x256 tile on a CTA

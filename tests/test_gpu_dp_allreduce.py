@@ -1,0 +1,95 @@
+"""The library's in-switch all-reduce of dW (ab_dp_allreduce_start / _wait) on two GPUs, one process per GPU,
+against NCCL's all-reduce of the same buffers.  Needs two GPUs of one NVSwitch domain; skipped otherwise."""
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path[:0] = [os.path.dirname(here), os.path.join(os.path.dirname(here), "alice-train_b200")]
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import alice_train
+        from alice_train import bitlinear as bl, parallel
+        ctx = alice_train.GpuContext.on_torch_stream(rank)
+        shapes = [(300, 520), (1024, 2048), (7, 3)]
+        try:
+            red = parallel.SwitchDwAllReducer(ctx, shapes, dev)
+        except RuntimeError as e:
+            q.put((rank, "skip", str(e)))
+            return
+        gen = torch.Generator(device=dev)
+        worst, exact = 0.0, True
+        for it in range(4):
+            want = []
+            for i, shape in enumerate(shapes):
+                gen.manual_seed(1000 * it + 10 * i + rank)
+                red.dW[i].copy_(torch.randn(shape, generator=gen, device=dev))
+                ref = red.dW[i].clone()
+                dist.all_reduce(ref)
+                want.append(ref)
+            for i in range(len(shapes)):
+                red.submit(i)
+            red.wait()
+            ctx.sync()
+            for i in range(len(shapes)):
+                err = float((red.dW[i] - want[i]).abs().max() / want[i].abs().max())
+                worst = max(worst, err)
+                exact = exact and torch.equal(red.dW[i], want[i])
+        # the way the benchmark uses it: the gradient GEMM, its exchange, and more work behind it
+        m, out, inn = 256, 1024, 2048
+        gen.manual_seed(50 + rank)
+        x = torch.randn((m, inn), generator=gen, device=dev).to(torch.bfloat16)
+        dy = (torch.randn((m, out), generator=gen, device=dev) * 1e-2).to(torch.bfloat16)
+        local = torch.zeros((out, inn), dtype=torch.float32, device=dev)
+        bl.ste_dw(ctx, dy, x, local, beta=0.0)
+        dist.all_reduce(local)
+        for _ in range(3):
+            bl.ste_dw(ctx, dy, x, red.dW[1], beta=0.0)
+            red.submit(1)
+            qa = bl.act_quant_int8(ctx, x)
+            red.wait()
+        ctx.sync()
+        err_gemm = float((red.dW[1] - local).abs().max() / local.abs().max())
+        q.put((rank, "ok", worst, exact, err_gemm))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_switch_allreduce_matches_nccl_world2():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    if any(r[1] == "skip" for r in res):
+        pytest.skip(res[0][2])
+    for rank, _, worst, exact, err_gemm in res:
+        assert exact and worst == 0.0, (rank, worst)       # a + b in f32 does not depend on who adds
+        assert err_gemm <= 1e-6, (rank, err_gemm)

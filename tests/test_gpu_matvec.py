@@ -106,10 +106,15 @@ def test_length_mismatch_raises_assertion(at, golden):
                                    np.zeros(c["dw_len"], np.float32))
 
 
-@pytest.mark.parametrize("out,inn", [(2048, 2048), (1, 3), (3, 1), (7, 130), (257, 33), (4096, 14336), (100, 2049)])
-def test_matvec_path_vs_oracle(at, orc, out, inn):
+@pytest.mark.parametrize("exact", [False, True], ids=["integer-path", "f32-path"])
+@pytest.mark.parametrize("out,inn", [(2048, 2048), (1, 3), (3, 1), (7, 130), (257, 33), (4096, 14336), (100, 2049),
+                                     (300, 777), (1000, 5000), (8192, 28672), (65, 512), (64, 513)])
+def test_matvec_path_vs_oracle(at, orc, out, inn, exact):
     """configs[0] of the target specification is (2048, 2048): W ~ N(0, 0.02^2) seed 1 ternarised
-    by absmean, x ~ N(0,1) seed 2, dy ~ N(0,1) seed 3, eps 1e-6."""
+    by absmean, x ~ N(0,1) seed 2, dy ~ N(0,1) seed 3, eps 1e-6.  Both arithmetic paths of the library:
+    the default (matrices of at least 64 x 512 sum in integers on the tensor cores) and f32 adds."""
+    from alice_train.context import default_context
+    default_context().set_exact_matvec(exact)
     w_lat = normal_f32(1, (out, inn), 0.02)
     _, codes, _ = orc.quantize_and_pack(w_lat)
     x, dy = normal_f32(2, (inn,)), normal_f32(3, (out,))
@@ -133,6 +138,48 @@ def test_matvec_path_vs_oracle(at, orc, out, inn):
         e = rel_err(dxb, ref)
         assert e <= RTOL_F32, (pre_norm, e)
         assert np.array_equal(db, refb)
+    w.close()
+    default_context().set_exact_matvec(False)
+
+
+def test_integer_matvec_is_exact_on_integers(at, orc):
+    """With integer-valued vectors the fixed-point conversion is exact, so the integer path must return the exact
+    sums bit for bit (they are below 2^24): a check of the fragment layout, the digit split and the offset."""
+    from alice_train.context import default_context
+    default_context().set_exact_matvec(False)
+    rng = np.random.Generator(np.random.Philox(77))
+    for out, inn in [(96, 1536), (1040, 2000), (4096, 14336)]:
+        codes = rng.integers(-1, 2, size=(out, inn)).astype(np.int8)
+        x = rng.integers(-1000, 1001, size=inn).astype(np.float32)
+        dy = rng.integers(-1000, 1001, size=out).astype(np.float32)
+        w = at.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
+        y, dx = np.zeros(out, np.float32), np.zeros(inn, np.float32)
+        at.ternary_matvec_kernel(x, w, y)
+        at.ternary_matvec_backward(dy, w, dx)
+        assert np.array_equal(y, (codes.astype(np.int64) @ x.astype(np.int64)).astype(np.float32))
+        assert np.array_equal(dx, (codes.astype(np.int64).T @ dy.astype(np.int64)).astype(np.float32))
+        w.close()
+
+
+def test_integer_matvec_edge_vectors(at, orc):
+    """Zero vector, one huge element, non-finite input."""
+    from alice_train.context import default_context
+    default_context().set_exact_matvec(False)
+    out, inn = 128, 1024
+    rng = np.random.Generator(np.random.Philox(78))
+    codes = rng.integers(-1, 2, size=(out, inn)).astype(np.int8)
+    w = at.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
+    y = np.ones(out, np.float32)
+    at.ternary_matvec_kernel(np.zeros(inn, np.float32), w, y)
+    assert not y.any()
+    x = normal_f32(5, (inn,))
+    x[3] = 3.0e38
+    at.ternary_matvec_kernel(x, w, y)
+    ref = orc.ternary_matvec(x, orc.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn))
+    assert rel_err(y, ref) <= RTOL_F32
+    x[5] = np.inf
+    at.ternary_matvec_kernel(x, w, y)
+    assert np.isnan(y).all()
     w.close()
 
 

@@ -84,3 +84,10 @@ def test_host_state_logic_matches_reference_rules():
     c = QatConfig()
     assert c.bits == QuantBits.Ternary and c.learn_scale and c.temperature == 1.0
     assert QatConfig.int4().grad_clip == 1.0 and not QatConfig.int8().learn_scale
+
+
+def test_integration_doc_binds_every_entry_point():
+    """The Rust `extern "C"` block shown to the reference's maintainers names every symbol of the header."""
+    doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    missing = [n for n in _declared_symbols() if f"fn {n}(" not in doc]
+    assert not missing, missing
