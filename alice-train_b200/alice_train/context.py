@@ -49,6 +49,10 @@ class GpuContext:
         least 64 x 512 use the integer tensor-core path (vector rounded to 32-bit fixed point, sums exact)."""
         _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_EXACT_MATVEC, int(bool(on))), self._h)
 
+    def set_async_host_step(self, on: bool):
+        """True: ab_bitlinear_step_host only queues its work; sync() before touching the host buffers."""
+        _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_ASYNC_HOST_STEP, int(bool(on))), self._h)
+
     def launch_count(self) -> int:
         return int(self._lib.ab_ctx_launch_count(self._h))
 

@@ -120,8 +120,10 @@ int ab_ctx_destroy(ab_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
-    for (int i = 0; i < 6; ++i)
+    for (int i = 0; i < 12; ++i)
         if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+    for (int i = 0; i < 2; ++i)
+        if (ctx->set_free[i]) cudaEventDestroy(ctx->set_free[i]);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
@@ -142,6 +144,10 @@ int ab_ctx_set_option(ab_ctx* ctx, int option, int value) {
     AB_REQUIRE(ctx, AB_ERR_NULL);
     if (option == AB_OPT_EXACT_MATVEC) {
         ctx->exact_matvec = value != 0;
+        return AB_OK;
+    }
+    if (option == AB_OPT_ASYNC_HOST_STEP) {
+        ctx->async_host_step = value != 0;
         return AB_OK;
     }
     return AB_ERR_UNSUPPORTED;
@@ -801,13 +807,16 @@ int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host,
     AB_REQUIRE(x_host && dy_host && y_host && dx_host && dW_dev, AB_ERR_NULL);
     const size_t in = w->in, out = w->out;
     AB_REQUIRE(in % 16 == 0 && out % 8 == 0, AB_ERR_UNSUPPORTED);
+    // two sets of staging buffers: the copies in of one call overlap the compute and the copies out of the call before
+    const int set = ctx->next_set;
+    ctx->next_set ^= 1;
     void *dx_in = nullptr, *ddy = nullptr, *dxq = nullptr, *dsc = nullptr, *dy_out = nullptr, *ddx = nullptr;
-    AB_TRY(ab_ctx_stage(ctx, 0, m * in * 2, &dx_in));
-    AB_TRY(ab_ctx_stage(ctx, 1, m * out * 2, &ddy));
-    AB_TRY(ab_ctx_stage(ctx, 2, m * in, &dxq));
-    AB_TRY(ab_ctx_stage(ctx, 3, m * 8, &dsc));
-    AB_TRY(ab_ctx_stage(ctx, 4, m * out * 2, &dy_out));
-    AB_TRY(ab_ctx_stage(ctx, 5, m * in * 2, &ddx));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 0, m * in * 2, &dx_in));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 1, m * out * 2, &ddy));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 2, m * in, &dxq));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 3, m * 8, &dsc));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 4, m * out * 2, &dy_out));
+    AB_TRY(ab_ctx_stage(ctx, 6 * set + 5, m * in * 2, &ddx));
     float* scales = (float*)dsc;
     int32_t* rowsums = (int32_t*)((char*)dsc + m * 4);
     // Three streams so that PCIe runs in both directions while the tensor cores work:
@@ -816,13 +825,17 @@ int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host,
         AB_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
         AB_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
         for (int i = 0; i < 6; ++i) AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->ev[i], cudaEventDisableTiming));
+        for (int i = 0; i < 2; ++i) AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->set_free[i], cudaEventDisableTiming));
     }
     cudaStream_t s = ctx->stream, si = ctx->copy_in, so = ctx->copy_out;
-    cudaEvent_t e_start = ctx->ev[0], e_x = ctx->ev[1], e_dy = ctx->ev[2], e_y = ctx->ev[3], e_dx = ctx->ev[4],
+    cudaEvent_t e_x = ctx->ev[1], e_dy = ctx->ev[2], e_y = ctx->ev[3], e_dx = ctx->ev[4],
                 e_out = ctx->ev[5];
-    AB_CUDA_CHECK(ctx, cudaEventRecord(e_start, s));  // staging buffers are free once earlier work on s is done
-    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(si, e_start, 0));
-    AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(so, e_start, 0));
+    // this set's buffers are free once the call that used them last (two calls ago) has finished; work queued on the
+    // context's stream by OTHER entry points never touches them
+    if (ctx->set_used[set]) {
+        AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(si, ctx->set_free[set], 0));
+        AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(so, ctx->set_free[set], 0));
+    }
     AB_CUDA_CHECK(ctx, cudaMemcpyAsync(dx_in, x_host, m * in * 2, cudaMemcpyHostToDevice, si));
     AB_CUDA_CHECK(ctx, cudaEventRecord(e_x, si));
     AB_CUDA_CHECK(ctx, cudaMemcpyAsync(ddy, dy_host, m * out * 2, cudaMemcpyHostToDevice, si));
@@ -841,7 +854,9 @@ int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host,
     AB_CUDA_CHECK(ctx, cudaEventRecord(e_out, so));
     AB_TRY(abk_gemm_dw(ctx, ddy, out, dx_in, in, m, out, in, dW_dev, in, 1.0f));
     AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(s, e_out, 0));  // the context stream now also covers the copies out
-    return ab_ctx_sync(ctx);
+    AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->set_free[set], s));
+    ctx->set_used[set] = true;
+    return ctx->async_host_step ? AB_OK : ab_ctx_sync(ctx);
 }
 
 }  // extern "C"

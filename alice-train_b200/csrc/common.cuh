@@ -41,8 +41,8 @@ struct ab_ctx {
     // grow-only device scratch (reduction partials, host-API staging)
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
-    void* stage[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-    size_t stage_bytes[6] = {0, 0, 0, 0, 0, 0};
+    void* stage[12] = {};          // two sets of six: consecutive host-buffer steps alternate between them
+    size_t stage_bytes[12] = {};
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
     int* dev_status = nullptr;
     // copy streams + events of the host-buffer step (created on first use)
@@ -52,6 +52,10 @@ struct ab_ctx {
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_ready = nullptr, comm_done = nullptr;
     bool comm_pending = false;
+    cudaEvent_t set_free[2] = {nullptr, nullptr};  // staging set s may be overwritten once set_free[s] has fired
+    bool set_used[2] = {false, false};
+    int next_set = 0;
+    bool async_host_step = false;  // AB_OPT_ASYNC_HOST_STEP
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     uint64_t launches = 0;
     std::string last_error;

@@ -60,26 +60,16 @@ matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
     const bool have = k0 / 4 < pitch;  // inside the (zero padded) row pitch
     const uint8_t* cbase = codes + k0 / 4;
     float* pdst = partial + (b * tiles + tile) * partial_stride;
-    // every warp of the grid takes one contiguous run of rows (x stays in registers for all of them); the codes of
-    // the next row pair are requested before the current pair is consumed, so their latency hides behind 128 FFMAs
-    const size_t nwarps = (size_t)gridDim.x * kFwdWarps;
-    const size_t chunk = (((out + nwarps - 1) / nwarps) + 1) & ~(size_t)1;
-    const size_t row0 = ((size_t)blockIdx.x * kFwdWarps + wid) * chunk;
-    const size_t row1 = row0 + chunk < out ? row0 + chunk : out;
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    uint4 n0 = zero4, n1 = zero4;
-    if (have && row0 < row1) {
-        n0 = __ldg(reinterpret_cast<const uint4*>(cbase + row0 * pitch));
-        if (row0 + 1 < row1) n1 = __ldg(reinterpret_cast<const uint4*>(cbase + (row0 + 1) * pitch));
-    }
+    // row groups are dealt round-robin to the warps of the grid, so x stays in registers for all of them
+    for (size_t row0 = ((size_t)blockIdx.x * kFwdWarps + wid) * kFwdRows; row0 < out;
+         row0 += (size_t)gridDim.x * kFwdWarps * kFwdRows) {
+    const size_t row1 = row0 + kFwdRows < out ? row0 + kFwdRows : out;
     for (size_t r = row0; r < row1; r += 2) {
         const bool two = r + 1 < row1;
-        const uint4 c0 = n0, c1 = n1;
-        n0 = zero4;
-        n1 = zero4;
-        if (have && r + 2 < row1) {
-            n0 = __ldg(reinterpret_cast<const uint4*>(cbase + (r + 2) * pitch));
-            if (r + 3 < row1) n1 = __ldg(reinterpret_cast<const uint4*>(cbase + (r + 3) * pitch));
+        uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
+        if (have) {
+            c0 = __ldg(reinterpret_cast<const uint4*>(cbase + r * pitch));
+            if (two) c1 = __ldg(reinterpret_cast<const uint4*>(cbase + (r + 1) * pitch));
         }
         const uint32_t w0[4] = {code_flags(c0.x), code_flags(c0.y), code_flags(c0.z), code_flags(c0.w)};
         const uint32_t w1[4] = {code_flags(c1.x), code_flags(c1.y), code_flags(c1.z), code_flags(c1.w)};
@@ -101,6 +91,7 @@ matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
             pdst[r] = s0;
             if (two) pdst[r + 1] = s1;
         }
+    }
     }
 }
 
@@ -147,25 +138,25 @@ matvec_bwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
     if (word < words_per_row) {
         const uint32_t* col = reinterpret_cast<const uint32_t*>(codes) + word;
         const size_t wstride = pitch / 4;
-        constexpr int U = 4;  // rows per batch; the next batch's loads are issued before this batch is consumed
+        constexpr int U = 4;  // independent loads in flight per thread
         size_t r = r0 + wid;
-        uint32_t nxt[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) nxt[u] = r + u * kBwdWarps < r1 ? __ldg(col + (r + u * kBwdWarps) * wstride) : 0u;
-        for (; r < r1; r += U * kBwdWarps) {
+        for (; r + (U - 1) * kBwdWarps < r1; r += U * kBwdWarps) {
             uint32_t w[U];
 #pragma unroll
-            for (int u = 0; u < U; ++u) w[u] = nxt[u];
-            const size_t rn = r + U * kBwdWarps;
-#pragma unroll
-            for (int u = 0; u < U; ++u) nxt[u] = rn + u * kBwdWarps < r1 ? __ldg(col + (rn + u * kBwdWarps) * wstride) : 0u;
+            for (int u = 0; u < U; ++u) w[u] = __ldg(col + (r + u * kBwdWarps) * wstride);
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const uint32_t f = code_flags(w[u]);
-                const float d = r + u * kBwdWarps < r1 ? s_dy[r - r0 + u * kBwdWarps] : 0.0f;  // past the slice: adds nothing
+                const float d = s_dy[r - r0 + u * kBwdWarps];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
             }
+        }
+        for (; r < r1; r += kBwdWarps) {
+            const uint32_t f = code_flags(__ldg(col + r * wstride));
+            const float d = s_dy[r - r0];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
         }
     }
 #pragma unroll

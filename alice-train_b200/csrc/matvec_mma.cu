@@ -6,8 +6,9 @@
 //   * v is cut into spans of 512 elements; each span is converted to 32-bit fixed point with its own power-of-two
 //     scale, v_k = n_k * 2^-s with |n_k| < 2^30, and n_k is split into four balanced base-256 digits (signed bytes);
 //   * the codes are stored offset-binary (w+1 in {0,1,2}) in the permuted layout the GEMM operand copies use, so
-//     `(word >> 2q) & 0x03030303` IS four unsigned bytes of the A operand of an int8 `mma.sync.m16n8k32`: two
-//     integer instructions per four weights, no table, no shared memory;
+//     `word & (0x03030303 << 2q)` IS four unsigned bytes, 4^q (w+1), of the A operand of an int8
+//     `mma.sync.m16n8k32`: one integer instruction per four weights, no shift, no table, no shared memory; the
+//     factor 4^q is taken out of the accumulator (exactly) once per span;
 //   * the four digit planes of v are four columns of the B operand (the other four columns are unused); after each
 //     span the s32 accumulators are recombined as sum_p acc_p * 256^p, scaled by 2^-s and added in f64 (every term
 //     is exact in f64); the offset sum_k n_k 2^-s is subtracted and the result is rounded to f32 once.
@@ -18,16 +19,16 @@
 // AB_OPT_EXACT_MATVEC on the context and get the FFMA kernels of matvec.cu.  A non-finite input makes every
 // output NaN, as it does there.
 //
-// Work layout: one block of 16 warps per SM; a warp owns 16 matrix rows and walks K in spans (128 contiguous bytes of codes per row, 32 per
-// thread, two 128-bit loads), with the loads of the next two spans in flight while the 16 MMAs of the current one
-// run.  Every block first converts its K slice of v into digits in shared memory (in MMA fragment order).  K is
-// cut into slices (grid.y) only where the rows alone do not give every SM enough warps; slices then write f64
-// partial sums that a small kernel adds in slice order, otherwise the main kernel writes y itself.
+// Work layout: one block of up to 14 warps per SM; a warp owns 16 matrix rows and walks K in spans (128 contiguous
+// bytes of codes per row, 32 per thread, two 128-bit loads into registers, three spans in flight).  Every
+// block first converts its K slice of v into digits in shared memory (in MMA fragment order).  K is cut into slices
+// (grid.y) only where the rows alone do not give every SM enough warps; slices then write f64 partial sums that a
+// small kernel adds in slice order, otherwise the main kernel writes y itself.
 #include "common.cuh"
 
 namespace {
 
-constexpr int kWarps = 16;           // per block; one block per SM
+constexpr int kMaxWarps = 14;        // per block (146 registers per thread); the launch picks 4..14 so that the row tiles divide evenly
 constexpr int kSpan = 512;           // codes per row per warp step
 constexpr int kMaxSpans = 23;        // per slice: 11776 elements = 46 KB of digits
 
@@ -38,9 +39,34 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 }
 __device__ __forceinline__ uint32_t ext(uint32_t w, int q) { return (q == 0 ? w : (w >> (2 * q))) & 0x03030303u; }
 
+struct RowPtrs {
+    const uint8_t *pa, *pb;
+    size_t ra, rb;
+    bool va, vb;
+    __device__ __forceinline__ void set(const uint8_t* codes, size_t pitch, size_t rows, size_t tile, int g, int t, size_t k0) {
+        ra = tile * 16 + g;
+        rb = ra + 8;
+        va = ra < rows;
+        vb = rb < rows;
+        pa = codes + (va ? ra : 0) * pitch + k0 / 4 + t * 32;
+        pb = codes + (vb ? rb : 0) * pitch + k0 / 4 + t * 32;
+    }
+};
+struct SpanBuf { uint4 a[2], b[2]; };   // 32 bytes of codes of row g and of row g+8 for one span
+// a span may reach past the row pitch: those 32-byte chunks are skipped (their digits are zero)
+__device__ __forceinline__ void load_span(SpanBuf& d, const RowPtrs& rp, int sp, int spans, int t, size_t chunk_limit) {
+    const size_t off = (size_t)sp * (kSpan / 4);
+    const bool in = sp < spans && off + (size_t)t * 32 + 32 <= chunk_limit;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    d.a[0] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pa + off)) : z;
+    d.a[1] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pa + off) + 1) : z;
+    d.b[0] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pb + off)) : z;
+    d.b[1] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pb + off) + 1) : z;
+}
+
 // codes: offset-binary, element e of each 16-group at bit 8(e%4)+2(e/4); `pitch` bytes per row (a multiple of 32).
 // slices == 1: y[row] (+)= scale * result.  Otherwise partial[slice][row] = this slice's f64 sum.
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kMaxWarps * 32)
 matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, const float* __restrict__ v, size_t k,
                   size_t k_slice, double* __restrict__ partial, size_t partial_stride, float* __restrict__ y, float scale,
                   int accumulate, int use_scale) {
@@ -55,11 +81,22 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
     const size_t klen = k0 + k_slice <= k_pad ? k_slice : k_pad - k0;   // a multiple of kSpan
     const int spans = (int)(klen / kSpan);
     if (threadIdx.x == 0) s_bad = 0;
+    // the codes of this warp's first row tile do not depend on v: request them before the conversion below
+    const size_t tiles = (rows + 15) / 16;
+    const size_t chunk_limit = pitch - k0 / 4;   // bytes of this slice inside a row
+    const int nwarps = (int)(blockDim.x >> 5);
+    size_t tile = (size_t)wid * gridDim.x + blockIdx.x;
+    RowPtrs rp;
+    SpanBuf buf[3];                              // three spans in flight
+    bool first = true;
+    rp.set(codes, pitch, rows, tile < tiles ? tile : 0, g, t, k0);
+#pragma unroll
+    for (int d = 0; d < 3; ++d) load_span(buf[d], rp, tile < tiles ? d : spans, spans, t, chunk_limit);
     __syncthreads();
     // ---- v[k0 .. k0+klen) -> digits.  A warp converts one span at a time; lane l takes the 16 elements that are word
     // (l % 8) of MMA thread (l / 8)'s 128 codes.  Shared-memory order = fragment order: 16-byte chunk
     // ((span * 8 + word) * 4 + plane) * 4 + t, so the 16 distinct chunks one LDS.128 of a warp touches are contiguous.
-    for (int sp = wid; sp < spans; sp += kWarps) {
+    for (int sp = wid; sp < spans; sp += nwarps) {
         const size_t base = k0 + (size_t)sp * kSpan + (size_t)lane * 16;
         float f[16];
         if (base + 16 <= k && (reinterpret_cast<uintptr_t>(v + base) & 15) == 0) {
@@ -80,25 +117,34 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
         }
         m = __reduce_max_sync(0xffffffffu, m);
         const bool bad = m >= 0x7f800000u;
-        // 2^s puts the span's largest magnitude into [2^29, 2^30); scaling by a power of two is exact
-        int ex = 0;
-        if (m != 0u && !bad) frexpf(__uint_as_float(m), &ex);
-        const int shift = (m != 0u && !bad) ? 30 - ex : 0;
+        // 2^shift puts the span's largest magnitude into [2^29, 2^30).  Scaling by a power of two = adding to the exponent
+        // field (exact); elements whose scaled exponent would leave the normal range are below 2^-96 and round to 0, and a
+        // span whose largest magnitude is subnormal (< 1.2e-38) counts as zero.
+        const int shift = (m >= 0x00800000u && !bad) ? 30 - ((int)(m >> 23) - 126) : 0;
+        const bool live = m >= 0x00800000u && !bad;
         long long sum = 0;
         uint32_t dg[4][4];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            int r = bad ? 0 : __float2int_rn(scalbnf(f[e], shift));
-            sum += r;
-            const int d0 = (int)(signed char)(r & 0xff); r = (r - d0) >> 8;
-            const int d1 = (int)(signed char)(r & 0xff); r = (r - d1) >> 8;
-            const int d2 = (int)(signed char)(r & 0xff); r = (r - d2) >> 8;    // |r| <= 65 is the top digit
-            const int sh = 8 * (e & 3);
-            if ((e & 3) == 0) { dg[0][e >> 2] = 0u; dg[1][e >> 2] = 0u; dg[2][e >> 2] = 0u; dg[3][e >> 2] = 0u; }
-            dg[0][e >> 2] |= (uint32_t)(d0 & 0xff) << sh;
-            dg[1][e >> 2] |= (uint32_t)(d1 & 0xff) << sh;
-            dg[2][e >> 2] |= (uint32_t)(d2 & 0xff) << sh;
-            dg[3][e >> 2] |= (uint32_t)(r & 0xff) << sh;
+        for (int q = 0; q < 4; ++q) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t bits = __float_as_uint(f[4 * q + i]);
+                const int be = (int)((bits >> 23) & 0xffu), nb = be + shift;
+                const float scaled = (live && be != 0 && nb > 0) ? __uint_as_float(bits + ((uint32_t)shift << 23)) : 0.0f;
+                const int n = __float2int_rn(scaled);
+                sum += n;
+                // balanced base-256 digits of n, all four at once: the bytes of (n + 0x00808080) ^ 0x00808080 are
+                // d0 (lowest) .. d3 (top, signed) with n = d0 + 256 d1 + 65536 d2 + 2^24 d3 and every |d| <= 128
+                wd[i] = ((uint32_t)n + 0x00808080u) ^ 0x00808080u;
+            }
+            // 4 x 4 byte transpose: register p of the result holds digit p of the four elements
+            const uint32_t t0 = __byte_perm(wd[0], wd[1], 0x5140), t1 = __byte_perm(wd[2], wd[3], 0x5140);   // d0,d1 of e0,e1 | e2,e3
+            const uint32_t t2 = __byte_perm(wd[0], wd[1], 0x7362), t3 = __byte_perm(wd[2], wd[3], 0x7362);   // d2,d3
+            dg[0][q] = __byte_perm(t0, t1, 0x5410);
+            dg[1][q] = __byte_perm(t0, t1, 0x7632);
+            dg[2][q] = __byte_perm(t2, t3, 0x5410);
+            dg[3][q] = __byte_perm(t2, t3, 0x7632);
         }
         const int tt = lane >> 3, word = lane & 7;
         uint4* dst = reinterpret_cast<uint4*>(s_digits) + ((size_t)(sp * 8 + word) * 4) * 4 + tt;
@@ -119,56 +165,51 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
         s_offset = o;
     }
     __syncthreads();
-    const size_t tiles = (rows + 15) / 16;
     const uint4* bsrc = reinterpret_cast<const uint4*>(s_digits) + (g & 3) * 4 + t;   // columns 4..7 repeat 0..3, unused
-    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-    const size_t chunk_limit = pitch - k0 / 4;   // bytes of this slice inside a row: a span may reach past the pitch
     // row tiles are dealt warp-major, so a short list still reaches every block (= every SM)
-    for (size_t tile = (size_t)wid * gridDim.x + blockIdx.x; tile < tiles; tile += (size_t)gridDim.x * kWarps) {
-        const size_t ra = tile * 16 + g, rb = ra + 8;
-        const bool va = ra < rows, vb = rb < rows;
-        const uint8_t* pa = codes + (va ? ra : 0) * pitch + k0 / 4 + t * 32;
-        const uint8_t* pb = codes + (vb ? rb : 0) * pitch + k0 / 4 + t * 32;
-        // three spans in flight: [0] is consumed, [1] and [2] are on their way
-        uint4 qa[3][2], qb[3][2];
+    for (; tile < tiles; tile += (size_t)gridDim.x * nwarps) {
+        if (!first) {
+            rp.set(codes, pitch, rows, tile, g, t, k0);
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            const size_t off = (size_t)d * (kSpan / 4);
-            const bool in = d < spans && off + (size_t)t * 32 + 32 <= chunk_limit;
-            qa[d][0] = in ? __ldg(reinterpret_cast<const uint4*>(pa + off)) : z;
-            qa[d][1] = in ? __ldg(reinterpret_cast<const uint4*>(pa + off) + 1) : z;
-            qb[d][0] = in ? __ldg(reinterpret_cast<const uint4*>(pb + off)) : z;
-            qb[d][1] = in ? __ldg(reinterpret_cast<const uint4*>(pb + off) + 1) : z;
+            for (int d = 0; d < 3; ++d) load_span(buf[d], rp, d, spans, t, chunk_limit);
         }
+        first = false;
         double acc_a = 0.0, acc_b = 0.0;
-        for (int sp = 0; sp < spans; ++sp) {
-            const uint4 a[2] = {qa[0][0], qa[0][1]}, b[2] = {qb[0][0], qb[0][1]};
-            qa[0][0] = qa[1][0]; qa[0][1] = qa[1][1]; qb[0][0] = qb[1][0]; qb[0][1] = qb[1][1];
-            qa[1][0] = qa[2][0]; qa[1][1] = qa[2][1]; qb[1][0] = qb[2][0]; qb[1][1] = qb[2][1];
-            {
-                const size_t off = (size_t)(sp + 3) * (kSpan / 4);
-                const bool in = sp + 3 < spans && off + (size_t)t * 32 + 32 <= chunk_limit;
-                qa[2][0] = in ? __ldg(reinterpret_cast<const uint4*>(pa + off)) : z;
-                qa[2][1] = in ? __ldg(reinterpret_cast<const uint4*>(pa + off) + 1) : z;
-                qb[2][0] = in ? __ldg(reinterpret_cast<const uint4*>(pb + off)) : z;
-                qb[2][1] = in ? __ldg(reinterpret_cast<const uint4*>(pb + off) + 1) : z;
-            }
-            const uint4* bs = bsrc + (size_t)sp * 128;
-            int c[4] = {0, 0, 0, 0};
+        for (int sp0 = 0; sp0 < spans; sp0 += 3) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t wa[4] = {a[h].x, a[h].y, a[h].z, a[h].w}, wb[4] = {b[h].x, b[h].y, b[h].z, b[h].w};
+            for (int d = 0; d < 3; ++d) {     // buffer d holds span sp0 + d: compile-time buffer index, no register moves
+                const int sp = sp0 + d;
+                if (sp < spans) {
+                    const SpanBuf cur = buf[d];
+                    load_span(buf[d], rp, sp + 3, spans, t, chunk_limit);
+                    const uint4* bs = bsrc + (size_t)sp * 128;
+                    // Field q of every byte is used where it lies: `word & (0x03030303 << 2q)` is 4^q * (w+1) as an unsigned
+                    // byte (one LOP3, no shift), and all MMAs of field q go to accumulator set q, which therefore holds
+                    // 4^q times its sum and is shifted back (exactly) at the end of the span.  Each MMA takes field q of two
+                    // neighbouring words as its two k-halves, with digit register q of those words' chunks as B.
+                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0}, c3[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const uint4 d = bs[(h * 4 + wi) * 16];   // this thread's digits of plane g for the 16 codes of this word
-                    mma_u8s8(c, ext(wa[wi], 0), ext(wb[wi], 0), ext(wa[wi], 1), ext(wb[wi], 1), d.x, d.y);
-                    mma_u8s8(c, ext(wa[wi], 2), ext(wb[wi], 2), ext(wa[wi], 3), ext(wb[wi], 3), d.z, d.w);
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t wa[4] = {cur.a[h].x, cur.a[h].y, cur.a[h].z, cur.a[h].w};
+                        const uint32_t wb[4] = {cur.b[h].x, cur.b[h].y, cur.b[h].z, cur.b[h].w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; wi += 2) {
+                            const uint4 d0 = bs[(h * 4 + wi) * 16];       // this thread's digits of plane g for the 16 codes of a word
+                            const uint4 d1 = bs[(h * 4 + wi + 1) * 16];
+                            mma_u8s8(c0, wa[wi] & 0x03030303u, wb[wi] & 0x03030303u, wa[wi + 1] & 0x03030303u, wb[wi + 1] & 0x03030303u, d0.x, d1.x);
+                            mma_u8s8(c1, wa[wi] & 0x0C0C0C0Cu, wb[wi] & 0x0C0C0C0Cu, wa[wi + 1] & 0x0C0C0C0Cu, wb[wi + 1] & 0x0C0C0C0Cu, d0.y, d1.y);
+                            mma_u8s8(c2, wa[wi] & 0x30303030u, wb[wi] & 0x30303030u, wa[wi + 1] & 0x30303030u, wb[wi + 1] & 0x30303030u, d0.z, d1.z);
+                            mma_u8s8(c3, wa[wi] & 0xC0C0C0C0u, wb[wi] & 0xC0C0C0C0u, wa[wi + 1] & 0xC0C0C0C0u, wb[wi + 1] & 0xC0C0C0C0u, d0.w, d1.w);
+                        }
+                    }
+                    // c[0], c[1]: row g, columns (= digit planes) 2t, 2t+1; c[2], c[3]: row g+8.  |sum| <= 2^17 per span.
+                    const int e0 = (c0[0] + (c1[0] >> 2)) + ((c2[0] >> 4) + (c3[0] >> 6)), e1 = (c0[1] + (c1[1] >> 2)) + ((c2[1] >> 4) + (c3[1] >> 6));
+                    const int e2 = (c0[2] + (c1[2] >> 2)) + ((c2[2] >> 4) + (c3[2] >> 6)), e3 = (c0[3] + (c1[3] >> 2)) + ((c2[3] >> 4) + (c3[3] >> 6));
+                    const double sc = s_scale[sp];
+                    acc_a = fma((double)(e0 + e1 * 256), sc, acc_a);
+                    acc_b = fma((double)(e2 + e3 * 256), sc, acc_b);
                 }
             }
-            // c[0], c[1]: row g, columns (= digit planes) 2t, 2t+1; c[2], c[3]: row g+8.  |c| <= 2^17 per span.
-            const double sc = s_scale[sp];
-            acc_a = fma((double)(c[0] + c[1] * 256), sc, acc_a);
-            acc_b = fma((double)(c[2] + c[3] * 256), sc, acc_b);
         }
         // planes 0,1 sit in t = 0, planes 2,3 (weight 2^16) in t = 1; t = 2,3 hold the unused columns
         acc_a = t == 0 ? acc_a : (t == 1 ? acc_a * 65536.0 : 0.0);
@@ -180,11 +221,11 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
             const double ra_v = s_bad ? nan : acc_a - s_offset, rb_v = s_bad ? nan : acc_b - s_offset;
             if (partial) {
                 double* dst = partial + (size_t)blockIdx.y * partial_stride;
-                if (va) dst[ra] = ra_v;
-                if (vb) dst[rb] = rb_v;
+                if (rp.va) dst[rp.ra] = ra_v;
+                if (rp.vb) dst[rp.rb] = rb_v;
             } else {
-                if (va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, scale); y[ra] = accumulate ? __fadd_rn(y[ra], r) : r; }
-                if (vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, scale); y[rb] = accumulate ? __fadd_rn(y[rb], r) : r; }
+                if (rp.va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, scale); y[rp.ra] = accumulate ? __fadd_rn(y[rp.ra], r) : r; }
+                if (rp.vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, scale); y[rp.rb] = accumulate ? __fadd_rn(y[rp.rb], r) : r; }
             }
         }
     }
@@ -226,11 +267,16 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
         if (st) return st;
         partial = static_cast<double*>(scratch);
     }
-    size_t gx = (size_t)ctx->sm_count / slices;   // one block of 16 warps per SM over all slices
+    size_t gx = (size_t)ctx->sm_count / slices;   // one block per SM over all slices
     if (gx > tiles) gx = tiles;
     if (gx < 1) gx = 1;
+    // warps per block: as many as give every warp the same number of row tiles (a 13th warp beats a second pass)
+    size_t per_block = (tiles + gx - 1) / gx;
+    size_t passes = (per_block + kMaxWarps - 1) / kMaxWarps;
+    size_t nw = (per_block + passes - 1) / passes;
+    if (nw < 4) nw = 4;
     dim3 grid((unsigned)gx, (unsigned)slices);
-    matvec_mma_kernel<<<grid, kWarps * 32, 4 * k_slice, ctx->stream>>>(codes, pitch, rows, v, k, k_slice, partial, pstride, y, scale,
+    matvec_mma_kernel<<<grid, (unsigned)nw * 32, 4 * k_slice, ctx->stream>>>(codes, pitch, rows, v, k, k_slice, partial, pstride, y, scale,
                                                                         accumulate, use_scale);
     AB_LAUNCH_CHECK(ctx);
     if (slices > 1) {

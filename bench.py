@@ -331,9 +331,16 @@ def run_native(args):
                              dx=torch.empty((tokens, L["inn"]), dtype=torch.bfloat16).pin_memory()))
         lib = _ffi.load()
 
+        # calls only queue their work (AB_OPT_ASYNC_HOST_STEP) and the step ends with one sync, so the copies in of
+        # one projection overlap the GEMMs and copies out of the one before; the projection with the largest dx
+        # (down) goes first so that the step does not end on its copy out
+        ctx.set_async_host_step(True)
+        order = sorted(range(len(layers)), key=lambda i: -layers[i]["inn"])
+
         def e2e_step():
             pending = []
-            for li, (L, Hh) in enumerate(zip(layers, host)):
+            for li in order:
+                L, Hh = layers[li], host[li]
                 _ffi.check(lib.ab_bitlinear_step_host(ctx.handle, L["w"].handle, C.c_void_p(Hh["x"].data_ptr()),
                                                       C.c_void_p(Hh["dy"].data_ptr()), tokens,
                                                       C.c_void_p(Hh["y"].data_ptr()), C.c_void_p(Hh["dx"].data_ptr()),
@@ -346,6 +353,7 @@ def run_native(args):
                 hnd.wait()
             if switch is not None:
                 switch.wait()
+            ctx.sync()
         e2e_steps = max(2, min(args.steps, 5))
         e2e_step()
         fence()
@@ -359,7 +367,8 @@ def run_native(args):
         h2d = sum(tokens * (i + o) * 2 for _, o, i in projs)
         e2e = {"value": world * tokens * e2e_steps / float(dt.item()), "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": h2d, "steps": e2e_steps,
-               "note": "ab_bitlinear_step_host per projection: x, dy in and y, dx out as bf16 through pinned host memory; dW stays on the device"}
+               "note": "ab_bitlinear_step_host per projection (queued, one sync per step): x, dy in and y, dx out as bf16 through pinned host memory; dW stays on the device"}
+        ctx.set_async_host_step(False)
 
     # ---- CPU baseline (oracle port), rank 0 at N = 1 only, bounded sample
     cpu_baseline = None
@@ -410,6 +419,11 @@ def run_hbm(args):
 
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
+    # everything runs on one explicit stream so that the timed launch sequences can be captured into CUDA graphs:
+    # these kernels take 10-50 us, less than the Python + ctypes cost of issuing one, and a replayed graph times the
+    # device, not the host
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     ctx = alice_train.GpuContext.on_torch_stream(0)
     lib = _ffi.load()
     pk = peaks()
@@ -429,17 +443,34 @@ def run_hbm(args):
     ctx.sync()
     vp = lambda t: C.c_void_p(t.data_ptr())
 
+    timing = {"mode": "cuda-graph replay"}
+
     def timeit(fn, reps, rotate):
         for i in range(3):
             fn(mats[i % nmat])
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(reps):
-            fn(mats[i % nmat] if rotate else mats[0])
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / reps * 1e-3
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(reps):
+                    fn(mats[i % nmat] if rotate else mats[0])
+            graph.replay()
+            torch.cuda.synchronize()
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps * 1e-3
+        except Exception as e:  # capture refused: time the launch loop itself
+            timing["mode"] = f"launch loop (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(reps):
+                fn(mats[i % nmat] if rotate else mats[0])
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps * 1e-3
 
     code_bytes = out * inn / 4
     res = {}
@@ -457,6 +488,13 @@ def run_hbm(args):
         res[name] = {"bytes": nbytes, "cold_us": cold * 1e6, "cold_gbs": nbytes / cold / 1e9,
                      "cold_frac_of_hbm": nbytes / cold / 1e9 / pk["hbm_gbs"], "l2_resident_us": warm * 1e6,
                      "l2_resident_gbs": nbytes / warm / 1e9}
+    # the same three entry points with AB_OPT_EXACT_MATVEC: f32 adds on the CUDA cores, as the reference's loops do
+    ctx.set_exact_matvec(True)
+    for name, (fn, nbytes) in cases.items():
+        cold = timeit(fn, 6 * nmat, True)
+        res[name + " [f32 adds]"] = {"bytes": nbytes, "cold_us": cold * 1e6, "cold_gbs": nbytes / cold / 1e9,
+                                     "cold_frac_of_hbm": nbytes / cold / 1e9 / pk["hbm_gbs"]}
+    ctx.set_exact_matvec(False)
     t = timeit(lambda w: _ffi.check(lib.ab_ste_weight_grad(ctx.handle, vp(x), 8192, vp(dy), 8192, vp(dW)), ctx.handle), 20, False)
     nb = 8.0 * 8192 * 8192 + 4 * (8192 + 8192)
     res["ste_weight_grad"] = {"bytes": nb, "cold_us": t * 1e6, "cold_gbs": nb / t / 1e9, "cold_frac_of_hbm": nb / t / 1e9 / pk["hbm_gbs"]}
@@ -477,9 +515,9 @@ def run_hbm(args):
     line = {"metric": "batch-1 ternary kernels, achieved HBM GB/s", "value": dom["cold_gbs"], "unit": "GB/s", "n_gpus": 1,
             "higher_is_better": True, "data": "synthetic", "dtype": "f32 x 2-bit codes",
             "config": {"workload": "hbm-kernels", "matrix": [out, inn], "rotation": f"{nmat} distinct packed matrices ({nmat * code_bytes / 2**20:.0f} MiB of codes) so every launch reads cold lines"},
-            "roofline": {"bound": "hbm", "kernel": "matvec_bwd_kernel", "achieved": dom["cold_gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "matvec_mma_kernel (dx = W^T dy, integer path)", "achieved": dom["cold_gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": dom["cold_frac_of_hbm"], "traffic": None, "peak_source": pk["source"] + " copy bandwidth"},
-            "kernels": res}
+            "timing": timing["mode"], "kernels": res}
     print(json.dumps(line), flush=True)
     return 0
 

@@ -89,7 +89,10 @@ AB_API int ab_ctx_destroy(ab_ctx* ctx);
  * sums are then exact integers on the tensor cores and are rounded to f32 once.  That path reaches the HBM
  * roofline; it differs from f32 accumulation only in rounding, except that elements below 2^-31 of the vector's
  * largest magnitude drop out. */
-typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1 } ab_option;
+/* AB_OPT_ASYNC_HOST_STEP (default 0): when 1, ab_bitlinear_step_host returns as soon as its copies and kernels are
+ * queued; the host buffers of a call may be read (y, dx) or reused (x, dy) after the next ab_ctx_sync().  Consecutive
+ * calls then overlap: the copies in of one run beside the GEMMs and the copies out of the one before. */
+typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2 } ab_option;
 AB_API int ab_ctx_set_option(ab_ctx* ctx, int option, int value);
 /* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
 AB_API int ab_ctx_sync(ab_ctx* ctx);

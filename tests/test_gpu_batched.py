@@ -200,8 +200,10 @@ def test_model_linear_shapes_sampled(env, orc, name, out, inn, std):
     _check_linear_sampled(env, orc, rng(out * 31 + inn), name, 8192, out, inn, 300 + out % 97, std, samples=200)
 
 
-def test_bitlinear_step_host(env, orc):
-    """The host-buffer entry point (H2D, act-quant, fwd, dx, dW +=, D2H) against its parts."""
+@pytest.mark.parametrize("queued", [False, True], ids=["blocking", "queued"])
+def test_bitlinear_step_host(env, orc, queued):
+    """The host-buffer entry point (H2D, act-quant, fwd, dx, dW +=, D2H) against its parts; blocking, and with
+    AB_OPT_ASYNC_HOST_STEP (calls only queue, buffers are read after a sync)."""
     import ctypes as C
     at, bl, ctx, torch = env
     from alice_train import _ffi
@@ -213,10 +215,13 @@ def test_bitlinear_step_host(env, orc):
     y_h = torch.empty((m, out), dtype=torch.bfloat16).pin_memory()
     dx_h = torch.empty((m, inn), dtype=torch.bfloat16).pin_memory()
     dw = torch.zeros((out, inn), dtype=torch.float32, device="cuda")
+    ctx.set_async_host_step(queued)
     for _ in range(2):  # dW accumulates across calls
         _ffi.check(_ffi.load().ab_bitlinear_step_host(ctx.handle, h.handle, C.c_void_p(xb.data_ptr()),
                                                       C.c_void_p(dyb.data_ptr()), m, C.c_void_p(y_h.data_ptr()),
                                                       C.c_void_p(dx_h.data_ptr()), C.c_void_p(dw.data_ptr())), ctx.handle)
+    ctx.sync()
+    ctx.set_async_host_step(False)
     qa = bl.act_quant_int8(ctx, xb.cuda())
     y_ref = bl.bitlinear_fwd(h, qa, dtype=torch.bfloat16)
     dx_ref = bl.bitlinear_dx(h, dyb.cuda(), dtype=torch.bfloat16)
