@@ -183,7 +183,9 @@ static int weights_create(ab_ctx* ctx, size_t out, size_t in, bool gemm_copies, 
     w->in = in;
     w->pitch = ab_round_up(in ? in : 1, 128) / 4;
     w->tpitch = ab_round_up(out ? out : 1, 128) / 4;
-    size_t cbytes = (out ? out : 1) * w->pitch, tbytes = (in ? in : 1) * w->tpitch;
+    // 128 bytes of slack behind the last row: the integer matvec reads whole 128-byte spans, up to 96 bytes past a
+    // row's pitch (into the next row, or into this slack)
+    size_t cbytes = (out ? out : 1) * w->pitch + 128, tbytes = (in ? in : 1) * w->tpitch + 128;
     cudaError_t e = cudaMalloc(&w->codes, cbytes);
     if (e == cudaSuccess && gemm_copies) e = cudaMalloc(&w->codes_fwd, cbytes);
     if (e == cudaSuccess && gemm_copies) e = cudaMalloc(&w->codes_t, tbytes);

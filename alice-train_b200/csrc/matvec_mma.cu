@@ -1,4 +1,4 @@
-// Batch-1 matvec at the HBM roofline: y = M v for a ternary matrix M held as 2-bit codes, M = W (forward,
+// Batch-1 matvec towards the HBM roofline: y = M v for a ternary matrix M held as 2-bit codes, M = W (forward,
 // rows = output features) or M = W^T (dx = W^T dy, rows = input features).
 //
 // At 0.25 byte per weight HBM delivers about 26 T weights/s, several times what the SMs can add one weight at a

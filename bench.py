@@ -314,7 +314,7 @@ def run_native(args):
                 "frac": per[dom]["tops_avg"] / peak if per[dom]["tops_avg"] else None,
                 # DRAM read + write bytes of one launch from the ncu capture summarised in
                 # profiles/gemm_pair_kernel_llama8b_mlp.md (gate projection; llama3-8b-mlp workload only)
-                "traffic": ({"fwd": 95.4e6, "dx": 171.0e6, "dw": 392.4e6}[dom] if args.workload == "llama3-8b-mlp" else None),
+                "traffic": ({"fwd": 95.0e6, "dx": 158.3e6, "dw": 363.3e6}[dom] if args.workload == "llama3-8b-mlp" else None),
                 "peak_source": ("int8 MMA-only probe (ab_tensor_peak_probe) in this run" if dom == "fwd"
                                 else f"{pk['source']} bf16 sustained {peak_bf16} TFLOP/s"),
                 "algorithmic_ops_per_launch": ops_per_launch}
