@@ -18,6 +18,7 @@ AB_F32, AB_BF16 = 0, 1
 AB_TERNARY, AB_BINARY2, AB_INT4, AB_INT8 = 0, 1, 2, 3
 AB_GUARD_INV_ZERO, AB_GUARD_FLOOR = 0, 1
 AB_OPT_EXACT_MATVEC, AB_OPT_ASYNC_HOST_STEP = 1, 2
+AB_XCHG_ALLREDUCE_F32, AB_XCHG_ALLGATHER, AB_XCHG_REDUCESCATTER_BF16 = 0, 1, 2
 
 
 class FqReport(C.Structure):
@@ -59,6 +60,7 @@ SIGNATURES = {
     "ab_weights_fq_report": (_i, [_vp, C.POINTER(FqReport)]),
     "ab_dp_allreduce_start": (_i, [_vp, _vp, _sz, _vp, _vp, _i, _i, C.c_uint32, _i]),
     "ab_dp_allreduce_wait": (_i, [_vp]),
+    "ab_switch_exchange_start": (_i, [_vp, _i, _vp, _vp, _vp, _sz, _vp, _vp, _i, _i, C.c_uint32, _i]),
     "ab_quantize_and_pack_host": (_i, [_vp, _vp, _sz, C.POINTER(_f), _vp]),
     "ab_calibrate_scale": (_i, [_vp, _vp, _sz, _vp]),
     "ab_fake_quantize_forward": (_i, [_vp, _vp, _vp, _sz, _vp, _f, _i]),

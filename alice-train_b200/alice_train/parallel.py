@@ -49,51 +49,74 @@ class DwAllReducer:
         self._pending.clear()
 
 
+class SwitchBuffer:
+    """A buffer in symmetric memory (every GPU of the group maps its own copy and the group's NVSwitch multicast
+    address) plus the 16 bytes of barrier counters the library's exchange kernels need.  torch's symmetric-memory
+    allocator provides the mapping; the transfers and the inter-GPU barriers are in the CUDA library
+    (ab_switch_exchange_start / ab_dp_allreduce_wait).  Construction is collective: every rank, same sizes."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, ctx, nbytes: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _ffi
+        self._ffi, self.ctx = _ffi, ctx
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world < 2:
+            raise ValueError("a SwitchBuffer needs at least two GPUs")
+        unit = 16 * self.world
+        self.nbytes = (nbytes + unit - 1) // unit * unit
+        self._t = symm_mem.empty(self.nbytes + self.FLAG_BYTES, dtype=torch.uint8, device=device)
+        self._hdl = symm_mem.rendezvous(self._t, self.group)
+        if not self._hdl.multicast_ptr:
+            raise RuntimeError("this group of GPUs has no NVSwitch multicast mapping")
+        self._t[nbytes:].zero_()  # padding and the barrier counters
+        self._mc = self._hdl.multicast_ptr + (self._t.data_ptr() - self._hdl.buffer_ptrs[self._hdl.rank])
+        self._epoch = 0
+        self.bytes = self._t[:nbytes]
+
+    def view(self, dtype, shape):
+        """The buffer's first prod(shape) elements as a tensor of `dtype` (the local copy)."""
+        n = 1
+        for d in shape:
+            n *= d
+        return self._t[:n * torch.empty((), dtype=dtype).element_size()].view(dtype).view(shape)
+
+    def start(self, op: int, out_local: torch.Tensor | None = None, ctas: int = 0):
+        self._epoch += 1
+        self._ffi.check(self._ffi.load().ab_switch_exchange_start(
+            self.ctx.handle, op, self._mc, self._t.data_ptr(), out_local.data_ptr() if out_local is not None else None,
+            self.nbytes, self._t.data_ptr() + self.nbytes, self._mc + self.nbytes, self.rank, self.world, self._epoch, int(ctas)),
+            self.ctx.handle)
+
+    @staticmethod
+    def ready(buffers, device):
+        """After constructing all buffers: make their zeroed counters visible on every GPU before the first exchange."""
+        torch.cuda.synchronize(device)
+        dist.barrier(buffers[0].group if buffers else None)
+        torch.cuda.synchronize(device)
+
+
 class SwitchDwAllReducer:
-    """dW buffers in symmetric memory, summed over the GPUs inside NVSwitch by the library's own kernel
-    (ab_dp_allreduce_start / _wait) instead of NCCL: no staging copies and 8 CTAs per exchange, so the GEMMs that
-    overlap it keep their SMs.  torch's symmetric-memory allocator provides the mapping (each GPU's buffer plus the
-    group's multicast address); the arithmetic and the inter-GPU barriers are in the CUDA library.
+    """dW buffers in symmetric memory, summed over the GPUs inside NVSwitch by the library's own kernel instead of
+    NCCL: no staging copies and a handful of small CTAs per exchange, so the GEMMs that overlap it keep their SMs.
 
         red = SwitchDwAllReducer(ctx, [(out, inn), ...], device)   # collective: every rank, same shapes
         ste_dw(ctx, dy, x, red.dW[i], beta=0.0); red.submit(i); ...; red.wait()
     """
 
-    FLAG_FLOATS = 64
-
     def __init__(self, ctx, shapes, device, group=None, ctas: int = 0):
         import math
-
-        import torch.distributed._symmetric_memory as symm_mem
         from . import _ffi
         self._ffi, self.ctx, self.ctas = _ffi, ctx, int(ctas)
-        self.group = group if group is not None else dist.group.WORLD
-        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        if self.world < 2:
-            raise ValueError("SwitchDwAllReducer needs at least two GPUs")
-        self.dW, self._bufs, self._epoch = [], [], []
-        for shape in shapes:
-            n = math.prod(shape)
-            n_pad = (n + 4 * self.world - 1) // (4 * self.world) * (4 * self.world)
-            t = symm_mem.empty(n_pad + self.FLAG_FLOATS, dtype=torch.float32, device=device)
-            hdl = symm_mem.rendezvous(t, self.group)
-            if not hdl.multicast_ptr:
-                raise RuntimeError("this group of GPUs has no NVSwitch multicast mapping")
-            t[n:].zero_()  # padding and the barrier counters
-            mc = hdl.multicast_ptr + (t.data_ptr() - hdl.buffer_ptrs[hdl.rank])
-            self._bufs.append((t, hdl, mc, n_pad))
-            self._epoch.append(0)
-            self.dW.append(t[:n].view(shape))
-        torch.cuda.synchronize(device)
-        dist.barrier(self.group)
-        torch.cuda.synchronize(device)
+        self._bufs = [SwitchBuffer(ctx, 4 * math.prod(shape), device, group) for shape in shapes]
+        self.world, self.rank = self._bufs[0].world, self._bufs[0].rank
+        self.dW = [b.view(torch.float32, shape) for b, shape in zip(self._bufs, shapes)]
+        SwitchBuffer.ready(self._bufs, device)
 
     def submit(self, i: int):
-        t, _, mc, n_pad = self._bufs[i]
-        self._epoch[i] += 1
-        self._ffi.check(self._ffi.load().ab_dp_allreduce_start(
-            self.ctx.handle, mc, n_pad, t.data_ptr() + 4 * n_pad, mc + 4 * n_pad, self.rank, self.world, self._epoch[i],
-            self.ctas), self.ctx.handle)
+        self._bufs[i].start(self._ffi.AB_XCHG_ALLREDUCE_F32, ctas=self.ctas)
 
     def wait(self):
         self._ffi.check(self._ffi.load().ab_dp_allreduce_wait(self.ctx.handle), self.ctx.handle)

@@ -406,6 +406,22 @@ int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, uint32_t*
     return abk_dp_allreduce_start(ctx, multicast_buf, n, flags_local, flags_multicast, rank, world, epoch, ctas);
 }
 
+int ab_switch_exchange_start(ab_ctx* ctx, int op, void* multicast_buf, const void* local_buf, void* out_local, size_t bytes,
+                             uint32_t* flags_local, uint32_t* flags_multicast, int rank, int world, uint32_t epoch, int ctas) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(multicast_buf && flags_local && flags_multicast, AB_ERR_NULL);
+    AB_REQUIRE(op == AB_XCHG_ALLREDUCE_F32 || op == AB_XCHG_ALLGATHER || op == AB_XCHG_REDUCESCATTER_BF16, AB_ERR_UNSUPPORTED);
+    if (op == AB_XCHG_ALLGATHER) AB_REQUIRE(local_buf, AB_ERR_NULL);
+    if (op == AB_XCHG_REDUCESCATTER_BF16) AB_REQUIRE(out_local, AB_ERR_NULL);
+    AB_REQUIRE(world >= 2 && world <= 64 && rank >= 0 && rank < world && epoch >= 1, AB_ERR_SHAPE);
+    AB_REQUIRE(bytes > 0 && bytes % (16 * (size_t)world) == 0, AB_ERR_SHAPE);
+    AB_REQUIRE(((reinterpret_cast<uintptr_t>(multicast_buf) | reinterpret_cast<uintptr_t>(local_buf) | reinterpret_cast<uintptr_t>(out_local) |
+                 reinterpret_cast<uintptr_t>(flags_local) | reinterpret_cast<uintptr_t>(flags_multicast)) & 15) == 0, AB_ERR_ALIGN);
+    AB_REQUIRE(ctas >= 0 && ctas <= 148, AB_ERR_UNSUPPORTED);
+    if (ctas == 0) ctas = world <= 2 ? 16 : (world <= 4 ? 12 : 8);
+    return abk_switch_exchange_start(ctx, op, multicast_buf, local_buf, out_local, bytes, flags_local, flags_multicast, rank, world, epoch, ctas);
+}
+
 int ab_dp_allreduce_wait(ab_ctx* ctx) {
     AB_TRY(bind(ctx));
     return abk_dp_allreduce_wait(ctx);

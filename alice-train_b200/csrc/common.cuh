@@ -149,6 +149,8 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
 // dp_allreduce.cu
 int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* flags_local, unsigned int* flags_mc, int rank,
                            int world, unsigned int epoch, int ctas);
+int abk_switch_exchange_start(ab_ctx* ctx, int op, void* mc_buf, const void* local_buf, void* out_local, size_t bytes,
+                              unsigned int* flags_local, unsigned int* flags_mc, int rank, int world, unsigned int epoch, int ctas);
 int abk_dp_allreduce_wait(ab_ctx* ctx);
 
 // gemm_tc.cu

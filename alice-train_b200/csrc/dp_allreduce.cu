@@ -1,5 +1,5 @@
-// Data-parallel exchange of the latent-weight gradient: dW summed over the GPUs of one NVSwitch domain, in place,
-// by the switch itself.
+// Exchanges between the GPUs of one NVSwitch domain done by the switch itself.  First and foremost the data-parallel
+// exchange of the latent-weight gradient: dW summed over the GPUs, in place.
 //
 // The buffer lives in memory that every GPU of the group has mapped twice: its own copy (plain pointer) and the
 // group's multicast address.  GPU r owns the r-th slice of the buffer: one `multimem.ld_reduce.add.v4.f32` returns
@@ -7,6 +7,10 @@
 // sum back to all of them.  Per GPU and call n*4 bytes leave and n*4 bytes arrive over NVLink, nothing is staged,
 // and a handful of small CTAs keep enough requests in flight: the GEMMs that run beside it keep their SMs.  The
 // reference has no counterpart: it trains on one device (CudaContext::new(0), src/cuda_matmul.rs:954).
+//
+// The same skeleton also serves the two exchanges of the row-sharded layer: the all-gather of the forward output (every
+// GPU stores its shard to all copies with `multimem.st`) and the reduce-scatter of dx over tokens (bf16 partial
+// products summed in f32 by `multimem.ld_reduce`, each GPU keeping its token slice).
 //
 // Two device-side barriers bracket the transfer, each a counter in the same multicast mapping that every GPU
 // increments with `multimem.red` and polls on its own copy: before the first read every GPU's gradient kernel must
@@ -54,12 +58,34 @@ __device__ __forceinline__ void mc_st(float* mc, float4 v) {
                  : "memory");
 }
 
+__device__ __forceinline__ uint4 mc_ld_reduce_bf16(const void* mc) {   // 8 bf16 per address, added in f32 inside the switch
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void mc_st_raw(void* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
+// The three exchanges share one skeleton: start barrier, this GPU's share of the transfer, end barrier.
+//   ALLREDUCE_F32      : slice `rank` of the buffer: ld_reduce (sum over GPUs, in the switch) -> st to all GPUs
+//   ALLGATHER          : slice `rank` of the buffer holds this GPU's contribution: plain local load -> st to all GPUs
+//   REDUCESCATTER_BF16 : slice `rank` of the buffer: ld_reduce (bf16, f32 accumulation) -> plain store to `out_local`
 // flags (u32, in the multicast-mapped allocation): [0] start barrier, [1] end barrier, [2] CTAs of this GPU done.
 // The CTA is small on purpose (256 threads, no shared memory of its own, at most 64 registers a thread): it fits on
 // an SM beside a resident CTA of the pair GEMMs, so the exchange takes issue slots from them, not SMs.
+enum { OP_ALLREDUCE_F32 = 0, OP_ALLGATHER = 1, OP_REDUCESCATTER_BF16 = 2 };
+
+template <int OP>
 __global__ void __launch_bounds__(kArThreads, 4)
-nvls_allreduce_kernel(float* __restrict__ mc_buf, size_t n_vec4, unsigned int* __restrict__ flags_local,
-                      unsigned int* __restrict__ flags_mc, int rank, int world, unsigned int target, int* __restrict__ status) {
+nvls_exchange_kernel(uint4* __restrict__ mc_buf, const uint4* __restrict__ local_buf, uint4* __restrict__ out_local, size_t n_vec,
+                     unsigned int* __restrict__ flags_local, unsigned int* __restrict__ flags_mc, int rank, int world,
+                     unsigned int target, int* __restrict__ status) {
     int go = 0;
     if (threadIdx.x == 0) {
         if (blockIdx.x == 0) mc_signal(flags_mc + 0);
@@ -68,19 +94,44 @@ nvls_allreduce_kernel(float* __restrict__ mc_buf, size_t n_vec4, unsigned int* _
     }
     go = __syncthreads_or(go);
     if (go) {
-        const size_t per = n_vec4 / (size_t)world;       // the host checked divisibility
-        float* mine = mc_buf + (size_t)rank * per * 4;
+        const size_t per = n_vec / (size_t)world;        // 16-byte units per GPU; the host checked divisibility
+        const size_t base = (size_t)rank * per;
         const size_t stride = (size_t)gridDim.x * kArThreads;
         size_t i = (size_t)blockIdx.x * kArThreads + threadIdx.x;
         constexpr int U = 8;                             // independent round trips in flight per thread
         for (; i + (U - 1) * stride < per; i += U * stride) {
-            float4 v[U];
+            uint4 v[U];
 #pragma unroll
-            for (int u = 0; u < U; ++u) v[u] = mc_ld_reduce(mine + 4 * (i + u * stride));
+            for (int u = 0; u < U; ++u) {
+                const size_t j = base + i + u * stride;
+                if (OP == OP_ALLREDUCE_F32) {
+                    const float4 f = mc_ld_reduce(reinterpret_cast<const float*>(mc_buf + j));
+                    v[u] = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+                } else if (OP == OP_ALLGATHER) {
+                    v[u] = local_buf[j];
+                } else {
+                    v[u] = mc_ld_reduce_bf16(mc_buf + j);
+                }
+            }
 #pragma unroll
-            for (int u = 0; u < U; ++u) mc_st(mine + 4 * (i + u * stride), v[u]);
+            for (int u = 0; u < U; ++u) {
+                if (OP == OP_REDUCESCATTER_BF16) out_local[i + u * stride] = v[u];
+                else mc_st_raw(mc_buf + base + i + u * stride, v[u]);
+            }
         }
-        for (; i < per; i += stride) mc_st(mine + 4 * i, mc_ld_reduce(mine + 4 * i));
+        for (; i < per; i += stride) {
+            uint4 v;
+            if (OP == OP_ALLREDUCE_F32) {
+                const float4 f = mc_ld_reduce(reinterpret_cast<const float*>(mc_buf + base + i));
+                v = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+            } else if (OP == OP_ALLGATHER) {
+                v = local_buf[base + i];
+            } else {
+                v = mc_ld_reduce_bf16(mc_buf + base + i);
+            }
+            if (OP == OP_REDUCESCATTER_BF16) out_local[i] = v;
+            else mc_st_raw(mc_buf + base + i, v);
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -97,28 +148,53 @@ nvls_allreduce_kernel(float* __restrict__ mc_buf, size_t n_vec4, unsigned int* _
 
 }  // namespace
 
-int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* flags_local, unsigned int* flags_mc, int rank,
-                           int world, unsigned int epoch, int ctas) {
+template <int OP>
+static int exchange_launch(ab_ctx* ctx, void* mc_buf, const void* local_buf, void* out_local, size_t bytes, unsigned int* flags_local,
+                           unsigned int* flags_mc, int rank, int world, unsigned int epoch, int ctas) {
+    static bool attr_set[64] = {};
     if (!ctx->comm_stream) {
         int lo = 0, hi = 0;
         AB_CUDA_CHECK(ctx, cudaDeviceGetStreamPriorityRange(&lo, &hi));
         AB_CUDA_CHECK(ctx, cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, hi));
         AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming));
         AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+    }
+    if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
         // ask for the same L1 / shared-memory split the GEMMs run with: an SM only changes its split when it is
         // idle, so a CTA of this kernel that arrived first would otherwise keep the GEMM's CTA off that SM
-        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(nvls_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(nvls_exchange_kernel<OP>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                                 cudaSharedmemCarveoutMaxShared));
+        attr_set[ctx->device] = true;
     }
-    // the exchange starts once everything queued on the context's stream so far (the dW GEMM) has finished
+    // the exchange starts once everything queued on the context's stream so far (the producing GEMM) has finished
     AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
     AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
-    nvls_allreduce_kernel<<<ctas, kArThreads, 0, ctx->comm_stream>>>(mc_buf, n / 4, flags_local, flags_mc, rank, world,
-                                                                      epoch * (unsigned int)world, ctx->dev_status);
+    nvls_exchange_kernel<OP><<<ctas, kArThreads, 0, ctx->comm_stream>>>(
+        static_cast<uint4*>(mc_buf), static_cast<const uint4*>(local_buf), static_cast<uint4*>(out_local), bytes / 16, flags_local,
+        flags_mc, rank, world, epoch * (unsigned int)world, ctx->dev_status);
     AB_LAUNCH_CHECK(ctx);
     AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
     ctx->comm_pending = true;
     return AB_OK;
+}
+
+int abk_switch_exchange_start(ab_ctx* ctx, int op, void* mc_buf, const void* local_buf, void* out_local, size_t bytes,
+                              unsigned int* flags_local, unsigned int* flags_mc, int rank, int world, unsigned int epoch, int ctas) {
+    switch (op) {
+        case OP_ALLREDUCE_F32:
+            return exchange_launch<OP_ALLREDUCE_F32>(ctx, mc_buf, local_buf, out_local, bytes, flags_local, flags_mc, rank, world, epoch, ctas);
+        case OP_ALLGATHER:
+            return exchange_launch<OP_ALLGATHER>(ctx, mc_buf, local_buf, out_local, bytes, flags_local, flags_mc, rank, world, epoch, ctas);
+        case OP_REDUCESCATTER_BF16:
+            return exchange_launch<OP_REDUCESCATTER_BF16>(ctx, mc_buf, local_buf, out_local, bytes, flags_local, flags_mc, rank, world, epoch, ctas);
+    }
+    return AB_ERR_UNSUPPORTED;
+}
+
+int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* flags_local, unsigned int* flags_mc, int rank,
+                           int world, unsigned int epoch, int ctas) {
+    return abk_switch_exchange_start(ctx, OP_ALLREDUCE_F32, mc_buf, nullptr, nullptr, n * sizeof(float), flags_local, flags_mc, rank, world,
+                                     epoch, ctas);
 }
 
 int abk_dp_allreduce_wait(ab_ctx* ctx) {

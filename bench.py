@@ -537,7 +537,7 @@ def run_rowshard(args):
     import torch.distributed as dist
 
     import alice_train
-    from alice_train import bitlinear as bl, parallel
+    from alice_train import _ffi, bitlinear as bl, parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -574,6 +574,26 @@ def run_rowshard(args):
             dx_mine=torch.empty((tokens // world, inn), dtype=torch.bfloat16, device=dev) if world > 1 else None,
             dW=torch.zeros((rows, inn), dtype=torch.float32, device=dev)))
         del dy
+    # the two big exchanges: the library's in-switch kernels on symmetric-memory buffers (forward shards are written
+    # straight into the gathered layout, dx partials into the buffer the switch reduces), NCCL otherwise
+    exchange = "none"
+    if world > 1:
+        exchange = "nccl"
+        if args.dw_exchange == "switch":
+            try:
+                bufs = []
+                for L in layers:
+                    L["ybuf"] = parallel.SwitchBuffer(ctx, world * tokens * L["rows"] * 2, dev)
+                    L["dxbuf"] = parallel.SwitchBuffer(ctx, tokens * L["inn"] * 2, dev)
+                    bufs += [L["ybuf"], L["dxbuf"]]
+                    L["y_all"] = L["ybuf"].view(torch.bfloat16, (world, tokens, L["rows"]))
+                    L["y"] = L["y_all"][rank]
+                    L["dx"] = L["dxbuf"].view(torch.bfloat16, (tokens, L["inn"]))
+                parallel.SwitchBuffer.ready(bufs, dev)
+                exchange = "switch"
+            except RuntimeError as e:
+                if rank == 0:
+                    print(f"[bench] in-switch exchange unavailable ({e}); using NCCL", file=sys.stderr)
     ctx.sync()
     classes = ("fq", "act_quant", "fwd", "dx", "dw")
     ev = {c: [] for c in classes}
@@ -604,14 +624,20 @@ def run_rowshard(args):
 
             timed("act_quant", lambda: bl.act_quant_int8(ctx, L["x"], L["qa"]))
             timed("fwd", lambda: bl.bitlinear_fwd(L["w"], L["qa"], y=L["y"]))
-            if world > 1:
+            if exchange == "switch":
+                L["ybuf"].start(_ffi.AB_XCHG_ALLGATHER, ctas=args.exchange_ctas)
+            elif world > 1:
                 handles.append(dist.all_gather_into_tensor(L["y_all"], L["y"], async_op=True))
             timed("dx", lambda: bl.bitlinear_dx(L["w"], L["dy"], dx=L["dx"]))
-            if world > 1:
+            if exchange == "switch":
+                L["dxbuf"].start(_ffi.AB_XCHG_REDUCESCATTER_BF16, out_local=L["dx_mine"], ctas=args.exchange_ctas)
+            elif world > 1:
                 handles.append(dist.reduce_scatter_tensor(L["dx_mine"], L["dx"], op=dist.ReduceOp.SUM, async_op=True))
             timed("dw", lambda: bl.ste_dw(ctx, L["dy"], L["x"], L["dW"], beta=0.0))
         for hnd in handles:
             hnd.wait()
+        if exchange == "switch":
+            _ffi.check(_ffi.load().ab_dp_allreduce_wait(ctx.handle), ctx.handle)
 
     def fence():
         if world > 1:
@@ -661,6 +687,7 @@ def run_rowshard(args):
                        "parallelism": f"rows/{world}" if world > 1 else "single",
                        "step": "quantise the local rows of all linears (one all-reduce of the 7 sums of |w|); then per linear: act-quant, fwd -> all-gather y (bf16), "
                                "dx partial -> reduce-scatter over tokens (bf16), dW rows (local)",
+                       "exchange": exchange,
                        "exchange_bytes_per_step": {"all_gather_y_total": gather_bytes, "reduce_scatter_dx_input_per_gpu": rs_bytes},
                        "l2": "latent shards, dW and activations exceed the 126 MB L2 at every N; no explicit flush"},
             "roofline": {"bound": "tensor", "kernel": f"gemm_pair_kernel<{dom.upper()}>", "achieved": per[dom]["tops"], "peak": peak_bf16,

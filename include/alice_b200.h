@@ -299,6 +299,21 @@ AB_API int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, ui
                                  uint32_t* flags_multicast, int rank, int world, uint32_t epoch, int ctas);
 AB_API int ab_dp_allreduce_wait(ab_ctx* ctx);
 
+/* The same mechanism for the two exchanges of a layer whose weights are split by output rows over the GPUs (no
+ * counterpart in the reference, which runs on one device; these are the exchanges the row partition of
+ * y = x W^T (src/blas.rs:161-198) and dx = dy W (src/llama_backward.rs:107-138) needs):
+ *   AB_XCHG_ALLGATHER          every GPU holds its contribution in slice `rank` of its own copy of the buffer
+ *                              (`local_buf`, `bytes` / world per slice) and stores it to the same place of all copies;
+ *   AB_XCHG_REDUCESCATTER_BF16 the buffer holds bf16 partial sums; GPU `rank` receives the sum over all GPUs
+ *                              (f32 accumulation in the switch) of slice `rank` in `out_local` (bytes / world);
+ *   AB_XCHG_ALLREDUCE_F32      what ab_dp_allreduce_start does.
+ * `bytes` is a multiple of 16*world; flags, epoch, ctas, ordering and time limits as for ab_dp_allreduce_start;
+ * ab_dp_allreduce_wait joins these exchanges as well.  Each buffer needs its own 16 bytes of flags. */
+typedef enum ab_exchange_op { AB_XCHG_ALLREDUCE_F32 = 0, AB_XCHG_ALLGATHER = 1, AB_XCHG_REDUCESCATTER_BF16 = 2 } ab_exchange_op;
+AB_API int ab_switch_exchange_start(ab_ctx* ctx, int op, void* multicast_buf, const void* local_buf, void* out_local,
+                                    size_t bytes, uint32_t* flags_local, uint32_t* flags_multicast, int rank, int world,
+                                    uint32_t epoch, int ctas);
+
 /* Measurement aid (no counterpart in the reference): launches, on the context's stream, a kernel
  * that only issues the tensor-core instruction of the production kernels (256x256 tile on a CTA
  * pair, operands resident in shared memory, no loads, no epilogue) — `iters` x 4 MMAs per SM

@@ -1,5 +1,5 @@
-"""The library's in-switch all-reduce of dW (ab_dp_allreduce_start / _wait) on two GPUs, one process per GPU,
-against NCCL's all-reduce of the same buffers.  Needs two GPUs of one NVSwitch domain; skipped otherwise."""
+"""The library's in-switch exchanges (all-reduce of dW, all-gather and bf16 reduce-scatter of the row-sharded layer;
+ab_switch_exchange_start / ab_dp_allreduce_wait) on two GPUs, one process per GPU, against NCCL on the same buffers.  Needs two GPUs of one NVSwitch domain; skipped otherwise."""
 import os
 import socket
 
@@ -69,7 +69,35 @@ def _worker(rank, world, port, q):
             red.wait()
         ctx.sync()
         err_gemm = float((red.dW[1] - local).abs().max() / local.abs().max())
-        q.put((rank, "ok", worst, exact, err_gemm))
+        # the two exchanges of the row-sharded layer on the same mechanism
+        from alice_train import _ffi
+        tokens, rows, inn2 = 64, 96, 256
+        gbuf = parallel.SwitchBuffer(ctx, world * tokens * rows * 2, dev)
+        rbuf = parallel.SwitchBuffer(ctx, tokens * inn2 * 2, dev)
+        parallel.SwitchBuffer.ready([gbuf, rbuf], dev)
+        y_all = gbuf.view(torch.bfloat16, (world, tokens, rows))
+        part = rbuf.view(torch.bfloat16, (tokens, inn2))
+        mine = torch.empty((tokens // world, inn2), dtype=torch.bfloat16, device=dev)
+        ok_gather, rs_err, rs_diff = True, 0.0, 0
+        for it in range(3):
+            gen.manual_seed(7000 + 10 * it + rank)
+            y_all[rank].copy_(torch.randn((tokens, rows), generator=gen, device=dev).to(torch.bfloat16))
+            part.copy_(torch.randn((tokens, inn2), generator=gen, device=dev).to(torch.bfloat16))
+            want_y = [torch.empty_like(y_all[rank]) for _ in range(world)]
+            dist.all_gather(want_y, y_all[rank].contiguous())
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part.clone())
+            total = sum(p_.float() for p_ in parts).to(torch.bfloat16)   # f32 accumulation, one rounding
+            gbuf.start(_ffi.AB_XCHG_ALLGATHER)
+            rbuf.start(_ffi.AB_XCHG_REDUCESCATTER_BF16, out_local=mine)
+            red.wait()
+            ctx.sync()
+            ok_gather = ok_gather and all(torch.equal(y_all[r], want_y[r]) for r in range(world))
+            t0 = rank * (tokens // world)
+            want_rs = total[t0:t0 + tokens // world].float()
+            rs_err = max(rs_err, float((mine.float() - want_rs).abs().max() / want_rs.abs().max()))
+            rs_diff += int((mine.float() != want_rs).sum())
+        q.put((rank, "ok", worst, exact, err_gemm, ok_gather, rs_err, rs_diff))
     finally:
         dist.destroy_process_group()
 
@@ -90,6 +118,9 @@ def test_switch_allreduce_matches_nccl_world2():
         p.join(timeout=60)
     if any(r[1] == "skip" for r in res):
         pytest.skip(res[0][2])
-    for rank, _, worst, exact, err_gemm in res:
+    for rank, _, worst, exact, err_gemm, ok_gather, rs_err, rs_diff in res:
         assert exact and worst == 0.0, (rank, worst)       # a + b in f32 does not depend on who adds
         assert err_gemm <= 1e-6, (rank, err_gemm)
+        assert ok_gather, rank
+        print(f"rank {rank}: bf16 reduce-scatter rel err {rs_err:.2e}, {rs_diff} elements differ from f32-accumulate-then-round")
+        assert rs_err <= 1e-2, (rank, rs_err, rs_diff)      # the stated bf16 tolerance; the switch rounds its own way
