@@ -53,10 +53,6 @@ __device__ __forceinline__ float4 mc_ld_reduce(const float* mc) {
                  : "memory");
     return v;
 }
-__device__ __forceinline__ void mc_st(float* mc, float4 v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                 : "memory");
-}
 
 __device__ __forceinline__ uint4 mc_ld_reduce_bf16(const void* mc) {   // 8 bf16 per address, added in f32 inside the switch
     uint4 v;

@@ -37,7 +37,6 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t ext(uint32_t w, int q) { return (q == 0 ? w : (w >> (2 * q))) & 0x03030303u; }
 
 struct RowPtrs {
     const uint8_t *pa, *pb;

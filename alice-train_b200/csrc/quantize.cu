@@ -350,47 +350,48 @@ repack_fwd_kernel(const uint32_t* __restrict__ codes, uint32_t* __restrict__ cod
     codes_fwd[wi] = f;
 }
 
-// codes_t[i][jg] gathers column i of the 16 rows j = 16*jg + e, re-encoded as w+1.  A block transposes a tile of
-// 128 rows x 128 columns through shared memory: 32-byte row segments in (coalesced), 32-byte
-// segments of the transposed rows out (coalesced), the 2-bit shuffle in between.
-constexpr int kTT = 128;
+// codes_t[i][jg] gathers column i of the 16 rows j = 16*jg + e, re-encoded as w+1.  One thread transposes one
+// 16 x 16 block of 2-bit fields held in 16 registers with the word-level butterfly (4 stages of masked swaps, 0.75
+// instruction per element); the in-group permutation of the result (row e at bit 8(e%4)+2(e/4)) costs nothing: row e is
+// simply loaded into register 4(e%4)+e/4.  A warp covers 8 row groups x 4 column words, so every store instruction
+// writes four full 32-byte sectors of codes_t; the loads hit the L2, which the pack kernel has just filled.
 __global__ void __launch_bounds__(kThreads)
 transpose_codes_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
                        uint32_t* __restrict__ codes_t, size_t twords_per_row) {
-    __shared__ uint4 s_in[kTT][2];        // [row j][32 bytes = 128 columns]
-    __shared__ uint32_t s_out[kTT][9];    // [column i][8 words = 128 rows], padded against bank conflicts
-    const size_t i0 = (size_t)blockIdx.x * kTT, j0 = (size_t)blockIdx.y * kTT;
-    const int t = threadIdx.x;
-    {
-        const size_t row = j0 + (t >> 1);
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < out) v = __ldg(reinterpret_cast<const uint4*>(codes + row * pitch + i0 / 4) + (t & 1));
-        s_in[t >> 1][t & 1] = v;
+    const size_t wpr = pitch / 4;
+    const size_t jg_blocks = (twords_per_row + 7) / 8, iw_count = (in + 15) / 16;
+    const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const size_t jg = (warp % jg_blocks) * 8 + (lane & 7), iw = (warp / jg_blocks) * 4 + (lane >> 3);
+    if (jg >= twords_per_row || iw >= iw_count) return;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(codes) + iw;
+    uint32_t w[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const size_t row = jg * 16 + e;
+        uint32_t x = row < out ? __ldg(src + row * wpr) : 0u;
+        const uint32_t both = x & (x >> 1) & 0x55555555u;   // the unused code 11 reads as 0
+        w[4 * (e & 3) + (e >> 2)] = x ^ (both * 3u);
     }
-    __syncthreads();
-    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&s_in[0][0]);
-    const int il = t & (kTT - 1), sh = 2 * (il & 3);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int jgl = (t >> 7) + 2 * k;  // word of 16 rows inside the tile
-        uint32_t word = 0;
+    for (int st = 0; st < 4; ++st) {
+        const int jj = 8 >> st;
+        const uint32_t m = st == 0 ? 0x0000FFFFu : (st == 1 ? 0x00FF00FFu : (st == 2 ? 0x0F0F0F0Fu : 0x33333333u));
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            uint32_t c = ((uint32_t)sb[(jgl * 16 + e) * 32 + (il >> 2)] >> sh) & 3u;
-            if (c == 3u) c = 0u;
-            word |= c << ab_perm_bit(e);
+        for (int k = 0; k < 16; ++k) {
+            if (k & jj) continue;
+            const uint32_t t = ((w[k] >> (2 * jj)) ^ w[k + jj]) & m;
+            w[k] ^= t << (2 * jj);
+            w[k + jj] ^= t;
         }
-        // canonical (01 = +1, 10 = -1) -> offset binary w+1 (10, 00; zero = 01), all 16 fields at once
-        const uint32_t plus = word & 0x55555555u, minus = (word >> 1) & 0x55555555u;
-        s_out[il][jgl] = (plus << 1) | (~(plus | minus) & 0x55555555u);
     }
-    __syncthreads();
-    {
-        const size_t i = i0 + (t >> 1);
-        const int h = (t & 1) * 4;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+        const size_t i = iw * 16 + c;
         if (i < in) {
-            uint4 v = make_uint4(s_out[t >> 1][h], s_out[t >> 1][h + 1], s_out[t >> 1][h + 2], s_out[t >> 1][h + 3]);
-            *reinterpret_cast<uint4*>(codes_t + i * twords_per_row + j0 / 16 + h) = v;
+            // canonical (01 = +1, 10 = -1) -> offset binary w+1 (10, 00; zero = 01), all 16 fields at once
+            const uint32_t plus = w[c] & 0x55555555u, minus = (w[c] >> 1) & 0x55555555u;
+            codes_t[i * twords_per_row + jg] = (plus << 1) | (~(plus | minus) & 0x55555555u);
         }
     }
 }
@@ -576,6 +577,14 @@ inline unsigned int grid_for(size_t items, int per_block) {
 
 float ab_key_to_float(unsigned int k) { return key_float(k); }
 
+// one warp per 8 row groups x 4 column words of the transpose
+static unsigned int transpose_grid(const ab_weights* w) {
+    const size_t twpr = w->tpitch / 4;
+    const size_t warps = ((twpr + 7) / 8) * (((w->in + 15) / 16 + 3) / 4);
+    const size_t blocks = (warps * 32 + kThreads - 1) / kThreads;
+    return (unsigned int)(blocks ? blocks : 1);
+}
+
 static int reduce_launch(ab_ctx* ctx, const float* w, size_t n, ab_fq_dev_report* rep, float* gamma_out,
                          int guard, int keep_when_empty) {
     // a few resident blocks per SM keep enough 128-bit loads in flight to saturate HBM
@@ -672,9 +681,8 @@ static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float*
         AB_LAUNCH_CHECK(ctx);
         if (w->codes_t) {
             const size_t twpr = w->tpitch / 4;
-            dim3 tg(grid_for(w->in, kTT), grid_for(w->out, kTT));
-            transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
-                                                                    reinterpret_cast<uint32_t*>(w->codes_t), twpr);
+            transpose_codes_kernel<<<transpose_grid(w), kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
+                                                                                   reinterpret_cast<uint32_t*>(w->codes_t), twpr);
             AB_LAUNCH_CHECK(ctx);
         }
     }
@@ -690,9 +698,8 @@ int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w) {
         reinterpret_cast<const uint32_t*>(w->codes), reinterpret_cast<uint32_t*>(w->codes_fwd), words);
     AB_LAUNCH_CHECK(ctx);
     const size_t twpr = w->tpitch / 4;
-    dim3 tg(grid_for(w->in, kTT), grid_for(w->out, kTT));
-    transpose_codes_kernel<<<tg, kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
-                                                            reinterpret_cast<uint32_t*>(w->codes_t), twpr);
+    transpose_codes_kernel<<<transpose_grid(w), kThreads, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in,
+                                                                           reinterpret_cast<uint32_t*>(w->codes_t), twpr);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }
