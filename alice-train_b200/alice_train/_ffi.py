@@ -55,6 +55,7 @@ SIGNATURES = {
     "ab_weights_set_gamma": (_i, [_vp, _f]),
     "ab_weights_get_gamma": (_i, [_vp, C.POINTER(_f)]),
     "ab_fq_absmean_pack": (_i, [_vp, _vp, _vp, _vp, _i, _i]),
+    "ab_fq_merge_quantize_alpha": (_i, [_vp, _vp, _vp, _vp, _sz, _f, _f, C.POINTER(_f), C.POINTER(C.c_double)]),
     "ab_fq_shard_abs_sum": (_i, [_vp, _vp, _vp, _vp]),
     "ab_fq_shard_pack": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i, _i]),
     "ab_weights_fq_report": (_i, [_vp, C.POINTER(FqReport)]),

@@ -79,6 +79,23 @@ class BitLinearWeights(TernaryWeightKernel):
         return self
 
 
+def merge_quantize_alpha(ctx: GpuContext, base: torch.Tensor, delta: torch.Tensor | None, w_out: torch.Tensor,
+                         temperature: float = 1.0, alpha: float = 1.0):
+    """LayerDeltaCache::fused_merge_and_quantize_alpha for one projection (src/bin/train_qat_70b.rs:2109-2172):
+    w_out = blend of (base + delta) and its ternary fake-quantisation.  Returns (scale, [sum|w-q|, sum w*q, sum w*w,
+    sum q*q])."""
+    for t in (base, w_out) + ((delta,) if delta is not None else ()):
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError("tensors must be contiguous float32 CUDA tensors")
+        if t.numel() != base.numel():
+            raise AssertionError("assertion `left == right` failed: base.len() == delta.len() == out.len()")
+    scale = C.c_float(0.0)
+    stats = (C.c_double * 4)()
+    _ffi.check(_ffi.load().ab_fq_merge_quantize_alpha(ctx.handle, _dp(base), _dp(delta), _dp(w_out), base.numel(),
+                                                      float(temperature), float(alpha), C.byref(scale), stats), ctx.handle)
+    return float(scale.value), [float(v) for v in stats]
+
+
 @dataclasses.dataclass
 class QuantizedActivations:
     xq: torch.Tensor       # int8 [m, k]

@@ -427,6 +427,26 @@ int ab_dp_allreduce_wait(ab_ctx* ctx) {
     return abk_dp_allreduce_wait(ctx);
 }
 
+int ab_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n, float temperature,
+                               float alpha, float* scale_out, double* stats4_out) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(scale_out, AB_ERR_NULL);
+    if (n == 0) {
+        *scale_out = 0.0f;
+        if (stats4_out) stats4_out[0] = stats4_out[1] = stats4_out[2] = stats4_out[3] = 0.0;
+        return AB_OK;
+    }
+    AB_REQUIRE(base && w_out, AB_ERR_NULL);
+    float* scale_dev = nullptr;
+    double* stats_dev = nullptr;
+    AB_TRY(abk_fq_merge_quantize_alpha(ctx, base, delta, w_out, n, temperature, alpha, &scale_dev, &stats_dev));
+    AB_CUDA_CHECK(ctx, cudaMemcpyAsync(scale_out, scale_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    if (stats4_out)
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(stats4_out, stats_dev, 4 * sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    return AB_OK;
+}
+
 int ab_weights_fq_report(ab_weights* w, ab_fq_report* r) {
     AB_REQUIRE(w && r, AB_ERR_NULL);
     ab_ctx* ctx = w->ctx;

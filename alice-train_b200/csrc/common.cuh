@@ -114,6 +114,8 @@ int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float
 int abk_fq_shard_abs_sum(ab_ctx* ctx, const float* w_latent, ab_weights* w, double* sum_abs_dev);
 int abk_fq_shard_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, const double* total_dev, size_t n_total,
                       float* fq_out, int guard, int want_stats);
+int abk_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n, float temperature,
+                                float alpha, float** scale_dev, double** stats_dev);
 int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w);
 int abk_codes_from_ternary(ab_ctx* ctx, ab_weights* w, const int8_t* vals_dev);
 int abk_codes_from_bitplanes(ab_ctx* ctx, ab_weights* w, const uint32_t* plus_dev,

@@ -787,6 +787,70 @@ int abk_ste_backward(ab_ctx* ctx, const float* g, float* out, size_t n, float cl
     return AB_OK;
 }
 
+// fused_merge_and_quantize_alpha for one projection (src/bin/train_qat_70b.rs:2109-2172):
+//   w = base + delta;  scale = max(f32(sum_f64|w| / n), 1e-10);  q = clamp(round(w * (1/scale) * (1/T)), -1, 1) * scale;
+//   w_out = w * (1 - alpha) + q * alpha (two products, one sum, as written there);  f64 sums of |w-w_out|, w*w_out,
+//   w*w, w_out*w_out.  Three streaming passes: merge (writes w into w_out), the absmean reduction, the blend in place.
+__global__ void __launch_bounds__(kThreads)
+merge_kernel(const float* __restrict__ base, const float* __restrict__ delta, float* __restrict__ w_out, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        w_out[i] = delta ? __fadd_rn(base[i], delta[i]) : base[i];
+}
+
+__global__ void __launch_bounds__(kThreads)
+blend_alpha_kernel(float* __restrict__ w_io, size_t n, const ab_fq_dev_report* __restrict__ rep, float inv_temp, float alpha,
+                   double* __restrict__ stats4) {
+    __shared__ double sd[32];
+    const float scale = rep->gamma, inv_scale = __fdiv_rn(1.0f, scale), one_minus_alpha = __fsub_rn(1.0f, alpha);
+    double se = 0, wq = 0, ww = 0, qq = 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float wv = w_io[i];
+        const float scaled = __fmul_rn(__fmul_rn(wv, inv_scale), inv_temp);
+        float r = roundf(scaled);                       // half away from zero, as f32::round
+        r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);  // NaN stays NaN, as clamp() leaves it
+        const float qh = __fmul_rn(r, scale);
+        const float qv = __fadd_rn(__fmul_rn(wv, one_minus_alpha), __fmul_rn(qh, alpha));
+        w_io[i] = qv;
+        const double a = (double)wv, b = (double)qv;
+        se += fabs(a - b);
+        wq += a * b;
+        ww += a * a;
+        qq += b * b;
+    }
+    double v;
+    v = block_sum(se, sd); if (threadIdx.x == 0) atomicAdd(stats4 + 0, v);
+    v = block_sum(wq, sd); if (threadIdx.x == 0) atomicAdd(stats4 + 1, v);
+    v = block_sum(ww, sd); if (threadIdx.x == 0) atomicAdd(stats4 + 2, v);
+    v = block_sum(qq, sd); if (threadIdx.x == 0) atomicAdd(stats4 + 3, v);
+}
+
+// scratch layout: [partials of the reduction][ab_fq_dev_report][4 doubles]; results stay on the device
+int abk_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n, float temperature,
+                                float alpha, float** scale_dev, double** stats_dev) {
+    const size_t part_bytes = ab_round_up(sizeof(double) * (size_t)ctx->sm_count * 8, 256);
+    void* scratch = nullptr;
+    int st = ab_ctx_scratch(ctx, part_bytes + 512, &scratch);
+    if (st) return st;
+    ab_fq_dev_report* rep = reinterpret_cast<ab_fq_dev_report*>(static_cast<char*>(scratch) + part_bytes);
+    double* stats4 = reinterpret_cast<double*>(static_cast<char*>(scratch) + part_bytes + 256);
+    AB_CUDA_CHECK(ctx, cudaMemsetAsync(rep, 0, 512, ctx->stream));
+    unsigned int blocks = (unsigned int)(ctx->sm_count * 8);
+    unsigned int need = grid_for(n, kThreads);
+    if (need < blocks) blocks = need;
+    merge_kernel<<<blocks, kThreads, 0, ctx->stream>>>(base, delta, w_out, n);
+    AB_LAUNCH_CHECK(ctx);
+    st = reduce_launch(ctx, w_out, n, rep, &rep->w_max /* scratch float for the gamma copy */, AB_GUARD_FLOOR, 0);
+    if (st) return st;
+    const float temp = temperature > 1e-10f ? temperature : 1e-10f;
+    blend_alpha_kernel<<<blocks, kThreads, 0, ctx->stream>>>(w_out, n, rep, 1.0f / temp, alpha, stats4);
+    AB_LAUNCH_CHECK(ctx);
+    *scale_dev = &rep->gamma;
+    *stats_dev = stats4;
+    return AB_OK;
+}
+
 int abk_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n, double* out7_dev) {
     init_stats_kernel<<<1, 1, 0, ctx->stream>>>(out7_dev);
     AB_LAUNCH_CHECK(ctx);

@@ -154,6 +154,15 @@ AB_API int ab_fq_shard_abs_sum(ab_ctx* ctx, const float* w_latent_shard, ab_weig
 AB_API int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_shard,
                             const double* sum_abs_total_dev, size_t n_total, float* fq_out, int guard,
                             int want_stats);
+/* The 70B trainer's quantiser in its general form, LayerDeltaCache::fused_merge_and_quantize_alpha for one projection
+ * (src/bin/train_qat_70b.rs:2109-2172): w = base + delta (`delta` may be NULL); scale = max(f32(sum_f64|w|/n), 1e-10);
+ * q = clamp(round(w * (1/scale) * (1/max(T,1e-10))), -1, 1) * scale; w_out = w*(1-alpha) + q*alpha.  While alpha < 1
+ * the reference multiplies by this blended f32 tensor, so no codes are produced here; at alpha = 1, T = 1 this is
+ * ab_fq_absmean_pack(guard = AB_GUARD_FLOOR) with fq_out, which also fills the handle.  Device pointers for the
+ * tensors (`w_out` may alias `base`); `scale_out` (what the trainer passes to FakeQuantize::set_scale, :2130) and
+ * `stats4_out` (f64 sums of |w - w_out|, w*w_out, w*w, w_out*w_out; may be NULL) are host memory.  Blocks. */
+AB_API int ab_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n,
+                                      float temperature, float alpha, float* scale_out, double* stats4_out);
 /* Waits for the stream and copies the report of the last ab_fq_absmean_pack on `w`. */
 AB_API int ab_weights_fq_report(ab_weights* w, ab_fq_report* report);
 

@@ -201,3 +201,29 @@ def test_qat_trainer_steps(ctx, at, golden):
     assert trainer.stats().weight_mean_abs >= 0.0
     trainer.reset_stats()
     assert trainer.stats().sample_count == 0 and trainer.stats().weight_min == np.finfo(np.float32).max
+
+
+@pytest.mark.parametrize("n,temperature,alpha,with_delta", [(4096 * 33, 1.0, 1.0, True), (100003, 0.7, 0.35, True),
+                                                            (5000, 2.0, 0.0, False), (257, 1.0, 0.9, False), (1, 1.0, 0.5, True)])
+def test_merge_quantize_alpha_vs_oracle(ctx, orc, n, temperature, alpha, with_delta):
+    """The 70B trainer's quantiser in its general form (base + delta, temperature, alpha blend;
+    src/bin/train_qat_70b.rs:2109-2172): blended tensor and scale bit-exact, f64 statistics to 1e-10."""
+    import torch
+    from alice_train.bitlinear import merge_quantize_alpha
+    base = normal_f32(31, (n,), 0.02)
+    delta = normal_f32(32, (n,), 0.002) if with_delta else None
+    g_ref, out_ref, stats_ref = orc.merge_quantize_alpha(base, delta, temperature, alpha, threads=orc.max_threads())
+    bt = torch.from_numpy(base).cuda()
+    dt = torch.from_numpy(delta).cuda() if with_delta else None
+    out = torch.empty_like(bt)
+    g, stats = merge_quantize_alpha(ctx, bt, dt, out, temperature, alpha)
+    assert g == g_ref
+    assert np.array_equal(out.cpu().numpy(), out_ref)
+    for a, b in zip(stats, stats_ref):
+        assert abs(a - b) <= 1e-10 * max(abs(b), 1e-30) + 1e-300, (stats, stats_ref)   # f64 sums in another order
+    # in place (w_out aliases base), and the all-zero tensor: scale floors at 1e-10
+    g2, _ = merge_quantize_alpha(ctx, bt, dt, bt, temperature, alpha)
+    assert g2 == g_ref and torch.equal(bt, out)
+    z = torch.zeros(64, device="cuda")
+    gz, _ = merge_quantize_alpha(ctx, z, None, z, 1.0, 1.0)
+    assert gz == np.float32(1e-10) and not z.any()
