@@ -19,7 +19,7 @@
 // AB_OPT_EXACT_MATVEC on the context and get the FFMA kernels of matvec.cu.  A non-finite input makes every
 // output NaN, as it does there.
 //
-// Work layout: one block of up to 14 warps per SM; a warp owns 16 matrix rows and walks K in spans (128 contiguous
+// Work layout: one block of up to 16 warps per SM; a warp owns 16 matrix rows and walks K in spans (128 contiguous
 // bytes of codes per row, 32 per thread, two 128-bit loads into registers, three spans in flight).  Every
 // block first converts its K slice of v into digits in shared memory (in MMA fragment order).  K is cut into slices
 // (grid.y) only where the rows alone do not give every SM enough warps; slices then write f64 partial sums that a
@@ -28,9 +28,9 @@
 
 namespace {
 
-constexpr int kMaxWarps = 14;        // per block (146 registers per thread); the launch picks 4..14 so that the row tiles divide evenly
+constexpr int kMaxWarps = 16;        // per block (128 registers per thread); the launch picks 4..16
 constexpr int kSpan = 512;           // codes per row per warp step
-constexpr int kMaxSpans = 23;        // per slice: 11776 elements = 46 KB of digits
+constexpr int kMaxSpans = 16;        // per slice: 8192 elements = 32 KB of digits, one span per warp in the conversion
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -273,6 +273,8 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
     size_t per_block = (tiles + gx - 1) / gx;
     size_t passes = (per_block + kMaxWarps - 1) / kMaxWarps;
     size_t nw = (per_block + passes - 1) / passes;
+    const size_t spans = k_slice / kSpan;
+    if (nw < spans) nw = spans;   // the conversion in front of the loop then takes a single round (one span per warp)
     if (nw < 4) nw = 4;
     dim3 grid((unsigned)gx, (unsigned)slices);
     matvec_mma_kernel<<<grid, (unsigned)nw * 32, 4 * k_slice, ctx->stream>>>(codes, pitch, rows, v, k, k_slice, partial, pstride, y, scale,
