@@ -153,7 +153,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens_per_gpu": tokens_full, "projections": [p[0] for p in projs],
+        "config": {"workload": args.workload, "tokens_per_gpu": tokens_full, "projections": {n: [o, i] for n, o, i in projs},
+                   "parallelism": "host cores (rank 0 only)",
+                   "step": "per projection: forward, dx, dW of the reference's CPU code path on fake-quantised f32 weights",
                    "note": "CPU restatement of the reference's f32 path; each step is a bounded sample of the workload"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
                          "sample": f"{sample} of {tokens_full} tokens per step through all projections "
