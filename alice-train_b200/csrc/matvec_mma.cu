@@ -3,64 +3,56 @@
 //
 // At 0.25 byte per weight HBM delivers about 26 T weights/s, several times what the SMs can add one weight at a
 // time (a shift, a mask and an FFMA each).  So the additions go to the tensor cores, exactly:
-//   * v is cut into spans of 512 elements; each span is converted to 32-bit fixed point with its own power-of-two
-//     scale, v_k = n_k * 2^-s with |n_k| < 2^30, and n_k is split into four balanced base-256 digits (signed bytes);
+//   * the part of v a block works on (its K slice, at most 8192 elements) is converted to 32-bit fixed point with
+//     one power-of-two scale, v_k = n_k * 2^-s with |n_k| < 2^30, and n_k is split into four balanced base-256
+//     digits (signed bytes);
 //   * the codes are stored offset-binary (w+1 in {0,1,2}) in the permuted layout the GEMM operand copies use, so
 //     `word & (0x03030303 << 2q)` IS four unsigned bytes, 4^q (w+1), of the A operand of an int8
-//     `mma.sync.m16n8k32`: one integer instruction per four weights, no shift, no table, no shared memory; the
-//     factor 4^q is taken out of the accumulator (exactly) once per span;
-//   * the four digit planes of v are four columns of the B operand (the other four columns are unused); after each
-//     span the s32 accumulators are recombined as sum_p acc_p * 256^p, scaled by 2^-s and added in f64 (every term
-//     is exact in f64); the offset sum_k n_k 2^-s is subtracted and the result is rounded to f32 once.
-// Every product and every sum inside a span is an integer operation, so the only approximation is the rounding of
-// v_k to a multiple of its span's 2^-s (at most 2^-31 of the span's largest magnitude per element), which is below
-// what one f32 addition of the reference's sequential sum (src/backward.rs:45-80) loses.  Elements smaller than
-// 2^-31 of their span's largest magnitude vanish; callers that need f32 semantics for such vectors set
-// AB_OPT_EXACT_MATVEC on the context and get the FFMA kernels of matvec.cu.  A non-finite input makes every
-// output NaN, as it does there.
+//     `mma.sync.m16n8k32`: one integer instruction per four weights, no shift, no table, no shared memory; field q
+//     has its own accumulator set, from which the factor 4^q is taken out (exactly) at the end;
+//   * the four digit planes of v are four columns of the B operand (the other four columns are unused); at the
+//     end the s32 accumulators are recombined as sum_p acc_p * 256^p in 64-bit integers, the offset sum_k n_k is
+//     subtracted, and the result is scaled by 2^-s and rounded to f32 once.
+// Every product and every sum is an integer operation, so the only approximation is the rounding of v_k to a
+// multiple of 2^-s (at most 2^-31 of the slice's largest magnitude per element), which is below what one f32
+// addition of the reference's sequential sum (src/backward.rs:45-80) loses.  Elements smaller than 2^-31 of the
+// largest magnitude vanish, and a slice whose largest magnitude is subnormal counts as zero; callers that need
+// f32 semantics for such vectors set AB_OPT_EXACT_MATVEC on the context and get the FFMA kernels of matvec.cu.
+// A non-finite input makes every output NaN, as it does there.
 //
-// Work layout: one block of up to 16 warps per SM; a warp owns 16 matrix rows and walks K in spans (128 contiguous
-// bytes of codes per row, 32 per thread, two 128-bit loads into registers, three spans in flight).  Every
-// block first converts its K slice of v into digits in shared memory (in MMA fragment order).  K is cut into slices
-// (grid.y) only where the rows alone do not give every SM enough warps; slices then write f64 partial sums that a
-// small kernel adds in slice order, otherwise the main kernel writes y itself.
+// Work layout: one block of up to 16 warps per SM; a warp owns 16 matrix rows and walks K in spans of 512 codes
+// (128 contiguous bytes per row, 32 per thread, two 128-bit loads into registers, three spans in flight); per
+// span it issues 64 LOP3 and 16 MMAs.  Every block first converts its K slice of v into digits in shared memory
+// (in MMA fragment order, one span per warp, one barrier for the slice's largest magnitude).  K is cut into
+// slices (grid.y) of at most 16 spans, and further where the rows alone do not give every SM enough warps;
+// with more than one slice the blocks write f64 partial sums that a small kernel adds in slice order, otherwise
+// the main kernel writes y itself.
 #include "common.cuh"
 
 namespace {
 
 constexpr int kMaxWarps = 16;        // per block (128 registers per thread); the launch picks 4..16
 constexpr int kSpan = 512;           // codes per row per warp step
+constexpr int kBufs = 3;             // spans of codes in flight per warp (16 registers each)
 constexpr int kMaxSpans = 16;        // per slice: 8192 elements = 32 KB of digits, one span per warp in the conversion
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-struct RowPtrs {
-    const uint8_t *pa, *pb;
-    size_t ra, rb;
-    bool va, vb;
-    __device__ __forceinline__ void set(const uint8_t* codes, size_t pitch, size_t rows, size_t tile, int g, int t, size_t k0) {
-        ra = tile * 16 + g;
-        rb = ra + 8;
-        va = ra < rows;
-        vb = rb < rows;
-        pa = codes + (va ? ra : 0) * pitch + k0 / 4 + t * 32;
-        pb = codes + (vb ? rb : 0) * pitch + k0 / 4 + t * 32;
-    }
-};
 struct SpanBuf { uint4 a[2], b[2]; };   // 32 bytes of codes of row g and of row g+8 for one span
-// a span may reach past the row pitch: those 32-byte chunks are skipped (their digits are zero)
-__device__ __forceinline__ void load_span(SpanBuf& d, const RowPtrs& rp, int sp, int spans, int t, size_t chunk_limit) {
-    const size_t off = (size_t)sp * (kSpan / 4);
-    const bool in = sp < spans && off + (size_t)t * 32 + 32 <= chunk_limit;
-    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-    d.a[0] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pa + off)) : z;
-    d.a[1] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pa + off) + 1) : z;
-    d.b[0] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pb + off)) : z;
-    d.b[1] = in ? __ldg(reinterpret_cast<const uint4*>(rp.pb + off) + 1) : z;
+// Whole 128-byte spans are read even where the last one reaches up to 96 bytes past the row pitch (into the next row, or
+// into the slack the handle allocates behind its last row): those codes meet digits that are zero.
+__device__ __forceinline__ void load_span(SpanBuf& d, const uint8_t* pa, const uint8_t* pb, int sp, int spans) {
+    if (sp < spans) {   // warp-uniform
+        const uint32_t off = (uint32_t)sp * (kSpan / 4);
+        d.a[0] = __ldg(reinterpret_cast<const uint4*>(pa + off));
+        d.a[1] = __ldg(reinterpret_cast<const uint4*>(pa + off) + 1);
+        d.b[0] = __ldg(reinterpret_cast<const uint4*>(pb + off));
+        d.b[1] = __ldg(reinterpret_cast<const uint4*>(pb + off) + 1);
+    }
 }
 
 // codes: offset-binary, element e of each 16-group at bit 8(e%4)+2(e/4); `pitch` bytes per row (a multiple of 32).
@@ -70,34 +62,35 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
                   size_t k_slice, double* __restrict__ partial, size_t partial_stride, float* __restrict__ y, float scale,
                   int accumulate, int use_scale) {
     extern __shared__ __align__(16) int8_t s_digits[];   // 4 * k_slice bytes, order given below
-    __shared__ double s_scale[kMaxSpans];                // 2^-s of each span
-    __shared__ double s_off[kMaxSpans];                  // sum_k n_k * 2^-s of each span
-    __shared__ int s_bad;
-    __shared__ double s_offset;
+    __shared__ long long s_sum[kMaxWarps];               // per-warp sums of n_k
+    __shared__ unsigned int s_max;                       // largest |v_k| of the slice, as an ordered integer
+    __shared__ long long s_offset;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int nwarps = (int)(blockDim.x >> 5);
     const size_t k0 = (size_t)blockIdx.y * k_slice;
     const size_t k_pad = (k + kSpan - 1) / kSpan * kSpan;
     const size_t klen = k0 + k_slice <= k_pad ? k_slice : k_pad - k0;   // a multiple of kSpan
-    const int spans = (int)(klen / kSpan);
-    if (threadIdx.x == 0) s_bad = 0;
+    const int spans = (int)(klen / kSpan);                               // <= nwarps (the launch sees to it)
+    if (threadIdx.x == 0) s_max = 0u;
     // the codes of this warp's first row tile do not depend on v: request them before the conversion below
     const size_t tiles = (rows + 15) / 16;
-    const size_t chunk_limit = pitch - k0 / 4;   // bytes of this slice inside a row
-    const int nwarps = (int)(blockDim.x >> 5);
-    size_t tile = (size_t)wid * gridDim.x + blockIdx.x;
-    RowPtrs rp;
-    SpanBuf buf[3];                              // three spans in flight
-    bool first = true;
-    rp.set(codes, pitch, rows, tile < tiles ? tile : 0, g, t, k0);
+    size_t tile = (size_t)wid * gridDim.x + blockIdx.x;   // row tiles are dealt warp-major: a short list still reaches every SM
+    SpanBuf buf[kBufs];
+    const uint8_t *pa, *pb;
+    {
+        const size_t t0 = tile < tiles ? tile : 0, ra = t0 * 16 + g, rb = ra + 8;
+        pa = codes + (ra < rows ? ra : 0) * pitch + k0 / 4 + t * 32;
+        pb = codes + (rb < rows ? rb : 0) * pitch + k0 / 4 + t * 32;
 #pragma unroll
-    for (int d = 0; d < 3; ++d) load_span(buf[d], rp, tile < tiles ? d : spans, spans, t, chunk_limit);
+        for (int d = 0; d < kBufs; ++d) load_span(buf[d], pa, pb, tile < tiles ? d : spans, spans);
+    }
     __syncthreads();
-    // ---- v[k0 .. k0+klen) -> digits.  A warp converts one span at a time; lane l takes the 16 elements that are word
-    // (l % 8) of MMA thread (l / 8)'s 128 codes.  Shared-memory order = fragment order: 16-byte chunk
-    // ((span * 8 + word) * 4 + plane) * 4 + t, so the 16 distinct chunks one LDS.128 of a warp touches are contiguous.
-    for (int sp = wid; sp < spans; sp += nwarps) {
-        const size_t base = k0 + (size_t)sp * kSpan + (size_t)lane * 16;
-        float f[16];
+    // ---- v[k0 .. k0+klen) -> digits: warp w takes span w; lane l holds the 16 elements that are word (l % 8) of MMA thread
+    // (l / 8)'s 128 codes.  First the slice's largest magnitude (one barrier), then the conversion from the registers.
+    float f[16];
+    unsigned int m = 0u;
+    if (wid < spans) {
+        const size_t base = k0 + (size_t)wid * kSpan + (size_t)lane * 16;
         if (base + 16 <= k && (reinterpret_cast<uintptr_t>(v + base) & 15) == 0) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -108,20 +101,25 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
 #pragma unroll
             for (int e = 0; e < 16; ++e) f[e] = base + e < k ? v[base + e] : 0.0f;
         }
-        unsigned int m = 0u;
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
             const unsigned int b = __float_as_uint(f[e]) & 0x7fffffffu;   // |v| as an ordered integer
             m = b > m ? b : m;
         }
         m = __reduce_max_sync(0xffffffffu, m);
-        const bool bad = m >= 0x7f800000u;
-        // 2^shift puts the span's largest magnitude into [2^29, 2^30).  Scaling by a power of two = adding to the exponent
-        // field (exact); elements whose scaled exponent would leave the normal range are below 2^-96 and round to 0, and a
-        // span whose largest magnitude is subnormal (< 1.2e-38) counts as zero.
-        const int shift = (m >= 0x00800000u && !bad) ? 30 - ((int)(m >> 23) - 126) : 0;
-        const bool live = m >= 0x00800000u && !bad;
-        long long sum = 0;
+        if (lane == 0 && m) atomicMax(&s_max, m);
+    }
+    __syncthreads();
+    m = s_max;
+    const bool bad = m >= 0x7f800000u;               // Inf or NaN somewhere in the slice
+    const bool live = m >= 0x00800000u && !bad;      // a subnormal maximum counts as zero
+    // 2^shift puts the largest magnitude into [2^29, 2^30).  Scaling by a power of two = adding to the exponent field
+    // (exact); elements whose scaled exponent would leave the normal range are below 2^-96 and round to 0.
+    const int shift = live ? 30 - ((int)(m >> 23) - 126) : 0;
+    long long sum = 0;
+    if (wid < spans) {
+        // Shared-memory order = fragment order: 16-byte chunk ((span * 8 + word) * 4 + plane) * 4 + t, so the 16 distinct
+        // chunks one LDS.128 of a warp touches are contiguous.
         uint32_t dg[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -146,47 +144,44 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
             dg[3][q] = __byte_perm(t2, t3, 0x7632);
         }
         const int tt = lane >> 3, word = lane & 7;
-        uint4* dst = reinterpret_cast<uint4*>(s_digits) + ((size_t)(sp * 8 + word) * 4) * 4 + tt;
+        uint4* dst = reinterpret_cast<uint4*>(s_digits) + ((size_t)(wid * 8 + word) * 4) * 4 + tt;
 #pragma unroll
         for (int p = 0; p < 4; ++p) dst[p * 4] = make_uint4(dg[p][0], dg[p][1], dg[p][2], dg[p][3]);
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, o);
-        if (lane == 0) {
-            const double sc = scalbn(1.0, -shift);
-            s_scale[sp] = sc;
-            s_off[sp] = (double)sum * sc;      // |sum| < 2^39: exact
-            if (bad) s_bad = 1;
-        }
     }
+    if (lane == 0) s_sum[wid] = sum;
     __syncthreads();
     if (threadIdx.x == 0) {
-        double o = 0.0;
-        for (int sp = 0; sp < spans; ++sp) o += s_off[sp];
-        s_offset = o;
+        long long o = 0;
+        for (int w = 0; w < nwarps; ++w) o += s_sum[w];
+        s_offset = o;     // weights are stored as w+1: sum_k (w_k+1) n_k - sum_k n_k
     }
     __syncthreads();
     const uint4* bsrc = reinterpret_cast<const uint4*>(s_digits) + (g & 3) * 4 + t;   // columns 4..7 repeat 0..3, unused
-    // row tiles are dealt warp-major, so a short list still reaches every block (= every SM)
+    bool first = true;
     for (; tile < tiles; tile += (size_t)gridDim.x * nwarps) {
+        const size_t ra = tile * 16 + g, rb = ra + 8;
+        const bool va = ra < rows, vb = rb < rows;
         if (!first) {
-            rp.set(codes, pitch, rows, tile, g, t, k0);
+            pa = codes + (va ? ra : 0) * pitch + k0 / 4 + t * 32;
+            pb = codes + (vb ? rb : 0) * pitch + k0 / 4 + t * 32;
 #pragma unroll
-            for (int d = 0; d < 3; ++d) load_span(buf[d], rp, d, spans, t, chunk_limit);
+            for (int d = 0; d < kBufs; ++d) load_span(buf[d], pa, pb, d, spans);
         }
         first = false;
-        double acc_a = 0.0, acc_b = 0.0;
-        for (int sp0 = 0; sp0 < spans; sp0 += 3) {
+        // Field q of every byte is used where it lies: `word & (0x03030303 << 2q)` is 4^q * (w+1) as an unsigned byte
+        // (one LOP3, no shift); all MMAs of field q go to accumulator set q, which therefore holds 4^q times its sum
+        // (|c_q| < 2^26 over a slice).  Each MMA takes field q of two neighbouring words as its two k-halves, with digit
+        // register q of those words' chunks as B.
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0}, c3[4] = {0, 0, 0, 0};
+        for (int sp0 = 0; sp0 < spans; sp0 += kBufs) {
 #pragma unroll
-            for (int d = 0; d < 3; ++d) {     // buffer d holds span sp0 + d: compile-time buffer index, no register moves
+            for (int d = 0; d < kBufs; ++d) {     // buffer d holds span sp0 + d: compile-time buffer index, no register moves
                 const int sp = sp0 + d;
                 if (sp < spans) {
                     const SpanBuf cur = buf[d];
-                    load_span(buf[d], rp, sp + 3, spans, t, chunk_limit);
+                    load_span(buf[d], pa, pb, sp + kBufs, spans);
                     const uint4* bs = bsrc + (size_t)sp * 128;
-                    // Field q of every byte is used where it lies: `word & (0x03030303 << 2q)` is 4^q * (w+1) as an unsigned
-                    // byte (one LOP3, no shift), and all MMAs of field q go to accumulator set q, which therefore holds
-                    // 4^q times its sum and is shifted back (exactly) at the end of the span.  Each MMA takes field q of two
-                    // neighbouring words as its two k-halves, with digit register q of those words' chunks as B.
-                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0}, c3[4] = {0, 0, 0, 0};
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t wa[4] = {cur.a[h].x, cur.a[h].y, cur.a[h].z, cur.a[h].w};
@@ -201,30 +196,30 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
                             mma_u8s8(c3, wa[wi] & 0xC0C0C0C0u, wb[wi] & 0xC0C0C0C0u, wa[wi + 1] & 0xC0C0C0C0u, wb[wi + 1] & 0xC0C0C0C0u, d0.w, d1.w);
                         }
                     }
-                    // c[0], c[1]: row g, columns (= digit planes) 2t, 2t+1; c[2], c[3]: row g+8.  |sum| <= 2^17 per span.
-                    const int e0 = (c0[0] + (c1[0] >> 2)) + ((c2[0] >> 4) + (c3[0] >> 6)), e1 = (c0[1] + (c1[1] >> 2)) + ((c2[1] >> 4) + (c3[1] >> 6));
-                    const int e2 = (c0[2] + (c1[2] >> 2)) + ((c2[2] >> 4) + (c3[2] >> 6)), e3 = (c0[3] + (c1[3] >> 2)) + ((c2[3] >> 4) + (c3[3] >> 6));
-                    const double sc = s_scale[sp];
-                    acc_a = fma((double)(e0 + e1 * 256), sc, acc_a);
-                    acc_b = fma((double)(e2 + e3 * 256), sc, acc_b);
                 }
             }
         }
-        // planes 0,1 sit in t = 0, planes 2,3 (weight 2^16) in t = 1; t = 2,3 hold the unused columns
-        acc_a = t == 0 ? acc_a : (t == 1 ? acc_a * 65536.0 : 0.0);
-        acc_b = t == 0 ? acc_b : (t == 1 ? acc_b * 65536.0 : 0.0);
-        acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
-        acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+        // c[0], c[1]: row g, columns (= digit planes) 2t, 2t+1; c[2], c[3]: row g+8.  Take the 4^q out, then the planes:
+        // 0,1 sit in t = 0, planes 2,3 (weight 2^16) in t = 1; t = 2,3 hold the unused columns.
+        const long long e0 = (long long)(c0[0] + (c1[0] >> 2)) + ((c2[0] >> 4) + (c3[0] >> 6));
+        const long long e1 = (long long)(c0[1] + (c1[1] >> 2)) + ((c2[1] >> 4) + (c3[1] >> 6));
+        const long long e2 = (long long)(c0[2] + (c1[2] >> 2)) + ((c2[2] >> 4) + (c3[2] >> 6));
+        const long long e3 = (long long)(c0[3] + (c1[3] >> 2)) + ((c2[3] >> 4) + (c3[3] >> 6));
+        long long sa = t < 2 ? (e0 + (e1 << 8)) << (16 * t) : 0ll;
+        long long sb = t < 2 ? (e2 + (e3 << 8)) << (16 * t) : 0ll;
+        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+        sb += __shfl_xor_sync(0xffffffffu, sb, 1);
         if (t == 0) {
             const double nan = __longlong_as_double(0x7ff8000000000000ll);
-            const double ra_v = s_bad ? nan : acc_a - s_offset, rb_v = s_bad ? nan : acc_b - s_offset;
+            const double ra_v = bad ? nan : scalbn((double)(sa - s_offset), -shift);
+            const double rb_v = bad ? nan : scalbn((double)(sb - s_offset), -shift);
             if (partial) {
                 double* dst = partial + (size_t)blockIdx.y * partial_stride;
-                if (rp.va) dst[rp.ra] = ra_v;
-                if (rp.vb) dst[rp.rb] = rb_v;
+                if (va) dst[ra] = ra_v;
+                if (vb) dst[rb] = rb_v;
             } else {
-                if (rp.va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, scale); y[rp.ra] = accumulate ? __fadd_rn(y[rp.ra], r) : r; }
-                if (rp.vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, scale); y[rp.rb] = accumulate ? __fadd_rn(y[rp.rb], r) : r; }
+                if (va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, scale); y[ra] = accumulate ? __fadd_rn(y[ra], r) : r; }
+                if (vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, scale); y[rb] = accumulate ? __fadd_rn(y[rb], r) : r; }
             }
         }
     }
