@@ -21,7 +21,7 @@
 // A non-finite input makes every output NaN, as it does there.
 //
 // Work layout: one block of up to 16 warps per SM; a warp owns 16 matrix rows and walks K in spans of 512 codes
-// (128 contiguous bytes per row, 32 per thread, two 128-bit loads into registers, three spans in flight); per
+// (128 contiguous bytes per row, 32 per thread in one 256-bit load, three spans in flight); per
 // span it issues 64 LOP3 and 16 MMAs.  Every block first converts its K slice of v into digits in shared memory
 // (in MMA fragment order, one span per warp, one barrier for the slice's largest magnitude).  K is cut into
 // slices (grid.y) of at most 16 spans, and further where the rows alone do not give every SM enough warps;
@@ -42,16 +42,20 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// one 256-bit read-only load (32-byte aligned): a thread's 32 bytes of one row in a single request
+__device__ __forceinline__ void ldg256(uint4 (&d)[2], const uint8_t* p) {
+    asm("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+        : "=r"(d[0].x), "=r"(d[0].y), "=r"(d[0].z), "=r"(d[0].w), "=r"(d[1].x), "=r"(d[1].y), "=r"(d[1].z), "=r"(d[1].w)
+        : "l"(p));
+}
 struct SpanBuf { uint4 a[2], b[2]; };   // 32 bytes of codes of row g and of row g+8 for one span
 // Whole 128-byte spans are read even where the last one reaches up to 96 bytes past the row pitch (into the next row, or
 // into the slack the handle allocates behind its last row): those codes meet digits that are zero.
 __device__ __forceinline__ void load_span(SpanBuf& d, const uint8_t* pa, const uint8_t* pb, int sp, int spans) {
     if (sp < spans) {   // warp-uniform
         const uint32_t off = (uint32_t)sp * (kSpan / 4);
-        d.a[0] = __ldg(reinterpret_cast<const uint4*>(pa + off));
-        d.a[1] = __ldg(reinterpret_cast<const uint4*>(pa + off) + 1);
-        d.b[0] = __ldg(reinterpret_cast<const uint4*>(pb + off));
-        d.b[1] = __ldg(reinterpret_cast<const uint4*>(pb + off) + 1);
+        ldg256(d.a, pa + off);
+        ldg256(d.b, pb + off);
     }
 }
 
