@@ -91,3 +91,27 @@ def test_integration_doc_binds_every_entry_point():
     doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
     missing = [n for n in _declared_symbols() if f"fn {n}(" not in doc]
     assert not missing, missing
+
+
+def test_python_constants_match_header():
+    """Enumerators the Python binding repeats (status codes, options, exchange ops, guards) carry the header's values."""
+    from alice_train import _ffi
+    text = open(os.path.join(ROOT, "include", "alice_b200.h")).read()
+    values = {}
+    for body in re.findall(r"typedef enum \w+ \{(.*?)\}", text, flags=re.S):
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        nxt = 0
+        for item in body.split(","):
+            item = item.strip()
+            if not item:
+                continue
+            name, _, val = item.partition("=")
+            nxt = int(val.strip(), 0) if val.strip() else nxt
+            values[name.strip()] = nxt
+            nxt += 1
+    checked = 0
+    for name, val in values.items():
+        if hasattr(_ffi, name):
+            assert getattr(_ffi, name) == val, name
+            checked += 1
+    assert checked >= 12
