@@ -106,13 +106,17 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------- reference (CPU) arm
-def cpu_step(orc, layers, tokens, seed=0):
+def cpu_step(orc, layers, tokens, seed=0, row_frac=1.0):
     """One pass of the reference's CPU code path over `tokens` tokens: for each projection the
     dense f32 products it runs on fake-quantised weights — tiled_matmul_bt (src/blas.rs:161-198)
     for the forward and matmul_bt_backward (src/llama_backward.rs:107-138) for dx and dW.
-    Single-threaded, as those functions are in the reference.  Returns seconds."""
+    Single-threaded, as those functions are in the reference.  `row_frac` < 1 runs the first
+    ceil(out * row_frac) output rows of every projection only (the work of all three products is
+    proportional to the rows), i.e. that fraction of a token's work.  Returns seconds."""
     t = 0.0
-    for li, (_, out, inn, wq) in enumerate(layers):
+    for li, (_, out_full, inn, wq_full) in enumerate(layers):
+        out = max(1, int(np.ceil(out_full * row_frac)))
+        wq = wq_full if out == out_full else np.ascontiguousarray(wq_full[:out])
         g = np.random.Generator(np.random.Philox(1000 + seed + li))
         x = g.standard_normal((tokens, inn), dtype=np.float32)
         dy = (g.standard_normal((tokens, out), dtype=np.float32) * np.float32(1e-2)).astype(np.float32)
@@ -144,11 +148,16 @@ def run_reference(args):
     tokens_full, projs = WORKLOADS[args.workload]
     layers = cpu_layers(orc, projs)
     sample = args.cpu_tokens
+    # ~2e-8 s per weight and token on one core: keep warm-up + timed steps near two minutes whatever K is by
+    # running a fraction of every projection's output rows per step (never less than 1/64)
+    est = 2e-8 * sum(o * i for _, o, i in projs) * sample * (args.steps + args.warmup)
+    row_frac = 1.0 if est <= 120.0 else max(1.0 / 64.0, 120.0 / est)
     for i in range(args.warmup):
-        cpu_step(orc, layers, 1, seed=i)
-    times = [cpu_step(orc, layers, sample, seed=100 + i) for i in range(args.steps)]
+        cpu_step(orc, layers, sample, seed=i, row_frac=row_frac)
+    times = [cpu_step(orc, layers, sample, seed=100 + i, row_frac=row_frac) for i in range(args.steps)]
     total = sum(times)
-    value = sample * args.steps / total
+    rows_done = sum(max(1, int(np.ceil(o * row_frac))) * i for _, o, i in projs) / sum(o * i for _, o, i in projs)
+    value = sample * rows_done * args.steps / total
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
@@ -158,8 +167,8 @@ def run_reference(args):
                    "step": "per projection: forward, dx, dW of the reference's CPU code path on fake-quantised f32 weights",
                    "note": "CPU restatement of the reference's f32 path; each step is a bounded sample of the workload"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
-                         "sample": f"{sample} of {tokens_full} tokens per step through all projections "
-                                   f"(fwd tiled_matmul_bt + matmul_bt_backward), single thread as in the reference; "
+                         "sample": f"{sample} of {tokens_full} tokens per step through {100 * rows_done:.1f} % of the output rows of "
+                                   f"all projections (fwd tiled_matmul_bt + matmul_bt_backward), single thread as in the reference; "
                                    f"weights fake-quantised with {orc.max_threads()} threads outside the timed region"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -719,7 +728,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
-        if args.steps * args.cpu_tokens > 24:  # ~3.5 s of CPU per token: keep the whole run within minutes
+        if args.steps * args.cpu_tokens > 24:  # ~3.5 s of CPU per token: one token per step is enough when K is large
             args.cpu_tokens = max(1, 24 // args.steps)
         return run_reference(args)
     if args.workload == "hbm-kernels":
