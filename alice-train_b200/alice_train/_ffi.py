@@ -17,7 +17,7 @@ AB_ERR_DEVICE_TIMEOUT, AB_ERR_UNSUPPORTED, AB_ERR_NO_DEVICE, AB_ERR_STATE = 5, 6
 AB_F32, AB_BF16 = 0, 1
 AB_TERNARY, AB_BINARY2, AB_INT4, AB_INT8 = 0, 1, 2, 3
 AB_GUARD_INV_ZERO, AB_GUARD_FLOOR = 0, 1
-AB_OPT_EXACT_MATVEC, AB_OPT_ASYNC_HOST_STEP = 1, 2
+AB_OPT_EXACT_MATVEC, AB_OPT_ASYNC_HOST_STEP, AB_OPT_HOST_INTEGER_MATVEC = 1, 2, 3
 AB_XCHG_ALLREDUCE_F32, AB_XCHG_ALLGATHER, AB_XCHG_REDUCESCATTER_BF16 = 0, 1, 2
 
 
@@ -88,6 +88,7 @@ SIGNATURES = {
     "ab_ste_dw": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _f]),
     "ab_bitlinear_step_host": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp]),
     "ab_tensor_peak_probe": (_i, [_vp, _i, _i, C.POINTER(C.c_double)]),
+    "ab_selftest_bounded_wait": (_i, [_vp, C.c_uint32]),
 }
 
 _lib = None

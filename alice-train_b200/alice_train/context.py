@@ -49,6 +49,12 @@ class GpuContext:
         least 64 x 512 use the integer tensor-core path (vector rounded to 32-bit fixed point, sums exact)."""
         _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_EXACT_MATVEC, int(bool(on))), self._h)
 
+    def set_host_integer_matvec(self, on: bool):
+        """False (default): the numpy-slice functions (ternary_matvec_backward, bitlinear_backward,
+        ternary_matvec_kernel) add in f32 exactly as the reference's CPU loops do; True: they may take the integer
+        tensor-core path like the device-pointer entry points."""
+        _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_HOST_INTEGER_MATVEC, int(bool(on))), self._h)
+
     def set_async_host_step(self, on: bool):
         """True: ab_bitlinear_step_host only queues its work; sync() before touching the host buffers."""
         _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_ASYNC_HOST_STEP, int(bool(on))), self._h)

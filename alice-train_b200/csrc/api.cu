@@ -146,6 +146,10 @@ int ab_ctx_set_option(ab_ctx* ctx, int option, int value) {
         ctx->exact_matvec = value != 0;
         return AB_OK;
     }
+    if (option == AB_OPT_HOST_INTEGER_MATVEC) {
+        ctx->host_integer_matvec = value != 0;
+        return AB_OK;
+    }
     if (option == AB_OPT_ASYNC_HOST_STEP) {
         ctx->async_host_step = value != 0;
         return AB_OK;
@@ -669,6 +673,17 @@ int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float
     return abk_ternary_matmul_bt(ctx, a, w, scale, c, m);
 }
 
+// The host-slice forms stand in for the reference's CPU functions one to one, so they add in f32 as those do unless
+// the caller has opted into the integer path for them as well.
+struct HostMatvecArithmetic {
+    ab_ctx* ctx;
+    bool saved;
+    explicit HostMatvecArithmetic(ab_ctx* c) : ctx(c), saved(c->exact_matvec) {
+        if (!c->host_integer_matvec) c->exact_matvec = true;
+    }
+    ~HostMatvecArithmetic() { ctx->exact_matvec = saved; }
+};
+
 static int h2d(ab_ctx* ctx, int slot, const void* src, size_t bytes, void** dev) {
     AB_TRY(ab_ctx_stage(ctx, slot, bytes ? bytes : 4, dev));
     if (bytes) AB_CUDA_CHECK(ctx, cudaMemcpyAsync(*dev, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -682,6 +697,7 @@ static int d2h_sync(ab_ctx* ctx, void* dst, const void* dev, size_t bytes) {
 
 int ab_ternary_matvec_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len, float* y, size_t y_len) {
     AB_TRY(bind(ctx));
+    HostMatvecArithmetic arithmetic(ctx);
     AB_TRY(check_w(ctx, w));
     AB_REQUIRE(x_len == w->in && y_len == w->out, AB_ERR_SHAPE);
     if (x_len) AB_REQUIRE(x, AB_ERR_NULL);
@@ -696,6 +712,7 @@ int ab_ternary_matvec_host(ab_ctx* ctx, const ab_weights* w, const float* x, siz
 int ab_ternary_matvec_backward_host(ab_ctx* ctx, const ab_weights* w, const float* dy, size_t dy_len, float* dx,
                                     size_t dx_len) {
     AB_TRY(bind(ctx));
+    HostMatvecArithmetic arithmetic(ctx);
     AB_TRY(check_w(ctx, w));
     AB_REQUIRE(dy_len == w->out, AB_ERR_SHAPE);  // assert_eq!(grad_output.len(), out_features)  src/backward.rs:36
     AB_REQUIRE(dx_len == w->in, AB_ERR_SHAPE);   // assert_eq!(grad_input.len(), in_features)    src/backward.rs:37
@@ -712,6 +729,7 @@ int ab_bitlinear_backward_host(ab_ctx* ctx, const ab_weights* w, const float* x,
                                size_t dy_len, int pre_norm, float norm_eps, float* dx, size_t dx_len, float* d_bias,
                                size_t d_bias_len) {
     AB_TRY(bind(ctx));
+    HostMatvecArithmetic arithmetic(ctx);
     AB_TRY(check_w(ctx, w));
     AB_REQUIRE(x_len == w->in, AB_ERR_SHAPE);    // src/backward.rs:117
     AB_REQUIRE(dy_len == w->out, AB_ERR_SHAPE);  // src/backward.rs:118
@@ -759,6 +777,8 @@ int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed
     if (pk) {
         cudaError_t e = cudaMemcpy2DAsync(w->codes, w->pitch, packed_b, pk, pk, n, cudaMemcpyHostToDevice, ctx->stream);
         if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+        // the bytes are the caller's: code 11 decodes to 0 and bits past column k are not part of the matrix (src/blas.rs:436-447)
+        if (!st) st = abk_codes_sanitize(ctx, w);
     }
     w->has_data = true;
     void *da = nullptr, *dc = nullptr;
@@ -828,6 +848,12 @@ __attribute__((visibility("default"))) int ab_debug_trace(ab_ctx* ctx, long long
     return AB_OK;
 }
 #endif
+
+int ab_selftest_bounded_wait(ab_ctx* ctx, unsigned int limit_ms) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, AB_ERR_UNSUPPORTED);
+    return abk_bounded_wait_probe(ctx, limit_ms);
+}
 
 int ab_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
     AB_TRY(bind(ctx));

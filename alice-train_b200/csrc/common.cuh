@@ -57,6 +57,7 @@ struct ab_ctx {
     int next_set = 0;
     bool async_host_step = false;  // AB_OPT_ASYNC_HOST_STEP
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
+    bool host_integer_matvec = false;  // AB_OPT_HOST_INTEGER_MATVEC: the host-slice forms may take the integer path too
     uint64_t launches = 0;
     std::string last_error;
 };
@@ -121,6 +122,7 @@ int abk_codes_from_ternary(ab_ctx* ctx, ab_weights* w, const int8_t* vals_dev);
 int abk_codes_from_bitplanes(ab_ctx* ctx, ab_weights* w, const uint32_t* plus_dev,
                              const uint32_t* minus_dev);
 int abk_codes_from_flat(ab_ctx* ctx, ab_weights* w, const uint8_t* flat_dev);
+int abk_codes_sanitize(ab_ctx* ctx, ab_weights* w);
 int abk_codes_to_bitplanes(ab_ctx* ctx, const ab_weights* w, uint32_t* plus_dev, uint32_t* minus_dev);
 int abk_codes_to_flat(ab_ctx* ctx, const ab_weights* w, uint8_t* flat_dev);
 int abk_codes_to_ternary(ab_ctx* ctx, const ab_weights* w, int8_t* vals_dev);
@@ -154,6 +156,7 @@ int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* f
 int abk_switch_exchange_start(ab_ctx* ctx, int op, void* mc_buf, const void* local_buf, void* out_local, size_t bytes,
                               unsigned int* flags_local, unsigned int* flags_mc, int rank, int world, unsigned int epoch, int ctas);
 int abk_dp_allreduce_wait(ab_ctx* ctx);
+int abk_bounded_wait_probe(ab_ctx* ctx, unsigned int limit_ms);
 
 // gemm_tc.cu
 int abk_gemm_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,

@@ -37,13 +37,21 @@ __device__ __forceinline__ void mc_signal(unsigned int* mc_flag) {
     asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_flag), "r"(1u) : "memory");
 }
 // true once *flag has reached `target` (wrap-safe), false when the time limit passed first
-__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int target) {
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int target, unsigned long long limit_ns = kSpinNs) {
     const unsigned long long t0 = now_ns();
     for (;;) {
         if ((int)(ld_acquire_sys(flag) - target) >= 0) return true;
-        if (now_ns() - t0 > kSpinNs) return false;
+        if (now_ns() - t0 > limit_ns) return false;
         __nanosleep(200);
     }
+}
+
+// The bounded wait of the exchange kernels on its own: one thread polls an ordinary device word that nothing raises and
+// gives up after `limit_ns`, leaving the same status code a timed-out start barrier leaves.  No multimem instruction,
+// no peer: it exists so that the time-limit path (status word -> AB_ERR_DEVICE_TIMEOUT -> context usable again) can be
+// exercised without a second GPU and without a fault.
+__global__ void bounded_wait_probe_kernel(const unsigned int* flag, unsigned int target, unsigned long long limit_ns, int* status) {
+    if (!wait_flag(flag, target, limit_ns)) atomicExch(status, 0x4152);
 }
 __device__ __forceinline__ float4 mc_ld_reduce(const float* mc) {
     float4 v;
@@ -136,8 +144,12 @@ nvls_exchange_kernel(uint4* __restrict__ mc_buf, const uint4* __restrict__ local
         if (prev == gridDim.x - 1) {  // last CTA of this GPU: everything this GPU wrote is ordered before the signal
             __threadfence_system();
             flags_local[2] = 0u;
-            mc_signal(flags_mc + 1);
-            if (!wait_flag(flags_local + 1, target)) atomicExch(status, 0x4153);
+            // A GPU that gave up at the start barrier moved nothing: it does not signal the end barrier either, so the
+            // end barrier of every other GPU runs out as well and the whole group learns that this exchange failed.
+            if (go) {
+                mc_signal(flags_mc + 1);
+                if (!wait_flag(flags_local + 1, target)) atomicExch(status, 0x4153);
+            }
         }
     }
 }
@@ -147,6 +159,7 @@ nvls_exchange_kernel(uint4* __restrict__ mc_buf, const uint4* __restrict__ local
 template <int OP>
 static int exchange_launch(ab_ctx* ctx, void* mc_buf, const void* local_buf, void* out_local, size_t bytes, unsigned int* flags_local,
                            unsigned int* flags_mc, int rank, int world, unsigned int epoch, int ctas) {
+    static std::mutex attr_mu;
     static bool attr_set[64] = {};
     if (!ctx->comm_stream) {
         int lo = 0, hi = 0;
@@ -155,12 +168,15 @@ static int exchange_launch(ab_ctx* ctx, void* mc_buf, const void* local_buf, voi
         AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming));
         AB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
     }
-    if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
-        // ask for the same L1 / shared-memory split the GEMMs run with: an SM only changes its split when it is
-        // idle, so a CTA of this kernel that arrived first would otherwise keep the GEMM's CTA off that SM
-        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(nvls_exchange_kernel<OP>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                                cudaSharedmemCarveoutMaxShared));
-        attr_set[ctx->device] = true;
+    if (ctx->device >= 0 && ctx->device < 64) {
+        std::lock_guard<std::mutex> lock(attr_mu);
+        if (!attr_set[ctx->device]) {
+            // ask for the same L1 / shared-memory split the GEMMs run with: an SM only changes its split when it is
+            // idle, so a CTA of this kernel that arrived first would otherwise keep the GEMM's CTA off that SM
+            AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(nvls_exchange_kernel<OP>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                    cudaSharedmemCarveoutMaxShared));
+            attr_set[ctx->device] = true;
+        }
     }
     // the exchange starts once everything queued on the context's stream so far (the producing GEMM) has finished
     AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
@@ -191,6 +207,14 @@ int abk_dp_allreduce_start(ab_ctx* ctx, float* mc_buf, size_t n, unsigned int* f
                            int world, unsigned int epoch, int ctas) {
     return abk_switch_exchange_start(ctx, OP_ALLREDUCE_F32, mc_buf, nullptr, nullptr, n * sizeof(float), flags_local, flags_mc, rank, world,
                                      epoch, ctas);
+}
+
+int abk_bounded_wait_probe(ab_ctx* ctx, unsigned int limit_ms) {
+    // the word at byte 128 of the status block is never written by any kernel: the wait below always runs out
+    const unsigned int* flag = reinterpret_cast<const unsigned int*>(reinterpret_cast<const char*>(ctx->dev_status) + 128);
+    bounded_wait_probe_kernel<<<1, 1, 0, ctx->stream>>>(flag, 1u, (unsigned long long)limit_ms * 1000000ull, ctx->dev_status);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
 }
 
 int abk_dp_allreduce_wait(ab_ctx* ctx) {

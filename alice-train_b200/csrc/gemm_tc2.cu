@@ -651,10 +651,17 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     constexpr int STAGES = Cfg<MODE>::STAGES;
     constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (MODE == DW ? 0 : P_BYTES)) + 512;
     static_assert((4 * STAGES + 4 + 2 * SCHED_SLOTS) * 8 + 16 + 4 * SCHED_SLOTS <= 512, "barrier block");
-    static bool attr_set[8] = {false, false, false, false, false, false, false, false};
-    if (!attr_set[ctx->device & 7]) {
-        AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[ctx->device & 7] = true;
+    // per-device launch facts, looked up once; contexts on several host threads share them
+    static std::mutex cache_mu;
+    static bool attr_set[64] = {};
+    static int max_clusters[64] = {};
+    const int dev = ctx->device & 63;
+    {
+        std::lock_guard<std::mutex> lock(cache_mu);
+        if (!attr_set[dev]) {
+            AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[dev] = true;
+        }
     }
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
@@ -678,18 +685,22 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // one resident CTA pair per two SMs; ask the runtime how many pairs the device can co-schedule
-    static int max_clusters[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (max_clusters[ctx->device & 7] == 0) {
-        cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1), 1, 1);
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || n <= 0) {
-            cudaGetLastError();
-            n = ctx->sm_count / 2;
+    int max_pairs;
+    {
+        std::lock_guard<std::mutex> lock(cache_mu);
+        if (max_clusters[dev] == 0) {
+            cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1), 1, 1);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || n <= 0) {
+                cudaGetLastError();
+                n = ctx->sm_count / 2;
+            }
+            max_clusters[dev] = n < ctx->sm_count / 2 ? n : ctx->sm_count / 2;
         }
-        max_clusters[ctx->device & 7] = n < ctx->sm_count / 2 ? n : ctx->sm_count / 2;
+        max_pairs = max_clusters[dev];
     }
     long long tiles = (long long)p.tiles_m * p.tiles_n;
-    int clusters = (int)(tiles < max_clusters[ctx->device & 7] ? tiles : max_clusters[ctx->device & 7]);
+    int clusters = (int)(tiles < max_pairs ? tiles : max_pairs);
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, ta, tb, p));
     ctx->launches++;

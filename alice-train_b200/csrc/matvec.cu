@@ -26,6 +26,12 @@ __device__ __forceinline__ uint32_t code_flags(uint32_t w) {
 __device__ __forceinline__ float coef2(uint32_t u, int e) {  // +-2.0 or 0.0 for element e
     return __uint_as_float((e == 15 ? u : (u << (30 - 2 * e))) & 0xC0000000u);
 }
+// true where the FFMA form (+-2.0 times the halved value) would not equal adding or subtracting the value itself:
+// non-finite values (0 * inf), and non-zero values below 2^-125, whose halves are not exact.
+__device__ __forceinline__ bool special_full(float v) {
+    const uint32_t b = __float_as_uint(v) & 0x7fffffffu;
+    return b >= 0x7f800000u || (b != 0u && b < 0x01000000u);   // non-finite, or 0 < |v| < 2^-125
+}
 
 // ------------------------------------------------------------------------------- forward
 // y[j] = sum_k W[j][k] x[k].  A warp owns a tile of 2048 columns: every lane keeps its 64 values
@@ -40,23 +46,34 @@ constexpr int kFwdTile = 2048;   // columns per warp pass
 __global__ void __launch_bounds__(kFwdWarps * 32)
 matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
                   const float* __restrict__ x, size_t x_stride, float* __restrict__ partial,
-                  size_t partial_stride /* floats per (batch row, column tile) */, size_t tiles) {
+                  size_t partial_stride /* floats per (batch row, column tile) */, size_t tiles,
+                  int zero_times_x /* a zero weight still contributes 0 * x_k (NaN for a non-finite x_k) */) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const size_t tile = blockIdx.y, b = blockIdx.z;
     const float* xv = x + b * x_stride;
     const size_t k0 = tile * kFwdTile + (size_t)lane * 64;
     float xh[64];
+    bool odd = false;   // see `select` below
     if (k0 + 64 <= in && (reinterpret_cast<uintptr_t>(xv + k0) & 15) == 0) {
         const float4* x4 = reinterpret_cast<const float4*>(xv + k0);
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
             float4 t = __ldg(x4 + q);
+            odd |= special_full(t.x) | special_full(t.y) | special_full(t.z) | special_full(t.w);
             xh[4 * q] = 0.5f * t.x; xh[4 * q + 1] = 0.5f * t.y; xh[4 * q + 2] = 0.5f * t.z; xh[4 * q + 3] = 0.5f * t.w;
         }
     } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) xh[e] = k0 + e < in ? 0.5f * xv[k0 + e] : 0.0f;
+        for (int e = 0; e < 64; ++e) {
+            const float t = k0 + e < in ? xv[k0 + e] : 0.0f;
+            odd |= special_full(t);
+            xh[e] = 0.5f * t;
+        }
     }
+    // A non-finite x_k must reach only the rows whose weight at k is non-zero, as a loop that adds or subtracts the
+    // selected elements does (0 * inf would poison every row), and halving is not exact below 2^-125: a tile that
+    // holds such a value adds or subtracts the original x_k under a select instead of multiplying.
+    const bool select = __any_sync(0xffffffffu, odd);
     const bool have = k0 / 4 < pitch;  // inside the (zero padded) row pitch
     const uint8_t* cbase = codes + k0 / 4;
     float* pdst = partial + (b * tiles + tile) * partial_stride;
@@ -74,12 +91,31 @@ matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
         const uint32_t w0[4] = {code_flags(c0.x), code_flags(c0.y), code_flags(c0.z), code_flags(c0.w)};
         const uint32_t w1[4] = {code_flags(c1.x), code_flags(c1.y), code_flags(c1.z), code_flags(c1.w)};
         float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!select) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 4; ++q) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                a0[e & 3] = fmaf(coef2(w0[q], e), xh[16 * q + e], a0[e & 3]);
-                a1[e & 3] = fmaf(coef2(w1[q], e), xh[16 * q + e], a1[e & 3]);
+                for (int e = 0; e < 16; ++e) {
+                    a0[e & 3] = fmaf(coef2(w0[q], e), xh[16 * q + e], a0[e & 3]);
+                    a1[e & 3] = fmaf(coef2(w1[q], e), xh[16 * q + e], a1[e & 3]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float c0f = coef2(w0[q], e), c1f = coef2(w1[q], e);
+                    const size_t kk = k0 + 16 * q + e;
+                    const float xf = kk < in ? __ldg(xv + kk) : 0.0f;
+                    // ternary_matvec_kernel adds or subtracts the selected elements only; ternary_matmul_bt forms
+                    // LUT[code] * a (src/blas.rs:436-447), so there a zero weight meeting Inf or NaN gives NaN
+                    const float zx = 0.0f * xf;
+                    if (c0f != 0.0f) a0[e & 3] = __fadd_rn(a0[e & 3], c0f > 0.0f ? xf : -xf);
+                    else if (zero_times_x) a0[e & 3] = __fadd_rn(a0[e & 3], zx);
+                    if (c1f != 0.0f) a1[e & 3] = __fadd_rn(a1[e & 3], c1f > 0.0f ? xf : -xf);
+                    else if (zero_times_x) a1[e & 3] = __fadd_rn(a1[e & 3], zx);
+                }
             }
         }
         float s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]), s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
@@ -117,6 +153,24 @@ constexpr int kBwdWarps = 8;
 constexpr int kBwdThreads = kBwdWarps * 32;
 constexpr int kBwdMaxSlice = 2048;  // rows of dy staged in shared memory per block
 
+// One row's contribution to a thread's 16 columns.  dy_j is the same for the whole warp, so the rare non-finite value
+// (or one below 2^-125, whose half is not exact) takes a branch of its own in which dy_j itself is added or subtracted
+// and reaches only the columns whose weight is non-zero (the reference scatters +-dy_j per set bit,
+// src/backward.rs:57-79; 0 * inf would poison every column).
+__device__ __forceinline__ void bwd_row(float (&acc)[16], uint32_t f, float d) {
+    if (!special_full(d)) {
+        const float h = 0.5f * d;   // exact: |d| >= 2^-125
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), h, acc[e]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float c = coef2(f, e);
+            if (c != 0.0f) acc[e] = __fadd_rn(acc[e], c > 0.0f ? d : -d);
+        }
+    }
+}
+
 // Block = 8 warps over the same 32 code words (512 columns): lane l owns word l, warp w takes rows
 // r0+w, r0+w+8, ... of the block's row slice (each warp load is 128 contiguous bytes of one row).
 // The eight partial sums per column meet in shared memory, so one slice costs one row of partials.
@@ -124,13 +178,13 @@ __global__ void __launch_bounds__(kBwdThreads)
 matvec_bwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t words_per_row,
                   const float* __restrict__ dy, size_t rows_per_slice, float* __restrict__ partial,
                   size_t partial_stride /* floats per slice */) {
-    __shared__ float s_dy[kBwdMaxSlice];              // halved, see coef2()
+    __shared__ float s_dy[kBwdMaxSlice];
     __shared__ float s_red[kBwdWarps][32 * 16 + 4];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const size_t word = (size_t)blockIdx.x * 32 + lane;
     const size_t r0 = (size_t)blockIdx.y * rows_per_slice;
     const size_t r1 = r0 + rows_per_slice < out ? r0 + rows_per_slice : out;
-    for (size_t r = r0 + threadIdx.x; r < r1; r += kBwdThreads) s_dy[r - r0] = 0.5f * dy[r];
+    for (size_t r = r0 + threadIdx.x; r < r1; r += kBwdThreads) s_dy[r - r0] = dy[r];
     __syncthreads();
     float acc[16];
 #pragma unroll
@@ -145,19 +199,9 @@ matvec_bwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
 #pragma unroll
             for (int u = 0; u < U; ++u) w[u] = __ldg(col + (r + u * kBwdWarps) * wstride);
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t f = code_flags(w[u]);
-                const float d = s_dy[r - r0 + u * kBwdWarps];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
-            }
+            for (int u = 0; u < U; ++u) bwd_row(acc, code_flags(w[u]), s_dy[r - r0 + u * kBwdWarps]);
         }
-        for (; r < r1; r += kBwdWarps) {
-            const uint32_t f = code_flags(__ldg(col + r * wstride));
-            const float d = s_dy[r - r0];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) acc[e] = fmaf(coef2(f, e), d, acc[e]);
-        }
+        for (; r < r1; r += kBwdWarps) bwd_row(acc, code_flags(__ldg(col + r * wstride)), s_dy[r - r0]);
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q)
@@ -252,7 +296,7 @@ ste_outer_kernel(const float* __restrict__ x, size_t in, const float* __restrict
 }  // namespace
 
 static int matvec_fwd_launch(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_stride, float* y,
-                             size_t y_stride, size_t m, float scale, int accumulate, int use_scale) {
+                             size_t y_stride, size_t m, float scale, int accumulate, int use_scale, int zero_times_x) {
     const size_t tiles = (w->in + kFwdTile - 1) / kFwdTile;
     const size_t pstride = ab_round_up(w->out, 32);
     void* partial = nullptr;
@@ -266,7 +310,7 @@ static int matvec_fwd_launch(ab_ctx* ctx, const ab_weights* w, const float* x, s
         if (gx < 1) gx = 1;
         dim3 grid((unsigned)gx, (unsigned)tiles, (unsigned)m);
         matvec_fwd_kernel<<<grid, kFwdWarps * 32, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, x, x_stride,
-                                                                  (float*)partial, pstride, tiles);
+                                                                  (float*)partial, pstride, tiles, zero_times_x);
         AB_LAUNCH_CHECK(ctx);
     }
     dim3 rgrid((unsigned)((w->out + 255) / 256), (unsigned)m);
@@ -288,13 +332,18 @@ static bool use_mma(const ab_ctx* ctx, const ab_weights* w, bool transposed) {
 int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y) {
     if (w->out == 0) return AB_OK;
     if (use_mma(ctx, w, false)) return abk_matvec_mma(ctx, w->codes_fwd, w->pitch, w->out, w->in, x, y, 1.0f, 0, 0);
-    return matvec_fwd_launch(ctx, w, x, 0, y, 0, 1, 1.0f, 0, 0);
+    return matvec_fwd_launch(ctx, w, x, 0, y, 0, 1, 1.0f, 0, 0, 0);
 }
 
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
     if (w->out == 0 || m == 0) return AB_OK;
-    if (m > 65535) return AB_ERR_UNSUPPORTED;
-    return matvec_fwd_launch(ctx, w, a, w->in, c, w->out, m, scale, 1, 1);
+    // the batch index is a grid dimension (at most 65535): longer batches go out in slabs
+    for (size_t m0 = 0; m0 < m; m0 += 65535) {
+        const size_t mm = m - m0 < 65535 ? m - m0 : 65535;
+        int st = matvec_fwd_launch(ctx, w, a + m0 * w->in, w->in, c + m0 * w->out, w->out, mm, scale, 1, 1, 1);
+        if (st) return st;
+    }
+    return AB_OK;
 }
 
 // Row slicing of the transposed matvec: enough blocks for ~6 per SM, slices no longer than the
@@ -389,13 +438,8 @@ int abk_ternary_matvec_backward_static(ab_ctx* ctx, const ab_weights* w, const f
                           std::to_string(kStaticScratchFloats) + " (use ab_ternary_matvec_backward)";
         return AB_ERR_UNSUPPORTED;
     }
-    // fewer, longer row slices until the partial sums fit the fixed array
-    while ((size_t)slices * pstride > kStaticScratchFloats) {
-        slices = (slices + 1) / 2;
-        rps = (w->out + slices - 1) / slices;
-        slices = (int)((w->out + rps - 1) / rps);
-    }
-    if (rps > (size_t)kBwdMaxSlice) {
+    // the plan never exceeds the array except where the 2048-row limit of a slice forces more slices than fit
+    if ((size_t)slices * pstride > kStaticScratchFloats) {
         ctx->last_error = "ab_ternary_matvec_backward_static: out_features " + std::to_string(w->out) + " x in_features " +
                           std::to_string(w->in) + " exceeds what the fixed scratch array can slice (use ab_ternary_matvec_backward)";
         return AB_ERR_UNSUPPORTED;

@@ -451,6 +451,20 @@ __global__ void codes_from_flat_kernel(const uint8_t* __restrict__ flat, size_t 
     codes[wi] = cw;
 }
 
+// Canonical rows as a caller packed them (row stride = pitch): the unused code 11 reads as 0 (src/blas.rs:436,
+// src/export.rs:143-148) and the fields of the last word that lie beyond `in` are cleared, so that every kernel
+// sees the same matrix the reference's decoder does.
+__global__ void sanitize_codes_kernel(uint32_t* __restrict__ codes, size_t out, size_t in, size_t wpr) {
+    size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= out * wpr) return;
+    const size_t col0 = (wi % wpr) * 16;
+    uint32_t x = codes[wi];
+    x ^= (x & (x >> 1) & 0x55555555u) * 3u;
+    if (col0 >= in) x = 0u;
+    else if (in - col0 < 16) x &= (1u << (2 * (in - col0))) - 1u;
+    codes[wi] = x;
+}
+
 __device__ __forceinline__ uint32_t code_at(const uint8_t* codes, size_t pitch, size_t row, size_t k) {
     return ((uint32_t)codes[row * pitch + (k >> 2)] >> (2 * (k & 3))) & 3u;
 }
@@ -729,6 +743,14 @@ int abk_codes_from_flat(ab_ctx* ctx, ab_weights* w, const uint8_t* flat_dev) {
         flat_dev, w->out, w->in, wpr, reinterpret_cast<uint32_t*>(w->codes));
     AB_LAUNCH_CHECK(ctx);
     return abk_rebuild_operand_copies(ctx, w);
+}
+
+int abk_codes_sanitize(ab_ctx* ctx, ab_weights* w) {
+    const size_t wpr = w->pitch / 4, words = w->out * wpr;
+    if (!words) return AB_OK;
+    sanitize_codes_kernel<<<grid_for(words, kThreads), kThreads, 0, ctx->stream>>>(reinterpret_cast<uint32_t*>(w->codes), w->out, w->in, wpr);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
 }
 
 int abk_codes_to_bitplanes(ab_ctx* ctx, const ab_weights* w, uint32_t* plus_dev, uint32_t* minus_dev) {

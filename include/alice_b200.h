@@ -82,17 +82,27 @@ typedef struct ab_fq_report {
  * (src/blas.rs:19-24). */
 AB_API int ab_ctx_create(int device, void* cuda_stream, ab_ctx** ctx);
 AB_API int ab_ctx_destroy(ab_ctx* ctx);
-/* Context options.  AB_OPT_EXACT_MATVEC (default 0): when 1, ab_ternary_matvec, ab_ternary_matvec_backward and
- * ab_bitlinear_backward add the selected elements in f32 as the reference's loops do (src/backward.rs:45-80).
- * By default, matrices of at least 64 x 512 go through an integer path instead: the vector is rounded to 32-bit
- * fixed point with one shared power-of-two scale (error at most 2^-31 of its largest magnitude per element), the
- * sums are then exact integers on the tensor cores and are rounded to f32 once.  That path reaches the HBM
- * roofline; it differs from f32 accumulation only in rounding, except that elements below 2^-31 of the vector's
- * largest magnitude drop out. */
-/* AB_OPT_ASYNC_HOST_STEP (default 0): when 1, ab_bitlinear_step_host returns as soon as its copies and kernels are
- * queued; the host buffers of a call may be read (y, dx) or reused (x, dy) after the next ab_ctx_sync().  Consecutive
- * calls then overlap: the copies in of one run beside the GEMMs and the copies out of the one before. */
-typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2 } ab_option;
+/* Context options (all default 0).
+ * The batch-1 entry points (ab_ternary_matvec, ab_ternary_matvec_backward, ab_bitlinear_backward) have two arithmetic
+ * paths.  f32: the selected elements are added in f32 as the reference's loops do (src/backward.rs:45-80): a zero
+ * weight contributes nothing, so a NaN or Inf in the vector reaches only the outputs it is connected to, and rows with
+ * dy_j == 0 change nothing.  Integer: for matrices of at least 64 x 512 the vector is rounded to 32-bit fixed point
+ * with one power-of-two scale per K slice (error at most 2^-31 of the slice's largest magnitude per element), the sums
+ * are exact integers on the tensor cores and are rounded to f32 once; that path is the one that approaches the HBM
+ * roofline.  It differs from f32 accumulation in rounding only, except that elements below 2^-31 of the largest
+ * magnitude drop out, a slice whose largest magnitude is subnormal counts as zero, and one non-finite element makes
+ * every output of its slice NaN.
+ *   AB_OPT_EXACT_MATVEC        1: every batch-1 entry point uses the f32 path.
+ *                              0: the DEVICE-pointer entry points use the integer path where it applies.
+ *   AB_OPT_HOST_INTEGER_MATVEC 0: the HOST-slice forms (ab_ternary_matvec_host, ab_ternary_matvec_backward_host,
+ *                                 ab_bitlinear_backward_host), which stand in for the reference's CPU functions one
+ *                                 to one and are bound by the PCIe copies anyway, use the f32 path.
+ *                              1: they follow the rule of the device-pointer entry points.
+ *   AB_OPT_ASYNC_HOST_STEP     1: ab_bitlinear_step_host returns as soon as its copies and kernels are queued; the host
+ *                                 buffers of a call may be read (y, dx) or reused (x, dy) after the next ab_ctx_sync().
+ *                                 Consecutive calls then overlap: the copies in of one run beside the GEMMs and the
+ *                                 copies out of the one before. */
+typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2, AB_OPT_HOST_INTEGER_MATVEC = 3 } ab_option;
 AB_API int ab_ctx_set_option(ab_ctx* ctx, int option, int value);
 /* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
 AB_API int ab_ctx_sync(ab_ctx* ctx);
@@ -302,8 +312,13 @@ AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* 
  *                    (16 for 2 GPUs, 12 for up to 4, 8 beyond: sized for a gradient exchange that overlaps GEMMs)
  * _start queues the exchange on a high-priority stream of the context behind the work already queued on the
  * context's stream and returns; _wait makes the context's stream wait for every exchange started so far.  Every
- * GPU of the group must make the same calls in the same order.  Waits on the other GPUs are bounded (4 s): when
- * one runs out the buffer is left as it was and ab_ctx_sync() returns AB_ERR_DEVICE_TIMEOUT. */
+ * GPU of the group must make the same calls in the same order.  Waits on the other GPUs are bounded (4 s, the first
+ * call included, where the skew between the GPUs' launches is largest).  An exchange's result is valid only once
+ * ab_ctx_sync() has returned AB_OK: when a GPU's wait at the start barrier runs out it moves no data and does not
+ * signal the end barrier, so the end barrier of every other GPU runs out as well; _wait still returns AB_OK (it only
+ * orders streams) and every GPU's next ab_ctx_sync() returns AB_ERR_DEVICE_TIMEOUT.  After that the buffer holds a mix
+ * of summed and unsummed slices and the counters are out of step: before the next exchange on that buffer every GPU
+ * must zero the 16 flag bytes again, synchronise with the others, and restart `epoch` at 1. */
 AB_API int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, uint32_t* flags_local,
                                  uint32_t* flags_multicast, int rank, int world, uint32_t epoch, int ctas);
 AB_API int ab_dp_allreduce_wait(ab_ctx* ctx);
@@ -322,6 +337,13 @@ typedef enum ab_exchange_op { AB_XCHG_ALLREDUCE_F32 = 0, AB_XCHG_ALLGATHER = 1, 
 AB_API int ab_switch_exchange_start(ab_ctx* ctx, int op, void* multicast_buf, const void* local_buf, void* out_local,
                                     size_t bytes, uint32_t* flags_local, uint32_t* flags_multicast, int rank, int world,
                                     uint32_t epoch, int ctas);
+
+/* Self-test of the time-limit path (no counterpart in the reference, whose GPU calls .expect() and abort,
+ * src/cuda_matmul.rs:953-964): queues a one-thread kernel that waits, exactly as the exchange kernels wait for their
+ * peers, on a device word that nothing ever raises, and gives up after `limit_ms` (1..1000).  The next ab_ctx_sync()
+ * then returns AB_ERR_DEVICE_TIMEOUT, clears the status and leaves the context usable.  No other GPU, no multimem
+ * instruction and no fault is involved. */
+AB_API int ab_selftest_bounded_wait(ab_ctx* ctx, unsigned int limit_ms);
 
 /* Measurement aid (no counterpart in the reference): launches, on the context's stream, a kernel
  * that only issues the tensor-core instruction of the production kernels (256x256 tile on a CTA

@@ -115,6 +115,7 @@ def test_matvec_path_vs_oracle(at, orc, out, inn, exact):
     the default (matrices of at least 64 x 512 sum in integers on the tensor cores) and f32 adds."""
     from alice_train.context import default_context
     default_context().set_exact_matvec(exact)
+    default_context().set_host_integer_matvec(not exact)   # the numpy-slice functions add in f32 unless told otherwise
     w_lat = normal_f32(1, (out, inn), 0.02)
     _, codes, _ = orc.quantize_and_pack(w_lat)
     x, dy = normal_f32(2, (inn,)), normal_f32(3, (out,))
@@ -140,6 +141,7 @@ def test_matvec_path_vs_oracle(at, orc, out, inn, exact):
         assert np.array_equal(db, refb)
     w.close()
     default_context().set_exact_matvec(False)
+    default_context().set_host_integer_matvec(False)
 
 
 def test_integer_matvec_is_exact_on_integers(at, orc):
@@ -147,6 +149,7 @@ def test_integer_matvec_is_exact_on_integers(at, orc):
     sums bit for bit (they are below 2^24): a check of the fragment layout, the digit split and the offset."""
     from alice_train.context import default_context
     default_context().set_exact_matvec(False)
+    default_context().set_host_integer_matvec(True)
     rng = np.random.Generator(np.random.Philox(77))
     for out, inn in [(96, 1536), (1040, 2000), (4096, 14336)]:
         codes = rng.integers(-1, 2, size=(out, inn)).astype(np.int8)
@@ -159,28 +162,102 @@ def test_integer_matvec_is_exact_on_integers(at, orc):
         assert np.array_equal(y, (codes.astype(np.int64) @ x.astype(np.int64)).astype(np.float32))
         assert np.array_equal(dx, (codes.astype(np.int64).T @ dy.astype(np.int64)).astype(np.float32))
         w.close()
+    default_context().set_host_integer_matvec(False)
 
 
-def test_integer_matvec_edge_vectors(at, orc):
-    """Zero vector, one huge element, non-finite input."""
+def _edge_vectors(n, seed):
+    """Vectors on which f32 accumulation and the fixed-point path part ways (name -> vector of length n)."""
+    base = normal_f32(seed, (n,))
+    v = {}
+    a = base.copy(); a[5] = np.nan; v["one NaN"] = a
+    a = base.copy(); a[7] = np.inf; a[n - 3] = -np.inf; v["+Inf and -Inf"] = a
+    a = base.copy(); a[::2] = 0.0; v["every second element exactly 0"] = a
+    a = (base * np.float32(2.0 ** -40)).astype(np.float32); a[11] = 1.0; v["all but one element 2^-40 of the maximum"] = a
+    a = (base * np.float32(2.0 ** -140)).astype(np.float32); v["subnormal vector"] = a
+    a = np.zeros(n, np.float32); a[3] = np.float32(1e-45); a[n // 2] = -np.float32(3e-45); v["two lone subnormals"] = a
+    a = base.copy(); a[3] = 3.0e38; v["one huge element"] = a
+    v["zero vector"] = np.zeros(n, np.float32)
+    return v
+
+
+def test_edge_vectors_f32_path_equals_oracle(at, orc):
+    """Default arithmetic of the slice API (f32 adds): on vectors with NaN / Inf / exact zeros / tiny and subnormal
+    elements the result has the oracle's NaN and Inf pattern exactly (a zero weight contributes nothing and rows with
+    dy_j == 0 are skipped, src/backward.rs:48,57-59) and its finite values within 1e-5 of the largest finite one.
+    With integer codes and integer-representable sums (the subnormal and lone-element cases) equality is exact."""
     from alice_train.context import default_context
     default_context().set_exact_matvec(False)
-    out, inn = 128, 1024
+    default_context().set_host_integer_matvec(False)
     rng = np.random.Generator(np.random.Philox(78))
+    for out, inn in [(128, 1024), (96, 2500), (2048, 2048)]:
+        codes = rng.integers(-1, 2, size=(out, inn)).astype(np.int8)
+        w = at.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
+        ow = orc.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
+        for direction, n_in, n_out, fn, ofn in (("dx = W^T dy", out, inn, at.ternary_matvec_backward, orc.ternary_matvec_backward),
+                                                ("y = W x", inn, out, at.ternary_matvec_kernel, orc.ternary_matvec)):
+            for name, v in _edge_vectors(n_in, 5).items():
+                got = np.full(n_out, 7.0, np.float32)
+                fn(v, w, got)
+                ref = ofn(v, ow)
+                where = (out, inn, direction, name)
+                assert np.array_equal(np.isnan(got), np.isnan(ref)), where
+                inf = np.isinf(ref)
+                assert np.array_equal(got[inf], ref[inf]), where
+                fin = np.isfinite(ref)
+                if fin.any() and np.abs(ref[fin]).max() > 0:
+                    assert np.abs(got[fin].astype(np.float64) - ref[fin]).max() <= RTOL_F32 * np.abs(ref[fin]).max(), where
+                else:
+                    assert not got[fin].any(), where
+                if name in ("two lone subnormals", "zero vector"):
+                    assert np.array_equal(got, ref), where
+        # pre-norm backward with a NaN in dy: the correction term makes every element NaN in the reference as well
+        x = normal_f32(6, (inn,))
+        for name, dy in _edge_vectors(out, 9).items():
+            got = np.zeros(inn, np.float32)
+            at.bitlinear_backward(x, dy, w, True, 1e-6, got)
+            ref = orc.bitlinear_backward(x, dy, ow, True, 1e-6)
+            assert np.array_equal(np.isnan(got), np.isnan(ref)), (out, inn, "pre-norm", name)
+        w.close()
+
+
+def test_edge_vectors_integer_path_census(at, orc, capsys):
+    """The integer tensor-core path on the same vectors: where it cannot follow f32 semantics the number of differing
+    outputs is COUNTED and printed (like the quantiser's threshold census), and bounded by what its definition allows:
+    a non-finite element makes every output of its K slice NaN; elements below 2^-31 of the slice maximum and
+    subnormal slices drop out (difference at most the dropped mass); everything else stays within 1e-5."""
+    from alice_train.context import default_context
+    ctx = default_context()
+    ctx.set_exact_matvec(False)
+    ctx.set_host_integer_matvec(True)
+    rng = np.random.Generator(np.random.Philox(78))
+    out, inn = 128, 1024
     codes = rng.integers(-1, 2, size=(out, inn)).astype(np.int8)
     w = at.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
-    y = np.ones(out, np.float32)
-    at.ternary_matvec_kernel(np.zeros(inn, np.float32), w, y)
-    assert not y.any()
-    x = normal_f32(5, (inn,))
-    x[3] = 3.0e38
-    at.ternary_matvec_kernel(x, w, y)
-    ref = orc.ternary_matvec(x, orc.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn))
-    assert rel_err(y, ref) <= RTOL_F32
-    x[5] = np.inf
-    at.ternary_matvec_kernel(x, w, y)
-    assert np.isnan(y).all()
+    ow = orc.TernaryWeightKernel.from_ternary(codes.reshape(-1), out, inn)
+    census = {}
+    for name, x in _edge_vectors(inn, 5).items():
+        y = np.ones(out, np.float32)
+        at.ternary_matvec_kernel(x, w, y)
+        ref = orc.ternary_matvec(x, ow)
+        both_nan = np.isnan(y) & np.isnan(ref)
+        differ = ~both_nan & ~(y == ref)
+        fin = np.isfinite(ref) & np.isfinite(y)
+        scale = max(float(np.abs(ref[np.isfinite(ref)]).max()) if np.isfinite(ref).any() else 0.0, 1e-45)
+        beyond = int((np.abs(y[fin].astype(np.float64) - ref[fin]) > RTOL_F32 * scale).sum()) + int((~fin & ~both_nan & ~((y == ref))).sum())
+        census[name] = (int(differ.sum()), beyond)
+        if name in ("one NaN", "+Inf and -Inf"):
+            assert np.isnan(y).all(), name               # the documented behaviour of the integer path
+        elif name in ("subnormal vector", "two lone subnormals"):
+            assert not y.any(), name                     # a subnormal slice counts as zero
+        elif name == "all but one element 2^-40 of the maximum":
+            # only the element of magnitude 1 survives the 2^-31 cut: every output is its code for that column
+            assert np.array_equal(y, codes[:, 11].astype(np.float32)), name
+        else:
+            assert beyond == 0, (name, census[name])
+    with capsys.disabled():
+        print("\ninteger-path census (outputs differing from the f32 oracle, of %d; beyond 1e-5): %s" % (out, census))
     w.close()
+    ctx.set_host_integer_matvec(False)
 
 
 @pytest.mark.parametrize("out,inn", [(2048, 2048), (5, 3), (33, 130)])
@@ -202,3 +279,29 @@ def test_ternary_matmul_bt(at, orc, m, n, k):
     c = c0.copy()
     at.blas.ternary_matmul_bt(a, rows, g, c, m, n, k)
     assert rel_err(c, orc.ternary_matmul_bt(a, rows, g, c0, m, n, k)) <= RTOL_F32
+
+
+@pytest.mark.parametrize("m,n,k", [(2, 33, 37), (1, 64, 256), (3, 8, 5)])
+def test_ternary_matmul_bt_unused_code_and_padding_bits(at, orc, m, n, k):
+    """Bytes as a foreign writer may leave them: the unused code 0b11 sprinkled over the matrix (it decodes to 0,
+    src/blas.rs:436 and src/export.rs:143-148) and the bits of each row's last byte beyond column k set to ones (the
+    reference never reads them, src/blas.rs:440-447).  Same result as the oracle's decoder."""
+    rng = np.random.Generator(np.random.Philox(21))
+    fields = rng.integers(0, 4, size=(n, 4 * ((k + 3) // 4))).astype(np.uint8)     # codes 0..3, 0b11 included
+    fields[:, k:] = 3                                                              # padding bits all ones
+    rows = (fields[:, 0::4] | (fields[:, 1::4] << 2) | (fields[:, 2::4] << 4) | (fields[:, 3::4] << 6)).astype(np.uint8).reshape(-1)
+    assert (fields[:, :k] == 3).any()
+    a = normal_f32(9, (m, k))
+    c0 = normal_f32(10, (m, n))
+    c = c0.copy()
+    at.blas.ternary_matmul_bt(a, rows, 0.37, c, m, n, k)
+    ref = orc.ternary_matmul_bt(a, rows, 0.37, c0, m, n, k)
+    assert rel_err(c, ref) <= RTOL_F32
+    # this function multiplies (LUT[code] * a), so an Inf in `a` turns every output of its row to NaN or Inf
+    a[m - 1, k // 2] = np.inf
+    c = c0.copy()
+    at.blas.ternary_matmul_bt(a, rows, 0.37, c, m, n, k)
+    ref = orc.ternary_matmul_bt(a, rows, 0.37, c0, m, n, k)
+    assert np.array_equal(np.isnan(c), np.isnan(ref)) and np.array_equal(np.isinf(c), np.isinf(ref))
+    ok = np.isfinite(ref)
+    assert rel_err(c[ok], ref[ok]) <= RTOL_F32
