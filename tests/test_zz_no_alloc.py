@@ -71,3 +71,25 @@ def test_static_scratch_rejects_oversize():
     ctx.sync()
     assert not dx.any().item()
     w.close()
+
+
+def test_static_scratch_rejects_too_many_row_slices():
+    """A row slice holds at most 2048 rows; 16384 rows are 8 slices, and 8 x 131200 partial sums are more than the
+    2^20 floats of the fixed array although one slice alone would fit: refused with the second reason."""
+    import torch
+
+    import alice_train
+    from alice_train import _ffi
+    lib = _ffi.load()
+    ctx = alice_train.GpuContext.on_torch_stream(0)
+    out, inn = 16384, 131200
+    packed = np.zeros(out * inn // 4, np.uint8)             # an all-zero matrix: 0.5 GB of codes, no latent tensor needed
+    w = alice_train.TernaryWeightKernel.from_packed(packed, out, inn, 1.0, ctx)
+    dy = torch.ones(out, device="cuda")
+    dx = torch.ones(inn, device="cuda")
+    st = lib.ab_ternary_matvec_backward_static(ctx.handle, w.handle, C.c_void_p(dy.data_ptr()), C.c_void_p(dx.data_ptr()))
+    assert st == _ffi.AB_ERR_UNSUPPORTED
+    assert b"can slice" in lib.ab_ctx_last_error(ctx.handle)
+    ctx.sync()
+    assert dx.min().item() == 1.0                           # refused before anything was launched
+    w.close()
