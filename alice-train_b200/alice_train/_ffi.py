@@ -30,6 +30,15 @@ class FqReport(C.Structure):
 
 _vp, _sz, _i, _f = C.c_void_p, C.c_size_t, C.c_int, C.c_float
 
+
+class LinearStep(C.Structure):
+    """ab_linear_step of the header: one linear of ab_qat_linear_steps."""
+    _fields_ = [("w", C.c_void_p), ("w_latent", C.c_void_p), ("x_bf16", C.c_void_p), ("dy_bf16", C.c_void_p),
+                ("xq", C.c_void_p), ("scales", C.c_void_p), ("rowsums", C.c_void_p), ("y_bf16", C.c_void_p),
+                ("dx_bf16", C.c_void_p), ("dW", C.c_void_p), ("dw_beta", C.c_float), ("dw_multicast", C.c_void_p),
+                ("flags_local", C.c_void_p), ("flags_multicast", C.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/alice_b200.h declares
 SIGNATURES = {
     "ab_ctx_create": (_i, [_i, _vp, C.POINTER(_vp)]),
@@ -87,6 +96,7 @@ SIGNATURES = {
     "ab_bitlinear_dx": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _i, _sz, _f]),
     "ab_ste_dw": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _f]),
     "ab_bitlinear_step_host": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "ab_qat_linear_steps": (_i, [_vp, _vp, _sz, _sz, _i, _i, _i, C.c_uint32, _i]),
     "ab_tensor_peak_probe": (_i, [_vp, _i, _i, C.POINTER(C.c_double)]),
     "ab_selftest_bounded_wait": (_i, [_vp, C.c_uint32]),
 }

@@ -98,6 +98,61 @@ class SwitchBuffer:
         torch.cuda.synchronize(device)
 
 
+class SwitchArena:
+    """Several exchange buffers carved out of ONE symmetric-memory allocation (one rendezvous instead of one per
+    buffer): `sizes` are byte counts; buffer i occupies [offset[i], offset[i] + sizes[i]) rounded up to 256 * world
+    bytes, and its 16 bytes of barrier counters sit in a block of 256-byte slots behind the data.  Construction is
+    collective.  Pointers come back as plain integers for the C ABI (local, multicast, flags local, flags multicast)."""
+
+    SLOT = 256
+
+    def __init__(self, ctx, sizes, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.ctx = ctx
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world < 2:
+            raise ValueError("a SwitchArena needs at least two GPUs")
+        unit = 256 * self.world
+        self.sizes = [int(b) for b in sizes]
+        self.offsets, off = [], 0
+        for b in self.sizes:
+            self.offsets.append(off)
+            off += (b + unit - 1) // unit * unit
+        self.data_bytes = off
+        self._t = symm_mem.empty(off + self.SLOT * len(self.sizes), dtype=torch.uint8, device=device)
+        self._hdl = symm_mem.rendezvous(self._t, self.group)
+        if not self._hdl.multicast_ptr:
+            raise RuntimeError("this group of GPUs has no NVSwitch multicast mapping")
+        self._t[off:].zero_()
+        self.local_ptr = self._t.data_ptr()
+        self.mc_ptr = self._hdl.multicast_ptr + (self._t.data_ptr() - self._hdl.buffer_ptrs[self._hdl.rank])
+        self.epoch = 0
+
+    def view(self, i: int, dtype, shape):
+        n = 1
+        for d in shape:
+            n *= d
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        assert nb <= self.sizes[i]
+        return self._t[self.offsets[i]:self.offsets[i] + nb].view(dtype).view(shape)
+
+    def pointers(self, i: int):
+        """(local, multicast, flags_local, flags_multicast) of buffer i."""
+        f = self.data_bytes + self.SLOT * i
+        return (self.local_ptr + self.offsets[i], self.mc_ptr + self.offsets[i], self.local_ptr + f, self.mc_ptr + f)
+
+    def reset_flags(self):
+        """Zero the barrier counters and restart the epoch count (collective; call between two uses whose numbers of
+        exchanges per buffer differ, or after a timed-out exchange)."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self._t[self.data_bytes:].zero_()
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+
 class SwitchDwAllReducer:
     """dW buffers in symmetric memory, summed over the GPUs inside NVSwitch by the library's own kernel instead of
     NCCL: no staging copies and a handful of small CTAs per exchange, so the GEMMs that overlap it keep their SMs.

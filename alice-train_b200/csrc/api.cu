@@ -862,6 +862,52 @@ int ab_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) {
     return abk_tensor_peak_probe(ctx, kind_i8, iters, ops_out);
 }
 
+int ab_qat_linear_steps(ab_ctx* ctx, const ab_linear_step* steps, size_t count, size_t m, int guard, int rank, int world,
+                        uint32_t epoch, int ctas) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(guard == AB_GUARD_INV_ZERO || guard == AB_GUARD_FLOOR, AB_ERR_UNSUPPORTED);
+    if (count == 0) return AB_OK;
+    AB_REQUIRE(steps, AB_ERR_NULL);
+    bool any_exchange = false;
+    for (size_t i = 0; i < count; ++i) {   // every entry is checked before anything is queued
+        const ab_linear_step& s = steps[i];
+        AB_REQUIRE(s.w, AB_ERR_NULL);
+        AB_REQUIRE(s.w->ctx == ctx, AB_ERR_STATE);
+        AB_REQUIRE(s.w->codes_fwd && s.w->codes_t, AB_ERR_STATE);
+        AB_REQUIRE(s.w_latent || s.w->has_data, AB_ERR_STATE);
+        AB_REQUIRE((reinterpret_cast<uintptr_t>(s.w_latent) & 3) == 0, AB_ERR_ALIGN);
+        AB_REQUIRE(s.dw_beta == 0.0f || s.dw_beta == 1.0f, AB_ERR_UNSUPPORTED);
+        if (m && s.w->out && s.w->in)
+            AB_REQUIRE(s.x_bf16 && s.dy_bf16 && s.xq && s.scales && s.rowsums && s.y_bf16 && s.dx_bf16 && s.dW, AB_ERR_NULL);
+        if (s.dw_multicast) {
+            any_exchange = true;
+            AB_REQUIRE(s.flags_local && s.flags_multicast && s.dW, AB_ERR_NULL);
+            AB_REQUIRE(world >= 2 && world <= 64 && rank >= 0 && rank < world && epoch >= 1, AB_ERR_SHAPE);
+            AB_REQUIRE((s.w->out * s.w->in) % (4 * (size_t)world) == 0, AB_ERR_SHAPE);
+            AB_REQUIRE(((reinterpret_cast<uintptr_t>(s.dw_multicast) | reinterpret_cast<uintptr_t>(s.flags_local) |
+                         reinterpret_cast<uintptr_t>(s.flags_multicast)) & 15) == 0, AB_ERR_ALIGN);
+        }
+    }
+    AB_REQUIRE(ctas >= 0 && ctas <= 148, AB_ERR_UNSUPPORTED);
+    if (ctas == 0) ctas = world <= 2 ? 16 : (world <= 4 ? 12 : 8);
+    for (size_t i = 0; i < count; ++i) {
+        const ab_linear_step& s = steps[i];
+        ab_weights* w = s.w;
+        const size_t out = w->out, in = w->in;
+        if (s.w_latent) AB_TRY(abk_fq_absmean_pack(ctx, s.w_latent, w, nullptr, guard, 0));
+        if (m == 0 || out == 0 || in == 0) continue;
+        // dW first: its exchange then runs beside this linear's other kernels and the next linear's dW
+        AB_TRY(abk_gemm_dw(ctx, s.dy_bf16, out, s.x_bf16, in, m, out, in, s.dW, in, s.dw_beta));
+        if (s.dw_multicast)
+            AB_TRY(abk_dp_allreduce_start(ctx, s.dw_multicast, out * in, s.flags_local, s.flags_multicast, rank, world, epoch, ctas));
+        AB_TRY(abk_act_quant_int8(ctx, s.x_bf16, AB_BF16, m, in, in, s.xq, in, s.scales, s.rowsums));
+        AB_TRY(abk_gemm_fwd(ctx, w, s.xq, in, s.scales, s.rowsums, m, s.y_bf16, AB_BF16, out, nullptr));
+        AB_TRY(abk_gemm_dx(ctx, w, s.dy_bf16, out, m, s.dx_bf16, AB_BF16, in, 0.0f));
+    }
+    if (any_exchange) AB_TRY(abk_dp_allreduce_wait(ctx));
+    return AB_OK;
+}
+
 int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* x_host, const void* dy_host, size_t m,
                            void* y_host, void* dx_host, float* dW_dev) {
     AB_TRY(bind(ctx));

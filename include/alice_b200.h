@@ -295,6 +295,35 @@ AB_API int ab_bitlinear_step_host(ab_ctx* ctx, const ab_weights* w, const void* 
                                   const void* dy_bf16_host, size_t m, void* y_bf16_host,
                                   void* dx_bf16_host, float* dW_dev);
 
+/* One QAT micro-step over a list of linears in a single call: for each entry, in order,
+ *   kernel (1) on `w_latent` when it is not NULL (gamma and codes into `w` under `guard`: AB_GUARD_FLOOR is the Llama
+ *   trainer's rule, src/bin/train_qat_70b.rs:2129, AB_GUARD_INV_ZERO the Qwen one's, src/qwen35.rs:226-228), dW = dy^T x (beta = dw_beta), the start of dW's exchange when
+ *   `dw_multicast` is not NULL (see ab_dp_allreduce_start: flags, epoch and ctas as there), act-quant of x, the
+ *   forward into `y`, and dx; after the last entry the context's stream waits for every exchange started.
+ * This is the per-projection sequence of the reference's training step (quantise -> matmul_bt -> matmul_nn ->
+ * matmul_tn for every projection of every layer, src/bin/train_qat_70b.rs:885-917,1157-1229,
+ * src/bin/train_qat_qwen35.rs:839,922) behind one call, so that a step of a few hundred small linears is not paced by
+ * the host.  All pointers are device memory; x, dy, y, dx are bf16 with pitches in, out, out, in; `xq` (int8 [m x in]),
+ * `scales` (f32 [m]) and `rowsums` (s32 [m]) are caller-owned work buffers that consecutive entries may share. */
+typedef struct ab_linear_step {
+    ab_weights* w;
+    const float* w_latent;
+    const void* x_bf16;
+    const void* dy_bf16;
+    int8_t* xq;
+    float* scales;
+    int32_t* rowsums;
+    void* y_bf16;
+    void* dx_bf16;
+    float* dW;
+    float dw_beta;
+    float* dw_multicast;
+    uint32_t* flags_local;
+    uint32_t* flags_multicast;
+} ab_linear_step;
+AB_API int ab_qat_linear_steps(ab_ctx* ctx, const ab_linear_step* steps, size_t count, size_t m, int guard, int rank,
+                               int world, uint32_t epoch, int ctas);
+
 /* ------------------------------------------------- data-parallel exchange of dW (NVSwitch) */
 
 /* Sums a f32 buffer over the GPUs of one NVSwitch domain, in place, inside the switch (multimem.ld_reduce /

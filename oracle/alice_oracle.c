@@ -19,9 +19,10 @@
  *     activation quantisation is not in the reference at all; it is defined by this build's
  *     target specification and its exact operation order is fixed here.
  *
- * Build: gcc -O2 -std=c99 -ffp-contract=off -fno-fast-math -fopenmp -shared -fPIC
+ * Build: gcc -O3 -march=x86-64-v3 -std=c99 -ffp-contract=off -fno-fast-math -fopenmp -shared -fPIC
  * (-ffp-contract=off so that `a*b + c` rounds twice like the Rust source; fmaf() is used
- * exactly where the reference calls mul_add).
+ * exactly where the reference calls mul_add and compiles to the hardware fused multiply-add,
+ * as the reference's release builds with target-cpu=native do, scripts/setup_runpod.sh:149).
  */
 #include <math.h>
 #include <stdint.h>
@@ -493,6 +494,48 @@ ORC_API void orc_matmul_bt_backward(const float* d_output, const float* a, const
     }
 }
 
+/* The same two products for WHOLE tensors at full problem size: rows in parallel (OpenMP), and inside a row the loops
+ * over h and j interchanged so that the compiler can vectorise over j.  Every element d_a[i][j] / d_b[i][j] still
+ * receives its fmaf chain in ascending h, i.e. exactly the operation sequence of the loops above
+ * (src/llama_backward.rs:118-137), so the results are bit-identical to orc_matmul_bt_backward. */
+ORC_API void orc_matmul_bt_backward_rows(const float* d_output, const float* a, const float* b, float* d_a,
+                                         float* d_b, size_t m, size_t n, size_t k) {
+    if (d_a) {
+#pragma omp parallel
+        {
+            float* sum = (float*)malloc(k * sizeof(float));
+#pragma omp for schedule(static)
+            for (size_t i = 0; i < m; ++i) {
+                for (size_t j = 0; j < k; ++j) sum[j] = 0.0f;
+                for (size_t h = 0; h < n; ++h) {
+                    const float d = d_output[i * n + h];
+                    const float* brow = b + h * k;
+                    for (size_t j = 0; j < k; ++j) sum[j] = fmaf(d, brow[j], sum[j]);
+                }
+                for (size_t j = 0; j < k; ++j) d_a[i * k + j] += sum[j];
+            }
+            free(sum);
+        }
+    }
+    if (d_b) {
+#pragma omp parallel
+        {
+            float* sum = (float*)malloc(k * sizeof(float));
+#pragma omp for schedule(static)
+            for (size_t i = 0; i < n; ++i) {
+                for (size_t j = 0; j < k; ++j) sum[j] = 0.0f;
+                for (size_t h = 0; h < m; ++h) {
+                    const float d = d_output[h * n + i];
+                    const float* arow = a + h * k;
+                    for (size_t j = 0; j < k; ++j) sum[j] = fmaf(d, arow[j], sum[j]);
+                }
+                for (size_t j = 0; j < k; ++j) d_b[i * k + j] += sum[j];
+            }
+            free(sum);
+        }
+    }
+}
+
 /* Single elements of the two backward products, for sampled checks at full problem size. */
 ORC_API float orc_dx_element(const float* d_output, const float* b, size_t n, size_t k, size_t i,
                              size_t j) {
@@ -562,6 +605,97 @@ ORC_API int32_t orc_int8_ternary_acc_element(const int8_t* xq, const int8_t* cod
 
 ORC_API float orc_bitlinear_fwd_scale(int32_t acc, float s_t, float gamma) {
     return ((float)acc * (s_t / 127.0f)) * gamma;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Steps on either side of the linears.
+ *   rmsnorm            (src/llama_forward.rs:78-86)     f64 sum of squares per row; x *= inv_rms * weight
+ *   rmsnorm_backward   (src/llama_backward.rs:149-210)  d_input accumulates; d_weight accumulates
+ *   SwiGLU             (src/cuda_matmul.rs:684-696)     out = g / (1 + expf(-g)) * up
+ *   SwiGLU backward    (src/cuda_matmul.rs:4135-4147)   with fast_sigmoid (src/fast_math.rs:11-23)
+ *   sgd_update         (src/qwen35_backward.rs:386-390) w -= lr * (g + wd * w)
+ *   AdamW              (src/cuda_matmul.rs:815-839, src/bin/train_qat_70b.rs:2231-2241)
+ * ---------------------------------------------------------------------------------------- */
+ORC_API void orc_rmsnorm(float* x, const float* weight, size_t rows, size_t dim, float eps) {
+    for (size_t t = 0; t < rows; ++t) {
+        float* row = x + t * dim;
+        double ss = 0.0;
+        for (size_t d = 0; d < dim; ++d) ss += (double)row[d] * (double)row[d];
+        float inv_rms = 1.0f / (float)sqrt(ss / (double)dim + (double)eps);
+        for (size_t d = 0; d < dim; ++d) row[d] *= inv_rms * weight[d];
+    }
+}
+
+/* d_weight: the reference folds per-thread partial vectors (rayon) whose grouping is scheduling-defined; restated as
+ * the sequential sum over tokens, compared at tolerance. */
+ORC_API void orc_rmsnorm_backward(const float* d_output, const float* input, const float* weight, float* d_input,
+                                  float* d_weight, size_t rows, size_t dim, float eps) {
+    for (size_t t = 0; t < rows; ++t) {
+        const float* x = input + t * dim;
+        const float* dy = d_output + t * dim;
+        double ss = 0.0;
+        for (size_t d = 0; d < dim; ++d) ss += (double)x[d] * (double)x[d];
+        float inv_rms = (float)(1.0 / sqrt(ss / (double)dim + (double)eps));
+        float inv_rms3 = inv_rms * inv_rms * inv_rms;
+        float d_rms_sum = 0.0f;
+        for (size_t d = 0; d < dim; ++d) d_rms_sum += dy[d] * weight[d] * x[d];
+        for (size_t d = 0; d < dim; ++d) {
+            float d_norm = dy[d] * weight[d];
+            d_input[t * dim + d] += d_norm * inv_rms - d_rms_sum * x[d] * inv_rms3 / (float)dim;
+        }
+        if (d_weight)
+            for (size_t d = 0; d < dim; ++d) d_weight[d] += dy[d] * x[d] * inv_rms;
+    }
+}
+
+ORC_API void orc_swiglu(const float* gate, const float* up, float* out, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        float g = gate[i];
+        float silu_g = g / (1.0f + expf(-g));
+        out[i] = silu_g * up[i];
+    }
+}
+
+static inline float orc_fast_exp(float x) { /* src/fast_math.rs:11-16 */
+    x = orc_clampf(x, -87.3f, 88.7f);
+    float val = fmaf(x, 1.44269504088896340736f, 126.942695f);
+    float scaled = val * 8388608.0f;
+    uint32_t bits = scaled <= 0.0f ? 0u : (scaled >= 4294967296.0f ? 0xFFFFFFFFu : (uint32_t)scaled); /* `as u32` saturates */
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+ORC_API float orc_fast_sigmoid(float x) { return 1.0f / (1.0f + orc_fast_exp(-x)); }
+
+/* d_gate, d_up from d_intermediate, the cached gate, up and gate_silu = silu(gate) (src/cuda_matmul.rs:4135-4147) */
+ORC_API void orc_swiglu_backward(const float* d_inter, const float* gate, const float* up, const float* gate_silu,
+                                 float* d_gate, float* d_up, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        float d_gate_silu = d_inter[i] * up[i];
+        d_up[i] = d_inter[i] * gate_silu[i];
+        float x = gate[i];
+        float sig = orc_fast_sigmoid(x);
+        float silu_grad = sig * (1.0f + x * (1.0f - sig));
+        d_gate[i] = d_gate_silu * silu_grad;
+    }
+}
+
+ORC_API void orc_sgd_update(float* w, const float* grad, size_t n, float lr, float wd) {
+    for (size_t i = 0; i < n; ++i) w[i] -= lr * (grad[i] + wd * w[i]);
+}
+
+/* bc1 = 1 - beta1^t, bc2 = 1 - beta2^t are formed by the caller (powf), as in the reference */
+ORC_API void orc_adamw_update(float* delta, const float* grad, float* m, float* v, size_t n, float lr, float beta1,
+                              float beta2, float eps, float bc1, float bc2, float wd) {
+    for (size_t i = 0; i < n; ++i) {
+        float g = grad[i];
+        m[i] = beta1 * m[i] + (1.0f - beta1) * g;
+        v[i] = beta2 * v[i] + (1.0f - beta2) * g * g;
+        float m_hat = m[i] / bc1;
+        float v_hat = v[i] / bc2;
+        delta[i] -= lr * (m_hat / (sqrtf(v_hat) + eps) + wd * delta[i]);
+    }
 }
 
 ORC_API int orc_max_threads(void) {

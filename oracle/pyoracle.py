@@ -65,6 +65,14 @@ def _load():
         "orc_matmul_bt": (None, [_f32p, _f32p, _f32p, sz, sz, sz]),
         "orc_tiled_matmul_bt": (None, [_f32p, _f32p, _f32p, sz, sz, sz]),
         "orc_matmul_bt_backward": (None, [_f32p, _f32p, _f32p, C.c_void_p, C.c_void_p, sz, sz, sz]),
+        "orc_matmul_bt_backward_rows": (None, [_f32p, _f32p, _f32p, C.c_void_p, C.c_void_p, sz, sz, sz]),
+        "orc_rmsnorm": (None, [_f32p, _f32p, sz, sz, C.c_float]),
+        "orc_rmsnorm_backward": (None, [_f32p, _f32p, _f32p, _f32p, C.c_void_p, sz, sz, C.c_float]),
+        "orc_swiglu": (None, [_f32p, _f32p, _f32p, sz]),
+        "orc_fast_sigmoid": (C.c_float, [C.c_float]),
+        "orc_swiglu_backward": (None, [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, sz]),
+        "orc_sgd_update": (None, [_f32p, _f32p, sz, C.c_float, C.c_float]),
+        "orc_adamw_update": (None, [_f32p, _f32p, _f32p, _f32p, sz] + [C.c_float] * 7),
         "orc_dx_element": (C.c_float, [_f32p, _f32p, sz, sz, sz, sz]),
         "orc_dw_element": (C.c_float, [_f32p, _f32p, sz, sz, sz, sz, sz]),
         "orc_act_quant_int8": (None, [_f32p, sz, sz, _i8p, _f32p]),
@@ -348,6 +356,67 @@ def bitlinear_fwd_scale(acc, s_t, gamma) -> np.ndarray:
     st = (np.asarray(s_t, np.float32) / np.float32(127.0)).astype(np.float32)
     y = (acc.astype(np.float32) * st[:, None]).astype(np.float32)
     return (y * np.float32(gamma)).astype(np.float32)
+
+
+def matmul_bt_backward_rows(d_out, a, b, m, n, k, want=("da", "db")):
+    """orc_matmul_bt_backward for whole tensors at full size: rows in parallel, per-element order unchanged."""
+    d_out, a, b = _f32(d_out).reshape(-1), _f32(a).reshape(-1), _f32(b).reshape(-1)
+    da = np.zeros(m * k, np.float32) if "da" in want else None
+    db = np.zeros(n * k, np.float32) if "db" in want else None
+    lib.orc_matmul_bt_backward_rows(d_out, a, b, da.ctypes.data_as(C.c_void_p) if da is not None else None,
+                                    db.ctypes.data_as(C.c_void_p) if db is not None else None, m, n, k)
+    return (da.reshape(m, k) if da is not None else None), (db.reshape(n, k) if db is not None else None)
+
+
+def rmsnorm(x, weight, eps) -> np.ndarray:
+    x = np.array(x, dtype=np.float32, order="C").copy()
+    rows, dim = x.shape
+    lib.orc_rmsnorm(x.reshape(-1), _f32(weight), rows, dim, eps)
+    return x
+
+
+def rmsnorm_backward(d_output, x, weight, eps, d_input=None, d_weight=None):
+    x = _f32(x)
+    rows, dim = x.shape
+    di = np.zeros(rows * dim, np.float32) if d_input is None else np.array(d_input, np.float32).reshape(-1).copy()
+    dw = np.zeros(dim, np.float32) if d_weight is None else np.array(d_weight, np.float32).reshape(-1).copy()
+    lib.orc_rmsnorm_backward(_f32(d_output).reshape(-1), x.reshape(-1), _f32(weight), di, dw.ctypes.data_as(C.c_void_p),
+                             rows, dim, eps)
+    return di.reshape(rows, dim), dw
+
+
+def swiglu(gate, up) -> np.ndarray:
+    gate, up = _f32(gate), _f32(up)
+    out = np.empty(gate.shape, np.float32)
+    lib.orc_swiglu(gate.reshape(-1), up.reshape(-1), out.reshape(-1), gate.size)
+    return out
+
+
+def fast_sigmoid(x: float) -> float:
+    return float(lib.orc_fast_sigmoid(float(x)))
+
+
+def swiglu_backward(d_inter, gate, up, gate_silu):
+    d_inter, gate, up, gate_silu = _f32(d_inter), _f32(gate), _f32(up), _f32(gate_silu)
+    dg, du = np.empty(gate.shape, np.float32), np.empty(gate.shape, np.float32)
+    lib.orc_swiglu_backward(d_inter.reshape(-1), gate.reshape(-1), up.reshape(-1), gate_silu.reshape(-1), dg.reshape(-1),
+                            du.reshape(-1), gate.size)
+    return dg, du
+
+
+def sgd_update(w, grad, lr, wd) -> np.ndarray:
+    w = np.array(w, dtype=np.float32).reshape(-1).copy()
+    lib.orc_sgd_update(w, _f32(grad).reshape(-1), w.size, lr, wd)
+    return w
+
+
+def adamw_update(delta, grad, m, v, lr, beta1, beta2, eps, step, wd):
+    """One AdamW step on (delta, m, v) copies; bias corrections 1 - beta^t in f32 as the reference forms them."""
+    delta, m, v = (np.array(t, dtype=np.float32).reshape(-1).copy() for t in (delta, m, v))
+    bc1 = np.float32(1.0) - np.float32(np.float32(beta1) ** np.float32(step))
+    bc2 = np.float32(1.0) - np.float32(np.float32(beta2) ** np.float32(step))
+    lib.orc_adamw_update(delta, _f32(grad).reshape(-1), m, v, delta.size, lr, beta1, beta2, eps, float(bc1), float(bc2), wd)
+    return delta, m, v, float(bc1), float(bc2)
 
 
 def max_threads() -> int:
