@@ -44,10 +44,48 @@ int ab_ctx_scratch(ab_ctx* ctx, size_t bytes, void** out) {
     return AB_OK;
 }
 
+int ab_ctx_counters(ab_ctx* ctx, size_t count, unsigned int** out) {
+    if (count > ctx->counters_len || !ctx->counters) {
+        if (ctx->counters) {
+            AB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+            AB_CUDA_CHECK(ctx, cudaFree(ctx->counters));
+            ctx->counters = nullptr;
+            ctx->counters_len = 0;
+        }
+        const size_t want = count < 4096 ? 4096 : count;
+        AB_CUDA_CHECK(ctx, cudaMalloc(&ctx->counters, want * sizeof(unsigned int)));
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(ctx->counters, 0, want * sizeof(unsigned int), ctx->stream));
+        ctx->counters_len = want;
+    }
+    *out = ctx->counters;
+    return AB_OK;
+}
+
 int ab_ctx_stage(ab_ctx* ctx, int slot, size_t bytes, void** out) {
     AB_TRY(grow(ctx, &ctx->stage[slot], &ctx->stage_bytes[slot], bytes));
     *out = ctx->stage[slot];
     return AB_OK;
+}
+
+// Contexts that are still alive: a weight handle may outlive its context (a host language's finalisers run in any
+// order at exit) and must not touch it then.
+static std::mutex g_live_mu;
+static ab_ctx* g_live[256] = {};
+static void live_add(ab_ctx* c) {
+    std::lock_guard<std::mutex> lock(g_live_mu);
+    for (auto& s : g_live)
+        if (!s) { s = c; return; }
+}
+static void live_remove(ab_ctx* c) {
+    std::lock_guard<std::mutex> lock(g_live_mu);
+    for (auto& s : g_live)
+        if (s == c) s = nullptr;
+}
+static bool live_has(ab_ctx* c) {
+    std::lock_guard<std::mutex> lock(g_live_mu);
+    for (auto& s : g_live)
+        if (s == c) return true;
+    return false;
 }
 
 static int bind(ab_ctx* ctx) {
@@ -111,15 +149,18 @@ int ab_ctx_create(int device, void* cuda_stream, ab_ctx** out) {
         delete ctx;
         return st;
     }
+    live_add(ctx);
     *out = ctx;
     return AB_OK;
 }
 
 int ab_ctx_destroy(ab_ctx* ctx) {
     AB_REQUIRE(ctx, AB_ERR_NULL);
+    live_remove(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->counters) cudaFree(ctx->counters);
     for (int i = 0; i < 12; ++i)
         if (ctx->stage[i]) cudaFree(ctx->stage[i]);
     for (int i = 0; i < 2; ++i)
@@ -165,6 +206,7 @@ int ab_ctx_sync(ab_ctx* ctx) {
     if (status != 0) {
         ctx->last_error = "device-side wait timed out, code " + std::to_string(status);
         cudaMemset(ctx->dev_status, 0, 64);  // status word and the GEMM tile counter (left mid-count by an aborted launch)
+        if (ctx->counters) cudaMemset(ctx->counters, 0, ctx->counters_len * sizeof(unsigned int));
         return AB_ERR_DEVICE_TIMEOUT;
     }
     return AB_OK;
@@ -217,9 +259,11 @@ int ab_weights_create(ab_ctx* ctx, size_t out, size_t in, ab_weights** w) {
 
 int ab_weights_destroy(ab_weights* w) {
     AB_REQUIRE(w, AB_ERR_NULL);
-    if (w->ctx) {
+    if (w->ctx && live_has(w->ctx)) {
         cudaSetDevice(w->ctx->device);
         cudaStreamSynchronize(w->ctx->stream);
+    } else {
+        cudaDeviceSynchronize();   // the context is gone (and with it the stream): nothing of ours can still be queued
     }
     if (w->codes) cudaFree(w->codes);
     if (w->codes_fwd) cudaFree(w->codes_fwd);

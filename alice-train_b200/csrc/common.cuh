@@ -41,6 +41,10 @@ struct ab_ctx {
     // grow-only device scratch (reduction partials, host-API staging)
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // grow-only array of per-tile completion counters of the sliced matvec: zero between launches (the finishing warp
+    // of a tile resets its counter), never shared with other kernels
+    unsigned int* counters = nullptr;
+    size_t counters_len = 0;
     void* stage[12] = {};          // two sets of six: consecutive host-buffer steps alternate between them
     size_t stage_bytes[12] = {};
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
@@ -108,6 +112,7 @@ struct ab_weights {
 
 int ab_ctx_scratch(ab_ctx* ctx, size_t bytes, void** out);
 int ab_ctx_stage(ab_ctx* ctx, int slot, size_t bytes, void** out);
+int ab_ctx_counters(ab_ctx* ctx, size_t count, unsigned int** out);
 
 // quantize.cu
 int abk_fq_absmean_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int guard,

@@ -234,6 +234,9 @@ __global__ void __launch_bounds__(1024)
 prenorm_finish_kernel(const float* __restrict__ x, size_t n, float eps, float* __restrict__ dx) {
     __shared__ double s_a[32], s_b[32];
     __shared__ float s_inv, s_coef;
+    // launched with programmatic stream serialisation behind the matvec that produces dx: its launch overlaps that
+    // kernel's tail, its reads wait here until the producer has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     double ss = 0.0, dot = 0.0;
     for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
         double xv = (double)x[i];
@@ -457,8 +460,17 @@ int abk_bitlinear_backward(ab_ctx* ctx, const ab_weights* w, const float* x, con
                                            ctx->stream));
     int st = abk_ternary_matvec_backward(ctx, w, dy, dx);
     if (st || !pre_norm || w->in == 0) return st;
-    prenorm_finish_kernel<<<1, 1024, 0, ctx->stream>>>(x, w->in, norm_eps, dx);
-    AB_LAUNCH_CHECK(ctx);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, prenorm_finish_kernel, x, w->in, norm_eps, dx));
+    ctx->launches++;
     return AB_OK;
 }
 

@@ -243,8 +243,10 @@ __global__ void matvec_mma_finish_kernel(const double* __restrict__ partial, siz
 
 }  // namespace
 
-// codes: the handle's forward copy (rows = out, K = in) or transposed copy (rows = in, K = out)
-int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows, size_t k, const float* v, float* y, float scale,
+// codes: the handle's forward copy (rows = out, K = in) or transposed copy (rows = in, K = out).  This is the form with
+// per-thread loads; abk_matvec_mma (matvec_tma.cu) streams the same codes through shared memory with TMA and falls
+// back to this one where a tensor map cannot describe the operand.
+int abk_matvec_ldg(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows, size_t k, const float* v, float* y, float scale,
                    int accumulate, int use_scale) {
     const size_t k_pad = ab_round_up(k, kSpan);
     const size_t tiles = (rows + 15) / 16;

@@ -602,7 +602,7 @@ def hbm_block(env, full: bool = True):
 
         def timeit(fn, reps, rotate):
             for i in range(3):
-                fn(mats[i % nmat])
+                fn(mats[i % len(mats)])
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             try:
