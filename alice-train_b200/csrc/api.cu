@@ -161,7 +161,7 @@ int ab_ctx_destroy(ab_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->counters) cudaFree(ctx->counters);
-    for (int i = 0; i < 12; ++i)
+    for (int i = 0; i < 16; ++i)
         if (ctx->stage[i]) cudaFree(ctx->stage[i]);
     for (int i = 0; i < 2; ++i)
         if (ctx->set_free[i]) cudaEventDestroy(ctx->set_free[i]);

@@ -45,8 +45,8 @@ struct ab_ctx {
     // of a tile resets its counter), never shared with other kernels
     unsigned int* counters = nullptr;
     size_t counters_len = 0;
-    void* stage[12] = {};          // two sets of six: consecutive host-buffer steps alternate between them
-    size_t stage_bytes[12] = {};
+    void* stage[16] = {};          // 0-11: two sets of six, consecutive host-buffer steps alternate between them;
+    size_t stage_bytes[16] = {};   // 12, 13: converted vectors of the streaming matvec; 14, 15: diagnostics
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
     int* dev_status = nullptr;
     // copy streams + events of the host-buffer step (created on first use)
@@ -63,6 +63,10 @@ struct ab_ctx {
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     bool host_integer_matvec = false;  // AB_OPT_HOST_INTEGER_MATVEC: the host-slice forms may take the integer path too
     uint64_t launches = 0;
+    // true while the most recent kernel this context launched was a streaming matvec (kernels that never write codes):
+    // the next one may then request its codes before the previous kernel has completed.  Every other launch clears it.
+    bool matvec_chain = false;
+    int vec_turn = 0;              // which of the two converted-vector buffers the next matvec uses
     std::string last_error;
 };
 
@@ -103,6 +107,7 @@ struct ab_weights {
 #define AB_LAUNCH_CHECK(ctx)                                                                  \
     do {                                                                                      \
         (ctx)->launches++;                                                                    \
+        (ctx)->matvec_chain = false;                                                          \
         cudaError_t _e = cudaGetLastError();                                                  \
         if (_e != cudaSuccess) {                                                              \
             (ctx)->last_error = std::string("kernel launch: ") + cudaGetErrorString(_e);      \

@@ -87,11 +87,11 @@ AB_API int ab_ctx_destroy(ab_ctx* ctx);
  * paths.  f32: the selected elements are added in f32 as the reference's loops do (src/backward.rs:45-80): a zero
  * weight contributes nothing, so a NaN or Inf in the vector reaches only the outputs it is connected to, and rows with
  * dy_j == 0 change nothing.  Integer: for matrices of at least 64 x 512 the vector is rounded to 32-bit fixed point
- * with one power-of-two scale per K slice (error at most 2^-31 of the slice's largest magnitude per element), the sums
- * are exact integers on the tensor cores and are rounded to f32 once; that path is the one that approaches the HBM
- * roofline.  It differs from f32 accumulation in rounding only, except that elements below 2^-31 of the largest
- * magnitude drop out, a slice whose largest magnitude is subnormal counts as zero, and one non-finite element makes
- * every output of its slice NaN.
+ * with one power-of-two scale (error at most 2^-31 of the vector's largest magnitude per element), the sums are exact
+ * integers on the tensor cores and are rounded to f32 once; that path is the one that approaches the HBM roofline.
+ * It differs from f32 accumulation in rounding only, except that elements below 2^-31 of the largest magnitude drop
+ * out, a vector whose largest magnitude is subnormal counts as zero, and one non-finite element makes every output
+ * NaN.
  *   AB_OPT_EXACT_MATVEC        1: every batch-1 entry point uses the f32 path.
  *                              0: the DEVICE-pointer entry points use the integer path where it applies.
  *   AB_OPT_HOST_INTEGER_MATVEC 0: the HOST-slice forms (ab_ternary_matvec_host, ab_ternary_matvec_backward_host,
