@@ -9,6 +9,7 @@ that needs one creates the default context and raises if no B200 is present.
 from . import _ffi, blas
 from .backward import bitlinear_backward, ste_weight_grad, ternary_matvec_backward, ternary_matvec_kernel
 from .context import GpuContext, default_context, set_default_context
+from .cuda_matmul import CudaMatmul, GpuBackwardEngine, blas_matmul_bt, blas_matmul_nn, init_cuda_blas
 from .export import dequantize, pack_ternary, quantize_and_pack, unpack_ternary
 from .ops import TernaryWeightKernel
 from .qat import CalibrationStats, FakeQuantize, QatConfig, QatEpochResult, QatTrainer, QuantBits
@@ -18,4 +19,5 @@ __all__ = [
     "ternary_matvec_backward", "ternary_matvec_kernel", "bitlinear_backward", "ste_weight_grad",
     "FakeQuantize", "QatConfig", "QatTrainer", "QuantBits", "CalibrationStats", "QatEpochResult",
     "pack_ternary", "unpack_ternary", "quantize_and_pack", "dequantize", "blas",
+    "CudaMatmul", "GpuBackwardEngine", "blas_matmul_bt", "blas_matmul_nn", "init_cuda_blas",
 ]

@@ -67,6 +67,8 @@ SIGNATURES = {
     "ab_fq_merge_quantize_alpha": (_i, [_vp, _vp, _vp, _vp, _sz, _f, _f, C.POINTER(_f), C.POINTER(C.c_double)]),
     "ab_fq_shard_abs_sum": (_i, [_vp, _vp, _vp, _vp]),
     "ab_fq_shard_pack": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _i, _i]),
+    "ab_sgd_step_fq": (_i, [_vp, _vp, _vp, _sz, _f, _f, _vp, _i, _vp]),
+    "ab_adamw_step_fq": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _f, _f, _f, _f, _f, _f, _f, _vp, _i, _vp]),
     "ab_weights_fq_report": (_i, [_vp, C.POINTER(FqReport)]),
     "ab_dp_allreduce_start": (_i, [_vp, _vp, _sz, _vp, _vp, _i, _i, C.c_uint32, _i]),
     "ab_dp_allreduce_wait": (_i, [_vp]),
@@ -93,6 +95,10 @@ SIGNATURES = {
     "ab_ternary_matmul_bt_host": (_i, [_vp, _vp, _vp, _f, _vp, _sz, _sz, _sz]),
     "ab_act_quant_int8": (_i, [_vp, _vp, _i, _sz, _sz, _sz, _vp, _sz, _vp, _vp]),
     "ab_bitlinear_fwd": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _i, _sz, _vp]),
+    "ab_matmul_bt_host": (_i, [_vp, _vp, _sz, _vp, _vp, _sz, _sz]),
+    "ab_matmul_nn_host": (_i, [_vp, _vp, _sz, _vp, _vp, _sz, _sz]),
+    "ab_matmul_tn_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz]),
+    "ab_bitlinear_fwd_bf16": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _i, _sz, _f]),
     "ab_bitlinear_dx": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _i, _sz, _f]),
     "ab_ste_dw": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _f]),
     "ab_bitlinear_step_host": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp]),

@@ -128,6 +128,24 @@ def bitlinear_fwd(w: BitLinearWeights, a: QuantizedActivations, y: torch.Tensor 
     return y
 
 
+def bitlinear_fwd_bf16(w: BitLinearWeights, x: torch.Tensor, y: torch.Tensor | None = None, dtype=torch.float32,
+                       beta: float = 0.0) -> torch.Tensor:
+    """y = beta*y + gamma * x . codes^T on bf16 activations (no activation quantisation): the reference's matmul_bt on
+    fake-quantised weights (src/llama_forward.rs:43-55)."""
+    _chk2d(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("x must be bfloat16")
+    m = x.shape[0]
+    if x.shape[1] != w.in_features():
+        raise AssertionError("assertion `left == right` failed: x.cols == in_features")
+    if y is None:
+        y = torch.empty((m, w.out_features()), dtype=dtype, device=x.device)
+    _chk2d(y, "y")
+    _ffi.check(w._lib.ab_bitlinear_fwd_bf16(w.ctx.handle, w.handle, _dp(x), x.stride(0), m, _dp(y), _dt(y), y.stride(0),
+                                            float(beta)), w.ctx.handle)
+    return y
+
+
 def bitlinear_dx(w: BitLinearWeights, dy: torch.Tensor, dx: torch.Tensor | None = None, dtype=torch.bfloat16,
                  beta: float = 0.0) -> torch.Tensor:
     _chk2d(dy, "dy")
@@ -154,3 +172,43 @@ def ste_dw(ctx: GpuContext, dy: torch.Tensor, x: torch.Tensor, dW: torch.Tensor,
     _ffi.check(_ffi.load().ab_ste_dw(ctx.handle, _dp(dy), dy.stride(0), _dp(x), x.stride(0), m, out, x.shape[1],
                                      _dp(dW), dW.stride(0), float(beta)), ctx.handle)
     return dW
+
+
+def _chk_flat(t: torch.Tensor, name: str, n: int | None = None):
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    if n is not None and t.numel() != n:
+        raise AssertionError(f"assertion `left == right` failed: {name}.len() == weights.len()")
+
+
+def sgd_step_fq(ctx: GpuContext, w_latent: torch.Tensor, grad: torch.Tensor, lr: float, weight_decay: float = 0.0,
+                weights: BitLinearWeights | None = None, guard: int = _ffi.AB_GUARD_INV_ZERO,
+                sum_abs: torch.Tensor | None = None):
+    """w -= lr * (g + weight_decay * w) in place (sgd_update, src/qwen35_backward.rs:386-390), the f64 sum of |w_new| as a
+    by-product and, with `weights`, the codes rebuilt from ONE further read of the updated tensor."""
+    _chk_flat(w_latent, "w_latent")
+    _chk_flat(grad, "grad", w_latent.numel())
+    _ffi.check(_ffi.load().ab_sgd_step_fq(ctx.handle, _dp(w_latent), _dp(grad), w_latent.numel(), float(lr), float(weight_decay),
+                                          weights.handle if weights is not None else None, guard, _dp(sum_abs)), ctx.handle)
+
+
+def adamw_step_fq(ctx: GpuContext, w_latent: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, lr: float,
+                  step: int, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
+                  weights: BitLinearWeights | None = None, guard: int = _ffi.AB_GUARD_INV_ZERO,
+                  sum_abs: torch.Tensor | None = None, bias_corrections: tuple[float, float] | None = None):
+    """One AdamW step in place on (w_latent, m, v) (apply_adam, src/bin/train_qat_70b.rs:2215-2241; the fused_adamw
+    kernel, src/cuda_matmul.rs:815-839), fused with the quantiser's |w| sum like sgd_step_fq.  The bias corrections
+    1 - beta^step are formed in f32 as the reference forms them unless given."""
+    import numpy as np
+    n = w_latent.numel()
+    _chk_flat(w_latent, "w_latent")
+    for t, name in ((grad, "grad"), (m, "m"), (v, "v")):
+        _chk_flat(t, name, n)
+    if bias_corrections is None:
+        bc1 = float(np.float32(1.0) - np.float32(np.float32(beta1) ** np.float32(step)))
+        bc2 = float(np.float32(1.0) - np.float32(np.float32(beta2) ** np.float32(step)))
+    else:
+        bc1, bc2 = bias_corrections
+    _ffi.check(_ffi.load().ab_adamw_step_fq(ctx.handle, _dp(w_latent), _dp(grad), _dp(m), _dp(v), n, float(lr), float(beta1),
+                                            float(beta2), float(eps), bc1, bc2, float(weight_decay),
+                                            weights.handle if weights is not None else None, guard, _dp(sum_abs)), ctx.handle)

@@ -160,7 +160,23 @@ static void launch_act_quant(ab_ctx* ctx, const T* x, size_t m, size_t k, size_t
 #undef AB_AQ
 }
 
+// f32 -> bf16, round to nearest even (the reference's Bf16::from_f32, src/mixed_precision.rs:29-39; NaN stays a quiet NaN)
+__global__ void __launch_bounds__(kThreads)
+cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
 }  // namespace
+
+int abk_cast_f32_bf16(ab_ctx* ctx, const float* src, void* dst, size_t n) {
+    if (n == 0) return AB_OK;
+    size_t blocks = (n + kThreads - 1) / kThreads;
+    if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
+    cast_f32_bf16_kernel<<<(unsigned)blocks, kThreads, 0, ctx->stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
 
 int abk_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x,
                        int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums) {

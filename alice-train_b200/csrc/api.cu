@@ -439,6 +439,38 @@ int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights* w_sha
     return abk_fq_shard_pack(ctx, w_latent_shard, w_shard, sum_abs_total_dev, n_total, fq_out, guard, want_stats);
 }
 
+static int optimizer_common(ab_ctx* ctx, float* w_latent, const float* grad, size_t n, ab_weights* w, int guard,
+                            double* sum_abs_dev) {
+    AB_REQUIRE(guard == AB_GUARD_INV_ZERO || guard == AB_GUARD_FLOOR, AB_ERR_UNSUPPORTED);
+    if (w) {
+        AB_REQUIRE(w->ctx == ctx, AB_ERR_STATE);
+        AB_REQUIRE(w->codes_fwd && w->codes_t, AB_ERR_STATE);
+        AB_REQUIRE(n == w->out * w->in, AB_ERR_SHAPE);
+    }
+    if (n) AB_REQUIRE(w_latent && grad, AB_ERR_NULL);
+    AB_REQUIRE(((reinterpret_cast<uintptr_t>(w_latent) | reinterpret_cast<uintptr_t>(grad)) & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sum_abs_dev) & 7) == 0, AB_ERR_ALIGN);
+    return AB_OK;
+}
+
+int ab_sgd_step_fq(ab_ctx* ctx, float* w_latent, const float* grad, size_t n, float lr, float weight_decay, ab_weights* w,
+                   int guard, double* sum_abs_dev) {
+    AB_TRY(bind(ctx));
+    AB_TRY(optimizer_common(ctx, w_latent, grad, n, w, guard, sum_abs_dev));
+    return abk_optimizer_step_fq(ctx, 1, w_latent, grad, nullptr, nullptr, n, lr, weight_decay, 0.f, 0.f, 0.f, 1.f, 1.f, w, guard,
+                                 sum_abs_dev);
+}
+
+int ab_adamw_step_fq(ab_ctx* ctx, float* w_latent, const float* grad, float* m, float* v, size_t n, float lr, float beta1,
+                     float beta2, float eps, float bc1, float bc2, float weight_decay, ab_weights* w, int guard,
+                     double* sum_abs_dev) {
+    AB_TRY(bind(ctx));
+    AB_TRY(optimizer_common(ctx, w_latent, grad, n, w, guard, sum_abs_dev));
+    if (n) AB_REQUIRE(m && v, AB_ERR_NULL);
+    return abk_optimizer_step_fq(ctx, 2, w_latent, grad, m, v, n, lr, weight_decay, beta1, beta2, eps, bc1, bc2, w, guard,
+                                 sum_abs_dev);
+}
+
 int ab_dp_allreduce_start(ab_ctx* ctx, float* multicast_buf, size_t n, uint32_t* flags_local, uint32_t* flags_multicast,
                           int rank, int world, uint32_t epoch, int ctas) {
     AB_TRY(bind(ctx));
@@ -834,6 +866,63 @@ int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed
     return st;
 }
 
+// Host-slice forms of the three dense products of the reference's CudaMatmul (f32 slices in and out, blocking): the
+// operands are rounded to bf16 on the device (round to nearest even), the products run on the tensor cores with f32
+// accumulation, the results come back as f32.
+static int h2d_as_bf16(ab_ctx* ctx, int slot_f32, int slot_bf16, const float* host, size_t n, void** dev_bf16) {
+    void* d32 = nullptr;
+    AB_TRY(h2d(ctx, slot_f32, host, n * 4, &d32));
+    AB_TRY(ab_ctx_stage(ctx, slot_bf16, n * 2 + 16, dev_bf16));
+    return abk_cast_f32_bf16(ctx, (const float*)d32, *dev_bf16, n);
+}
+
+int ab_matmul_bt_host(ab_ctx* ctx, const float* a, size_t a_len, const ab_weights* w, float* c, size_t c_len, size_t m) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_fwd, AB_ERR_STATE);
+    AB_REQUIRE(a_len == m * w->in && c_len == m * w->out, AB_ERR_SHAPE);
+    if (c_len == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (a_len) AB_REQUIRE(a, AB_ERR_NULL);
+    void *da = nullptr, *dc = nullptr;
+    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
+    AB_TRY(ab_ctx_stage(ctx, 2, c_len * 4, &dc));
+    AB_TRY(abk_gemm_fwd_bf16(ctx, w, da, w->in, m, dc, AB_F32, w->out, 0.0f));
+    return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
+int ab_matmul_nn_host(ab_ctx* ctx, const float* a, size_t a_len, const ab_weights* w, float* c, size_t c_len, size_t m) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_t, AB_ERR_STATE);
+    AB_REQUIRE(a_len == m * w->out && c_len == m * w->in, AB_ERR_SHAPE);
+    if (c_len == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (a_len) AB_REQUIRE(a, AB_ERR_NULL);
+    void *da = nullptr, *dc = nullptr;
+    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
+    AB_TRY(ab_ctx_stage(ctx, 2, c_len * 4, &dc));
+    AB_TRY(abk_gemm_dx(ctx, w, da, w->out, m, dc, AB_F32, w->in, 0.0f));
+    return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
+int ab_matmul_tn_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                      size_t m, size_t k, size_t n) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(a_len == m * k && b_len == m * n && c_len == k * n, AB_ERR_SHAPE);
+    AB_REQUIRE(k < (1ull << 31) && n < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (c_len == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (m) AB_REQUIRE(a && b, AB_ERR_NULL);
+    void *da = nullptr, *db = nullptr, *dc = nullptr;
+    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
+    AB_TRY(h2d_as_bf16(ctx, 2, 3, b, b_len, &db));
+    AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
+    if (m == 0) AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
+    else AB_TRY(abk_gemm_dw(ctx, da, k, db, n, m, k, n, (float*)dc, n, 0.0f));
+    return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
 // ------------------------------------------------------------------------------- batched
 int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x, int8_t* xq,
                       size_t ld_xq, float* scales, int32_t* rowsums) {
@@ -853,6 +942,18 @@ int ab_bitlinear_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t 
     AB_REQUIRE(ld_xq >= w->in && ld_y >= w->out, AB_ERR_SHAPE);
     if (m && w->out) AB_REQUIRE(xq && scales && y, AB_ERR_NULL);
     return abk_gemm_fwd(ctx, w, xq, ld_xq, scales, rowsums, m, y, y_dtype, ld_y, acc_out);
+}
+
+int ab_bitlinear_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x_bf16, size_t ld_x, size_t m, void* y, int y_dtype,
+                          size_t ld_y, float beta) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    AB_REQUIRE(w->codes_fwd, AB_ERR_STATE);
+    AB_REQUIRE(y_dtype == AB_F32 || y_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(beta == 0.0f || beta == 1.0f, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_x >= w->in && ld_y >= w->out, AB_ERR_SHAPE);
+    if (m && w->out) AB_REQUIRE(x_bf16 && y, AB_ERR_NULL);
+    return abk_gemm_fwd_bf16(ctx, w, x_bf16, ld_x, m, y, y_dtype, ld_y, beta);
 }
 
 int ab_bitlinear_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx,

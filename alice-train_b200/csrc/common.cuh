@@ -128,6 +128,9 @@ int abk_fq_shard_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, const d
 int abk_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n, float temperature,
                                 float alpha, float** scale_dev, double** stats_dev);
 int abk_rebuild_operand_copies(ab_ctx* ctx, ab_weights* w);
+int abk_optimizer_step_fq(ab_ctx* ctx, int optimizer, float* w_latent, const float* grad, float* m, float* v, size_t n,
+                          float lr, float wd, float beta1, float beta2, float eps, float bc1, float bc2, ab_weights* w,
+                          int guard, double* sum_abs_dev);
 int abk_codes_from_ternary(ab_ctx* ctx, ab_weights* w, const int8_t* vals_dev);
 int abk_codes_from_bitplanes(ab_ctx* ctx, ab_weights* w, const uint32_t* plus_dev,
                              const uint32_t* minus_dev);
@@ -145,6 +148,8 @@ int abk_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n,
 // act_quant.cu
 int abk_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x,
                        int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
+
+int abk_cast_f32_bf16(ab_ctx* ctx, const float* src, void* dst_bf16, size_t n);
 
 // matvec.cu
 int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* y);
@@ -173,6 +178,8 @@ int abk_gemm_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_x
                  const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out);
 int abk_gemm_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx,
                 int dx_dtype, size_t ld_dx, float beta);
+int abk_gemm_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                      size_t ld_y, float beta);
 int abk_gemm_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m,
                 size_t out, size_t in, float* dW, size_t ld_dw, float beta);
 
@@ -184,6 +191,8 @@ int abk_simt_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_x
                  size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out);
 int abk_simt_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx,
                 int dx_dtype, size_t ld_dx, float beta);
+int abk_simt_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                      size_t ld_y, float beta);
 int abk_simt_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m,
                 size_t out, size_t in, float* dW, size_t ld_dw, float beta);
 

@@ -37,6 +37,22 @@ __global__ void simt_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch,
     store_out(y, y_dtype, t * ld_y + j, v);
 }
 
+__global__ void simt_fwd_bf16_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
+                                     const float* __restrict__ gamma, const __nv_bfloat16* __restrict__ x, size_t ld_x,
+                                     size_t m, void* y, int y_dtype, size_t ld_y, float beta) {
+    size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (j >= out || t >= m) return;
+    float acc = 0.0f;
+    for (size_t k = 0; k < in; ++k) {
+        int c = code_val(codes, pitch, j, k);
+        float a = __bfloat162float(x[t * ld_x + k]);
+        acc += c > 0 ? a : (c < 0 ? -a : 0.0f);
+    }
+    float v = __fmul_rn(acc, *gamma);
+    if (beta != 0.0f) v = __fadd_rn(v, load_out(y, y_dtype, t * ld_y + j));
+    store_out(y, y_dtype, t * ld_y + j, v);
+}
+
 __global__ void simt_dx_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, size_t in,
                                const float* __restrict__ gamma, const __nv_bfloat16* __restrict__ dy,
                                size_t ld_dy, size_t m, void* dx, int dx_dtype, size_t ld_dx, float beta) {
@@ -74,6 +90,17 @@ int abk_simt_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_x
     dim3 grid((unsigned)((w->out + 127) / 128), (unsigned)m);
     simt_fwd_kernel<<<grid, 128, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, w->gamma_dev, xq, ld_xq,
                                                   scales, m, y, y_dtype, ld_y, acc_out);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_simt_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                      size_t ld_y, float beta) {
+    if (m == 0 || w->out == 0) return AB_OK;
+    if (m > 65535) return AB_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)((w->out + 127) / 128), (unsigned)m);
+    simt_fwd_bf16_kernel<<<grid, 128, 0, ctx->stream>>>(w->codes, w->pitch, w->out, w->in, w->gamma_dev,
+                                                       (const __nv_bfloat16*)x, ld_x, m, y, y_dtype, ld_y, beta);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }

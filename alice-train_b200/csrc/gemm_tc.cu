@@ -58,6 +58,8 @@ int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy,
                  size_t ld_dx, float beta);
 int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,
                  float* dW, size_t ld_dw, float beta);
+int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                       size_t ld_y, float beta);
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -69,6 +71,14 @@ int abk_gemm_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_x
     if (w->in == 0 || !aligned16(xq) || ld_xq % 16 != 0 || !rowsums)
         return abk_simt_fwd(ctx, w, xq, ld_xq, scales, m, y, y_dtype, ld_y, acc_out);
     return abk_gemm2_fwd(ctx, w, xq, ld_xq, scales, rowsums, m, y, y_dtype, ld_y, acc_out);
+}
+
+int abk_gemm_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                      size_t ld_y, float beta) {
+    if (m == 0 || w->out == 0) return AB_OK;
+    if (w->in == 0 || !aligned16(x) || ld_x % 8 != 0)
+        return abk_simt_fwd_bf16(ctx, w, x, ld_x, m, y, y_dtype, ld_y, beta);
+    return abk_gemm2_fwd_bf16(ctx, w, x, ld_x, m, y, y_dtype, ld_y, beta);
 }
 
 int abk_gemm_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx, int dx_dtype,

@@ -771,6 +771,24 @@ int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy,
     return tc2::launch<tc::DX>(ctx, ta, tb, p);
 }
 
+// y = (beta * y +) gamma * x . codes^T with bf16 activations and f32 accumulation: the same kernel as dx (bf16 A operand
+// through TMA, ternary B operand expanded to bf16 in shared memory), fed with the forward copy of the codes, whose rows are
+// output features and whose in-group layout is the one the expander expects.
+int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
+                       size_t ld_y, float beta) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, w->in, m, ld_x * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_fwd, w->pitch, w->out, w->pitch, 16, 128,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)m; p.N = (int)w->out; p.K = (int)w->in;
+    p.gamma = w->gamma_dev; p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.beta = beta;
+    p.n_fast = 1;
+    return tc2::launch<tc::DX>(ctx, ta, tb, p);
+}
+
 int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,
                  float* dW, size_t ld_dw, float beta) {
     CUtensorMap ta, tb;

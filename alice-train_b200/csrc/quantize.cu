@@ -53,10 +53,44 @@ __host__ __device__ __forceinline__ float key_float(unsigned int k) {
 // Every block writes one f64 partial; the last block to finish adds the partials in block
 // order, derives gamma / inv_gamma under the requested guard and clears the counters that
 // pass B accumulates into.  The result does not depend on scheduling.
+//
+// The same kernel also carries the optimizer step that precedes the quantiser in a training loop: with OPT != 0 every
+// element is first updated in place (SGD with weight decay, src/qwen35_backward.rs:386-390; AdamW, the fused_adamw
+// kernel src/cuda_matmul.rs:815-839 and its CPU form src/bin/train_qat_70b.rs:2231-2241) and |w| is taken of the NEW
+// value, so the update pass already yields the next step's gamma and the quantiser that follows reads the weights once.
+// Thread-to-element mapping, summation order and block count are those of the plain reduction, so the sum (and gamma)
+// is bit-identical to what the two-pass quantiser would compute on the updated tensor.
+enum { OPT_NONE = 0, OPT_SGD = 1, OPT_ADAMW = 2 };
+struct OptArgs {
+    const float* grad;
+    float* m;
+    float* v;
+    float lr, wd, beta1, beta2, eps, bc1, bc2;
+};
+
+template <int OPT>
+__device__ __forceinline__ float opt_update(float w, size_t i, const OptArgs& o) {
+    if (OPT == OPT_SGD) {
+        // w -= lr * (g + wd * w)
+        return __fsub_rn(w, __fmul_rn(o.lr, __fadd_rn(o.grad[i], __fmul_rn(o.wd, w))));
+    } else if (OPT == OPT_ADAMW) {
+        const float g = o.grad[i];
+        const float mi = __fadd_rn(__fmul_rn(o.beta1, o.m[i]), __fmul_rn(__fsub_rn(1.0f, o.beta1), g));
+        const float vi = __fadd_rn(__fmul_rn(o.beta2, o.v[i]), __fmul_rn(__fmul_rn(__fsub_rn(1.0f, o.beta2), g), g));
+        o.m[i] = mi;
+        o.v[i] = vi;
+        const float m_hat = __fdiv_rn(mi, o.bc1), v_hat = __fdiv_rn(vi, o.bc2);
+        const float step = __fadd_rn(__fdiv_rn(m_hat, __fadd_rn(__fsqrt_rn(v_hat), o.eps)), __fmul_rn(o.wd, w));
+        return __fsub_rn(w, __fmul_rn(o.lr, step));
+    }
+    return w;
+}
+
+template <int OPT>
 __global__ void __launch_bounds__(kThreads)
-absmean_reduce_kernel(const float* __restrict__ w, size_t n, double* __restrict__ partials,
+absmean_reduce_kernel(float* __restrict__ w, size_t n, double* __restrict__ partials,
                       ab_fq_dev_report* __restrict__ rep, float* __restrict__ gamma_out, int guard,
-                      int keep_when_empty) {
+                      int keep_when_empty, OptArgs opt) {
     __shared__ double sm[32];
     __shared__ bool is_last;
     double acc = 0.0;
@@ -64,17 +98,32 @@ absmean_reduce_kernel(const float* __restrict__ w, size_t n, double* __restrict_
     size_t stride = (size_t)gridDim.x * blockDim.x;
     if ((reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         size_t n4 = n / 4;
-        const float4* w4 = reinterpret_cast<const float4*>(w);
+        float4* w4 = reinterpret_cast<float4*>(w);
         for (size_t i = tid; i < n4; i += stride) {
-            float4 v = __ldg(w4 + i);
+            float4 v = OPT == OPT_NONE ? __ldg(w4 + i) : w4[i];
+            if (OPT != OPT_NONE) {
+                v.x = opt_update<OPT>(v.x, 4 * i, opt);
+                v.y = opt_update<OPT>(v.y, 4 * i + 1, opt);
+                v.z = opt_update<OPT>(v.z, 4 * i + 2, opt);
+                v.w = opt_update<OPT>(v.w, 4 * i + 3, opt);
+                w4[i] = v;
+            }
             acc += (double)fabsf(v.x);
             acc += (double)fabsf(v.y);
             acc += (double)fabsf(v.z);
             acc += (double)fabsf(v.w);
         }
-        for (size_t i = n4 * 4 + tid; i < n; i += stride) acc += (double)fabsf(w[i]);
+        for (size_t i = n4 * 4 + tid; i < n; i += stride) {
+            float v = w[i];
+            if (OPT != OPT_NONE) { v = opt_update<OPT>(v, i, opt); w[i] = v; }
+            acc += (double)fabsf(v);
+        }
     } else {
-        for (size_t i = tid; i < n; i += stride) acc += (double)fabsf(w[i]);
+        for (size_t i = tid; i < n; i += stride) {
+            float v = w[i];
+            if (OPT != OPT_NONE) { v = opt_update<OPT>(v, i, opt); w[i] = v; }
+            acc += (double)fabsf(v);
+        }
     }
     double bs = block_sum(acc, sm);
     if (threadIdx.x == 0) {
@@ -600,7 +649,7 @@ static unsigned int transpose_grid(const ab_weights* w) {
 }
 
 static int reduce_launch(ab_ctx* ctx, const float* w, size_t n, ab_fq_dev_report* rep, float* gamma_out,
-                         int guard, int keep_when_empty) {
+                         int guard, int keep_when_empty, int optimizer = OPT_NONE, const OptArgs* opt = nullptr) {
     // a few resident blocks per SM keep enough 128-bit loads in flight to saturate HBM
     unsigned int blocks = (unsigned int)(ctx->sm_count * 8);
     size_t need = (n / 4 + kThreads - 1) / kThreads;
@@ -608,8 +657,14 @@ static int reduce_launch(ab_ctx* ctx, const float* w, size_t n, ab_fq_dev_report
     void* part = nullptr;
     int st = ab_ctx_scratch(ctx, sizeof(double) * blocks, &part);
     if (st) return st;
-    absmean_reduce_kernel<<<blocks, kThreads, 0, ctx->stream>>>(w, n, (double*)part, rep, gamma_out,
-                                                                guard, keep_when_empty);
+    float* wm = const_cast<float*>(w);   // written only by the optimizer forms
+    const OptArgs none{};
+    if (optimizer == OPT_SGD)
+        absmean_reduce_kernel<OPT_SGD><<<blocks, kThreads, 0, ctx->stream>>>(wm, n, (double*)part, rep, gamma_out, guard, keep_when_empty, *opt);
+    else if (optimizer == OPT_ADAMW)
+        absmean_reduce_kernel<OPT_ADAMW><<<blocks, kThreads, 0, ctx->stream>>>(wm, n, (double*)part, rep, gamma_out, guard, keep_when_empty, *opt);
+    else
+        absmean_reduce_kernel<OPT_NONE><<<blocks, kThreads, 0, ctx->stream>>>(wm, n, (double*)part, rep, gamma_out, guard, keep_when_empty, none);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }
@@ -702,6 +757,35 @@ static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float*
     }
     w->has_data = true;
     w->has_report = true;
+    return AB_OK;
+}
+
+// Optimizer step on the latent weights fused with the |w| reduction of the quantiser that follows.  With a handle the
+// codes are rebuilt as well (pack pass: ONE read of the updated weights); without one only the update runs and the sum
+// of |w_new| is left in `sum_abs_dev` for a caller that combines shards.
+int abk_optimizer_step_fq(ab_ctx* ctx, int optimizer, float* w_latent, const float* grad, float* m, float* v, size_t n,
+                          float lr, float wd, float beta1, float beta2, float eps, float bc1, float bc2, ab_weights* w,
+                          int guard, double* sum_abs_dev) {
+    OptArgs o{};
+    o.grad = grad; o.m = m; o.v = v; o.lr = lr; o.wd = wd; o.beta1 = beta1; o.beta2 = beta2; o.eps = eps; o.bc1 = bc1; o.bc2 = bc2;
+    ab_fq_dev_report* rep = nullptr;
+    float* gamma_out = nullptr;
+    if (w) {
+        rep = w->report_dev;
+        gamma_out = w->gamma_dev;
+    } else {
+        void* r = nullptr;
+        int st = ab_ctx_stage(ctx, 5, sizeof(ab_fq_dev_report), &r);
+        if (st) return st;
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(r, 0, sizeof(ab_fq_dev_report), ctx->stream));
+        rep = static_cast<ab_fq_dev_report*>(r);
+        gamma_out = &rep->w_max;   // scratch float
+    }
+    int st = reduce_launch(ctx, w_latent, n, rep, gamma_out, guard, 0, optimizer == 1 ? OPT_SGD : OPT_ADAMW, &o);
+    if (st) return st;
+    if (sum_abs_dev)
+        AB_CUDA_CHECK(ctx, cudaMemcpyAsync(sum_abs_dev, &rep->sum_abs, sizeof(double), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (w) return pack_launch(ctx, w_latent, w, nullptr, 0);
     return AB_OK;
 }
 

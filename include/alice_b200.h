@@ -173,6 +173,23 @@ AB_API int ab_fq_shard_pack(ab_ctx* ctx, const float* w_latent_shard, ab_weights
  * `stats4_out` (f64 sums of |w - w_out|, w*w_out, w*w, w_out*w_out; may be NULL) are host memory.  Blocks. */
 AB_API int ab_fq_merge_quantize_alpha(ab_ctx* ctx, const float* base, const float* delta, float* w_out, size_t n,
                                       float temperature, float alpha, float* scale_out, double* stats4_out);
+/* The optimizer step on the latent weights, fused with the quantiser that follows it in a training loop.  One pass
+ * updates `w_latent` in place AND sums |w_new| in f64 (same summation order as ab_fq_absmean_pack, so gamma comes out
+ * bit-identical to quantising the updated tensor from scratch); with a handle `w` (n = out * in) the codes are then
+ * rebuilt by the pack pass alone, i.e. the quantiser reads the weights ONCE instead of twice.  `w` may be NULL (update
+ * only); `sum_abs_dev` (device double, may be NULL) receives the sum of |w_new| for callers that combine shards with
+ * ab_fq_shard_pack.  Device pointers, asynchronous.
+ *   ab_sgd_step_fq    w -= lr * (g + weight_decay * w)                          sgd_update, src/qwen35_backward.rs:386-390
+ *   ab_adamw_step_fq  m = b1 m + (1-b1) g; v = b2 v + (1-b2) g g; w -= lr * ((m/bc1) / (sqrt(v/bc2) + eps) + weight_decay * w)
+ *                     with bc1 = 1 - b1^t, bc2 = 1 - b2^t formed by the caller: the fused_adamw kernel
+ *                     (src/cuda_matmul.rs:815-839) and apply_adam (src/bin/train_qat_70b.rs:2215-2241).
+ * Every operation is a separately rounded f32 operation in the order written, as in the reference's CPU code. */
+AB_API int ab_sgd_step_fq(ab_ctx* ctx, float* w_latent, const float* grad, size_t n, float lr, float weight_decay,
+                          ab_weights* w, int guard, double* sum_abs_dev);
+AB_API int ab_adamw_step_fq(ab_ctx* ctx, float* w_latent, const float* grad, float* m, float* v, size_t n, float lr,
+                            float beta1, float beta2, float eps, float bc1, float bc2, float weight_decay, ab_weights* w,
+                            int guard, double* sum_abs_dev);
+
 /* Waits for the stream and copies the report of the last ab_fq_absmean_pack on `w`. */
 AB_API int ab_weights_fq_report(ab_weights* w, ab_fq_report* report);
 
@@ -269,6 +286,31 @@ AB_API int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, 
 AB_API int ab_bitlinear_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq,
                             const float* scales, const int32_t* rowsums, size_t m, void* y,
                             int y_dtype, size_t ld_y, int32_t* acc_out);
+
+/* (2c) y[m x out] = beta*y + gamma * x[m x in] . codes^T with bf16 activations and f32 accumulation: the forward WITHOUT
+ * activation quantisation, i.e. the product the reference itself forms on fake-quantised weights, C = A B^T
+ * (matmul_bt, src/llama_forward.rs:43-55; tiled blas_matmul_bt, src/blas.rs:71-109,161-198; CudaMatmul::matmul_bt and
+ * its _with_gpu_b / _inplace forms, src/cuda_matmul.rs:1149-1199,1262-1318,1516-1575; GpuMatmul::matmul_bt,
+ * src/gpu_matmul.rs:405-535).  Products bf16 x {-1,0,1} are exact; the result differs from the reference's f32 chain
+ * on the same (bf16-representable) inputs only in summation order.  beta is 0 or 1. */
+AB_API int ab_bitlinear_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x_bf16, size_t ld_x, size_t m, void* y,
+                                 int y_dtype, size_t ld_y, float beta);
+
+/* Host-slice forms of the reference's three dense products, f32 slices in and out (blocking).  Operands are rounded to
+ * bf16 on the device, the products run on the tensor cores with f32 accumulation; against the reference's f32 results
+ * they hold the bf16 tolerance (1e-2 of the largest output).
+ *   ab_matmul_bt_host  C[m x out] = A[m x in] . W^T   CudaMatmul::matmul_bt_with_gpu_b (src/cuda_matmul.rs:1262-1318), with
+ *                      the handle in the place of the uploaded weight (upload_weight, src/cuda_matmul.rs:1136-1145);
+ *                      blas_matmul_bt (src/blas.rs:71-109)
+ *   ab_matmul_nn_host  C[m x in]  = A[m x out] . W    CudaMatmul::matmul_nn_with_gpu_b (src/cuda_matmul.rs:1459-1513);
+ *                      blas_matmul_nn (src/blas.rs:114-156)
+ *   ab_matmul_tn_host  C[k x n]   = A[m x k]^T . B[m x n]   CudaMatmul::matmul_tn (src/cuda_matmul.rs:1640-1699): dense
+ *                      bf16 x bf16, no weight handle (dW = dY^T X with A = dY, B = X)
+ * W is the handle's gamma * codes.  Lengths are checked as the reference's slices are (AB_ERR_SHAPE). */
+AB_API int ab_matmul_bt_host(ab_ctx* ctx, const float* a, size_t a_len, const ab_weights* w, float* c, size_t c_len, size_t m);
+AB_API int ab_matmul_nn_host(ab_ctx* ctx, const float* a, size_t a_len, const ab_weights* w, float* c, size_t c_len, size_t m);
+AB_API int ab_matmul_tn_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                             size_t m, size_t k, size_t n);
 
 /* (3) dx[m x in] = beta*dx + gamma * dy[m x out] . codes, dy bf16, f32 accumulation.
  * Replaces CudaMatmul::matmul_nn / matmul_nn_with_gpu_b / matmul_nn_inplace

@@ -76,6 +76,42 @@ def test_forward_accumulators_bit_exact(env, orc, m, out, inn):
     h.close()
 
 
+@pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 256, 128), (100, 300, 272), (1, 256, 4096), (130, 8, 48),
+                                       (257, 1000, 2000), (4, 4, 4), (3, 5, 7), (512, 32, 4096), (1024, 14336, 4096)])
+def test_forward_bf16_vs_matmul_bt_oracle(env, orc, m, out, inn):
+    """The forward without activation quantisation, C = A B^T on fake-quantised weights: against orc_matmul_bt
+    (src/llama_forward.rs:43-55, an fmaf chain in ascending k) on bf16-rounded x, 1e-5 of the largest output; the
+    largest shape against a seeded sample of single-output chains."""
+    at, bl, ctx, torch = env
+    h, g, codes = _weights(env, orc, out, inn, 45)
+    x = normal_f32(46, (m, inn))
+    xt, xr = to_bf16_tensor(orc, x, "cuda")
+    y32 = bl.bitlinear_fwd_bf16(h, xt, dtype=torch.float32)
+    y16 = bl.bitlinear_fwd_bf16(h, xt, dtype=torch.bfloat16)
+    ctx.sync()
+    wq = codes.astype(np.float32) * np.float32(g)
+    got = y32.cpu().numpy()
+    if m * out * inn <= 2 ** 31:
+        ref = orc.matmul_bt(xr, wq, m, out, inn)
+        e32, e16 = rel_err(got, ref), rel_err(y16.float().cpu().numpy(), ref)
+        print(f"[fwd bf16] {m}x{out}x{inn}: rel err f32 {e32:.2e}, bf16 {e16:.2e}")
+        assert e32 <= RTOL_F32 and e16 <= RTOL_BF16
+        base = normal_f32(47, (m, out))
+        acc = torch.from_numpy(base.copy()).cuda()
+        bl.bitlinear_fwd_bf16(h, xt, y=acc, beta=1.0)    # accumulate form, as ternary_matmul_bt's C += (src/blas.rs:455)
+        ctx.sync()
+        assert rel_err(acc.cpu().numpy(), ref + base) <= RTOL_F32
+    else:
+        r = rng(48)
+        ts, js = r.integers(0, m, 300), r.integers(0, out, 300)
+        ref = np.array([orc.matmul_bt(xr[t:t + 1], wq[j:j + 1], 1, 1, inn)[0, 0] for t, j in zip(ts, js)], np.float32)
+        scale = float(np.abs(got).max())
+        err = float(np.abs(got[ts, js].astype(np.float64) - ref).max()) / scale
+        print(f"[fwd bf16] {m}x{out}x{inn}: 300 sampled outputs, rel err {err:.2e}")
+        assert err <= RTOL_F32
+    h.close()
+
+
 @pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 64, 256), (100, 304, 264), (1, 4096, 256),
                                        (130, 48, 8), (257, 2000, 1000), (4, 4, 4), (3, 7, 5)])
 def test_dx_vs_oracle(env, orc, m, out, inn):
@@ -231,3 +267,48 @@ def test_bitlinear_step_host(env, orc, queued):
     assert torch.equal(y_h.cuda(), y_ref) and torch.equal(dx_h.cuda(), dx_ref)
     assert rel_err(dw.cpu().numpy(), 2 * dw_ref.cpu().numpy()) <= 1e-6
     h.close()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 256, 512), (5, 24, 40), (3, 7, 9), (128, 1024, 2048)])
+def test_cuda_matmul_call_sites(env, orc, m, n, k):
+    """CudaMatmul::{matmul_bt, matmul_nn, matmul_tn} and blas_matmul_bt / blas_matmul_nn with the reference's slice
+    signatures (src/cuda_matmul.rs:1149-1699, src/blas.rs:71,114): f32 slices in, f32 out, weights given as a
+    fake-quantised f32 matrix.  Operands are rounded to bf16 on the way in: 1e-2 of the largest output against the f32
+    oracle on the unrounded inputs, 1e-5 against the oracle on bf16-rounded inputs."""
+    at, bl, ctx, torch = env
+    cuda = at.CudaMatmul(ctx)
+    w_lat = normal_f32(70, (n, k), 0.02)
+    g, wq = orc.fq_vec(w_lat)
+    wq = wq.reshape(n, k)
+    a, dy = normal_f32(71, (m, k)), normal_f32(72, (m, n), 1e-2)
+    ar, dyr = orc.bf16_bits_to_f32(orc.bf16_round(a)), orc.bf16_bits_to_f32(orc.bf16_round(dy))
+    y = cuda.matmul_bt(a, wq, m, n, k).reshape(m, n)
+    assert rel_err(y, orc.matmul_bt(a, wq, m, n, k)) <= RTOL_BF16
+    assert rel_err(y, orc.matmul_bt(ar, wq, m, n, k)) <= RTOL_F32
+    dx = cuda.matmul_nn(dy, wq, m, k, n).reshape(m, k)          # C[m x k'] = A[m x n] . B[n x k']: the reference's (m, n, k) = (rows, cols, inner)
+    ref_dx, ref_dw = orc.matmul_bt_backward(dyr, ar, wq, m, n, k)
+    assert rel_err(dx, ref_dx) <= RTOL_F32
+    dw = cuda.matmul_tn(dy, a, m, k, n).reshape(n, k)           # C[n x k'] = A[m x n]^T . B[m x k']
+    assert rel_err(dw, ref_dw) <= RTOL_F32
+    full_dx, full_dw = orc.matmul_bt_backward(dy, a, wq, m, n, k)
+    assert rel_err(dx, full_dx) <= RTOL_BF16 and rel_err(dw, full_dw) <= RTOL_BF16
+    # the free functions behind the process-wide instance, destination passing
+    at.set_default_context(ctx)
+    c = np.zeros(m * n, np.float32)
+    at.blas_matmul_bt(a, wq, c, m, n, k)
+    assert np.array_equal(c.reshape(m, n), y)
+    c2 = np.zeros(m * k, np.float32)
+    at.blas_matmul_nn(dy, wq, c2, m, k, n)
+    assert np.array_equal(c2.reshape(m, k), dx)
+    with pytest.raises(AssertionError, match="assertion"):
+        cuda.matmul_bt(a[:-1], wq, m, n, k)
+    with pytest.raises(ValueError, match="ternary"):
+        cuda.upload_weight(w_lat, n, k)
+    eng = at.GpuBackwardEngine(ctx)
+    tw = cuda.upload_weight(wq, n, k)
+    gi = np.zeros(k, np.float32)
+    eng.ternary_matvec_backward(dy[0], tw, gi)
+    codes = np.sign(wq).astype(np.int8)
+    ow = orc.TernaryWeightKernel.from_ternary(codes.reshape(-1), n, k)
+    assert rel_err(gi, orc.ternary_matvec_backward(dy[0], ow)) <= RTOL_F32
+    tw.close()

@@ -1,5 +1,7 @@
 """The library's in-switch exchanges (all-reduce of dW, all-gather and bf16 reduce-scatter of the row-sharded layer;
-ab_switch_exchange_start / ab_dp_allreduce_wait) on two GPUs, one process per GPU, against NCCL on the same buffers.  Needs two GPUs of one NVSwitch domain; skipped otherwise."""
+ab_switch_exchange_start / ab_dp_allreduce_wait) on every GPU of the box (2, 4 or 8), one process per GPU, against NCCL
+on the same buffers, and the data-parallel QAT step over a small decoder with its own exchange checks.  Needs at least
+two GPUs of one NVSwitch domain; skipped otherwise."""
 import os
 import socket
 
@@ -97,17 +99,41 @@ def _worker(rank, world, port, q):
             want_rs = total[t0:t0 + tokens // world].float()
             rs_err = max(rs_err, float((mine.float() - want_rs).abs().max() / want_rs.abs().max()))
             rs_diff += int((mine.float() != want_rs).sum())
-        q.put((rank, "ok", worst, exact, err_gemm, ok_gather, rs_err, rs_diff))
+        # the whole-decoder step (ab_qat_linear_steps) with dW of every linear summed in the switch: its self-check
+        # (integer pattern bit-exact, real gradients against NCCL) and two steps against a run without exchange
+        from alice_train import decoder_step as ds
+        tokens_step, layers, std, guard = ds.MODELS["llama-tiny"]()
+        plan = ds.DataParallelQatStep(ctx, layers, tokens_step // world, dev, weight_std=std, guard=guard, exchange="switch")
+        plan.step()
+        ctx.sync()
+        chk = plan.check_exchange()
+        plan.resync_epochs()
+        plan.step()
+        plan.step()
+        ctx.sync()
+        summed = [w.clone() for w in plan.dW]
+        for s_ in plan._steps:
+            s_.dw_multicast = None
+        plan.step()
+        ctx.sync()
+        dec_err = 0.0
+        for a, b in zip(summed, plan.dW):
+            ref = b.clone()
+            dist.all_reduce(ref)
+            dec_err = max(dec_err, float((a - ref).abs().max() / ref.abs().max()))
+        plan.close()
+        q.put((rank, "ok", worst, exact, err_gemm, ok_gather, rs_err, rs_diff, chk, dec_err))
     finally:
         dist.destroy_process_group()
 
 
-def test_switch_allreduce_matches_nccl_world2():
+def test_switch_exchanges_match_nccl_on_all_gpus():
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    world, port = 2, _free_port()
+    world = 8 if torch.cuda.device_count() >= 8 else (4 if torch.cuda.device_count() >= 4 else 2)
+    port = _free_port()
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     procs = [mpc.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
@@ -118,9 +144,14 @@ def test_switch_allreduce_matches_nccl_world2():
         p.join(timeout=60)
     if any(r[1] == "skip" for r in res):
         pytest.skip(res[0][2])
-    for rank, _, worst, exact, err_gemm, ok_gather, rs_err, rs_diff in res:
-        assert exact and worst == 0.0, (rank, worst)       # a + b in f32 does not depend on who adds
+    for rank, _, worst, exact, err_gemm, ok_gather, rs_err, rs_diff, chk, dec_err in res:
+        if world == 2:
+            assert exact and worst == 0.0, (rank, worst)   # a + b in f32 does not depend on who adds
+        else:
+            assert worst <= 1e-6, (rank, worst)            # more than two addends: the switch and NCCL add in different orders
         assert err_gemm <= 1e-6, (rank, err_gemm)
+        assert chk["integer_pattern"] == "bit-exact" and chk["checked"] >= 14 and chk["vs_nccl_max_rel_diff"] <= 1e-6, (rank, chk)
+        assert dec_err <= 1e-6, (rank, dec_err)
         assert ok_gather, rank
         print(f"rank {rank}: bf16 reduce-scatter rel err {rs_err:.2e}, {rs_diff} elements differ from f32-accumulate-then-round")
         assert rs_err <= 1e-2, (rank, rs_err, rs_diff)      # the stated bf16 tolerance; the switch rounds its own way
