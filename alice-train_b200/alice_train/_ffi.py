@@ -94,6 +94,10 @@ SIGNATURES = {
     "ab_ste_weight_grad_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz]),
     "ab_ternary_matmul_bt_host": (_i, [_vp, _vp, _vp, _f, _vp, _sz, _sz, _sz]),
     "ab_act_quant_int8": (_i, [_vp, _vp, _i, _sz, _sz, _sz, _vp, _sz, _vp, _vp]),
+    "ab_rmsnorm_act_quant": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _sz, _f, _vp, _i, _sz, _vp, _sz, _vp, _vp]),
+    "ab_swiglu_act_quant": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _sz, _vp, _i, _sz, _vp, _sz, _vp, _vp]),
+    "ab_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f]),
+    "ab_swiglu_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
     "ab_bitlinear_fwd": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _i, _sz, _vp]),
     "ab_matmul_bt_host": (_i, [_vp, _vp, _sz, _vp, _vp, _sz, _sz]),
     "ab_matmul_nn_host": (_i, [_vp, _vp, _sz, _vp, _vp, _sz, _sz]),

@@ -212,3 +212,65 @@ def adamw_step_fq(ctx: GpuContext, w_latent: torch.Tensor, grad: torch.Tensor, m
     _ffi.check(_ffi.load().ab_adamw_step_fq(ctx.handle, _dp(w_latent), _dp(grad), _dp(m), _dp(v), n, float(lr), float(beta1),
                                             float(beta2), float(eps), bc1, bc2, float(weight_decay),
                                             weights.handle if weights is not None else None, guard, _dp(sum_abs)), ctx.handle)
+
+
+def rmsnorm_act_quant(ctx: GpuContext, x: torch.Tensor, weight: torch.Tensor, eps: float, y: torch.Tensor | None = None,
+                      out: QuantizedActivations | None = None, quantize: bool = True):
+    """RMSNorm of every token row (src/llama_forward.rs:78-86) and, in the same pass, the per-token int8 quantisation of
+    the normalised row.  Returns (y or None, QuantizedActivations or None)."""
+    _chk2d(x, "x")
+    m, k = x.shape
+    if weight.dtype != torch.float32 or weight.numel() != k:
+        raise AssertionError("assertion `left == right` failed: weight.len() == dim")
+    if quantize and out is None:
+        out = QuantizedActivations(torch.empty((m, k), dtype=torch.int8, device=x.device),
+                                   torch.empty(m, dtype=torch.float32, device=x.device),
+                                   torch.empty(m, dtype=torch.int32, device=x.device))
+    if y is not None:
+        _chk2d(y, "y")
+    _ffi.check(_ffi.load().ab_rmsnorm_act_quant(
+        ctx.handle, _dp(x), _dt(x), _dp(weight), m, k, x.stride(0), float(eps), _dp(y), _dt(y) if y is not None else _ffi.AB_F32,
+        y.stride(0) if y is not None else k, _dp(out.xq) if out else None, out.xq.stride(0) if out else k,
+        _dp(out.scales) if out else None, _dp(out.rowsums) if out else None), ctx.handle)
+    return y, out
+
+
+def swiglu_act_quant(ctx: GpuContext, gate: torch.Tensor, up: torch.Tensor, inter: torch.Tensor | None = None,
+                     out: QuantizedActivations | None = None, quantize: bool = True):
+    """silu(gate) * up (src/cuda_matmul.rs:684-696) and, in the same pass, its per-token int8 quantisation: the input of
+    the down projection.  Returns (inter or None, QuantizedActivations or None)."""
+    _chk2d(gate, "gate"); _chk2d(up, "up")
+    if gate.shape != up.shape or gate.dtype != up.dtype or gate.stride(0) != up.stride(0):
+        raise AssertionError("assertion `left == right` failed: gate and up have the same shape, type and pitch")
+    m, n = gate.shape
+    if quantize and out is None:
+        out = QuantizedActivations(torch.empty((m, n), dtype=torch.int8, device=gate.device),
+                                   torch.empty(m, dtype=torch.float32, device=gate.device),
+                                   torch.empty(m, dtype=torch.int32, device=gate.device))
+    if inter is not None:
+        _chk2d(inter, "inter")
+    _ffi.check(_ffi.load().ab_swiglu_act_quant(
+        ctx.handle, _dp(gate), _dp(up), _dt(gate), m, n, gate.stride(0), _dp(inter), _dt(inter) if inter is not None else _ffi.AB_F32,
+        inter.stride(0) if inter is not None else n, _dp(out.xq) if out else None, out.xq.stride(0) if out else n,
+        _dp(out.scales) if out else None, _dp(out.rowsums) if out else None), ctx.handle)
+    return inter, out
+
+
+def rmsnorm_backward(ctx: GpuContext, d_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
+                     d_input: torch.Tensor, d_weight: torch.Tensor | None = None):
+    """rmsnorm_backward (src/llama_backward.rs:149-210): d_input and d_weight accumulate.  f32, contiguous [m x dim]."""
+    m, dim = x.shape
+    for t_, name in ((d_output, "d_output"), (x, "input"), (d_input, "d_input")):
+        _chk_flat(t_, name, m * dim)
+    _ffi.check(_ffi.load().ab_rmsnorm_backward(ctx.handle, _dp(d_output), _dp(x), _dp(weight), _dp(d_input), _dp(d_weight), m, dim,
+                                               float(eps)), ctx.handle)
+
+
+def swiglu_backward(ctx: GpuContext, d_inter: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, d_gate: torch.Tensor,
+                    d_up: torch.Tensor, gate_silu: torch.Tensor | None = None):
+    """SwiGLU backward with the reference's fast_sigmoid (src/cuda_matmul.rs:4135-4147).  f32, same number of elements."""
+    n = gate.numel()
+    for t_, name in ((d_inter, "d_inter"), (gate, "gate"), (up, "up"), (d_gate, "d_gate"), (d_up, "d_up")):
+        _chk_flat(t_, name, n)
+    _ffi.check(_ffi.load().ab_swiglu_backward(ctx.handle, _dp(d_inter), _dp(gate), _dp(up), _dp(gate_silu), _dp(d_gate), _dp(d_up), n),
+               ctx.handle)

@@ -94,6 +94,12 @@ public:
     std::vector<uint32_t> minus_bits() const { return planes().second; }
     ab_weights* handle() const { return h_.get(); }
     const GpuContext& context() const { return ctx_; }
+    void set_gamma(float g) const { ctx_.check(ab_weights_set_gamma(h_.get(), g)); }
+    float gamma() const {
+        float g = 0.0f;
+        ctx_.check(ab_weights_get_gamma(h_.get(), &g));
+        return g;
+    }
 
 private:
     TernaryWeightKernel(size_t out, size_t in, const GpuContext& ctx) : ctx_(ctx) {
@@ -299,6 +305,84 @@ inline std::vector<float> dequantize(const std::vector<uint8_t>& packed, size_t 
     for (size_t i = 0; i < count; ++i) out[i] = static_cast<float>(t[i]) * scale;
     return out;
 }
+
+// ------------------------------------------------------------------------------ CudaMatmul
+// The reference multiplies host f32 slices by a dense f32 matrix that holds FAKE-QUANTISED values (-g, 0, +g); here the
+// weight side is a ternary handle (upload_weight, src/cuda_matmul.rs:1136-1145) and the products run on the tensor cores
+// with operands rounded to bf16.  Argument order as in the reference: (m, n, k).
+class CudaMatmul {  // src/cuda_matmul.rs:919-1969
+public:
+    explicit CudaMatmul(const GpuContext& ctx = GpuContext::global()) : ctx_(ctx) {}   // CudaMatmul::new, :953
+    TernaryWeightKernel upload_weight(const std::vector<float>& w, size_t out_features, size_t in_features) const {
+        if (w.size() != out_features * in_features) throw AssertionError("weights.len() == out * in");
+        float g = 0.0f;
+        for (float v : w) g = std::fabs(v) > g ? std::fabs(v) : g;
+        std::vector<int8_t> codes(w.size(), 0);
+        for (size_t i = 0; i < w.size(); ++i) {
+            if (w[i] == g && g > 0.0f) codes[i] = 1;
+            else if (w[i] == -g && g > 0.0f) codes[i] = -1;
+            else if (w[i] != 0.0f) throw std::invalid_argument("upload_weight: the matrix is not ternary-valued");
+        }
+        auto h = TernaryWeightKernel::from_ternary(codes, out_features, in_features, ctx_);
+        h.set_gamma(g > 0.0f ? g : 1.0f);
+        return h;
+    }
+    // C[m x n] = A[m x k] . B[n x k]^T   (src/cuda_matmul.rs:1149-1199, 1262-1318)
+    void matmul_bt_with_gpu_b(const std::vector<float>& a, const TernaryWeightKernel& b, std::vector<float>& c, size_t m, size_t n, size_t k) const {
+        if (n != b.out_features() || k != b.in_features() || a.size() < m * k || c.size() < m * n) throw AssertionError("a is m x k, b is n x k, c is m x n");
+        shape(ab_matmul_bt_host(ctx_.handle(), a.data(), m * k, b.handle(), c.data(), m * n, m));
+    }
+    std::vector<float> matmul_bt(const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k) const {
+        std::vector<float> c(m * n);
+        matmul_bt_with_gpu_b(a, upload_weight(b, n, k), c, m, n, k);
+        return c;
+    }
+    // C[m x n] = A[m x k] . B[k x n]   (src/cuda_matmul.rs:1204-1258, 1459-1513)
+    void matmul_nn_with_gpu_b(const std::vector<float>& a, const TernaryWeightKernel& b, std::vector<float>& c, size_t m, size_t n, size_t k) const {
+        if (k != b.out_features() || n != b.in_features() || a.size() < m * k || c.size() < m * n) throw AssertionError("a is m x k, b is k x n, c is m x n");
+        shape(ab_matmul_nn_host(ctx_.handle(), a.data(), m * k, b.handle(), c.data(), m * n, m));
+    }
+    std::vector<float> matmul_nn(const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k) const {
+        std::vector<float> c(m * n);
+        matmul_nn_with_gpu_b(a, upload_weight(b, k, n), c, m, n, k);
+        return c;
+    }
+    // C[k x n] = A[m x k]^T . B[m x n]   (src/cuda_matmul.rs:1640-1699)
+    std::vector<float> matmul_tn(const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k) const {
+        if (a.size() < m * k || b.size() < m * n) throw AssertionError("a is m x k, b is m x n");
+        std::vector<float> c(k * n);
+        shape(ab_matmul_tn_host(ctx_.handle(), a.data(), m * k, b.data(), m * n, c.data(), k * n, m, k, n));
+        return c;
+    }
+
+private:
+    void shape(int st) const {
+        if (st == AB_ERR_SHAPE) throw AssertionError("slice lengths");
+        ctx_.check(st);
+    }
+    GpuContext ctx_;
+};
+
+// blas_matmul_bt / blas_matmul_nn (src/blas.rs:71,114): destination passing, process-wide instance
+inline void blas_matmul_bt(const std::vector<float>& a, const std::vector<float>& b, std::vector<float>& c, size_t m, size_t n, size_t k) {
+    c = CudaMatmul().matmul_bt(a, b, m, n, k);
+}
+inline void blas_matmul_nn(const std::vector<float>& a, const std::vector<float>& b, std::vector<float>& c, size_t m, size_t n, size_t k) {
+    c = CudaMatmul().matmul_nn(a, b, m, n, k);
+}
+
+// GpuBackwardEngine::new(&GpuContext) + ternary_matvec_backward(&self, ...)   (src/gpu_backward.rs:59,170-175)
+class GpuBackwardEngine {
+public:
+    explicit GpuBackwardEngine(const GpuContext& ctx) : ctx_(ctx) {}
+    void ternary_matvec_backward(const std::vector<float>& grad_output, const TernaryWeightKernel& weights,
+                                 std::vector<float>& grad_input) const {
+        alice_train::ternary_matvec_backward(grad_output, weights, grad_input);
+    }
+
+private:
+    GpuContext ctx_;
+};
 
 namespace blas {
 // C[m x n] += scale * A[m x k] . B^T with B as 2-bit codes, row stride ceil(k/4).  src/blas.rs:403-457

@@ -933,6 +933,40 @@ int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t 
     return abk_act_quant_int8(ctx, x, x_dtype, m, k, ld_x, xq, ld_xq, scales, rowsums);
 }
 
+int ab_rmsnorm_act_quant(ab_ctx* ctx, const void* x, int x_dtype, const float* weight, size_t m, size_t dim, size_t ld_x, float eps,
+                         void* y, int y_dtype, size_t ld_y, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE((x_dtype == AB_F32 || x_dtype == AB_BF16) && (y_dtype == AB_F32 || y_dtype == AB_BF16), AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_x >= dim && (!y || ld_y >= dim) && (!xq || ld_xq >= dim), AB_ERR_SHAPE);
+    if (m && dim) AB_REQUIRE(x && weight && (y || xq), AB_ERR_NULL);
+    if (xq && m) AB_REQUIRE(scales, AB_ERR_NULL);
+    return abk_rmsnorm_act_quant(ctx, x, x_dtype, weight, m, dim, ld_x, eps, y, y_dtype, ld_y, xq, ld_xq, scales, rowsums);
+}
+
+int ab_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtype, size_t m, size_t n, size_t ld, void* inter,
+                        int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE((dtype == AB_F32 || dtype == AB_BF16) && (inter_dtype == AB_F32 || inter_dtype == AB_BF16), AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld >= n && (!inter || ld_inter >= n) && (!xq || ld_xq >= n), AB_ERR_SHAPE);
+    if (m && n) AB_REQUIRE(gate && up && (inter || xq), AB_ERR_NULL);
+    if (xq && m) AB_REQUIRE(scales, AB_ERR_NULL);
+    return abk_swiglu_act_quant(ctx, gate, up, dtype, m, n, ld, inter, inter_dtype, ld_inter, xq, ld_xq, scales, rowsums);
+}
+
+int ab_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
+                        float* d_weight, size_t m, size_t dim, float eps) {
+    AB_TRY(bind(ctx));
+    if (m && dim) AB_REQUIRE(d_output && input && weight && d_input, AB_ERR_NULL);
+    return abk_rmsnorm_backward(ctx, d_output, input, weight, d_input, d_weight, m, dim, eps);
+}
+
+int ab_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, const float* up, const float* gate_silu,
+                       float* d_gate, float* d_up, size_t n) {
+    AB_TRY(bind(ctx));
+    if (n) AB_REQUIRE(d_inter && gate && up && d_gate && d_up, AB_ERR_NULL);
+    return abk_swiglu_backward(ctx, d_inter, gate, up, gate_silu, d_gate, d_up, n);
+}
+
 int ab_bitlinear_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
                      const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {
     AB_TRY(bind(ctx));

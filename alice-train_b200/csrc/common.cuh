@@ -149,6 +149,15 @@ int abk_calibration_stats(ab_ctx* ctx, const float* w, const float* q, size_t n,
 int abk_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x,
                        int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
 
+// norm_act.cu
+int abk_rmsnorm_act_quant(ab_ctx* ctx, const void* x, int x_dtype, const float* weight, size_t m, size_t dim, size_t ld_x, float eps,
+                          void* y, int y_dtype, size_t ld_y, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
+int abk_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtype, size_t m, size_t n, size_t ld, void* inter,
+                         int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
+int abk_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
+                         float* d_weight, size_t m, size_t dim, float eps);
+int abk_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, const float* up, const float* gate_silu,
+                        float* d_gate, float* d_up, size_t n);
 int abk_cast_f32_bf16(ab_ctx* ctx, const float* src, void* dst_bf16, size_t n);
 
 // matvec.cu

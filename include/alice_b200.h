@@ -277,6 +277,29 @@ AB_API int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t*
 AB_API int ab_act_quant_int8(ab_ctx* ctx, const void* x, int x_dtype, size_t m, size_t k, size_t ld_x,
                              int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
 
+/* The steps on either side of the linears, fused with (2a) so that an activation is read once.  Device pointers.
+ *   ab_rmsnorm_act_quant   RMSNorm of every token row, rmsnorm (src/llama_forward.rs:78-86): f64 sum of squares,
+ *                          inv_rms = 1.0f / (float)sqrt(ss/dim + eps), v *= inv_rms * weight[d]; the normalised row goes
+ *                          to `y` (f32 or bf16, may be NULL) and/or, quantised exactly as ab_act_quant_int8 would quantise
+ *                          the f32 values, to xq / scales / rowsums (xq may be NULL): the input of q/k/v and gate/up.
+ *   ab_swiglu_act_quant    out = g / (1 + expf(-g)) * up, swiglu_elementwise_kernel (src/cuda_matmul.rs:684-696), to
+ *                          `inter` (may be NULL) and/or quantised per token: the input of the down projection.
+ *   ab_rmsnorm_backward    rmsnorm_backward (src/llama_backward.rs:149-210), f32; d_input and d_weight ACCUMULATE;
+ *                          d_weight may be NULL.  Its sums over tokens are added in a fixed order.
+ *   ab_swiglu_backward     d_up = d * silu(gate), d_gate = d * up * sig (1 + gate (1 - sig)) with the reference's
+ *                          fast_sigmoid (src/cuda_matmul.rs:4135-4147, src/fast_math.rs:11-23); `gate_silu` is the cached
+ *                          silu(gate) of the forward or NULL (recomputed).  Flat f32 tensors of n elements. */
+AB_API int ab_rmsnorm_act_quant(ab_ctx* ctx, const void* x, int x_dtype, const float* weight, size_t m, size_t dim, size_t ld_x,
+                                float eps, void* y, int y_dtype, size_t ld_y, int8_t* xq, size_t ld_xq, float* scales,
+                                int32_t* rowsums);
+AB_API int ab_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtype, size_t m, size_t n, size_t ld,
+                               void* inter, int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales,
+                               int32_t* rowsums);
+AB_API int ab_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
+                               float* d_weight, size_t m, size_t dim, float eps);
+AB_API int ab_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, const float* up, const float* gate_silu,
+                              float* d_gate, float* d_up, size_t n);
+
 /* (2b) y[m x out] = ((float)acc * (s_t/127)) * gamma with acc = xq . codes^T in s32 (exact).
  * `acc_out` (s32 [m x out], pitch out) may be NULL.  Stands where the reference runs
  * CudaMatmul::matmul_bt / matmul_bt_with_gpu_b / matmul_bt_inplace / gemm_gpu_bt

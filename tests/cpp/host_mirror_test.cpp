@@ -243,6 +243,48 @@ static void export_cases() {
     }
 }
 
+// CudaMatmul::{matmul_bt, matmul_nn, matmul_tn}, blas_matmul_bt / blas_matmul_nn and GpuBackwardEngine with the reference's
+// slice signatures (src/cuda_matmul.rs:1149-1699, src/blas.rs:71,114, src/gpu_backward.rs:59,170-175).  Small integers
+// are exact in bf16, so the results are compared exactly; the loose tolerance mirrors the reference's own GEMM checks
+// (src/cuda_matmul.rs:4436-4516).
+static void cuda_matmul_cases() {
+    const size_t m = 3, n = 4, k = 5;
+    const float g = 0.5f;
+    std::vector<float> a(m * k), dy(m * n), w(n * k);
+    for (size_t i = 0; i < a.size(); ++i) a[i] = float(int(i * 7 % 11) - 5);
+    for (size_t i = 0; i < dy.size(); ++i) dy[i] = float(int(i * 5 % 7) - 3);
+    for (size_t i = 0; i < w.size(); ++i) w[i] = g * float(int(i * 5 % 3) - 1);   // values in {-g, 0, +g}
+    std::vector<float> y_want(m * n, 0.f), dx_want(m * k, 0.f), dw_want(n * k, 0.f);
+    for (size_t i = 0; i < m; ++i)
+        for (size_t j = 0; j < n; ++j)
+            for (size_t p = 0; p < k; ++p) {
+                y_want[i * n + j] += a[i * k + p] * w[j * k + p];
+                dx_want[i * k + p] += dy[i * n + j] * w[j * k + p];
+                dw_want[j * k + p] += dy[i * n + j] * a[i * k + p];
+            }
+    CudaMatmul cuda;
+    expect(close_to(cuda.matmul_bt(a, w, m, n, k), y_want, 1e-6f), "src/cuda_matmul.rs:1149-1199", "matmul_bt");
+    expect(close_to(cuda.matmul_nn(dy, w, m, k, n), dx_want, 1e-6f), "src/cuda_matmul.rs:1204-1258", "matmul_nn");
+    expect(close_to(cuda.matmul_tn(dy, a, m, k, n), dw_want, 1e-6f), "src/cuda_matmul.rs:1640-1699", "matmul_tn");
+    std::vector<float> c;
+    blas_matmul_bt(a, w, c, m, n, k);
+    expect(close_to(c, y_want, 1e-6f), "src/blas.rs:71-109", "blas_matmul_bt");
+    blas_matmul_nn(dy, w, c, m, k, n);
+    expect(close_to(c, dx_want, 1e-6f), "src/blas.rs:114-156", "blas_matmul_nn");
+    bool threw = false;
+    try {
+        cuda.matmul_bt(a, w, m + 1, n, k);
+    } catch (const AssertionError&) {
+        threw = true;
+    }
+    expect(threw, "src/cuda_matmul.rs:1161", "matmul_bt with a short slice");
+    GpuBackwardEngine eng(GpuContext::global());
+    auto tw = TernaryWeightKernel::from_ternary({1, -1, 0, 1}, 2, 2);
+    std::vector<float> gi(2, 9.f);
+    eng.ternary_matvec_backward({1.f, 1.f}, tw, gi);
+    expect(close_to(gi, {1.f, 0.f}, 1e-6f), "src/gpu_backward.rs:327-345", "GpuBackwardEngine::ternary_matvec_backward");
+}
+
 int main(int argc, char** argv) {
     if (argc > 1 && std::strcmp(argv[1], "--no-device") == 0) {
         auto c = GpuContext::new_blocking(0);
@@ -266,6 +308,7 @@ int main(int argc, char** argv) {
         mismatch_cases();
         qat_cases();
         export_cases();
+        cuda_matmul_cases();
     } catch (const std::exception& e) {
         std::printf("unexpected exception: %s\n", e.what());
         return 3;
