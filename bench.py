@@ -984,7 +984,7 @@ def run_native(args):
                 line = {"metric": "batch-1 ternary kernels, achieved HBM GB/s", "value": dom["gbs"], "unit": "GB/s", "n_gpus": 1,
                         "higher_is_better": True, "data": "synthetic", "dtype": "f32 x 2-bit codes", "config": {"workload": "hbm-kernels"},
                         "roofline": {"bound": "hbm", "kernel": "matvec kernel (dx = W^T dy, integer path)", "achieved": dom["gbs"],
-                                     "peak": blk["peak_gbs"], "unit": "GB/s", "frac": dom["frac"], "traffic": None,
+                                     "peak": blk["peak_gbs"], "unit": "GB/s", "frac": dom["frac"], "traffic": dram_traffic("matvec", "hbm-kernels"),
                                      "peak_source": blk["peak_source"]}, "block": blk}
         else:
             line = run_main(env, args)
