@@ -88,6 +88,7 @@ SIGNATURES = {
     "ab_bitlinear_backward": (_i, [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp]),
     "ab_ste_weight_grad": (_i, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "ab_ternary_matmul_bt": (_i, [_vp, _vp, _vp, _f, _vp, _sz]),
+    "ab_ternary_swiglu_ffn": (_i, [_vp, _vp, _vp, _f, _vp, _f, _vp, _f, _vp, _vp, _vp, _sz]),
     "ab_ternary_matvec_host": (_i, [_vp, _vp, _vp, _sz, _vp, _sz]),
     "ab_ternary_matvec_backward_host": (_i, [_vp, _vp, _vp, _sz, _vp, _sz]),
     "ab_bitlinear_backward_host": (_i, [_vp, _vp, _vp, _sz, _vp, _sz, _i, _f, _vp, _sz, _vp, _sz]),

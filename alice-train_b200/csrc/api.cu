@@ -749,6 +749,27 @@ int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float
     return abk_ternary_matmul_bt(ctx, a, w, scale, c, m);
 }
 
+int ab_ternary_swiglu_ffn(ab_ctx* ctx, const float* input, const ab_weights* gate, float gate_scale, const ab_weights* up,
+                          float up_scale, const ab_weights* down, float down_scale, float* output, float* gate_buf,
+                          float* up_buf, size_t seq_len) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, gate));
+    AB_TRY(check_w(ctx, up));
+    AB_TRY(check_w(ctx, down));
+    const size_t hidden = gate->in, inter = gate->out;
+    AB_REQUIRE(up->in == hidden && up->out == inter && down->in == inter && down->out == hidden, AB_ERR_SHAPE);
+    if (seq_len == 0) return AB_OK;
+    if (hidden) AB_REQUIRE(input && output, AB_ERR_NULL);
+    if (inter) AB_REQUIRE(gate_buf && up_buf, AB_ERR_NULL);
+    AB_CUDA_CHECK(ctx, cudaMemsetAsync(gate_buf, 0, seq_len * inter * sizeof(float), ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemsetAsync(up_buf, 0, seq_len * inter * sizeof(float), ctx->stream));
+    AB_CUDA_CHECK(ctx, cudaMemsetAsync(output, 0, seq_len * hidden * sizeof(float), ctx->stream));
+    AB_TRY(abk_ternary_matmul_bt(ctx, input, gate, gate_scale, gate_buf, seq_len));
+    AB_TRY(abk_ternary_matmul_bt(ctx, input, up, up_scale, up_buf, seq_len));
+    AB_TRY(abk_silu_mul_inplace(ctx, gate_buf, up_buf, seq_len * inter));
+    return abk_ternary_matmul_bt(ctx, gate_buf, down, down_scale, output, seq_len);
+}
+
 // The host-slice forms stand in for the reference's CPU functions one to one, so they add in f32 as those do unless
 // the caller has opted into the integer path for them as well.
 struct HostMatvecArithmetic {

@@ -156,6 +156,7 @@ int abk_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtyp
                          int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
 int abk_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
                          float* d_weight, size_t m, size_t dim, float eps);
+int abk_silu_mul_inplace(ab_ctx* ctx, float* gate, const float* up, size_t n);
 int abk_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, const float* up, const float* gate_silu,
                         float* d_gate, float* d_up, size_t n);
 int abk_cast_f32_bf16(ab_ctx* ctx, const float* src, void* dst_bf16, size_t n);

@@ -340,6 +340,15 @@ int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* 
 
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
     if (w->out == 0 || m == 0) return AB_OK;
+    // The decode loop's shape (src/inference.rs:1305-1472 calls this with m = 1): a few rows of A against a matrix that
+    // is bandwidth bound take the tensor-core matvec row by row, each row's result scaled and added into C there.
+    if (m <= 4 && use_mma(ctx, w, false)) {
+        for (size_t i = 0; i < m; ++i) {
+            int st = abk_matvec_mma(ctx, w->codes_fwd, w->pitch, w->out, w->in, a + i * w->in, c + i * w->out, scale, 1, 1);
+            if (st) return st;
+        }
+        return AB_OK;
+    }
     // the batch index is a grid dimension (at most 65535): longer batches go out in slabs
     for (size_t m0 = 0; m0 < m; m0 += 65535) {
         const size_t mm = m - m0 < 65535 ? m - m0 : 65535;

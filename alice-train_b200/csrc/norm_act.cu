@@ -288,6 +288,16 @@ swiglu_backward_kernel(const float* __restrict__ d_inter, const float* __restric
     }
 }
 
+// In-place SiLU(gate) * up of the packed decode path (ternary_swiglu_ffn, src/blas.rs:481-485): gate <- gate / (1 + exp(-gate)) * up.
+__global__ void __launch_bounds__(kThreads)
+silu_mul_inplace_kernel(float* __restrict__ gate, const float* __restrict__ up, size_t n) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        const float g = gate[i];
+        gate[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), up[i]);
+    }
+}
+
 template <int MODE>
 int launch_row_op(ab_ctx* ctx, const void* x, const void* x2, int x_dtype, const float* w, size_t m, size_t k, size_t ld_x,
                   float eps, void* y, int y_dtype, size_t ld_y, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums) {
@@ -354,6 +364,15 @@ int abk_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, co
     size_t blocks = (n + kThreads - 1) / kThreads;
     if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
     swiglu_backward_kernel<<<(unsigned)blocks, kThreads, 0, ctx->stream>>>(d_inter, gate, up, gate_silu, d_gate, d_up, n);
+    AB_LAUNCH_CHECK(ctx);
+    return AB_OK;
+}
+
+int abk_silu_mul_inplace(ab_ctx* ctx, float* gate, const float* up, size_t n) {
+    if (n == 0) return AB_OK;
+    size_t blocks = (n + kThreads - 1) / kThreads;
+    if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
+    silu_mul_inplace_kernel<<<(unsigned)blocks, kThreads, 0, ctx->stream>>>(gate, up, n);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }

@@ -929,6 +929,111 @@ def rowshard_block(env, args, steps, warmup):
     return out
 
 
+def decode_block(env, layers=None, replays=20):
+    """Packed decode over a .alice file (src/inference.rs:1211-1490): a Qwen3.5-9B-shaped model (src/qwen35.rs:67-102) is
+    written by the library's exporter from latent weights drawn on the device, re-opened by the streaming reader, and one
+    token's linear chain (248 ternary matvecs at m = 1 for 32 layers) is replayed from a CUDA graph.  The embedding table is
+    cut to 4096 rows (it is not on the measured chain).  Bytes per token = the packed codes of every projection."""
+    torch = env.torch
+    import alice_train
+    from alice_train import bitlinear as bl, export as ex
+    dev = env.dev
+    stream = torch.cuda.Stream(device=dev)
+    prev = torch.cuda.current_stream(dev)
+    torch.cuda.set_stream(stream)
+    tmp = tempfile.NamedTemporaryFile(suffix=".alice", delete=False)
+    try:
+        ctx = alice_train.GpuContext.on_torch_stream(env.local)
+        cfg = ex.Qwen35Config.qwen35_9b()
+        cfg.vocab_size = 4096
+        if layers:
+            cfg.num_hidden_layers = layers
+            cfg.layer_types = cfg.layer_types[:layers]
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(21)
+
+        def layer_tensors():
+            for i in range(cfg.num_hidden_layers):
+                t = {}
+                for name, out, inn in cfg.projection_shapes(i):
+                    t[name] = (out, inn)
+                for name, count in cfg.fp32_shapes(i):
+                    t[name] = np.ones(count, np.float32)
+                yield t
+
+        def quantizer(shape):
+            out, inn = shape
+            w_lat = torch.randn((out, inn), generator=gen, device=dev) * 0.02
+            h = bl.BitLinearWeights(out, inn, ctx).quantize_(w_lat)
+            ctx.sync()
+            res = (h.gamma, h.to_packed())
+            h.close()
+            return res
+
+        t0 = time.time()
+        emb = np.zeros((cfg.vocab_size, cfg.hidden_size), np.float32)
+        stats = ex.export_alice_model(tmp, cfg, layer_tensors(), emb, np.ones(cfg.hidden_size, np.float32), None, 0, 0.0, ctx, quantizer)
+        tmp.flush()
+        t_write = time.time() - t0
+        t0 = time.time()
+        model = alice_train.StreamingAliceModel.from_file(tmp.name, ctx, load_embeddings=False)
+        ctx.sync()
+        t_open = time.time() - t0
+        h0 = torch.randn(cfg.hidden_size, generator=gen, device=dev)
+        h = h0.clone()
+        for _ in range(2):
+            h.copy_(h0)
+            model.decode_linears(h)
+        torch.cuda.synchronize()
+        finite = bool(torch.isfinite(h).all().item())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            model.decode_linears(h)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        sec = a.elapsed_time(b) * 1e-3 / replays
+        linears = sum(len(L["w"]) for L in model.layers)
+        nbytes = model.packed_bytes
+        # CPU: the reference's own loop (ternary_matmul_bt at m = 1, single thread) over one DeltaNet layer's projections
+        cpu = None
+        try:
+            from oracle import pyoracle as orc   # the CPU baseline leg: the only use of the oracle here
+            lay = model.layers[0]["w"]
+            r = np.random.default_rng(3)
+            t_cpu, cpu_bytes = 0.0, 0
+            for name, w in lay.items():
+                o, n = w.out_features(), w.in_features()
+                packed = w.to_packed()
+                x = r.standard_normal(n).astype(np.float32)
+                t1 = time.perf_counter()
+                orc.ternary_matmul_bt(x, packed, w.scale, np.zeros(o, np.float32), 1, o, n)
+                t_cpu += time.perf_counter() - t1
+                cpu_bytes += packed.size
+            cpu = {"tokens_per_s": 1.0 / (t_cpu * nbytes / cpu_bytes), "cores": 1, "kind": "port",
+                   "sample": f"ternary_matmul_bt at m = 1 over the 8 projections of layer 0 ({t_cpu:.2f} s), scaled to {linears} projections by bytes"}
+        except Exception as e:  # noqa: BLE001
+            cpu = {"error": f"{type(e).__name__}: {e}"[:200]}
+        model.close()
+        return {"model": "qwen35-9b shapes", "layers": cfg.num_hidden_layers, "linears": linears, "file_bytes": stats.total_bytes,
+                "packed_bytes_per_token": nbytes, "write_s": t_write, "open_s": t_open, "ms_per_token": sec * 1e3,
+                "tokens_per_s": 1.0 / sec, "gbs": nbytes / sec * 1e-9, "frac_of_hbm": nbytes / sec * 1e-9 / env.pk["hbm_gbs"],
+                "peak_gbs": env.pk["hbm_gbs"], "peak_source": f"{env.pk['source']} copy bandwidth", "timing": "cuda-graph replay of one token",
+                "finite": finite, "cpu_baseline": cpu}
+    finally:
+        torch.cuda.set_stream(prev)
+        tmp.close()
+        try:
+            os.unlink(tmp.name)
+        except OSError:
+            pass
+
+
 def guarded(env, fn, *a, **k):
     """An optional block must not cost the headline line: errors are recorded in its place."""
     try:
@@ -986,6 +1091,15 @@ def run_native(args):
                         "roofline": {"bound": "hbm", "kernel": "matvec kernel (dx = W^T dy, integer path)", "achieved": dom["gbs"],
                                      "peak": blk["peak_gbs"], "unit": "GB/s", "frac": dom["frac"], "traffic": dram_traffic("matvec", "hbm-kernels"),
                                      "peak_source": blk["peak_source"]}, "block": blk}
+        elif args.workload == "alice-decode":
+            blk = decode_block(env)
+            if env.rank == 0:
+                line = {"metric": "packed decode tokens/s over all ternary linears of a .alice model (m = 1)", "value": blk["tokens_per_s"],
+                        "unit": UNIT, "n_gpus": 1, "higher_is_better": True, "data": "synthetic", "dtype": "f32 x 2-bit codes",
+                        "config": {"workload": "alice-decode", "model": blk["model"]},
+                        "roofline": {"bound": "hbm", "kernel": "matvec_tma_kernel over the file's projections", "achieved": blk["gbs"],
+                                     "peak": blk["peak_gbs"], "unit": "GB/s", "frac": blk["frac_of_hbm"], "traffic": None,
+                                     "peak_source": blk["peak_source"]}, "cpu_baseline": blk.pop("cpu_baseline"), "block": blk}
         else:
             line = run_main(env, args)
             extras = args.workload == "llama3-8b-mlp" and not args.no_extras
@@ -1015,7 +1129,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS) + ["hbm-kernels"] + list(DECODER_WORKLOADS))
+    ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS) + ["hbm-kernels", "alice-decode"] + list(DECODER_WORKLOADS))
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens per CPU-baseline sample")
     ap.add_argument("--dw-exchange", default="switch", choices=["switch", "nccl"],
                     help="sum of dW / all-gather / reduce-scatter: the library's in-switch kernels (default) or NCCL")

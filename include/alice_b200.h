@@ -83,7 +83,8 @@ typedef struct ab_fq_report {
 AB_API int ab_ctx_create(int device, void* cuda_stream, ab_ctx** ctx);
 AB_API int ab_ctx_destroy(ab_ctx* ctx);
 /* Context options (all default 0).
- * The batch-1 entry points (ab_ternary_matvec, ab_ternary_matvec_backward, ab_bitlinear_backward) have two arithmetic
+ * The batch-1 entry points (ab_ternary_matvec, ab_ternary_matvec_backward, ab_bitlinear_backward, and ab_ternary_matmul_bt
+ * with up to four rows) have two arithmetic
  * paths.  f32: the selected elements are added in f32 as the reference's loops do (src/backward.rs:45-80): a zero
  * weight contributes nothing, so a NaN or Inf in the vector reaches only the outputs it is connected to, and rows with
  * dy_j == 0 change nothing.  Integer: for matrices of at least 64 x 512 the vector is rounded to 32-bit fixed point
@@ -254,6 +255,17 @@ AB_API int ab_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in_features, c
  * Replaces blas::ternary_matmul_bt (src/blas.rs:403-457). */
 AB_API int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale,
                                 float* c, size_t m);
+/* The packed decode step's feed-forward block, blas::ternary_swiglu_ffn (src/blas.rs:462-494), on device pointers:
+ *   gate_buf = gate_scale * input gate^T ; up_buf = up_scale * input up^T ; gate_buf = gate_buf / (1 + exp(-gate_buf)) * up_buf ;
+ *   output = down_scale * gate_buf down^T
+ * input [seq_len x hidden], gate_buf and up_buf [seq_len x intermediate], output [seq_len x hidden], all f32 and all
+ * OVERWRITTEN (the reference zero-fills the three results before it accumulates into them).  gate and up are
+ * [intermediate x hidden] handles, down is [hidden x intermediate]; the scales are passed like the reference passes
+ * them and are used instead of the handles' own gamma.  Each product is ab_ternary_matmul_bt (up to four rows on the
+ * integer matvec path unless AB_OPT_EXACT_MATVEC is set, f32 adds beyond). */
+AB_API int ab_ternary_swiglu_ffn(ab_ctx* ctx, const float* input, const ab_weights* gate, float gate_scale,
+                                 const ab_weights* up, float up_scale, const ab_weights* down, float down_scale,
+                                 float* output, float* gate_buf, float* up_buf, size_t seq_len);
 
 /* Host-slice forms with the reference's length checks (AB_ERR_SHAPE where it would panic). */
 AB_API int ab_ternary_matvec_host(ab_ctx* ctx, const ab_weights* w, const float* x, size_t x_len,

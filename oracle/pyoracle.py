@@ -421,3 +421,62 @@ def adamw_update(delta, grad, m, v, lr, beta1, beta2, eps, step, wd):
 
 def max_threads() -> int:
     return int(lib.orc_max_threads())
+
+
+# --------------------------------------------------------------- .alice files and the packed decode chain
+def ternary_swiglu_ffn(x, gate_packed, gate_scale, up_packed, up_scale, down_packed, down_scale, seq_len, hidden, inter):
+    """ternary_swiglu_ffn (src/blas.rs:462-494): three ternary_matmul_bt into zero-filled buffers around
+    gate <- gate / (1 + exp(-gate)) * up."""
+    g = ternary_matmul_bt(x, gate_packed, gate_scale, np.zeros(seq_len * inter, np.float32), seq_len, inter, hidden)
+    u = ternary_matmul_bt(x, up_packed, up_scale, np.zeros(seq_len * inter, np.float32), seq_len, inter, hidden)
+    mid = swiglu(g, u)
+    return ternary_matmul_bt(mid, down_packed, down_scale, np.zeros(seq_len * hidden, np.float32), seq_len, hidden, inter), mid
+
+
+def alice_file_bytes(header_json: bytes, projection_shapes, fp32_shapes, layers, embedding, output_norm, lm_head=None):
+    """The bytes of a .alice file after its JSON header is fixed (src/export.rs:379-425): magic, version 1, header
+    length, header, embed_tokens as bf16, output_norm as f32, lm_head as bf16 unless tied, then per layer every
+    projection as (f32 scale, flat 2-bit codes) followed by the layer's f32 tensors.  projection_shapes(i) / fp32_shapes(i)
+    give the names in file order.  Returns (bytes, [[(name, scale)] per layer])."""
+    import struct
+    out = [b"ALICEMOD", struct.pack("<I", 1), struct.pack("<Q", len(header_json)), header_json]
+    out.append(np.array([bf16_from_f32(float(v)) for v in _f32(embedding).reshape(-1)], dtype="<u2").tobytes())
+    out.append(_f32(output_norm).astype("<f4").tobytes())
+    if lm_head is not None:
+        out.append(np.array([bf16_from_f32(float(v)) for v in _f32(lm_head).reshape(-1)], dtype="<u2").tobytes())
+    scales = []
+    for i, tensors in enumerate(layers):
+        row = []
+        for name in projection_shapes(i):
+            s, _, packed = quantize_and_pack(tensors[name])
+            out.append(struct.pack("<f", s))
+            out.append(packed.tobytes())
+            row.append((name, s))
+        for name in fp32_shapes(i):
+            out.append(_f32(tensors[name]).reshape(-1).astype("<f4").tobytes())
+        scales.append(row)
+    return b"".join(out), scales
+
+
+def decode_linears(hidden, layers, eps, mix):
+    """One token through the linear chain of forward_incremental_streaming (src/inference.rs:1278-1490) with the
+    token mixer replaced by `mix(outputs, width)`.  layers[i] = {"attn": [(name, packed, scale, out, in)],
+    "out": (packed, scale, out, in), "gate"/"up"/"down": (packed, scale, out, in), "input_layernorm", "post_attn_layernorm"}."""
+    h = _f32(hidden).reshape(-1).copy()
+    n = h.size
+    for L in layers:
+        residual = h.copy()
+        x = rmsnorm(h.reshape(1, n), L["input_layernorm"], eps).reshape(-1)
+        outs = {}
+        for name, packed, scale, o, i in L["attn"]:
+            outs[name] = ternary_matmul_bt(x, packed, scale, np.zeros(o, np.float32), 1, o, i).reshape(-1)
+        packed, scale, o, i = L["out"]
+        m = _f32(mix(outs, i))
+        buf = ternary_matmul_bt(m, packed, scale, np.zeros(o, np.float32), 1, o, i).reshape(-1)
+        h = residual + buf
+        residual = h.copy()
+        x = rmsnorm(h.reshape(1, n), L["post_attn_layernorm"], eps).reshape(-1)
+        (gp, gs, inter, _), (up, us, _, _), (dp, ds, _, _) = L["gate"], L["up"], L["down"]
+        buf, _ = ternary_swiglu_ffn(x, gp, gs, up, us, dp, ds, 1, n, inter)
+        h = residual + buf.reshape(-1)
+    return h
