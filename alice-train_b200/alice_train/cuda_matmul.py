@@ -78,7 +78,15 @@ class CudaMatmul:
         return c
 
     def matmul_bt_inplace(self, a, b, c: np.ndarray, m: int, n: int, k: int):
-        w = self.upload_weight(b, n, k)
+        """B ternary-valued (a fake-quantised projection) goes through a weight handle; any other B (the output head,
+        src/bin/train_qat_70b.rs:1024-1031) through the dense product."""
+        try:
+            w = self.upload_weight(b, n, k)
+        except ValueError:
+            a, b, c = _f32(a), _f32(b), _out(c)
+            _assert_len(a.size >= m * k and b.size >= n * k and c.size >= m * n, "a.len() >= m*k, b.len() >= n*k, c.len() >= m*n")
+            _ffi.check(self._lib.ab_matmul_bt_dense_host(self.ctx.handle, _p(a), m * k, _p(b), n * k, _p(c), m * n, m, n, k), self.ctx.handle)
+            return
         try:
             self.matmul_bt_with_gpu_b(a, w, c, m, n, k)
         finally:
@@ -97,7 +105,13 @@ class CudaMatmul:
         return c
 
     def matmul_nn_inplace(self, a, b, c: np.ndarray, m: int, n: int, k: int):
-        w = self.upload_weight(b, k, n)
+        try:
+            w = self.upload_weight(b, k, n)
+        except ValueError:   # a dense B: d_hidden = d_logits . W of the output head (src/bin/train_qat_70b.rs:1094-1101)
+            a, b, c = _f32(a), _f32(b), _out(c)
+            _assert_len(a.size >= m * k and b.size >= k * n and c.size >= m * n, "a.len() >= m*k, b.len() >= k*n, c.len() >= m*n")
+            _ffi.check(self._lib.ab_matmul_nn_dense_host(self.ctx.handle, _p(a), m * k, _p(b), k * n, _p(c), m * n, m, n, k), self.ctx.handle)
+            return
         try:
             self.matmul_nn_with_gpu_b(a, w, c, m, n, k)
         finally:

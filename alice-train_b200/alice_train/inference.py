@@ -12,7 +12,9 @@ decode step runs, per layer, exactly the reference's sequence of linear operatio
     h += ternary_swiglu_ffn(x)                                    1369-1377              (src/blas.rs:462-494 + residual)
 
 ternary_matmul_bt accumulates into its result, so the two residual additions are the accumulation itself (h + sum*gamma
-is the one f32 addition the reference performs, in the same order).  The token mixer between the input projections and
+is the one f32 addition the reference performs, in the same order).  Projections that read the same vector (the
+attention inputs; gate and up) are stacked row-wise at load time into one matrix with one scale per row
+(ab_ternary_matvec_ex), so each group is one launch and no result buffer needs a zero-fill.  The token mixer between the input projections and
 the output projection (DeltaNet recurrence, softmax attention with its caches) is not part of this library: `mix` is a
 caller-supplied function of the projection outputs; the default takes the leading elements of the widest projection,
 which keeps the chain's shapes and data dependencies and nothing else.
@@ -76,6 +78,9 @@ def build_layer_index(config: export.Qwen35Config, cursor: int):
     return layers, cursor
 
 
+_ATTN_INPUTS = {"LinearAttention": ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a"), "FullAttention": ("q_proj", "k_proj", "v_proj")}
+
+
 def default_mix(outputs: dict, width: int):
     """Stand-in for the token mixer: the leading `width` elements of the widest input projection's output."""
     widest = max(outputs.values(), key=lambda t: t.numel())
@@ -89,7 +94,7 @@ class StreamingAliceModel:
         raise TypeError("use StreamingAliceModel.from_file")
 
     @classmethod
-    def from_file(cls, path, ctx: GpuContext | None = None, load_embeddings: bool = True):
+    def from_file(cls, path, ctx: GpuContext | None = None, load_embeddings: bool = True, stack: bool = True):
         import torch
         self = object.__new__(cls)
         self.ctx = ctx or default_context()
@@ -122,14 +127,25 @@ class StreamingAliceModel:
         self.layers = []
         self.packed_bytes = 0
         for L in self.layer_index:
-            W = {}
+            W, refs = {}, {}
             for r in L["packed"]:
                 scale = float(buf[r.scale_off:r.scale_off + 4].view("<f4")[0])
                 W[r.name] = TernaryWeightKernel.from_packed(buf[r.packed_off:r.end], r.out_features, r.in_features, scale, self.ctx)
                 W[r.name].scale = scale
+                refs[r.name] = r
                 self.packed_bytes += r.packed_len
             F = {r.name: torch.from_numpy(buf[r.off:r.end].view("<f4").copy()).to(dev) for r in L["fp32"]}
-            self.layers.append({"type": L["type"], "w": W, "f32": F})
+            # projections that read the same vector, stacked row-wise into one matrix with one scale per row: one launch each
+            stacked = {}
+            groups = {"in": _ATTN_INPUTS[L["type"]], "gate_up": ("gate_proj", "up_proj")}
+            for gname, names in groups.items():
+                rs = [refs[n] for n in names]
+                if stack and all(r.in_features == rs[0].in_features and r.in_features % 4 == 0 for r in rs):
+                    codes = np.concatenate([buf[r.packed_off:r.end] for r in rs])
+                    w = TernaryWeightKernel.from_packed(codes, sum(r.out_features for r in rs), rs[0].in_features, 1.0, self.ctx)
+                    row_scale = torch.cat([torch.full((r.out_features,), W[r.name].scale, dtype=torch.float32) for r in rs]).to(dev)
+                    stacked[gname] = (w, row_scale, [(r.name, r.out_features) for r in rs])
+            self.layers.append({"type": L["type"], "w": W, "f32": F, "stacked": stacked})
         self._bufs = None
         return self
 
@@ -139,6 +155,8 @@ class StreamingAliceModel:
     def close(self):
         for L in self.layers:
             for w in L["w"].values():
+                w.close()
+            for w, _, _ in L["stacked"].values():
                 w.close()
         self.layers = []
         self.mmap.close()
@@ -152,15 +170,8 @@ class StreamingAliceModel:
             dev = self.output_norm.device
             width = max(o for i in range(cfg.num_hidden_layers) for _, o, _ in cfg.projection_shapes(i))
             self._bufs = {"x": torch.empty((1, cfg.hidden_size), device=dev),
-                          "gate": torch.empty((1, cfg.intermediate_size), device=dev),
-                          "up": torch.empty((1, cfg.intermediate_size), device=dev),
-                          "inter": torch.empty((1, cfg.intermediate_size), device=dev),
-                          "proj": {}, "width": width}
+                          "inter": torch.empty((1, cfg.intermediate_size), device=dev), "proj": {}, "width": width}
         return self._bufs
-
-    def _matmul_bt(self, a, w, c):
-        _ffi.check(self._lib.ab_ternary_matmul_bt(self.ctx.handle, C.c_void_p(a.data_ptr()), w.handle, w.scale,
-                                                  C.c_void_p(c.data_ptr()), 1), self.ctx.handle)
 
     def _rmsnorm(self, h, weight, y):
         eps = self.meta.config.rms_norm_eps
@@ -168,36 +179,56 @@ class StreamingAliceModel:
                                                   1, h.numel(), h.numel(), float(eps), C.c_void_p(y.data_ptr()), _ffi.AB_F32,
                                                   y.numel(), None, y.numel(), None, None), self.ctx.handle)
 
-    def decode_linears(self, hidden, mix=default_mix):
-        """One token through every layer's linear chain, in place on `hidden` (f32 CUDA tensor of hidden_size
-        elements).  All work is queued on the context's stream; nothing is copied to the host."""
+    def _matvec(self, w, x, y, scale=1.0, row_scale=None, accumulate=False):
+        _ffi.check(self._lib.ab_ternary_matvec_ex(self.ctx.handle, w.handle, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), float(scale),
+                                                  C.c_void_p(row_scale.data_ptr()) if row_scale is not None else None, 1 if accumulate else 0),
+                   self.ctx.handle)
+
+    def _project(self, L, group, names, x, key):
+        """Outputs of the projections `names`, all of which read x: one stacked launch where the file allowed it."""
         import torch
         b = self._buffers()
+        W = L["w"]
+        if group in L["stacked"]:
+            w, row_scale, parts = L["stacked"][group]
+            if key not in b["proj"]:
+                b["proj"][key] = torch.empty(w.out_features(), device=x.device)
+            y = b["proj"][key]
+            self._matvec(w, x, y, 1.0, row_scale)
+            outs, off = {}, 0
+            for name, n in parts:
+                outs[name] = y[off:off + n]
+                off += n
+            return outs
+        outs = {}
+        for name in names:
+            k2 = key + (name,)
+            if k2 not in b["proj"]:
+                b["proj"][k2] = torch.empty(W[name].out_features(), device=x.device)
+            self._matvec(W[name], x, b["proj"][k2], W[name].scale)
+            outs[name] = b["proj"][k2]
+        return outs
+
+    def decode_linears(self, hidden, mix=default_mix):
+        """One token through every layer's linear chain, in place on `hidden` (f32 CUDA tensor of hidden_size
+        elements).  All work is queued on the context's stream; nothing is copied to the host.  Seven launches per
+        layer: two norms, the stacked input projections, the output projection, gate|up, SiLU * up, down."""
+        b = self._buffers()
         h = hidden.view(1, -1)
-        for li, L in enumerate(self.layers):
+        for L in self.layers:
             W, F = L["w"], L["f32"]
-            attn = ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a") if L["type"] == "LinearAttention" else ("q_proj", "k_proj", "v_proj")
             out_name = "out_proj" if L["type"] == "LinearAttention" else "o_proj"
             self._rmsnorm(h, F["input_layernorm"], b["x"])
-            outs = {}
-            for name in attn:
-                key = (L["type"], name)
-                if key not in b["proj"]:
-                    b["proj"][key] = torch.empty((1, W[name].out_features()), device=h.device)
-                c = b["proj"][key]
-                c.zero_()
-                self._matmul_bt(b["x"], W[name], c)
-                outs[name] = c.view(-1)
+            outs = self._project(L, "in", _ATTN_INPUTS[L["type"]], b["x"], (L["type"], "in"))
             m = mix(outs, W[out_name].in_features())
-            self._matmul_bt(m, W[out_name], h)                      # accumulates: the residual addition
+            self._matvec(W[out_name], m, h, W[out_name].scale, None, True)          # accumulates: the residual addition
             self._rmsnorm(h, F["post_attn_layernorm"], b["x"])
-            b["gate"].zero_(); b["up"].zero_()
-            self._matmul_bt(b["x"], W["gate_proj"], b["gate"])
-            self._matmul_bt(b["x"], W["up_proj"], b["up"])
-            _ffi.check(self._lib.ab_swiglu_act_quant(self.ctx.handle, C.c_void_p(b["gate"].data_ptr()), C.c_void_p(b["up"].data_ptr()),
-                                                     _ffi.AB_F32, 1, b["gate"].numel(), b["gate"].numel(), C.c_void_p(b["inter"].data_ptr()),
+            gu = self._project(L, "gate_up", ("gate_proj", "up_proj"), b["x"], ("gate_up",))
+            g, u = gu["gate_proj"].view(1, -1), gu["up_proj"].view(1, -1)
+            _ffi.check(self._lib.ab_swiglu_act_quant(self.ctx.handle, C.c_void_p(g.data_ptr()), C.c_void_p(u.data_ptr()),
+                                                     _ffi.AB_F32, 1, g.numel(), g.numel(), C.c_void_p(b["inter"].data_ptr()),
                                                      _ffi.AB_F32, b["inter"].numel(), None, b["inter"].numel(), None, None), self.ctx.handle)
-            self._matmul_bt(b["inter"], W["down_proj"], h)          # accumulates: the residual addition
+            self._matvec(W["down_proj"], b["inter"], h, W["down_proj"].scale, None, True)   # accumulates: the residual addition
         return hidden
 
     def ffn(self, layer: int, x, out=None):

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libalice_b200.so")
-SOURCES = ["api.cu", "quantize.cu", "act_quant.cu", "norm_act.cu", "matvec.cu", "matvec_mma.cu", "matvec_tma.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu", "dp_allreduce.cu"]
+SOURCES = ["api.cu", "quantize.cu", "act_quant.cu", "norm_act.cu", "lm_head.cu", "matvec.cu", "matvec_mma.cu", "matvec_tma.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu", "dp_allreduce.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

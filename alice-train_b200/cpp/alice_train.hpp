@@ -332,9 +332,15 @@ public:
         if (n != b.out_features() || k != b.in_features() || a.size() < m * k || c.size() < m * n) throw AssertionError("a is m x k, b is n x k, c is m x n");
         shape(ab_matmul_bt_host(ctx_.handle(), a.data(), m * k, b.handle(), c.data(), m * n, m));
     }
+    // a dense B (the unquantised output head, src/bin/train_qat_70b.rs:1024-1031) takes the dense product
     std::vector<float> matmul_bt(const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k) const {
         std::vector<float> c(m * n);
-        matmul_bt_with_gpu_b(a, upload_weight(b, n, k), c, m, n, k);
+        try {
+            matmul_bt_with_gpu_b(a, upload_weight(b, n, k), c, m, n, k);
+        } catch (const std::invalid_argument&) {
+            if (a.size() < m * k || b.size() < n * k) throw AssertionError("a is m x k, b is n x k");
+            shape(ab_matmul_bt_dense_host(ctx_.handle(), a.data(), m * k, b.data(), n * k, c.data(), m * n, m, n, k));
+        }
         return c;
     }
     // C[m x n] = A[m x k] . B[k x n]   (src/cuda_matmul.rs:1204-1258, 1459-1513)
@@ -344,7 +350,12 @@ public:
     }
     std::vector<float> matmul_nn(const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k) const {
         std::vector<float> c(m * n);
-        matmul_nn_with_gpu_b(a, upload_weight(b, k, n), c, m, n, k);
+        try {
+            matmul_nn_with_gpu_b(a, upload_weight(b, k, n), c, m, n, k);
+        } catch (const std::invalid_argument&) {   // d_hidden = d_logits . W of the output head (src/bin/train_qat_70b.rs:1094-1101)
+            if (a.size() < m * k || b.size() < k * n) throw AssertionError("a is m x k, b is k x n");
+            shape(ab_matmul_nn_dense_host(ctx_.handle(), a.data(), m * k, b.data(), k * n, c.data(), m * n, m, n, k));
+        }
         return c;
     }
     // C[k x n] = A[m x k]^T . B[m x n]   (src/cuda_matmul.rs:1640-1699)

@@ -749,6 +749,15 @@ int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float
     return abk_ternary_matmul_bt(ctx, a, w, scale, c, m);
 }
 
+int ab_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale, const float* row_scale,
+                         int accumulate) {
+    AB_TRY(bind(ctx));
+    AB_TRY(check_w(ctx, w));
+    if (w->out) AB_REQUIRE(y, AB_ERR_NULL);
+    if (w->out * w->in) AB_REQUIRE(x, AB_ERR_NULL);
+    return abk_ternary_matvec_ex(ctx, w, x, y, scale, row_scale, accumulate ? 1 : 0);
+}
+
 int ab_ternary_swiglu_ffn(ab_ctx* ctx, const float* input, const ab_weights* gate, float gate_scale, const ab_weights* up,
                           float up_scale, const ab_weights* down, float down_scale, float* output, float* gate_buf,
                           float* up_buf, size_t seq_len) {
@@ -941,6 +950,110 @@ int ab_matmul_tn_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b,
     AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
     if (m == 0) AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
     else AB_TRY(abk_gemm_dw(ctx, da, k, db, n, m, k, n, (float*)dc, n, 0.0f));
+    return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
+// ------------------------------------------------------------------------------- output head (dense, unquantised)
+int ab_transpose_bf16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(ld_in >= cols && ld_out >= rows, AB_ERR_SHAPE);
+    if (rows * cols) AB_REQUIRE(in && out, AB_ERR_NULL);
+    return abk_transpose16(ctx, in, rows, cols, ld_in, out, ld_out);
+}
+
+int ab_cross_entropy(ab_ctx* ctx, const void* logits, int logits_dtype, size_t ld, const uint32_t* targets, size_t m, size_t vocab,
+                     float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(logits_dtype == AB_F32 || logits_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld >= vocab && (!d_logits || ld_d >= vocab) && (!d_logits_t || ld_t >= m), AB_ERR_SHAPE);
+    if (m * vocab) AB_REQUIRE(logits && targets, AB_ERR_NULL);
+    return abk_cross_entropy(ctx, logits, logits_dtype, ld, targets, m, vocab, d_scale, loss, d_logits, ld_d, d_logits_t, ld_t);
+}
+
+int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w_t, size_t ld_wt, size_t m, size_t hidden, size_t vocab,
+                      float* logits, size_t ld_logits) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(ld_h >= hidden && ld_wt >= vocab && ld_logits >= vocab, AB_ERR_SHAPE);
+    AB_REQUIRE(m < (1ull << 31) && hidden < (1ull << 31) && vocab < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (m * vocab == 0) return AB_OK;
+    AB_REQUIRE(logits, AB_ERR_NULL);
+    if (hidden) AB_REQUIRE(h && w_t, AB_ERR_NULL);
+    // the pair GEMM contracts over the row index of both operands: h goes in transposed ([hidden x m], pitch padded to 8)
+    const size_t ld_ht = ab_round_up(m, 8);
+    void* ht = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 12, (hidden ? hidden : 1) * ld_ht * 2 + 16, &ht));
+    AB_TRY(abk_transpose16(ctx, h, m, hidden, ld_h, ht, ld_ht));
+    return abk_gemm_dw(ctx, ht, ld_ht, w_t, ld_wt, hidden, m, vocab, logits, ld_logits, 0.0f);
+}
+
+int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* d_logits_t, size_t ld_t, const void* w, size_t ld_w,
+                        const void* h, size_t ld_h, size_t m, size_t hidden, size_t vocab, float* d_hidden, size_t ld_dh, float* dW,
+                        size_t ld_dw, float dw_beta) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(dw_beta == 0.0f || dw_beta == 1.0f, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(m < (1ull << 31) && hidden < (1ull << 31) && vocab < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (d_hidden) {
+        AB_REQUIRE(ld_t >= m && ld_w >= hidden && ld_dh >= hidden, AB_ERR_SHAPE);
+        if (m * hidden * vocab) AB_REQUIRE(d_logits_t && w, AB_ERR_NULL);
+        // d_hidden[m x hidden] = sum_v d_logits_t[v][m] * w[v][hidden]
+        AB_TRY(abk_gemm_dw(ctx, d_logits_t, ld_t, w, ld_w, vocab, m, hidden, d_hidden, ld_dh, 0.0f));
+    }
+    if (dW) {
+        AB_REQUIRE(ld_d >= vocab && ld_h >= hidden && ld_dw >= hidden, AB_ERR_SHAPE);
+        if (m * hidden * vocab) AB_REQUIRE(d_logits && h, AB_ERR_NULL);
+        // dW[vocab x hidden] (+)= sum_t d_logits[t][vocab] * h[t][hidden]
+        AB_TRY(abk_gemm_dw(ctx, d_logits, ld_d, h, ld_h, m, vocab, hidden, dW, ld_dw, dw_beta));
+    }
+    return AB_OK;
+}
+
+// Dense host-slice products (the reference's matmul_bt_inplace / matmul_nn_inplace call sites whose B is not a ternary
+// matrix: the output head, src/bin/train_qat_70b.rs:1024-1031, 1094-1101).  f32 slices in and out, operands rounded to
+// bf16 on the device, f32 accumulation.
+int ab_matmul_bt_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                            size_t m, size_t n, size_t k) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(a_len == m * k && b_len == n * k && c_len == m * n, AB_ERR_SHAPE);
+    AB_REQUIRE(k < (1ull << 31) && n < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (c_len == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (k) AB_REQUIRE(a && b, AB_ERR_NULL);
+    void *da = nullptr, *db = nullptr, *dbt = nullptr, *dc = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
+    if (k == 0) {
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
+        return d2h_sync(ctx, c, dc, c_len * 4);
+    }
+    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
+    AB_TRY(h2d_as_bf16(ctx, 2, 3, b, b_len, &db));
+    const size_t ld_bt = ab_round_up(n, 8);
+    AB_TRY(ab_ctx_stage(ctx, 13, k * ld_bt * 2 + 16, &dbt));
+    AB_TRY(abk_transpose16(ctx, db, n, k, k, dbt, ld_bt));
+    AB_TRY(ab_lm_head_logits(ctx, da, k, dbt, ld_bt, m, k, n, (float*)dc, n));
+    return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
+int ab_matmul_nn_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                            size_t m, size_t n, size_t k) {
+    AB_TRY(bind(ctx));
+    AB_REQUIRE(a_len == m * k && b_len == k * n && c_len == m * n, AB_ERR_SHAPE);
+    AB_REQUIRE(k < (1ull << 31) && n < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
+    if (c_len == 0) return AB_OK;
+    AB_REQUIRE(c, AB_ERR_NULL);
+    if (k) AB_REQUIRE(a && b, AB_ERR_NULL);
+    void *da = nullptr, *db = nullptr, *dat = nullptr, *dc = nullptr;
+    AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
+    if (k == 0) {
+        AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
+        return d2h_sync(ctx, c, dc, c_len * 4);
+    }
+    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
+    AB_TRY(h2d_as_bf16(ctx, 2, 3, b, b_len, &db));
+    const size_t ld_at = ab_round_up(m, 8);
+    AB_TRY(ab_ctx_stage(ctx, 13, k * ld_at * 2 + 16, &dat));
+    AB_TRY(abk_transpose16(ctx, da, m, k, k, dat, ld_at));
+    // C[m x n] = sum_k at[k][m] * b[k][n]
+    AB_TRY(abk_gemm_dw(ctx, dat, ld_at, db, n, k, m, n, (float*)dc, n, 0.0f));
     return d2h_sync(ctx, c, dc, c_len * 4);
 }
 

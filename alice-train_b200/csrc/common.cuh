@@ -46,7 +46,7 @@ struct ab_ctx {
     unsigned int* counters = nullptr;
     size_t counters_len = 0;
     void* stage[16] = {};          // 0-11: two sets of six, consecutive host-buffer steps alternate between them;
-    size_t stage_bytes[16] = {};   // 12, 13: converted vectors of the streaming matvec; 14, 15: diagnostics
+    size_t stage_bytes[16] = {};   // 12, 13: transposed operands of the dense output-head products; 14, 15: diagnostics
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
     int* dev_status = nullptr;
     // copy streams + events of the host-buffer step (created on first use)
@@ -62,6 +62,7 @@ struct ab_ctx {
     bool async_host_step = false;  // AB_OPT_ASYNC_HOST_STEP
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     bool host_integer_matvec = false;  // AB_OPT_HOST_INTEGER_MATVEC: the host-slice forms may take the integer path too
+    const float* row_scale = nullptr;   // set for the duration of ab_ternary_matvec_ex: y_j is scaled by row_scale[j] instead of one scale
     uint64_t launches = 0;
     // true while the most recent kernel this context launched was a streaming matvec (kernels that never write codes):
     // the next one may then request its codes before the previous kernel has completed.  Every other launch clears it.
@@ -156,6 +157,11 @@ int abk_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtyp
                          int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
 int abk_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
                          float* d_weight, size_t m, size_t dim, float eps);
+int abk_cross_entropy(ab_ctx* ctx, const void* logits, int dtype, size_t ld, const uint32_t* targets, size_t m, size_t v,
+                      float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t);
+int abk_transpose16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out);
+int abk_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale, const float* row_scale,
+                          int accumulate);
 int abk_silu_mul_inplace(ab_ctx* ctx, float* gate, const float* up, size_t n);
 int abk_swiglu_backward(ab_ctx* ctx, const float* d_inter, const float* gate, const float* up, const float* gate_silu,
                         float* d_gate, float* d_up, size_t n);

@@ -134,12 +134,12 @@ matvec_fwd_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t out, s
 // y[b][j] (+)= scale * sum over column tiles, in tile order
 __global__ void matvec_fwd_reduce_kernel(const float* __restrict__ partial, size_t partial_stride, size_t tiles,
                                          size_t out, float* __restrict__ y, size_t y_stride, float scale,
-                                         int accumulate, int use_scale) {
+                                         int accumulate, int use_scale, const float* __restrict__ row_scale) {
     const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
     if (j >= out) return;
     float s = 0.0f;
     for (size_t t = 0; t < tiles; ++t) s += partial[(b * tiles + t) * partial_stride + j];
-    float r = use_scale ? __fmul_rn(s, scale) : s;
+    float r = use_scale ? __fmul_rn(s, row_scale ? row_scale[j] : scale) : s;
     float* dst = y + b * y_stride + j;
     *dst = accumulate ? __fadd_rn(*dst, r) : r;
 }
@@ -318,7 +318,7 @@ static int matvec_fwd_launch(ab_ctx* ctx, const ab_weights* w, const float* x, s
     }
     dim3 rgrid((unsigned)((w->out + 255) / 256), (unsigned)m);
     matvec_fwd_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>((const float*)partial, pstride, tiles, w->out, y, y_stride,
-                                                            scale, accumulate, use_scale);
+                                                            scale, accumulate, use_scale, ctx->row_scale);
     AB_LAUNCH_CHECK(ctx);
     return AB_OK;
 }
@@ -336,6 +336,18 @@ int abk_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, float* 
     if (w->out == 0) return AB_OK;
     if (use_mma(ctx, w, false)) return abk_matvec_mma(ctx, w->codes_fwd, w->pitch, w->out, w->in, x, y, 1.0f, 0, 0);
     return matvec_fwd_launch(ctx, w, x, 0, y, 0, 1, 1.0f, 0, 0, 0);
+}
+
+// y (+)= (row_scale[j] or scale) * (W x)_j: the forward matvec with the scaling and the accumulation of the decode chain
+int abk_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale, const float* row_scale,
+                          int accumulate) {
+    if (w->out == 0) return AB_OK;
+    ctx->row_scale = row_scale;
+    int st;
+    if (use_mma(ctx, w, false)) st = abk_matvec_mma(ctx, w->codes_fwd, w->pitch, w->out, w->in, x, y, scale, accumulate, 1);
+    else st = matvec_fwd_launch(ctx, w, x, 0, y, 0, 1, scale, accumulate, 1, 1);
+    ctx->row_scale = nullptr;
+    return st;
 }
 
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {

@@ -64,7 +64,7 @@ __device__ __forceinline__ void load_span(SpanBuf& d, const uint8_t* pa, const u
 __global__ void __launch_bounds__(kMaxWarps * 32)
 matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, const float* __restrict__ v, size_t k,
                   size_t k_slice, double* __restrict__ partial, size_t partial_stride, float* __restrict__ y, float scale,
-                  int accumulate, int use_scale) {
+                  int accumulate, int use_scale, const float* __restrict__ row_scale) {
     extern __shared__ __align__(16) int8_t s_digits[];   // 4 * k_slice bytes, order given below
     __shared__ long long s_sum[kMaxWarps];               // per-warp sums of n_k
     __shared__ unsigned int s_max;                       // largest |v_k| of the slice, as an ordered integer
@@ -222,8 +222,8 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
                 if (va) dst[ra] = ra_v;
                 if (vb) dst[rb] = rb_v;
             } else {
-                if (va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, scale); y[ra] = accumulate ? __fadd_rn(y[ra], r) : r; }
-                if (vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, scale); y[rb] = accumulate ? __fadd_rn(y[rb], r) : r; }
+                if (va) { float r = (float)ra_v; if (use_scale) r = __fmul_rn(r, row_scale ? row_scale[ra] : scale); y[ra] = accumulate ? __fadd_rn(y[ra], r) : r; }
+                if (vb) { float r = (float)rb_v; if (use_scale) r = __fmul_rn(r, row_scale ? row_scale[rb] : scale); y[rb] = accumulate ? __fadd_rn(y[rb], r) : r; }
             }
         }
     }
@@ -231,13 +231,14 @@ matvec_mma_kernel(const uint8_t* __restrict__ codes, size_t pitch, size_t rows, 
 
 // y[r] (+)= scale * (sum over slices, in slice order), rounded to f32 once
 __global__ void matvec_mma_finish_kernel(const double* __restrict__ partial, size_t partial_stride, int slices, size_t rows,
-                                         float* __restrict__ y, float scale, int accumulate, int use_scale) {
+                                         float* __restrict__ y, float scale, int accumulate, int use_scale,
+                                         const float* __restrict__ row_scale) {
     const size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     double s = 0.0;
     for (int k = 0; k < slices; ++k) s += partial[(size_t)k * partial_stride + r];
     float val = (float)s;
-    if (use_scale) val = __fmul_rn(val, scale);
+    if (use_scale) val = __fmul_rn(val, row_scale ? row_scale[r] : scale);
     y[r] = accumulate ? __fadd_rn(y[r], val) : val;
 }
 
@@ -279,11 +280,11 @@ int abk_matvec_ldg(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
     if (nw < 4) nw = 4;
     dim3 grid((unsigned)gx, (unsigned)slices);
     matvec_mma_kernel<<<grid, (unsigned)nw * 32, 4 * k_slice, ctx->stream>>>(codes, pitch, rows, v, k, k_slice, partial, pstride, y, scale,
-                                                                        accumulate, use_scale);
+                                                                        accumulate, use_scale, ctx->row_scale);
     AB_LAUNCH_CHECK(ctx);
     if (slices > 1) {
         matvec_mma_finish_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, ctx->stream>>>(partial, pstride, (int)slices, rows, y, scale,
-                                                                                           accumulate, use_scale);
+                                                                                           accumulate, use_scale, ctx->row_scale);
         AB_LAUNCH_CHECK(ctx);
     }
     return AB_OK;

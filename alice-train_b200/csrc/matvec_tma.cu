@@ -116,6 +116,7 @@ struct Params {
     unsigned long long* acc;   // [rows] packed (arrivals << 56) + integer sum; zero between launches
     float* y;
     float scale;
+    const float* row_scale;    // per-row scale (used instead of `scale` when not null)
     int accumulate, use_scale, stages;
     int* status;
     unsigned long long* trace;   // trace builds only
@@ -337,7 +338,7 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             const long long total = (long long)(pend_seen[j] - (arrived << 56));
             p.acc[row] = 0ull;               // ready for the next launch
             float val = bad ? nanf_ : (float)scalbn((double)total, -shift);
-            if (p.use_scale) val = __fmul_rn(val, p.scale);
+            if (p.use_scale) val = __fmul_rn(val, p.row_scale ? p.row_scale[row] : p.scale);
             p.y[row] = p.accumulate ? __fadd_rn(p.y[row], val) : val;
         }
     };
@@ -431,7 +432,7 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
                 const size_t row = row0 + (j >> 1) * 16 + (j & 1) * 8 + g;
                 if (row >= p.rows) continue;
                 float val = bad ? nanf_ : (float)scalbn((double)res[j], -shift);
-                if (p.use_scale) val = __fmul_rn(val, p.scale);
+                if (p.use_scale) val = __fmul_rn(val, p.row_scale ? p.row_scale[row] : p.scale);
                 p.y[row] = p.accumulate ? __fadd_rn(p.y[row], val) : val;
             }
         }
@@ -531,7 +532,7 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
     if (st) return st;
     Params p{};
     p.rows = rows; p.k = k; p.chunk_spans = (int)chunk_spans; p.unit_spans = (int)unit_spans; p.arrivals = (int)arrivals;
-    p.v = v; p.acc = acc; p.y = y; p.scale = scale;
+    p.v = v; p.acc = acc; p.y = y; p.scale = scale; p.row_scale = ctx->row_scale;
     p.accumulate = accumulate; p.use_scale = use_scale; p.stages = (int)stages; p.status = ctx->dev_status;
 #ifdef AB_MV_TRACE
     p.trace = reinterpret_cast<unsigned long long*>(ctx->stage[14]);   // reserved by ab_debug_mv_trace

@@ -1034,6 +1034,59 @@ def decode_block(env, layers=None, replays=20):
             pass
 
 
+def lm_head_block(env, steps=5, warmup=2, model="llama32-1b"):
+    """The unquantised output head over the whole vocabulary (src/bin/train_qat_70b.rs:1024-1101): logits = h W^T,
+    softmax cross-entropy with its gradient, d_hidden = d_logits W, dW += d_logits^T h; 8192 tokens.  Per-kernel CUDA events."""
+    torch = env.torch
+    import alice_train
+    from alice_train import lm_head as lh
+    vocab, hidden = {"llama32-1b": (128256, 2048), "qwen35-9b": (248320, 4096)}[model]
+    m = 8192
+    dev = env.dev
+    ctx = env.ctx
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(31)
+    w = (torch.randn((vocab, hidden), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    h = torch.randn((m, hidden), generator=gen, device=dev).to(torch.bfloat16)
+    tg = torch.randint(0, vocab, (m,), generator=gen, device=dev, dtype=torch.int32)
+    head = lh.LmHead(ctx, w)
+    logits = torch.empty((m, vocab), dtype=torch.float32, device=dev)
+    loss = torch.empty(m, dtype=torch.float32, device=dev)
+    d = torch.empty((m, vocab), dtype=torch.bfloat16, device=dev)
+    dt = torch.empty((vocab, m), dtype=torch.bfloat16, device=dev)
+    d_hidden = torch.empty((m, hidden), dtype=torch.float32, device=dev)
+    dW = torch.zeros((vocab, hidden), dtype=torch.float32, device=dev)
+    names = ("logits", "cross_entropy", "d_hidden", "dw")
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(steps)]
+    for it in range(warmup + steps):
+        e = ev[it - warmup] if it >= warmup else None
+        if e: e[0].record()
+        head.logits(h, logits)
+        if e: e[1].record()
+        lh.cross_entropy(ctx, logits, tg, 1.0 / m, loss, d, dt)
+        if e: e[2].record()
+        head.backward(d, dt, h, d_hidden, None, want_dw=False)
+        if e: e[3].record()
+        head.backward(d, dt, h, None, dW, dw_beta=1.0, want_dhidden=False)
+        if e: e[4].record()
+    torch.cuda.synchronize()
+    ms = {n: sum(e[i].elapsed_time(e[i + 1]) for e in ev) / steps for i, n in enumerate(names)}
+    flops = 2.0 * m * vocab * hidden
+    ce_bytes = m * vocab * (4 + 2 + 2) + 8 * m
+    total = sum(ms.values())
+    pk = env.pk
+    out = {"model": model, "tokens": m, "vocab": vocab, "hidden": hidden, "ms": ms, "ms_total": total, "tokens_per_s": m / (total * 1e-3),
+           "tflops": {n: flops / (ms[n] * 1e-3) * 1e-12 for n in ("logits", "d_hidden", "dw")},
+           "frac_of_bf16_burst": {n: flops / (ms[n] * 1e-3) * 1e-12 / pk["bf16_tflops"] for n in ("logits", "d_hidden", "dw")},
+           "cross_entropy_gbs": ce_bytes / (ms["cross_entropy"] * 1e-3) * 1e-9,
+           "cross_entropy_frac_of_hbm": ce_bytes / (ms["cross_entropy"] * 1e-3) * 1e-9 / pk["hbm_gbs"],
+           "loss_mean": float(loss.mean().item()), "ln_vocab": float(np.log(vocab)),
+           "note": "logits includes the transposition of h; W^T is refreshed once per optimizer step (not timed here); cross-entropy scored on 8 B per logit (f32 read once, two bf16 gradient copies written)"}
+    del head, logits, d, dt, dW, w
+    torch.cuda.empty_cache()
+    return out
+
+
 def guarded(env, fn, *a, **k):
     """An optional block must not cost the headline line: errors are recorded in its place."""
     try:
@@ -1091,6 +1144,17 @@ def run_native(args):
                         "roofline": {"bound": "hbm", "kernel": "matvec kernel (dx = W^T dy, integer path)", "achieved": dom["gbs"],
                                      "peak": blk["peak_gbs"], "unit": "GB/s", "frac": dom["frac"], "traffic": dram_traffic("matvec", "hbm-kernels"),
                                      "peak_source": blk["peak_source"]}, "block": blk}
+        elif args.workload == "lm-head":
+            blks = {mname: lm_head_block(env, model=mname) for mname in ("llama32-1b", "qwen35-9b")}
+            if env.rank == 0:
+                b0 = blks["llama32-1b"]
+                dom = max(("logits", "d_hidden", "dw"), key=lambda n: b0["ms"][n])
+                line = {"metric": "output head (logits + cross-entropy + backward) tokens/s, vocabulary 128256 x hidden 2048", "value": b0["tokens_per_s"],
+                        "unit": UNIT, "n_gpus": 1, "higher_is_better": True, "data": "synthetic", "dtype": "bf16 (f32 accumulate)",
+                        "config": {"workload": "lm-head"},
+                        "roofline": {"bound": "tensor", "kernel": f"gemm_pair_kernel<DW> bf16 x bf16 ({dom})", "achieved": b0["tflops"][dom],
+                                     "peak": env.pk["bf16_tflops"], "unit": "TFLOP/s", "frac": b0["frac_of_bf16_burst"][dom], "traffic": None,
+                                     "peak_source": f"{env.pk['source']} cuBLAS bf16 burst"}, "blocks": blks}
         elif args.workload == "alice-decode":
             blk = decode_block(env)
             if env.rank == 0:
@@ -1129,7 +1193,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS) + ["hbm-kernels", "alice-decode"] + list(DECODER_WORKLOADS))
+    ap.add_argument("--workload", default="llama3-8b-mlp", choices=sorted(WORKLOADS) + ["hbm-kernels", "alice-decode", "lm-head"] + list(DECODER_WORKLOADS))
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens per CPU-baseline sample")
     ap.add_argument("--dw-exchange", default="switch", choices=["switch", "nccl"],
                     help="sum of dW / all-gather / reduce-scatter: the library's in-switch kernels (default) or NCCL")

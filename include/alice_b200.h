@@ -255,6 +255,13 @@ AB_API int ab_ste_weight_grad(ab_ctx* ctx, const float* x, size_t in_features, c
  * Replaces blas::ternary_matmul_bt (src/blas.rs:403-457). */
 AB_API int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale,
                                 float* c, size_t m);
+/* y_j = s_j * (W x)_j, or y_j += s_j * (W x)_j with accumulate = 1, where s_j = row_scale[j] (a device array of
+ * out_features floats) or, with row_scale NULL, the one `scale`.  This is ternary_matmul_bt at m = 1 (src/blas.rs:403-457,
+ * the call shape of src/inference.rs:1305-1472) without the zero-fill in front of it, and with one scale per ROW so that
+ * projections which read the same vector (q|k|v, gate|up: src/inference.rs:1305-1317,1418-1422) can be stacked into one
+ * matrix and one launch, each keeping its own gamma.  Device pointers.  Same two arithmetic paths as ab_ternary_matvec. */
+AB_API int ab_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale,
+                                const float* row_scale, int accumulate);
 /* The packed decode step's feed-forward block, blas::ternary_swiglu_ffn (src/blas.rs:462-494), on device pointers:
  *   gate_buf = gate_scale * input gate^T ; up_buf = up_scale * input up^T ; gate_buf = gate_buf / (1 + exp(-gate_buf)) * up_buf ;
  *   output = down_scale * gate_buf down^T
@@ -279,6 +286,39 @@ AB_API int ab_ste_weight_grad_host(ab_ctx* ctx, const float* x, size_t x_len, co
                                    size_t dy_len, float* dW, size_t dw_len);
 AB_API int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed_b,
                                      float scale, float* c, size_t m, size_t n, size_t k);
+
+/* ------------------------------------------------- output head: dense logits and cross-entropy
+ * The reference keeps the output projection unquantised (src/bin/train_qat_70b.rs:1024-1031) and runs, per micro-batch,
+ * logits = h W^T (matmul_bt_inplace), cross_entropy_loss per token (src/bin/train_qat_70b.rs:98-112), d_hidden =
+ * d_logits W (matmul_nn_inplace, :1094-1101) and the weight gradient d_logits^T h.  Device pointers, bf16 operands, f32
+ * accumulation and f32 results.  The products contract over the ROW index of both operands, so the forward takes the
+ * weight matrix transposed ([hidden x vocab]; ab_transpose_bf16 makes that copy once per optimizer step) and the
+ * backward takes the gradient of the logits in both orientations, which ab_cross_entropy writes in one pass. */
+AB_API int ab_transpose_bf16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out);
+/* logits[m x vocab] (f32) = h[m x hidden] (bf16) . W^T, with w_t = W^T stored [hidden x vocab] (bf16). */
+AB_API int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w_t, size_t ld_wt, size_t m, size_t hidden,
+                             size_t vocab, float* logits, size_t ld_logits);
+/* Softmax cross-entropy of every token row and its gradient, cross_entropy_loss (src/bin/train_qat_70b.rs:98-112):
+ *   p = exp(x - max) / sum exp(x - max);  loss[t] = -ln(max(p[target_t], 1e-10));  d = (p - onehot(target_t)) * d_scale
+ * logits are f32 or bf16 [m x vocab].  A target >= vocab marks a token that does not count: loss 0, gradient row 0 (the
+ * reference's loop skips it, :1068-1072); d_scale is the caller's 1 / (counted tokens * accumulation steps) (:1080-1083).
+ * loss (f32 [m]), d_logits (bf16 [m x vocab]) and d_logits_t (bf16 [vocab x m], the same values transposed) may each be
+ * NULL. */
+AB_API int ab_cross_entropy(ab_ctx* ctx, const void* logits, int logits_dtype, size_t ld, const uint32_t* targets, size_t m,
+                            size_t vocab, float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t);
+/* d_hidden[m x hidden] (f32, overwritten; NULL to skip) = d_logits . W from d_logits_t [vocab x m] and w [vocab x hidden];
+ * dW[vocab x hidden] (f32; dw_beta 0 overwrites, 1 accumulates; NULL to skip) = d_logits^T . h from d_logits [m x vocab]
+ * and h [m x hidden].  All operands bf16. */
+AB_API int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* d_logits_t, size_t ld_t, const void* w,
+                               size_t ld_w, const void* h, size_t ld_h, size_t m, size_t hidden, size_t vocab, float* d_hidden,
+                               size_t ld_dh, float* dW, size_t ld_dw, float dw_beta);
+/* Host-slice forms of CudaMatmul::matmul_bt_inplace / matmul_nn_inplace (src/cuda_matmul.rs:1149-1258) for a DENSE B:
+ * C[m x n] = A[m x k] . B[n x k]^T and C[m x n] = A[m x k] . B[k x n]; f32 slices, operands rounded to bf16 on the
+ * device, f32 accumulation, blocking.  AB_ERR_SHAPE where the reference's length assertions would panic. */
+AB_API int ab_matmul_bt_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                                   size_t m, size_t n, size_t k);
+AB_API int ab_matmul_nn_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                                   size_t m, size_t n, size_t k);
 
 /* -------------------------------------------------------------------- batched (GEMM) path */
 

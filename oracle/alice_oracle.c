@@ -698,6 +698,36 @@ ORC_API void orc_adamw_update(float* delta, const float* grad, float* m, float* 
     }
 }
 
+/* ------------------------------------------------------------------ output head: cross-entropy
+ * cross_entropy_loss (src/bin/train_qat_70b.rs:98-112): max by a left fold, exp(x - max) per element, their f32 sum in
+ * index order, probabilities e / sum, loss = -ln(max(p[target], 1e-10)), gradient p - onehot(target).  The caller's loop
+ * (src/bin/train_qat_70b.rs:1066-1083) skips a token whose target is outside the vocabulary (zero gradient row, no
+ * loss) and scales every gradient by d_scale afterwards.  Returns the number of counted tokens. */
+ORC_API size_t orc_cross_entropy(const float* logits, const uint32_t* targets, size_t m, size_t v, float d_scale, float* loss,
+                                 float* d_logits) {
+    size_t counted = 0;
+    for (size_t t = 0; t < m; ++t) {
+        const float* x = logits + t * v;
+        float* g = d_logits + t * v;
+        if (targets[t] >= v) {
+            loss[t] = 0.0f;
+            for (size_t j = 0; j < v; ++j) g[j] = 0.0f;
+            continue;
+        }
+        float mx = -INFINITY;
+        for (size_t j = 0; j < v; ++j) mx = x[j] > mx ? x[j] : mx;
+        float sum = 0.0f;
+        for (size_t j = 0; j < v; ++j) { g[j] = expf(x[j] - mx); sum += g[j]; }
+        for (size_t j = 0; j < v; ++j) g[j] = g[j] / sum;
+        float p = g[targets[t]];
+        loss[t] = -logf(p > 1e-10f ? p : 1e-10f);
+        g[targets[t]] -= 1.0f;
+        for (size_t j = 0; j < v; ++j) g[j] *= d_scale;
+        ++counted;
+    }
+    return counted;
+}
+
 ORC_API int orc_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

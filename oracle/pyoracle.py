@@ -69,6 +69,7 @@ def _load():
         "orc_rmsnorm": (None, [_f32p, _f32p, sz, sz, C.c_float]),
         "orc_rmsnorm_backward": (None, [_f32p, _f32p, _f32p, _f32p, C.c_void_p, sz, sz, C.c_float]),
         "orc_swiglu": (None, [_f32p, _f32p, _f32p, sz]),
+        "orc_cross_entropy": (sz, [_f32p, np.ctypeslib.ndpointer(np.uint32, flags="C"), sz, sz, C.c_float, _f32p, _f32p]),
         "orc_fast_sigmoid": (C.c_float, [C.c_float]),
         "orc_swiglu_backward": (None, [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, sz]),
         "orc_sgd_update": (None, [_f32p, _f32p, sz, C.c_float, C.c_float]),
@@ -417,6 +418,17 @@ def adamw_update(delta, grad, m, v, lr, beta1, beta2, eps, step, wd):
     bc2 = np.float32(1.0) - np.float32(np.float32(beta2) ** np.float32(step))
     lib.orc_adamw_update(delta, _f32(grad).reshape(-1), m, v, delta.size, lr, beta1, beta2, eps, float(bc1), float(bc2), wd)
     return delta, m, v, float(bc1), float(bc2)
+
+
+def cross_entropy(logits, targets, d_scale=1.0):
+    """-> (loss per token, d_logits, counted tokens); cross_entropy_loss and its caller's loop."""
+    x = _f32(logits)
+    m, v = x.shape
+    t = np.ascontiguousarray(targets, dtype=np.uint32).reshape(-1)
+    loss = np.zeros(m, np.float32)
+    d = np.zeros(m * v, np.float32)
+    n = lib.orc_cross_entropy(x.reshape(-1), t, m, v, d_scale, loss, d)
+    return loss, d.reshape(m, v), int(n)
 
 
 def max_threads() -> int:

@@ -271,6 +271,18 @@ static void cuda_matmul_cases() {
     expect(close_to(c, y_want, 1e-6f), "src/blas.rs:71-109", "blas_matmul_bt");
     blas_matmul_nn(dy, w, c, m, k, n);
     expect(close_to(c, dx_want, 1e-6f), "src/blas.rs:114-156", "blas_matmul_nn");
+    // a dense (not ternary-valued) B: the output head's products; small integers are exact in bf16
+    std::vector<float> wd(n * k);
+    for (size_t i = 0; i < wd.size(); ++i) wd[i] = float(int(i * 3 % 9) - 4);
+    std::vector<float> yd_want(m * n, 0.f), dxd_want(m * k, 0.f);
+    for (size_t i = 0; i < m; ++i)
+        for (size_t j = 0; j < n; ++j)
+            for (size_t p = 0; p < k; ++p) {
+                yd_want[i * n + j] += a[i * k + p] * wd[j * k + p];
+                dxd_want[i * k + p] += dy[i * n + j] * wd[j * k + p];
+            }
+    expect(close_to(cuda.matmul_bt(a, wd, m, n, k), yd_want, 1e-6f), "src/bin/train_qat_70b.rs:1024-1031", "matmul_bt with a dense B");
+    expect(close_to(cuda.matmul_nn(dy, wd, m, k, n), dxd_want, 1e-6f), "src/bin/train_qat_70b.rs:1094-1101", "matmul_nn with a dense B");
     bool threw = false;
     try {
         cuda.matmul_bt(a, w, m + 1, n, k);

@@ -99,18 +99,21 @@ def oracle_layers(orc, cfg, layers):
     return out
 
 
-@pytest.mark.parametrize("hidden,inter,exact", [(64, 128, False), (1024, 2048, False), (1024, 2048, True)])
-def test_decode_chain_matches_the_oracle(env, orc, tmp_path, hidden, inter, exact):
+@pytest.mark.parametrize("hidden,inter,exact,stack", [(64, 128, False, True), (1024, 2048, False, True), (1024, 2048, True, True),
+                                                      (1024, 2048, False, False)])
+def test_decode_chain_matches_the_oracle(env, orc, tmp_path, hidden, inter, exact, stack):
     """hidden 64: every matrix is below the integer path's size limit (f32 adds); hidden 1024: the large projections
-    run on the tensor-core matvec unless AB_OPT_EXACT_MATVEC is set."""
+    run on the tensor-core matvec unless AB_OPT_EXACT_MATVEC is set.  stack: projections that share their input go out
+    as one stacked matrix with a scale per row (the default) or one by one."""
     at, ctx, torch = env
     cfg = small_config(hidden, inter, 4)
     raw, stats, layers, emb, norm, lm = write_model(at, ctx, cfg, 500, True)
     path = tmp_path / "m.alice"
     path.write_bytes(raw)
-    model = at.StreamingAliceModel.from_file(str(path), ctx)
+    model = at.StreamingAliceModel.from_file(str(path), ctx, stack=stack)
     try:
         assert model.config() == cfg and len(model.layers) == 4
+        assert all(bool(L["stacked"]) == stack for L in model.layers)
         assert model.packed_bytes == sum((o * n + 3) // 4 for i in range(4) for _, o, n in cfg.projection_shapes(i))
         # the handles hold the file's codes and scales
         s, _, packed = orc.quantize_and_pack(layers[1]["q_proj"])
@@ -128,7 +131,7 @@ def test_decode_chain_matches_the_oracle(env, orc, tmp_path, hidden, inter, exac
         ol = oracle_layers(orc, cfg, layers)
         ref = orc.decode_linears(orc.decode_linears(h0, ol, cfg.rms_norm_eps, mix), ol, cfg.rms_norm_eps, mix)
         err = rel_err(h.cpu().numpy(), ref)
-        print(f"decode chain hidden {hidden} exact={exact}: rel err {err:.2e}")
+        print(f"decode chain hidden {hidden} exact={exact} stack={stack}: rel err {err:.2e}")
         assert err <= RTOL
 
         # ternary_swiglu_ffn alone, 3 rows (matvec path) and 9 rows (batched f32 path)
@@ -170,3 +173,40 @@ def test_decode_chain_replays_from_a_cuda_graph(env, tmp_path):
         torch.cuda.synchronize()
         assert torch.equal(h, eager)
         model.close()
+
+
+@pytest.mark.parametrize("out,inn", [(48, 64), (96, 1024), (3000, 2048)])
+def test_matvec_ex_row_scales_and_accumulation(env, orc, out, inn):
+    """y_j (+)= s_j (W x)_j against ternary_matmul_bt (src/blas.rs:403-457) applied segment by segment."""
+    import ctypes as C
+    at, ctx, torch = env
+    lib = at._ffi.load()
+    w_lat = normal_f32(60, (out, inn), 0.02)
+    g, codes, packed = orc.quantize_and_pack(w_lat)
+    w = at.TernaryWeightKernel.from_packed(packed, out, inn, g, ctx)
+    x = normal_f32(61, inn)
+    y0 = normal_f32(62, out)
+    cut = out // 3
+    scales = np.concatenate([np.full(cut, 0.5, np.float32), np.full(out - cut, 0.125 * g, np.float32)])
+    rs = torch.from_numpy(scales).cuda()
+    xt = torch.from_numpy(x).cuda()
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    pk = (inn + 3) // 4
+    rows = np.frombuffer(packed.tobytes(), np.uint8).reshape(out, pk)
+    def ref(c0):
+        a = orc.ternary_matmul_bt(x, rows[:cut].reshape(-1), 0.5, c0[:cut], 1, cut, inn).reshape(-1)
+        b = orc.ternary_matmul_bt(x, rows[cut:].reshape(-1), float(np.float32(0.125 * g)), c0[cut:], 1, out - cut, inn).reshape(-1)
+        return np.concatenate([a, b])
+    for accumulate in (0, 1):
+        y = torch.from_numpy(y0.copy()).cuda()
+        at._ffi.check(lib.ab_ternary_matvec_ex(ctx.handle, w.handle, vp(xt), vp(y), 1.0, vp(rs), accumulate), ctx.handle)
+        ctx.sync()
+        want = ref(y0.copy() if accumulate else np.zeros(out, np.float32))
+        assert rel_err(y.cpu().numpy(), want) <= RTOL
+    # one scale for all rows
+    y = torch.from_numpy(y0.copy()).cuda()
+    at._ffi.check(lib.ab_ternary_matvec_ex(ctx.handle, w.handle, vp(xt), vp(y), g, None, 1), ctx.handle)
+    ctx.sync()
+    want = orc.ternary_matmul_bt(x, packed, g, y0.copy(), 1, out, inn).reshape(-1)
+    assert rel_err(y.cpu().numpy(), want) <= RTOL
+    w.close()
