@@ -258,3 +258,33 @@ def test_threshold_tie_count(orc):
     g = np.float32(0.5)
     w = np.array([0.25, np.nextafter(np.float32(0.25), np.float32(0)), 0.3, -0.25, 0.1], np.float32)
     assert orc.count_threshold_ties(w, float(g)) == 3
+
+
+def test_norm_activation_optimizer_vectors(golden, orc):
+    """The reference's own cases for the steps either side of the linears and for the optimizer update:
+    test_rmsnorm_identity, test_silu (src/llama_forward.rs:483-512), test_sgd_update, test_sgd_with_weight_decay
+    (src/llama_backward.rs:583-599), fast_sigmoid_range (src/fast_math.rs:52-60)."""
+    g = golden["rmsnorm_identity"]
+    y = orc.rmsnorm(np.array([g["x"]], np.float32), np.array(g["weight"], np.float32), g["eps"])[0]
+    assert abs(y[0] - g["expect_x0"]) < g["tol_x0"] and abs(y[1]) < g["expect_x1_abs_below"]
+    for c in golden["silu"]["cases"]:
+        got = orc.swiglu(np.array([c["x"]], np.float32), np.array([1.0], np.float32))[0]      # silu(x) * 1
+        assert abs(got - c["expect"]) < c["tol"]
+    # the SwiGLU backward of the production path uses fast_sigmoid (src/cuda_matmul.rs:4135-4147, src/fast_math.rs:11-23),
+    # which the reference pins by range and by its value at zero, not the exact silu_grad of src/llama_backward.rs:315-318
+    g = golden["fast_sigmoid"]
+    for i in range(g["range"][0], g["range"][1] + 1):
+        sgm = orc.fast_sigmoid(np.float32(i) * np.float32(g["step"]))
+        assert 0.0 <= sgm <= 1.0
+    assert abs(orc.fast_sigmoid(0.0) - g["at_zero"]) < g["tol_at_zero"]
+    x = np.float32(0.7)
+    sig = np.float32(orc.fast_sigmoid(x))
+    d_gate, d_up = orc.swiglu_backward(np.array([2.0], np.float32), np.array([x], np.float32), np.array([3.0], np.float32),
+                                       np.array([0.25], np.float32))
+    assert d_up[0] == np.float32(2.0) * np.float32(0.25)
+    assert d_gate[0] == np.float32(np.float32(2.0) * np.float32(3.0)) * np.float32(sig * np.float32(np.float32(1.0) + x * np.float32(np.float32(1.0) - sig)))
+    for key in ("sgd_update", "sgd_with_weight_decay"):
+        g = golden[key]
+        w = orc.sgd_update(np.array(g["w"], np.float32), np.array(g["grad"], np.float32), g["lr"], g["wd"])
+        for got, want in zip(w, g["expect"]):
+            assert abs(got - want) < g["tol"]
