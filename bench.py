@@ -267,7 +267,8 @@ class Env:
         return int(t.item()) == 0
 
     def close(self):
-        if self.world > 1:
+        if self.world > 1 and not getattr(self, "_closed", False):
+            self._closed = True
             self.dist.destroy_process_group()
 
 
@@ -382,9 +383,7 @@ def run_main(env, args):
             del ref
         exchange_check = {"buffers": len(layers), "vs_nccl_bit_identical": same, "vs_nccl_max_rel_diff": worst}
         if not env.all_ok(ok):
-            if rank == 0:
-                print(f"[bench] in-switch all-reduce of dW differs from NCCL: {exchange_check}", file=sys.stderr)
-            sys.exit(3)
+            raise ExchangeMismatch(f"in-switch all-reduce of dW differs from NCCL: {exchange_check}")
     sampler = ClockSampler(env.local)
     if rank == 0:
         sampler.start()
@@ -666,6 +665,29 @@ def hbm_block(env, full: bool = True):
         t = timeit(lambda w: bl.act_quant_int8(ctx, xa, qa), 20, False)
         nb = 4096 * 14336 * 3 + 8 * 4096
         res["act_quant_int8"] = {"us": t * 1e6, "gbs": nb / t / 1e9, "frac": nb / t / 1e9 / pk["hbm_gbs"]}
+        # the steps either side of the linears, fused with the activation quantiser, and the optimizer fused with kernel (1)
+        if full:
+            nw = 14336 * 4096
+            flat, grad = w_lat.view(-1), torch.randn(nw, generator=gen, device=dev) * 1e-3
+            t = timeit(lambda w: bl.sgd_step_fq(ctx, flat, grad, 1e-4, 0.0, hq), 10, False)
+            res["sgd_step_fq"] = {"us": t * 1e6, "gbs": (12.0 + 0.25) * nw / t / 1e9, "frac": (12.0 + 0.25) * nw / t / 1e9 / pk["hbm_gbs"],
+                                  "note": "w, g read + w written + codes; the separate quantiser call of the next step is saved"}
+            am, av = torch.zeros(nw, device=dev), torch.zeros(nw, device=dev)
+            t = timeit(lambda w: bl.adamw_step_fq(ctx, flat, grad, am, av, 1e-4, 3, weights=hq), 10, False)
+            res["adamw_step_fq"] = {"us": t * 1e6, "gbs": (28.0 + 0.25) * nw / t / 1e9, "frac": (28.0 + 0.25) * nw / t / 1e9 / pk["hbm_gbs"]}
+            del grad, am, av
+            xn = torch.randn((4096, 4096), generator=gen, device=dev).to(torch.bfloat16)
+            wn = torch.ones(4096, device=dev)
+            _, qn = bl.rmsnorm_act_quant(ctx, xn, wn, 1e-5)
+            t = timeit(lambda w: bl.rmsnorm_act_quant(ctx, xn, wn, 1e-5, None, qn), 20, False)
+            nb = 4096 * 4096 * 3 + 12 * 4096
+            res["rmsnorm_act_quant"] = {"us": t * 1e6, "gbs": nb / t / 1e9, "frac": nb / t / 1e9 / pk["hbm_gbs"]}
+            gate = torch.randn((4096, 14336), generator=gen, device=dev).to(torch.bfloat16)
+            _, qs = bl.swiglu_act_quant(ctx, gate, xa)
+            t = timeit(lambda w: bl.swiglu_act_quant(ctx, gate, xa, None, qs), 20, False)
+            nb = 4096 * 14336 * 5 + 12 * 4096
+            res["swiglu_act_quant"] = {"us": t * 1e6, "gbs": nb / t / 1e9, "frac": nb / t / 1e9 / pk["hbm_gbs"]}
+            del xn, gate
         # the CPU-runnable configuration: one 2048 x 2048 layer, batch 1 (1 MiB of codes: latency, not bandwidth)
         g1 = torch.randn((2048, 2048), generator=gen, device=dev) * 0.02
         h1 = bl.BitLinearWeights(2048, 2048, ctx).quantize_(g1)
@@ -719,9 +741,7 @@ def decoder_block(env, name, args, steps, warmup):
         except RuntimeError as e:
             ok, check = False, {"error": str(e)}
         if not env.all_ok(ok):
-            if env.rank == 0:
-                print(f"[bench] {name}: {check}", file=sys.stderr)
-            sys.exit(3)
+            raise ExchangeMismatch(f"{name}: {check}")
         plan.resync_epochs()
     launches0 = env.ctx.launch_count()
     ms = timed_steps(env, plan.step, steps, warmup) / steps
@@ -856,13 +876,15 @@ def rowshard_block(env, args, steps, warmup):
 
     for _ in range(warmup):
         step(False)
-    # both in-switch exchanges against NCCL on copies of the same inputs, before anything is timed: the all-gather must
-    # be bit-identical; the reduce-scatter adds in f32 inside the switch and truncates to bf16 where NCCL rounds, so it
-    # may differ by one bf16 unit in the last place
+    # both in-switch exchanges against NCCL on copies of the same inputs, before anything is timed.  The all-gather must
+    # be bit-identical.  The reduce-scatter adds the GPUs' bf16 partials in f32 inside the switch and truncates the sum
+    # to bf16, so it is held against NCCL's f32 reduce-scatter of the same partials: within one bf16 unit in the last
+    # place of the exact sum (2^-7 relative) at any number of GPUs.  (NCCL's own bf16 reduce-scatter rounds after every
+    # ring step and drifts further from the f32 sum than that where partials cancel.)
     check = None
     if exchange == "switch":
         ctx.sync()
-        ok, ag_same, rs_worst_ulp = True, 0, 0.0
+        ok, ag_same, rs_worst = True, 0, 0.0
         for L in layers:
             mine = L["y"].clone()
             ref_all = torch.empty_like(L["y_all"])
@@ -871,24 +893,21 @@ def rowshard_block(env, args, steps, warmup):
             ok &= torch.equal(ref_all, L["y_all"])
             bl.bitlinear_dx(L["w"], L["dy"], dx=L["dx"])
             ctx.sync()
-            part = L["dx"].clone()
-            ref_rs = torch.empty_like(L["dx_mine"])
+            part = L["dx"].float()
+            ref_rs = torch.empty(L["dx_mine"].shape, dtype=torch.float32, device=part.device)
             dist.reduce_scatter_tensor(ref_rs, part, op=dist.ReduceOp.SUM)
             L["dxbuf"].start(_ffi.AB_XCHG_REDUCESCATTER_BF16, out_local=L["dx_mine"], ctas=args.exchange_ctas)
             _ffi.check(_ffi.load().ab_dp_allreduce_wait(ctx.handle), ctx.handle)
             ctx.sync()
-            a, b = L["dx_mine"].float(), ref_rs.float()
-            # one bf16 unit in the last place is at most 2^-7 of the larger magnitude
-            tol = torch.maximum(a.abs(), b.abs()) * (2.0 ** -7) + 1e-30
-            ulp = float(((a - b).abs() / tol).max().item())
-            rs_worst_ulp = max(rs_worst_ulp, ulp)
-            ok &= ulp <= 1.0
+            a = L["dx_mine"].float()
+            tol = ref_rs.abs() * (2.0 ** -7) + 1e-6 * float(ref_rs.abs().max().item()) + 1e-30
+            worst = float(((a - ref_rs).abs() / tol).max().item())
+            rs_worst = max(rs_worst, worst)
+            ok &= worst <= 1.0
             del mine, ref_all, part, ref_rs
-        check = {"allgather_bit_identical": ag_same, "of": len(layers), "reduce_scatter_max_bf16_ulp_vs_nccl": rs_worst_ulp}
+        check = {"allgather_bit_identical": ag_same, "of": len(layers), "reduce_scatter_worst_over_one_bf16_ulp_of_f32_sum": rs_worst}
         if not env.all_ok(bool(ok)):
-            if rank == 0:
-                print(f"[bench] llama3-70b-layer: in-switch exchange differs from NCCL: {check}", file=sys.stderr)
-            sys.exit(3)
+            raise ExchangeMismatch(f"llama3-70b-layer: in-switch exchange differs from its reference: {check}")
     env.fence()
     launches0 = ctx.launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -1087,6 +1106,10 @@ def lm_head_block(env, steps=5, warmup=2, model="llama32-1b"):
     return out
 
 
+class ExchangeMismatch(RuntimeError):
+    """An in-switch exchange did not reproduce its reference: the run's numbers would describe a wrong result."""
+
+
 def guarded(env, fn, *a, **k):
     """An optional block must not cost the headline line: errors are recorded in its place."""
     try:
@@ -1182,6 +1205,10 @@ def run_native(args):
                     line["partitioned"] = part      # last key: survives a log that keeps only its tail
         if env.rank == 0 and line is not None:
             print(json.dumps(compact(line)), flush=True)
+    except ExchangeMismatch as e:     # of the workload that was asked for (inside the default line's extras it is recorded instead)
+        if env.rank == 0:
+            print(f"[bench] {e}", file=sys.stderr)
+        return 3
     finally:
         env.close()
     return 0
