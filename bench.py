@@ -1053,14 +1053,14 @@ def decode_block(env, layers=None, replays=20):
             pass
 
 
-def lm_head_block(env, steps=5, warmup=2, model="llama32-1b"):
+def lm_head_block(env, steps=5, warmup=2, model="llama32-1b", tokens=8192):
     """The unquantised output head over the whole vocabulary (src/bin/train_qat_70b.rs:1024-1101): logits = h W^T,
     softmax cross-entropy with its gradient, d_hidden = d_logits W, dW += d_logits^T h; 8192 tokens.  Per-kernel CUDA events."""
     torch = env.torch
     import alice_train
     from alice_train import lm_head as lh
     vocab, hidden = {"llama32-1b": (128256, 2048), "qwen35-9b": (248320, 4096)}[model]
-    m = 8192
+    m = tokens
     dev = env.dev
     ctx = env.ctx
     gen = torch.Generator(device=dev)
@@ -1168,7 +1168,8 @@ def run_native(args):
                                      "peak": blk["peak_gbs"], "unit": "GB/s", "frac": dom["frac"], "traffic": dram_traffic("matvec", "hbm-kernels"),
                                      "peak_source": blk["peak_source"]}, "block": blk}
         elif args.workload == "lm-head":
-            blks = {mname: lm_head_block(env, model=mname) for mname in ("llama32-1b", "qwen35-9b")}
+            models = ("llama32-1b", "qwen35-9b") if args.head_tokens == 8192 else ("llama32-1b",)
+            blks = {mname: lm_head_block(env, model=mname, tokens=args.head_tokens) for mname in models}
             if env.rank == 0:
                 b0 = blks["llama32-1b"]
                 dom = max(("logits", "d_hidden", "dw"), key=lambda n: b0["ms"][n])
@@ -1225,15 +1226,16 @@ def main():
     ap.add_argument("--dw-exchange", default="switch", choices=["switch", "nccl"],
                     help="sum of dW / all-gather / reduce-scatter: the library's in-switch kernels (default) or NCCL")
     ap.add_argument("--exchange-ctas", type=int, default=0, help="CTAs of the in-switch exchange kernel (0 = library default)")
-    ap.add_argument("--partitioned-ctas", type=int, default=0, help="the same for the decoder workloads, whose exchange is much larger per unit of compute (0 = 32)")
+    ap.add_argument("--partitioned-ctas", type=int, default=0, help="the same for the decoder workloads, whose exchange is much larger per unit of compute (0 = 32 at 2 GPUs, 16 beyond: measured)")
     ap.add_argument("--partitioned-steps", type=int, default=5, help="timed steps of each partitioned workload inside the default run")
     ap.add_argument("--check-linears", type=int, default=12, help="dW buffers per decoder workload whose in-switch sum is checked against NCCL (0 = all)")
+    ap.add_argument("--head-tokens", type=int, default=8192, help="tokens of the lm-head workload (a small value gives a case a profiler can capture)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (no hbm_kernels / partitioned blocks)")
     args = ap.parse_args()
     if args.partitioned_ctas == 0:
-        args.partitioned_ctas = 32
+        args.partitioned_ctas = 32 if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else 16
     if args.impl == "reference":
         return run_reference(args)
     return run_native(args)
