@@ -88,13 +88,13 @@ SIGNATURES = {
     "ab_bitlinear_backward": (_i, [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp]),
     "ab_ste_weight_grad": (_i, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "ab_ternary_matmul_bt": (_i, [_vp, _vp, _vp, _f, _vp, _sz]),
-    "ab_transpose_bf16": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _sz]),
-    "ab_lm_head_logits": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz]),
+    "ab_lm_head_logits": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _i, _sz]),
     "ab_cross_entropy": (_i, [_vp, _vp, _i, _sz, _vp, _sz, _sz, _f, _vp, _vp, _sz, _vp, _sz]),
-    "ab_lm_head_backward": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _f]),
+    "ab_lm_head_backward": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _f]),
     "ab_matmul_bt_dense_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz]),
     "ab_matmul_nn_dense_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz]),
     "ab_ternary_matvec_ex": (_i, [_vp, _vp, _vp, _vp, _f, _vp, _i]),
+    "ab_ternary_swiglu_ffn_host": (_i, [_vp, _vp, _vp, _f, _vp, _f, _vp, _f, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ab_ternary_swiglu_ffn": (_i, [_vp, _vp, _vp, _f, _vp, _f, _vp, _f, _vp, _vp, _vp, _sz]),
     "ab_ternary_matvec_host": (_i, [_vp, _vp, _vp, _sz, _vp, _sz]),
     "ab_ternary_matvec_backward_host": (_i, [_vp, _vp, _vp, _sz, _vp, _sz]),

@@ -20,20 +20,11 @@ def _chk(t, dtype, name):
         raise ValueError(f"{name} must be a 2-D CUDA {dtype} tensor with unit inner stride")
 
 
-def transpose_bf16(ctx: GpuContext, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    _chk(x, torch.bfloat16, "x")
-    r, c = x.shape
-    if out is None:
-        out = torch.empty((c, (r + 7) // 8 * 8), dtype=torch.bfloat16, device=x.device)[:, :r]
-    _chk(out, torch.bfloat16, "out")
-    _ffi.check(_ffi.load().ab_transpose_bf16(ctx.handle, _p(x), r, c, x.stride(0), _p(out), out.stride(0)), ctx.handle)
-    return out
-
-
 def cross_entropy(ctx: GpuContext, logits: torch.Tensor, targets: torch.Tensor, d_scale: float, loss: torch.Tensor | None = None,
-                  d_logits: torch.Tensor | None = None, d_logits_t: torch.Tensor | None = None, want_grad: bool = True):
-    """Per-token loss and (p - onehot) * d_scale in both orientations (bf16).  targets: CUDA int32 tensor; a value
-    outside [0, vocab) marks a token that does not count."""
+                  d_logits: torch.Tensor | None = None, d_logits_t: torch.Tensor | None = None, want_grad: bool = True,
+                  want_transposed: bool = False):
+    """Per-token loss and the gradient (p - onehot) * d_scale as bf16 [tokens x vocab] (and, on request, also transposed).
+    targets: CUDA int32 tensor; a value outside [0, vocab) marks a token that does not count."""
     if not logits.is_cuda or logits.dim() != 2 or logits.stride(1) != 1 or logits.dtype not in (torch.float32, torch.bfloat16):
         raise ValueError("logits must be a 2-D CUDA f32 or bf16 tensor with unit inner stride")
     m, v = logits.shape
@@ -43,7 +34,7 @@ def cross_entropy(ctx: GpuContext, logits: torch.Tensor, targets: torch.Tensor, 
         loss = torch.empty(m, dtype=torch.float32, device=logits.device)
     if want_grad and d_logits is None:
         d_logits = torch.empty((m, v), dtype=torch.bfloat16, device=logits.device)
-    if want_grad and d_logits_t is None:
+    if want_grad and want_transposed and d_logits_t is None:
         d_logits_t = torch.empty((v, (m + 7) // 8 * 8), dtype=torch.bfloat16, device=logits.device)[:, :m]
     dt = _ffi.AB_F32 if logits.dtype == torch.float32 else _ffi.AB_BF16
     _ffi.check(_ffi.load().ab_cross_entropy(ctx.handle, _p(logits), dt, logits.stride(0), _p(targets), m, v, float(d_scale), _p(loss),
@@ -53,7 +44,7 @@ def cross_entropy(ctx: GpuContext, logits: torch.Tensor, targets: torch.Tensor, 
 
 
 class LmHead:
-    """The output projection [vocab x hidden], unquantised, bf16 on the device in both orientations."""
+    """The output projection [vocab x hidden], unquantised, bf16 on the device."""
 
     def __init__(self, ctx: GpuContext, weight: torch.Tensor):
         if weight.dim() != 2 or not weight.is_cuda:
@@ -61,42 +52,37 @@ class LmHead:
         self.ctx = ctx
         self.vocab, self.hidden = weight.shape
         self.w = weight.to(torch.bfloat16).contiguous()
-        self.w_t = None
-        self.refresh()
 
-    def refresh(self):
-        """Re-derive the transposed copy after the weights changed (once per optimizer step)."""
-        self.w_t = transpose_bf16(self.ctx, self.w, self.w_t)
-
-    def logits(self, h: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def logits(self, h: torch.Tensor, out: torch.Tensor | None = None, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         _chk(h, torch.bfloat16, "h")
         m = h.shape[0]
         if h.shape[1] != self.hidden:
             raise AssertionError("assertion `left == right` failed: h is tokens x hidden")
         if out is None:
-            out = torch.empty((m, self.vocab), dtype=torch.float32, device=h.device)
-        _ffi.check(_ffi.load().ab_lm_head_logits(self.ctx.handle, _p(h), h.stride(0), _p(self.w_t), self.w_t.stride(0), m, self.hidden,
-                                                 self.vocab, _p(out), out.stride(0)), self.ctx.handle)
+            out = torch.empty((m, self.vocab), dtype=dtype, device=h.device)
+        dt = _ffi.AB_F32 if out.dtype == torch.float32 else _ffi.AB_BF16
+        _ffi.check(_ffi.load().ab_lm_head_logits(self.ctx.handle, _p(h), h.stride(0), _p(self.w), self.w.stride(0), m, self.hidden,
+                                                 self.vocab, _p(out), dt, out.stride(0)), self.ctx.handle)
         return out
 
     def loss_and_grad(self, logits: torch.Tensor, targets: torch.Tensor, accum_steps: int = 1, counted: int | None = None):
-        """-> (per-token loss, counted tokens, d_logits, d_logits_t) with the reference's mean scaling
+        """-> (per-token loss, counted tokens, d_logits) with the reference's mean scaling
         1 / (max(counted, 1) * accum_steps) (src/bin/train_qat_70b.rs:1080-1083)."""
         if counted is None:
             counted = int(((targets >= 0) & (targets < self.vocab)).sum().item())
         d_scale = 1.0 / (max(counted, 1) * accum_steps)
-        loss, d, dt = cross_entropy(self.ctx, logits, targets, d_scale)
-        return loss, counted, d, dt
+        loss, d, _ = cross_entropy(self.ctx, logits, targets, d_scale)
+        return loss, counted, d
 
-    def backward(self, d_logits: torch.Tensor, d_logits_t: torch.Tensor, h: torch.Tensor, d_hidden: torch.Tensor | None = None,
+    def backward(self, d_logits: torch.Tensor, h: torch.Tensor, d_hidden: torch.Tensor | None = None,
                  dW: torch.Tensor | None = None, dw_beta: float = 0.0, want_dw: bool = True, want_dhidden: bool = True):
         m = h.shape[0]
         if want_dhidden and d_hidden is None:
             d_hidden = torch.empty((m, self.hidden), dtype=torch.float32, device=h.device)
         if want_dw and dW is None:
             dW = torch.zeros((self.vocab, self.hidden), dtype=torch.float32, device=h.device)
-        _ffi.check(_ffi.load().ab_lm_head_backward(self.ctx.handle, _p(d_logits), d_logits.stride(0), _p(d_logits_t), d_logits_t.stride(0),
-                                                   _p(self.w), self.w.stride(0), _p(h), h.stride(0), m, self.hidden, self.vocab,
-                                                   _p(d_hidden), d_hidden.stride(0) if d_hidden is not None else self.hidden, _p(dW), dW.stride(0) if dW is not None else self.hidden,
-                                                   float(dw_beta)), self.ctx.handle)
+        _ffi.check(_ffi.load().ab_lm_head_backward(self.ctx.handle, _p(d_logits), d_logits.stride(0), _p(self.w), self.w.stride(0), _p(h),
+                                                   h.stride(0), m, self.hidden, self.vocab, _p(d_hidden),
+                                                   d_hidden.stride(0) if d_hidden is not None else self.hidden, _p(dW),
+                                                   dW.stride(0) if dW is not None else self.hidden, float(dw_beta)), self.ctx.handle)
         return d_hidden, dW

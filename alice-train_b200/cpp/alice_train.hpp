@@ -401,6 +401,19 @@ inline void ternary_matmul_bt(const std::vector<float>& a, const std::vector<uin
                               size_t m, size_t n, size_t k, const GpuContext& ctx = GpuContext::global()) {
     ctx.check(ab_ternary_matmul_bt_host(ctx.handle(), a.data(), packed_b.data(), scale, c.data(), m, n, k));
 }
+// output = (SiLU(input gate^T) * (input up^T)) down^T off the packed codes; gate_buf ends up holding SiLU(gate) * up.
+// src/blas.rs:462-494
+inline void ternary_swiglu_ffn(const std::vector<float>& input, const std::vector<uint8_t>& gate_packed, float gate_scale,
+                               const std::vector<uint8_t>& up_packed, float up_scale, const std::vector<uint8_t>& down_packed,
+                               float down_scale, std::vector<float>& output, std::vector<float>& gate_buf, std::vector<float>& up_buf,
+                               size_t seq_len, size_t hidden_dim, size_t intermediate_dim, const GpuContext& ctx = GpuContext::global()) {
+    if (input.size() < seq_len * hidden_dim || output.size() < seq_len * hidden_dim || gate_buf.size() < seq_len * intermediate_dim ||
+        up_buf.size() < seq_len * intermediate_dim)
+        throw AssertionError("slice lengths");
+    ctx.check(ab_ternary_swiglu_ffn_host(ctx.handle(), input.data(), gate_packed.data(), gate_scale, up_packed.data(), up_scale,
+                                         down_packed.data(), down_scale, output.data(), gate_buf.data(), up_buf.data(), seq_len,
+                                         hidden_dim, intermediate_dim));
+}
 }  // namespace blas
 
 }  // namespace alice_train

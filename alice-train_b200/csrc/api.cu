@@ -896,6 +896,56 @@ int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed
     return st;
 }
 
+// blas::ternary_swiglu_ffn with the reference's own argument list (src/blas.rs:462-494): host slices, packed rows of
+// stride ceil(k/4), the three buffers overwritten (gate_buf ends up holding SiLU(gate) * up, as in the reference).
+static int packed_rows_to_handle(ab_ctx* ctx, const uint8_t* packed, size_t n, size_t k, ab_weights** out) {
+    ab_weights* w = nullptr;
+    AB_TRY(weights_create(ctx, n, k, false, &w));
+    const size_t pk = (k + 3) / 4;
+    int st = AB_OK;
+    if (pk && n) {
+        cudaError_t e = cudaMemcpy2DAsync(w->codes, w->pitch, packed, pk, pk, n, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+        if (!st) st = abk_codes_sanitize(ctx, w);
+    }
+    w->has_data = true;
+    if (st) { ab_weights_destroy(w); return st; }
+    *out = w;
+    return AB_OK;
+}
+
+int ab_ternary_swiglu_ffn_host(ab_ctx* ctx, const float* input, const uint8_t* gate_packed, float gate_scale, const uint8_t* up_packed,
+                               float up_scale, const uint8_t* down_packed, float down_scale, float* output, float* gate_buf,
+                               float* up_buf, size_t seq_len, size_t hidden_dim, size_t intermediate_dim) {
+    AB_TRY(bind(ctx));
+    if (seq_len == 0) return AB_OK;
+    if (hidden_dim) AB_REQUIRE(input && output, AB_ERR_NULL);
+    if (intermediate_dim) AB_REQUIRE(gate_buf && up_buf, AB_ERR_NULL);
+    if (hidden_dim * intermediate_dim) AB_REQUIRE(gate_packed && up_packed && down_packed, AB_ERR_NULL);
+    ab_weights *g = nullptr, *u = nullptr, *d = nullptr;
+    int st = packed_rows_to_handle(ctx, gate_packed, intermediate_dim, hidden_dim, &g);
+    if (!st) st = packed_rows_to_handle(ctx, up_packed, intermediate_dim, hidden_dim, &u);
+    if (!st) st = packed_rows_to_handle(ctx, down_packed, hidden_dim, intermediate_dim, &d);
+    void *din = nullptr, *dout = nullptr, *dg = nullptr, *du = nullptr;
+    const size_t nh = seq_len * hidden_dim * 4, ni = seq_len * intermediate_dim * 4;
+    if (!st) st = h2d(ctx, 0, input, nh, &din);
+    if (!st) st = ab_ctx_stage(ctx, 1, nh + 4, &dout);
+    if (!st) st = ab_ctx_stage(ctx, 2, ni + 4, &dg);
+    if (!st) st = ab_ctx_stage(ctx, 3, ni + 4, &du);
+    if (!st) st = ab_ternary_swiglu_ffn(ctx, (const float*)din, g, gate_scale, u, up_scale, d, down_scale, (float*)dout, (float*)dg,
+                                        (float*)du, seq_len);
+    if (!st && ni) {
+        cudaError_t e = cudaMemcpyAsync(gate_buf, dg, ni, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(up_buf, du, ni, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e != cudaSuccess) { ctx->last_error = cudaGetErrorString(e); st = AB_ERR_CUDA; }
+    }
+    if (!st) st = d2h_sync(ctx, output, dout, nh);
+    if (g) ab_weights_destroy(g);
+    if (u) ab_weights_destroy(u);
+    if (d) ab_weights_destroy(d);
+    return st;
+}
+
 // Host-slice forms of the three dense products of the reference's CudaMatmul (f32 slices in and out, blocking): the
 // operands are rounded to bf16 on the device (round to nearest even), the products run on the tensor cores with f32
 // accumulation, the results come back as f32.
@@ -954,13 +1004,6 @@ int ab_matmul_tn_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b,
 }
 
 // ------------------------------------------------------------------------------- output head (dense, unquantised)
-int ab_transpose_bf16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out) {
-    AB_TRY(bind(ctx));
-    AB_REQUIRE(ld_in >= cols && ld_out >= rows, AB_ERR_SHAPE);
-    if (rows * cols) AB_REQUIRE(in && out, AB_ERR_NULL);
-    return abk_transpose16(ctx, in, rows, cols, ld_in, out, ld_out);
-}
-
 int ab_cross_entropy(ab_ctx* ctx, const void* logits, int logits_dtype, size_t ld, const uint32_t* targets, size_t m, size_t vocab,
                      float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t) {
     AB_TRY(bind(ctx));
@@ -970,37 +1013,34 @@ int ab_cross_entropy(ab_ctx* ctx, const void* logits, int logits_dtype, size_t l
     return abk_cross_entropy(ctx, logits, logits_dtype, ld, targets, m, vocab, d_scale, loss, d_logits, ld_d, d_logits_t, ld_t);
 }
 
-int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w_t, size_t ld_wt, size_t m, size_t hidden, size_t vocab,
-                      float* logits, size_t ld_logits) {
+int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w, size_t ld_w, size_t m, size_t hidden, size_t vocab,
+                      void* logits, int logits_dtype, size_t ld_logits) {
     AB_TRY(bind(ctx));
-    AB_REQUIRE(ld_h >= hidden && ld_wt >= vocab && ld_logits >= vocab, AB_ERR_SHAPE);
+    AB_REQUIRE(logits_dtype == AB_F32 || logits_dtype == AB_BF16, AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_h >= hidden && ld_w >= hidden && ld_logits >= vocab, AB_ERR_SHAPE);
     AB_REQUIRE(m < (1ull << 31) && hidden < (1ull << 31) && vocab < (1ull << 31), AB_ERR_UNSUPPORTED);
     if (m * vocab == 0) return AB_OK;
     AB_REQUIRE(logits, AB_ERR_NULL);
-    if (hidden) AB_REQUIRE(h && w_t, AB_ERR_NULL);
-    // the pair GEMM contracts over the row index of both operands: h goes in transposed ([hidden x m], pitch padded to 8)
-    const size_t ld_ht = ab_round_up(m, 8);
-    void* ht = nullptr;
-    AB_TRY(ab_ctx_stage(ctx, 12, (hidden ? hidden : 1) * ld_ht * 2 + 16, &ht));
-    AB_TRY(abk_transpose16(ctx, h, m, hidden, ld_h, ht, ld_ht));
-    return abk_gemm_dw(ctx, ht, ld_ht, w_t, ld_wt, hidden, m, vocab, logits, ld_logits, 0.0f);
+    if (hidden) AB_REQUIRE(h && w, AB_ERR_NULL);
+    return abk_gemm_nt(ctx, h, ld_h, w, ld_w, m, vocab, hidden, logits, logits_dtype, ld_logits, 0.0f);
 }
 
-int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* d_logits_t, size_t ld_t, const void* w, size_t ld_w,
-                        const void* h, size_t ld_h, size_t m, size_t hidden, size_t vocab, float* d_hidden, size_t ld_dh, float* dW,
-                        size_t ld_dw, float dw_beta) {
+int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* w, size_t ld_w, const void* h, size_t ld_h, size_t m,
+                        size_t hidden, size_t vocab, float* d_hidden, size_t ld_dh, float* dW, size_t ld_dw, float dw_beta) {
     AB_TRY(bind(ctx));
     AB_REQUIRE(dw_beta == 0.0f || dw_beta == 1.0f, AB_ERR_UNSUPPORTED);
     AB_REQUIRE(m < (1ull << 31) && hidden < (1ull << 31) && vocab < (1ull << 31), AB_ERR_UNSUPPORTED);
+    AB_REQUIRE(ld_d >= vocab, AB_ERR_SHAPE);
+    if ((d_hidden || dW) && m * hidden * vocab) AB_REQUIRE(d_logits, AB_ERR_NULL);
     if (d_hidden) {
-        AB_REQUIRE(ld_t >= m && ld_w >= hidden && ld_dh >= hidden, AB_ERR_SHAPE);
-        if (m * hidden * vocab) AB_REQUIRE(d_logits_t && w, AB_ERR_NULL);
-        // d_hidden[m x hidden] = sum_v d_logits_t[v][m] * w[v][hidden]
-        AB_TRY(abk_gemm_dw(ctx, d_logits_t, ld_t, w, ld_w, vocab, m, hidden, d_hidden, ld_dh, 0.0f));
+        AB_REQUIRE(ld_w >= hidden && ld_dh >= hidden, AB_ERR_SHAPE);
+        if (m * hidden * vocab) AB_REQUIRE(w, AB_ERR_NULL);
+        // d_hidden[m x hidden] = d_logits[m x vocab] . w[vocab x hidden]
+        AB_TRY(abk_gemm_nn(ctx, d_logits, ld_d, w, ld_w, m, hidden, vocab, d_hidden, AB_F32, ld_dh, 0.0f));
     }
     if (dW) {
-        AB_REQUIRE(ld_d >= vocab && ld_h >= hidden && ld_dw >= hidden, AB_ERR_SHAPE);
-        if (m * hidden * vocab) AB_REQUIRE(d_logits && h, AB_ERR_NULL);
+        AB_REQUIRE(ld_h >= hidden && ld_dw >= hidden, AB_ERR_SHAPE);
+        if (m * hidden * vocab) AB_REQUIRE(h, AB_ERR_NULL);
         // dW[vocab x hidden] (+)= sum_t d_logits[t][vocab] * h[t][hidden]
         AB_TRY(abk_gemm_dw(ctx, d_logits, ld_d, h, ld_h, m, vocab, hidden, dW, ld_dw, dw_beta));
     }
@@ -1010,15 +1050,15 @@ int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const vo
 // Dense host-slice products (the reference's matmul_bt_inplace / matmul_nn_inplace call sites whose B is not a ternary
 // matrix: the output head, src/bin/train_qat_70b.rs:1024-1031, 1094-1101).  f32 slices in and out, operands rounded to
 // bf16 on the device, f32 accumulation.
-int ab_matmul_bt_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
-                            size_t m, size_t n, size_t k) {
+static int dense_host(ab_ctx* ctx, bool nn, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len, size_t m,
+                      size_t n, size_t k) {
     AB_TRY(bind(ctx));
     AB_REQUIRE(a_len == m * k && b_len == n * k && c_len == m * n, AB_ERR_SHAPE);
     AB_REQUIRE(k < (1ull << 31) && n < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
     if (c_len == 0) return AB_OK;
     AB_REQUIRE(c, AB_ERR_NULL);
     if (k) AB_REQUIRE(a && b, AB_ERR_NULL);
-    void *da = nullptr, *db = nullptr, *dbt = nullptr, *dc = nullptr;
+    void *da = nullptr, *db = nullptr, *dc = nullptr;
     AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
     if (k == 0) {
         AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
@@ -1026,35 +1066,19 @@ int ab_matmul_bt_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const flo
     }
     AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
     AB_TRY(h2d_as_bf16(ctx, 2, 3, b, b_len, &db));
-    const size_t ld_bt = ab_round_up(n, 8);
-    AB_TRY(ab_ctx_stage(ctx, 13, k * ld_bt * 2 + 16, &dbt));
-    AB_TRY(abk_transpose16(ctx, db, n, k, k, dbt, ld_bt));
-    AB_TRY(ab_lm_head_logits(ctx, da, k, dbt, ld_bt, m, k, n, (float*)dc, n));
+    if (nn) AB_TRY(abk_gemm_nn(ctx, da, k, db, n, m, n, k, dc, AB_F32, n, 0.0f));
+    else AB_TRY(abk_gemm_nt(ctx, da, k, db, k, m, n, k, dc, AB_F32, n, 0.0f));
     return d2h_sync(ctx, c, dc, c_len * 4);
+}
+
+int ab_matmul_bt_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
+                            size_t m, size_t n, size_t k) {
+    return dense_host(ctx, false, a, a_len, b, b_len, c, c_len, m, n, k);
 }
 
 int ab_matmul_nn_dense_host(ab_ctx* ctx, const float* a, size_t a_len, const float* b, size_t b_len, float* c, size_t c_len,
                             size_t m, size_t n, size_t k) {
-    AB_TRY(bind(ctx));
-    AB_REQUIRE(a_len == m * k && b_len == k * n && c_len == m * n, AB_ERR_SHAPE);
-    AB_REQUIRE(k < (1ull << 31) && n < (1ull << 31) && m < (1ull << 31), AB_ERR_UNSUPPORTED);
-    if (c_len == 0) return AB_OK;
-    AB_REQUIRE(c, AB_ERR_NULL);
-    if (k) AB_REQUIRE(a && b, AB_ERR_NULL);
-    void *da = nullptr, *db = nullptr, *dat = nullptr, *dc = nullptr;
-    AB_TRY(ab_ctx_stage(ctx, 4, c_len * 4, &dc));
-    if (k == 0) {
-        AB_CUDA_CHECK(ctx, cudaMemsetAsync(dc, 0, c_len * 4, ctx->stream));
-        return d2h_sync(ctx, c, dc, c_len * 4);
-    }
-    AB_TRY(h2d_as_bf16(ctx, 0, 1, a, a_len, &da));
-    AB_TRY(h2d_as_bf16(ctx, 2, 3, b, b_len, &db));
-    const size_t ld_at = ab_round_up(m, 8);
-    AB_TRY(ab_ctx_stage(ctx, 13, k * ld_at * 2 + 16, &dat));
-    AB_TRY(abk_transpose16(ctx, da, m, k, k, dat, ld_at));
-    // C[m x n] = sum_k at[k][m] * b[k][n]
-    AB_TRY(abk_gemm_dw(ctx, dat, ld_at, db, n, k, m, n, (float*)dc, n, 0.0f));
-    return d2h_sync(ctx, c, dc, c_len * 4);
+    return dense_host(ctx, true, a, a_len, b, b_len, c, c_len, m, n, k);
 }
 
 // ------------------------------------------------------------------------------- batched

@@ -46,7 +46,7 @@ struct ab_ctx {
     unsigned int* counters = nullptr;
     size_t counters_len = 0;
     void* stage[16] = {};          // 0-11: two sets of six, consecutive host-buffer steps alternate between them;
-    size_t stage_bytes[16] = {};   // 12, 13: transposed operands of the dense output-head products; 14, 15: diagnostics
+    size_t stage_bytes[16] = {};   // 12, 13: spare; 14, 15: diagnostics
     // device status word: 0 = ok, otherwise the code a kernel's bounded wait left behind
     int* dev_status = nullptr;
     // copy streams + events of the host-buffer step (created on first use)
@@ -157,9 +157,14 @@ int abk_swiglu_act_quant(ab_ctx* ctx, const void* gate, const void* up, int dtyp
                          int inter_dtype, size_t ld_inter, int8_t* xq, size_t ld_xq, float* scales, int32_t* rowsums);
 int abk_rmsnorm_backward(ab_ctx* ctx, const float* d_output, const float* input, const float* weight, float* d_input,
                          float* d_weight, size_t m, size_t dim, float eps);
+int abk_simt_dense(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, int b_rows_are_k, size_t m, size_t n, size_t k,
+                   void* c, int c_dtype, size_t ld_c, float beta);
+int abk_gemm_nt(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                size_t ld_c, float beta);
+int abk_gemm_nn(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                size_t ld_c, float beta);
 int abk_cross_entropy(ab_ctx* ctx, const void* logits, int dtype, size_t ld, const uint32_t* targets, size_t m, size_t v,
                       float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t);
-int abk_transpose16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out);
 int abk_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale, const float* row_scale,
                           int accumulate);
 int abk_silu_mul_inplace(ab_ctx* ctx, float* gate, const float* up, size_t n);

@@ -81,7 +81,33 @@ __global__ void simt_dw_kernel(const __nv_bfloat16* __restrict__ dy, size_t ld_d
     *p = beta != 0.0f ? __fadd_rn(*p, acc) : acc;
 }
 
+// C[i][j] = (beta * C[i][j] +) sum_k A[i][k] * (b_rows_are_k ? B[k][j] : B[j][k]), bf16 operands, f32 accumulation
+__global__ void simt_dense_kernel(const __nv_bfloat16* __restrict__ a, size_t ld_a, const __nv_bfloat16* __restrict__ b, size_t ld_b,
+                                  int b_rows_are_k, size_t m, size_t n, size_t k, void* c, int c_dtype, size_t ld_c, float beta) {
+    size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
+    if (j >= n || i >= m) return;
+    float acc = 0.0f;
+    for (size_t t = 0; t < k; ++t)
+        acc = fmaf(__bfloat162float(a[i * ld_a + t]), __bfloat162float(b_rows_are_k ? b[t * ld_b + j] : b[j * ld_b + t]), acc);
+    if (beta != 0.0f) acc = __fadd_rn(acc, load_out(c, c_dtype, i * ld_c + j));
+    store_out(c, c_dtype, i * ld_c + j, acc);
+}
+
 }  // namespace
+
+int abk_simt_dense(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, int b_rows_are_k, size_t m, size_t n, size_t k,
+                   void* c, int c_dtype, size_t ld_c, float beta) {
+    if (m == 0 || n == 0) return AB_OK;
+    for (size_t m0 = 0; m0 < m; m0 += 65535) {   // the row index is a grid dimension
+        const size_t mm = m - m0 < 65535 ? m - m0 : 65535;
+        dim3 grid((unsigned)((n + 127) / 128), (unsigned)mm);
+        const size_t esz = c_dtype == AB_BF16 ? 2 : 4;
+        simt_dense_kernel<<<grid, 128, 0, ctx->stream>>>((const __nv_bfloat16*)a + m0 * ld_a, ld_a, (const __nv_bfloat16*)b, ld_b, b_rows_are_k,
+                                                        mm, n, k, (char*)c + m0 * ld_c * esz, c_dtype, ld_c, beta);
+        AB_LAUNCH_CHECK(ctx);
+    }
+    return AB_OK;
+}
 
 int abk_simt_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
                  size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {

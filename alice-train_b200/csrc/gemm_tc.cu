@@ -61,6 +61,11 @@ int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_
 int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
                        size_t ld_y, float beta);
 
+int abk_gemm2_nt(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                 size_t ld_c, float beta);
+int abk_gemm2_nn(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                 size_t ld_c, float beta);
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Dispatch: the CTA-pair tensor-core kernels take every operand TMA can describe (16-byte aligned
@@ -95,4 +100,21 @@ int abk_gemm_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t
     if (m == 0 || !aligned16(dy) || !aligned16(x) || ld_dy % 8 != 0 || ld_x % 8 != 0)
         return abk_simt_dw(ctx, dy, ld_dy, x, ld_x, m, out, in, dW, ld_dw, beta);
     return abk_gemm2_dw(ctx, dy, ld_dy, x, ld_x, m, out, in, dW, ld_dw, beta);
+}
+
+// Dense bf16 products (the unquantised output head): C = A . B^T and C = A . B, f32 accumulation.
+int abk_gemm_nt(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                size_t ld_c, float beta) {
+    if (m == 0 || n == 0) return AB_OK;
+    if (k == 0 || !aligned16(a) || !aligned16(b) || ld_a % 8 != 0 || ld_b % 8 != 0)
+        return abk_simt_dense(ctx, a, ld_a, b, ld_b, 0, m, n, k, c, c_dtype, ld_c, beta);
+    return abk_gemm2_nt(ctx, a, ld_a, b, ld_b, m, n, k, c, c_dtype, ld_c, beta);
+}
+
+int abk_gemm_nn(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                size_t ld_c, float beta) {
+    if (m == 0 || n == 0) return AB_OK;
+    if (k == 0 || !aligned16(a) || !aligned16(b) || ld_a % 8 != 0 || ld_b % 8 != 0)
+        return abk_simt_dense(ctx, a, ld_a, b, ld_b, 1, m, n, k, c, c_dtype, ld_c, beta);
+    return abk_gemm2_nn(ctx, a, ld_a, b, ld_b, m, n, k, c, c_dtype, ld_c, beta);
 }

@@ -6,6 +6,8 @@
 //   FWD  y  = (xq . Wc^T) * s_t/127 * gamma     int8 x ternary (unsigned w+1), s32 in TMEM
 //   DX   dx = gamma * dy . Wc                   bf16 x ternary, f32 in TMEM
 //   DW   dW = dy^T . x                          bf16 x bf16 (both MN-major), f32 in TMEM
+//   NT   C  = A . B^T                           bf16 x bf16 (both K-major): the dense output head's logits
+//   NN   C  = A . B                             bf16 x bf16 (A K-major, B MN-major): its d_hidden = d_logits . W
 //
 // A cluster of two CTAs walks 256x256 tiles persistently.  Per CTA:
 //   warp 0   TMA producer.  A (and for DW the B half) is loaded with the cta_group::2 form so
@@ -42,7 +44,7 @@ constexpr int kWarpsDW = 6;
 constexpr int kWarpsExp = 16;      // ids 0..15; 9 and 13 stay idle (they share the MMA warp's scheduler)
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's leader
 
-template <int MODE> struct Cfg { static constexpr int STAGES = MODE == DW ? 7 : 6; };
+template <int MODE> struct Cfg { static constexpr int STAGES = has_expanders(MODE) ? 6 : 7; };
 
 struct Params {
     int M, N, K;
@@ -190,7 +192,7 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint
 // The four MMAs of one pipeline stage in a single block of PTX.  Only the low word of a
 // shared-memory descriptor (start address, in 16-byte units) changes between them.  `first_acc`
 // is the accumulate flag of the first MMA (0 on the first k-block of a tile); the rest accumulate.
-template <int MODE, int KSTEP16>
+template <int MODE, int KSTEP16, int KSTEP16B = KSTEP16>
 __device__ __forceinline__ void umma_pair_x4(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                              uint32_t idesc, uint32_t first_acc) {
 #define AB_MMA4(KIND)                                                                              \
@@ -199,14 +201,14 @@ __device__ __forceinline__ void umma_pair_x4(uint32_t tmem_d, uint32_t a_lo, uin
         "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 pt, %6, %6;\n\t"                                     \
         "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"                                       \
         "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, p;\n\t"                         \
-        "add.u32 al, %1, %7;\n\tadd.u32 bl, %3, %7;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "add.u32 al, %1, %7;\n\tadd.u32 bl, %3, %10;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
         "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t"                        \
-        "add.u32 al, %1, %8;\n\tadd.u32 bl, %3, %8;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "add.u32 al, %1, %8;\n\tadd.u32 bl, %3, %11;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
         "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t"                        \
-        "add.u32 al, %1, %9;\n\tadd.u32 bl, %3, %9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
+        "add.u32 al, %1, %9;\n\tadd.u32 bl, %3, %12;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t" \
         "tcgen05.mma.cta_group::2.kind::" KIND " [%0], da, db, %5, pt;\n\t}"                       \
         ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first_acc),     \
-          "n"(KSTEP16), "n"(2 * KSTEP16), "n"(3 * KSTEP16)                                         \
+          "n"(KSTEP16), "n"(2 * KSTEP16), "n"(3 * KSTEP16), "n"(KSTEP16B), "n"(2 * KSTEP16B), "n"(3 * KSTEP16B) \
         : "memory")
     if (MODE == FWD) AB_MMA4("i8");
     else AB_MMA4("f16");
@@ -224,7 +226,7 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, 
 }
 
 template <int MODE>
-__global__ void __launch_bounds__((MODE == DW ? kWarpsDW : kWarpsExp) * 32, 1)
+__global__ void __launch_bounds__((has_expanders(MODE) ? kWarpsExp : kWarpsDW) * 32, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -232,7 +234,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint8_t* s_a = smem;
     uint8_t* s_b = s_a + STAGES * A_BYTES;
     uint8_t* s_p = s_b + STAGES * B_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + (MODE == DW ? 0 : STAGES * P_BYTES));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + (has_expanders(MODE) ? STAGES * P_BYTES : 0));
     // LEADER: "operands of the stage are ready in both CTAs".  FWD/DX: 16 expander-warp arrivals
     // (B halves written) plus the bytes of both A tiles; DW: one arrival plus the bytes of both
     // CTAs' A and B boxes.  One barrier, so the MMA thread waits once per stage.
@@ -252,11 +254,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t rank = cluster_ctarank();  // 0 = leader
     const int num_clusters = gridDim.x >> 1;
     // consumers of a published tile: the peer's producer, the MMA thread, 2 x 4 epilogue warps, 2 x 8 expander warps
-    constexpr uint32_t SCHED_CONSUMERS = MODE == DW ? 10 : 10 + 2 * NUM_EXP_WARPS;
+    constexpr uint32_t SCHED_CONSUMERS = has_expanders(MODE) ? 10 + 2 * NUM_EXP_WARPS : 10;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(full + s), MODE == DW ? 1 : 2 * NUM_EXP_WARPS);
+            mbar_init(smem_u32(full + s), has_expanders(MODE) ? 2 * NUM_EXP_WARPS : 1);
             mbar_init(smem_u32(unused_slot + s), 1);
             mbar_init(smem_u32(full_p + s), 1);
             mbar_init(smem_u32(empty + s), 1);
@@ -322,7 +324,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             // bytes counted on the leader's barrier per stage: both CTAs' A tiles (+ DW: both B halves)
-            constexpr uint32_t TX_LEADER = MODE == DW ? 2 * (A_BYTES + B_BYTES) : 2 * A_BYTES;
+            constexpr uint32_t TX_LEADER = has_expanders(MODE) ? 2 * A_BYTES : 2 * (A_BYTES + B_BYTES);
             constexpr uint32_t TX_P = MODE == FWD ? 128 * 32 : 128 * 16;
             bool ok = true;
             int gi = 0;
@@ -339,8 +341,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     // (FWD/DX) can only arrive after its codes landed, so the phase cannot complete
                     // on arrivals alone while the byte count is still unannounced.
                     if (rank == 0) {
-                        if (MODE == DW) mbar_expect_tx(smem_u32(full + stage), TX_LEADER);
-                        else mbar_expect_tx_only(smem_u32(full + stage), TX_LEADER);
+                        if (has_expanders(MODE)) mbar_expect_tx_only(smem_u32(full + stage), TX_LEADER);
+                        else mbar_expect_tx(smem_u32(full + stage), TX_LEADER);
                     }
                     if (MODE == FWD) {
                         mbar_expect_tx(smem_u32(full_p + stage), TX_P);
@@ -350,6 +352,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         mbar_expect_tx(smem_u32(full_p + stage), TX_P);
                         tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 16, n0);
                         tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
+                    } else if (MODE == NT) {
+                        // both operands K-major: 128 rows x 64 columns each, the layout the expanders write for B
+                        tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
+                        tma_load_2d_pair(smem_u32(s_b + stage * B_BYTES), &tm_b, lbar, kb * 64, n0);
+                    } else if (MODE == NN) {
+                        // A K-major as in DX, B MN-major as in DW (two boxes of 64 columns x 64 rows of K)
+                        tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
+#pragma unroll
+                        for (int b = 0; b < 2; ++b)
+                            tma_load_2d_pair(smem_u32(s_b + stage * B_BYTES + b * 8192), &tm_b, lbar, n0 + 64 * b, kb * 64);
                     } else {
 #ifdef AB_GEMM_TRACE
                         if (p.debug_flags & 1) {  // no loads: complete the byte count by hand
@@ -378,12 +390,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     } else if (warp == 1) {
         // ---------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN)
-                                                   : (MODE == DX ? make_idesc(1, 1, 1, 0, 0, BM, BN)
-                                                                 : make_idesc(1, 1, 1, 1, 1, BM, BN));
-            const uint64_t da0 = MODE == DW ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
-            const uint64_t db0 = MODE == DW ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
-            constexpr int KSTEP = (MODE == DW ? 2048 : 32) >> 4;
+            constexpr bool A_MN = MODE == DW, B_MN = MODE == DW || MODE == NN;   // operand stored with its M / N index contiguous
+            constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN) : make_idesc(1, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            const uint64_t da0 = A_MN ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
+            const uint64_t db0 = B_MN ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
+            constexpr int KSTEP = (A_MN ? 2048 : 32) >> 4, KSTEP_B = (B_MN ? 2048 : 32) >> 4;   // descriptor advance per K = 16
             // This single thread paces the whole pair: everything it executes per stage beyond the
             // MMAs themselves is tensor-pipe idle time.  So the ring is walked with the stage index
             // unrolled (barrier and descriptor addresses are immediates), the NEXT stage's barrier is
@@ -407,7 +418,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     AB_TRACE2(gi, 2);
                     tc_fence_after();
                     ready = mbar_try_cluster(full0 + 8 * ((s + 1) % STAGES), s + 1 == STAGES ? phase ^ 1 : phase);
-                    umma_pair_x4<MODE, KSTEP>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
+                    umma_pair_x4<MODE, KSTEP, KSTEP_B>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
                                               first_acc);
                     umma_commit_pair(empty0 + 8 * s);
                     AB_TRACE2(gi, 3);
@@ -431,7 +442,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int quad = warp & 3;
         int it = 0;
         bool ok = true;
-        const float gamma = MODE == DW ? 1.0f : *p.gamma;
+        const float gamma = has_expanders(MODE) ? *p.gamma : 1.0f;
         for (int tile = feed_next(feed, true, lane == 0, abort_flag); ok && tile < num_tiles;
              tile = feed_next(feed, true, lane == 0, abort_flag), ++it) {
             int m0, n0;
@@ -532,7 +543,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + acc) & PEER_MASK);
         }
-    } else if (MODE != DW && (warp & 3) != 1) {
+    } else if (has_expanders(MODE) && (warp & 3) != 1) {
         // --------------------------------------------------------------------- expanders
         // Warp slots 6,7,8,10,11,12,14,15 -> expander index 0..7; two threads per row of this CTA's
         // 128-row B half, four 16-byte chunks each.
@@ -649,7 +660,7 @@ __global__ void __launch_bounds__(128, 1) mma_pair_peak_kernel(int iters, int* s
 template <int MODE>
 static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
-    constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (MODE == DW ? 0 : P_BYTES)) + 512;
+    constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (has_expanders(MODE) ? P_BYTES : 0)) + 512;
     static_assert((4 * STAGES + 4 + 2 * SCHED_SLOTS) * 8 + 16 + 4 * SCHED_SLOTS <= 512, "barrier block");
     // per-device launch facts, looked up once; contexts on several host threads share them
     static std::mutex cache_mu;
@@ -674,7 +685,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     p.debug_flags = getenv("AB_TRACE_NOLOAD") ? 1 : 0;
 #endif
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3((MODE == DW ? kWarpsDW : kWarpsExp) * 32, 1, 1);
+    cfg.blockDim = dim3((has_expanders(MODE) ? kWarpsExp : kWarpsDW) * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -801,4 +812,35 @@ int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_
     p.out = dW; p.out_dtype = AB_F32; p.ld_out = (long long)ld_dw; p.beta = beta;
     p.n_fast = in <= out ? 1 : 0;
     return tc2::launch<tc::DW>(ctx, ta, tb, p);
+}
+
+// Dense products of the unquantised output head.  C[m x n] (f32 or bf16) = (beta * C +) A . B^T with A [m x k] and
+// B [n x k], both bf16 with the contraction index contiguous (the same operand layout the expanders produce for B).
+int abk_gemm2_nt(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                 size_t ld_c, float beta) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, k, m, ld_a * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, k, n, ld_b * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)m; p.N = (int)n; p.K = (int)k;
+    p.out = c; p.out_dtype = c_dtype; p.ld_out = (long long)ld_c; p.beta = beta;
+    p.n_fast = n <= m ? 1 : 0;   // walk the tiles so that the smaller operand is the one re-read from L2
+    return tc2::launch<tc::NT>(ctx, ta, tb, p);
+}
+
+// C[m x n] = (beta * C +) A . B with A [m x k] (contraction index contiguous) and B [k x n] (row index = contraction).
+int abk_gemm2_nn(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t ld_b, size_t m, size_t n, size_t k, void* c, int c_dtype,
+                 size_t ld_c, float beta) {
+    CUtensorMap ta, tb;
+    int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, k, m, ld_a * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, n, k, ld_b * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st) return st;
+    tc2::Params p{};
+    p.M = (int)m; p.N = (int)n; p.K = (int)k;
+    p.out = c; p.out_dtype = c_dtype; p.ld_out = (long long)ld_c; p.beta = beta;
+    p.n_fast = n <= m ? 1 : 0;
+    return tc2::launch<tc::NN>(ctx, ta, tb, p);
 }

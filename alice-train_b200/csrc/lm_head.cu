@@ -2,24 +2,21 @@
 // gradient, d_hidden = d_logits W and dW = d_logits^T h (src/bin/train_qat_70b.rs:98-112,1024-1101;
 // src/bin/train_qat_qwen35.rs:864-905).
 //
-// All three products run on the bf16 x bf16 pair GEMM of gemm_tc2.cu, which contracts over the ROW index of both
-// operands (C[a][b] = sum_t P[t][a] Q[t][b], the shape of dW = dy^T x).  Written that way:
-//     logits  [m x V]      = sum_k  hT[k][m]       * WT[k][V]        hT, WT: transposed copies (this file's transpose kernel)
-//     d_hidden[m x hidden] = sum_v  d_logitsT[v][m] * W[v][hidden]   d_logitsT: written by the cross-entropy kernel itself
-//     dW      [V x hidden] = sum_t  d_logits[t][V]  * h[t][hidden]
-// so the only extra traffic is the transposition of h (m x hidden) per step and of W once per optimizer step, a few
-// per cent of the 6 m V hidden flops at vocabulary size.
+// The three products run on the bf16 x bf16 modes of the pair GEMM (gemm_tc2.cu) with the operands as they lie in memory:
+//     logits  [m x V]      = h . W^T          NT: h [m x hidden] and W [V x hidden] both contract over their columns
+//     d_hidden[m x hidden] = d_logits . W     NN: d_logits [m x V] over its columns, W [V x hidden] over its rows
+//     dW      [V x hidden] = d_logits^T . h   DW: both over their rows (the shape of the STE gradient)
+// so nothing is transposed or copied.
 //
 // Cross-entropy in two launches, both streaming.  ce_row_stats_kernel: one block per token walks its row once with
 // 128-bit loads and keeps a running (max, sum of exp) per thread; the block's combined pair gives 1 / sum and the loss of
-// the target column.  ce_grad_kernel: a block takes 16 tokens x 1024 vocabulary entries, every thread four consecutive
-// entries of all 16 tokens (sixteen 128-bit loads in flight), forms p = exp(x - max) / sum and writes the gradient
-// (p - onehot) * scale twice: token-major (8 bytes per thread and token, coalesced along the vocabulary) and
-// vocabulary-major (16 tokens = one 32-byte sector per vocabulary entry, straight from the thread's registers).  The
-// logits are read twice in all (12 B moved per logit with f32 logits against 8 B of compulsory traffic).  A target
-// outside the vocabulary marks a token that does not count: loss 0 and a zero gradient row, as the reference's loop
-// skips it (src/bin/train_qat_70b.rs:1068-1072).  Arithmetic as the reference's cross_entropy_loss: f32 throughout,
-// probabilities floored at 1e-10 inside the logarithm; exp through the hardware's ex2 (relative error ~1e-6).
+// the target column.  ce_grad_kernel: every thread takes eight consecutive vocabulary entries of one token, forms
+// p = exp(x - max) / sum and writes the gradient (p - onehot) * scale as one 16-byte store of bf16.  (A variant that also
+// writes the gradient transposed, through shared-memory tiles, serves callers that want it vocabulary-major.)  The
+// logits are read twice in all.  A target outside the vocabulary marks a token that does not count: loss 0 and a zero
+// gradient row, as the reference's loop skips it (src/bin/train_qat_70b.rs:1068-1072).  Arithmetic as the reference's
+// cross_entropy_loss: f32 throughout, probabilities floored at 1e-10 inside the logarithm; exp through the hardware's
+// ex2 (relative error ~1e-6).
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
@@ -27,11 +24,10 @@
 
 namespace {
 
-constexpr int kTok = 16;        // tokens per gradient block: one full sector per vocabulary entry in the transposed gradient
 constexpr int kStatThreads = 256;
 constexpr int kGradThreads = 256;
-constexpr int kGradCols = kGradThreads * 4;
-constexpr int kTile = 64;       // transpose tile
+constexpr int kGTok = 64;       // tokens x vocabulary entries of a gradient tile: both orientations leave as whole 128-byte lines
+constexpr int kGVoc = 128;
 
 template <typename T> __device__ __forceinline__ float ld_logit(const T* p, size_t i);
 template <> __device__ __forceinline__ float ld_logit<float>(const float* p, size_t i) { return p[i]; }
@@ -59,16 +55,19 @@ template <> __device__ __forceinline__ void ld_logit4<__nv_bfloat16>(const __nv_
     }
 }
 
-__device__ __forceinline__ void online_add(float& mx, float& sm, float x) {
-    if (x > mx) { sm = sm * __expf(mx - x); mx = x; }
-    if (x > -CUDART_INF_F) sm += __expf(x - mx);
+// running (max, sum of exp(x - max)) over four more values; mx starts at a large negative FINITE number so that
+// exp(x - mx) of a masked slot (x = -inf) is 0 and never inf - inf
+__device__ __forceinline__ void online_add4(float& mx, float& sm, const float (&x)[4]) {
+    const float m4 = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    if (m4 > mx) { sm = sm * __expf(mx - m4); mx = m4; }
+    sm += (__expf(x[0] - mx) + __expf(x[1] - mx)) + (__expf(x[2] - mx) + __expf(x[3] - mx));
 }
 __device__ __forceinline__ void online_merge(float& mx, float& sm, float om, float os) {
     const float nm = fmaxf(mx, om);
-    const float a = mx > -CUDART_INF_F ? sm * __expf(mx - nm) : 0.0f;
-    const float b = om > -CUDART_INF_F ? os * __expf(om - nm) : 0.0f;
-    mx = nm; sm = a + b;
+    sm = sm * __expf(mx - nm) + os * __expf(om - nm);
+    mx = nm;
 }
+constexpr float kVeryNegative = -3.0e38f;
 
 template <typename T>
 __global__ void __launch_bounds__(kStatThreads)
@@ -78,20 +77,19 @@ ce_row_stats_kernel(const T* __restrict__ logits, size_t ld, const uint32_t* __r
     const size_t t = blockIdx.x;
     const T* row = logits + t * ld;
     const bool vec = (reinterpret_cast<uintptr_t>(row) & (4 * sizeof(T) - 1)) == 0;
-    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F}, sm[2] = {0.0f, 0.0f};
+    float mx[2] = {kVeryNegative, kVeryNegative}, sm[2] = {0.0f, 0.0f};
     size_t i = (size_t)threadIdx.x * 4;
     for (; i + (size_t)kStatThreads * 4 < v; i += (size_t)kStatThreads * 8) {   // two independent chains, two loads in flight
         float x0[4], x1[4];
         ld_logit4(row, i, v, vec, x0);
         ld_logit4(row, i + (size_t)kStatThreads * 4, v, vec, x1);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { online_add(mx[0], sm[0], x0[e]); online_add(mx[1], sm[1], x1[e]); }
+        online_add4(mx[0], sm[0], x0);
+        online_add4(mx[1], sm[1], x1);
     }
     if (i < v) {
         float x0[4];
         ld_logit4(row, i, v, vec, x0);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) online_add(mx[0], sm[0], x0[e]);
+        online_add4(mx[0], sm[0], x0);
     }
     online_merge(mx[0], sm[0], mx[1], sm[1]);
     for (int o = 16; o > 0; o >>= 1)
@@ -113,82 +111,123 @@ ce_row_stats_kernel(const T* __restrict__ logits, size_t ld, const uint32_t* __r
     }
 }
 
+// A block takes kGTok tokens x kGVoc vocabulary entries.  Phase 1: thread (v, t mod 2) walks the tokens of its column with
+// coalesced 4-byte loads, forms the gradient and drops it as bf16 into two shared tiles, token-major and vocabulary-major
+// (row pitches of 272 and 132 bytes keep both the 2-byte stores and the later reads conflict-free).  Phase 2: both
+// tiles leave as 16-byte stores that fill whole 128-byte lines: 256 bytes per token row, 128 bytes per vocabulary row.
 template <typename T>
 __global__ void __launch_bounds__(kGradThreads)
-ce_grad_kernel(const T* __restrict__ logits, size_t ld, const uint32_t* __restrict__ targets, size_t m, size_t v, float d_scale,
+ce_grad_both_kernel(const T* __restrict__ logits, size_t ld, const uint32_t* __restrict__ targets, size_t m, size_t v, float d_scale,
                const float* __restrict__ rmax, const float* __restrict__ rinv, __nv_bfloat16* __restrict__ d_logits, size_t ld_d,
                __nv_bfloat16* __restrict__ d_logits_t, size_t ld_t) {
-    const size_t t0 = (size_t)blockIdx.y * kTok;
-    const int ntok = (int)(m - t0 < (size_t)kTok ? m - t0 : (size_t)kTok);
-    const size_t j0 = (size_t)blockIdx.x * kGradCols + (size_t)threadIdx.x * 4;
-    if (j0 >= v) return;
-    const bool vec_in = (reinterpret_cast<uintptr_t>(logits) & (4 * sizeof(T) - 1)) == 0 && (ld % 4) == 0;
-    float x[kTok][4];
-#pragma unroll
-    for (int t = 0; t < kTok; ++t) {
-        if (t < ntok) ld_logit4(logits + (t0 + t) * ld, j0, v, vec_in, x[t]);
-        else { x[t][0] = x[t][1] = x[t][2] = x[t][3] = -CUDART_INF_F; }
+    __shared__ __align__(16) unsigned short s_nat[kGTok][kGVoc + 8];    // [token][vocab], pitch 272 B
+    __shared__ __align__(16) unsigned short s_tr[kGVoc][kGTok + 2];     // [vocab][token], pitch 132 B
+    __shared__ float s_max[kGTok], s_inv[kGTok];
+    __shared__ uint32_t s_tg[kGTok];
+    const size_t t0 = (size_t)blockIdx.y * kGTok, j0 = (size_t)blockIdx.x * kGVoc;
+    const int ntok = (int)(m - t0 < (size_t)kGTok ? m - t0 : (size_t)kGTok);
+    const int nvoc = (int)(v - j0 < (size_t)kGVoc ? v - j0 : (size_t)kGVoc);
+    if (threadIdx.x < kGTok) {
+        const int t = threadIdx.x;
+        const bool in = t < ntok;
+        s_tg[t] = in ? targets[t0 + t] : 0xffffffffu;
+        s_max[t] = in ? rmax[t0 + t] : 0.0f;
+        s_inv[t] = in ? rinv[t0 + t] : 0.0f;
     }
-    uint32_t pk[4][kTok / 2];   // [vocabulary entry][token pair]: a row is the 32 bytes of the transposed gradient
+    __syncthreads();
+    const int vl = threadIdx.x & (kGVoc - 1), tsub = threadIdx.x / kGVoc;   // 256 threads: two tokens per pass
+    const bool v_ok = vl < nvoc;
+    const size_t col = j0 + vl;
+#pragma unroll 1
+    for (int i0 = 0; i0 < kGTok / 2; i0 += 16) {   // sixteen loads in flight per thread
+        float x[16];
 #pragma unroll
-    for (int t = 0; t < kTok; ++t) {
-        uint32_t tg = 0xffffffffu;
-        float mx = 0.0f, inv = 0.0f;
-        if (t < ntok) { tg = targets[t0 + t]; mx = rmax[t0 + t]; inv = rinv[t0 + t]; }
-        const bool counted = tg < v;
-        uint32_t bits[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float gr = 0.0f;
-            if (counted && j0 + e < v) {
-                const float p = __expf(x[t][e] - mx) * inv;
-                gr = (j0 + e == tg ? p - 1.0f : p) * d_scale;
-            }
-            bits[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(gr));
-            if (t & 1) pk[e][t >> 1] |= bits[e] << 16;
-            else pk[e][t >> 1] = bits[e];
+        for (int u = 0; u < 16; ++u) {
+            const int t = 2 * (i0 + u) + tsub;
+            x[u] = (v_ok && t < ntok) ? ld_logit(logits, (t0 + t) * ld + col) : 0.0f;
         }
-        if (d_logits && t < ntok) {
-            __nv_bfloat16* dst = d_logits + (t0 + t) * ld_d + j0;
-            if (j0 + 4 <= v && (ld_d % 4) == 0 && (reinterpret_cast<uintptr_t>(d_logits) & 7) == 0)
-                *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (bits[1] << 16), bits[2] | (bits[3] << 16));
-            else
-                for (int e = 0; e < 4 && j0 + e < v; ++e) dst[e] = __ushort_as_bfloat16((unsigned short)bits[e]);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int t = 2 * (i0 + u) + tsub;
+            const uint32_t tg = s_tg[t];
+            float gr = 0.0f;
+            if (v_ok && t < ntok && tg < v) {
+                const float p = __expf(x[u] - s_max[t]) * s_inv[t];
+                gr = (col == tg ? p - 1.0f : p) * d_scale;
+            }
+            const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16_rn(gr));
+            s_nat[t][vl] = bits;
+            s_tr[vl][t] = bits;
+        }
+    }
+    __syncthreads();
+    if (d_logits) {
+        const bool vec = (ld_d % 8) == 0 && (reinterpret_cast<uintptr_t>(d_logits) & 15) == 0;
+        for (int idx = threadIdx.x; idx < kGTok * (kGVoc / 8); idx += kGradThreads) {
+            const int t = idx / (kGVoc / 8), c = idx % (kGVoc / 8);
+            if (t >= ntok || c * 8 >= nvoc) continue;
+            __nv_bfloat16* dst = d_logits + (t0 + t) * ld_d + j0 + c * 8;
+            if (vec && c * 8 + 8 <= nvoc) {
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s_nat[t][c * 8]);
+            } else {
+                for (int e = 0; e < 8 && c * 8 + e < nvoc; ++e) dst[e] = __ushort_as_bfloat16(s_nat[t][c * 8 + e]);
+            }
         }
     }
     if (d_logits_t) {
-        const bool vec_t = ntok == kTok && ((ld_t * 2) % 16 == 0) && ((reinterpret_cast<uintptr_t>(d_logits_t) & 15) == 0);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            if (j0 + e < v) {
-                __nv_bfloat16* dst = d_logits_t + (j0 + e) * ld_t + t0;
-                if (vec_t) {
-                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(pk[e][0], pk[e][1], pk[e][2], pk[e][3]);
-                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(pk[e][4], pk[e][5], pk[e][6], pk[e][7]);
-                } else {
-#pragma unroll
-                    for (int t = 0; t < kTok; ++t)
-                        if (t < ntok) dst[t] = __ushort_as_bfloat16((unsigned short)(pk[e][t >> 1] >> (16 * (t & 1))));
-                }
+        const bool vec = (ld_t % 8) == 0 && (reinterpret_cast<uintptr_t>(d_logits_t) & 15) == 0;
+        for (int idx = threadIdx.x; idx < kGVoc * (kGTok / 8); idx += kGradThreads) {
+            const int vv = idx / (kGTok / 8), c = idx % (kGTok / 8);
+            if (vv >= nvoc || c * 8 >= ntok) continue;
+            __nv_bfloat16* dst = d_logits_t + (j0 + vv) * ld_t + t0 + c * 8;
+            if (vec && c * 8 + 8 <= ntok) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(&s_tr[vv][c * 8]);   // 4-byte aligned: pitch 132, c * 16
+                *reinterpret_cast<uint4*>(dst) = make_uint4(src[0], src[1], src[2], src[3]);
+            } else {
+                for (int e = 0; e < 8 && c * 8 + e < ntok; ++e) dst[e] = __ushort_as_bfloat16(s_tr[vv][c * 8 + e]);
             }
         }
     }
 }
 
-// out[c][r] = in[r][c], 64 x 64 tiles through shared memory, 16-bit elements
-__global__ void __launch_bounds__(256)
-transpose16_kernel(const uint16_t* __restrict__ in, size_t rows, size_t cols, size_t ld_in, uint16_t* __restrict__ out, size_t ld_out) {
-    __shared__ uint16_t tile[kTile][kTile + 2];
-    const size_t r0 = (size_t)blockIdx.y * kTile, c0 = (size_t)blockIdx.x * kTile;
-    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   // 64 x 4
-    for (int i = ty; i < kTile; i += 4) {
-        const size_t r = r0 + i, c = c0 + tx;
-        tile[i][tx] = (r < rows && c < cols) ? in[r * ld_in + c] : (uint16_t)0;
+// Token-major gradient only: block = one token x 2048 vocabulary entries, thread = eight consecutive entries.
+template <typename T>
+__global__ void __launch_bounds__(kGradThreads)
+ce_grad_kernel(const T* __restrict__ logits, size_t ld, const uint32_t* __restrict__ targets, size_t v, float d_scale,
+               const float* __restrict__ rmax, const float* __restrict__ rinv, __nv_bfloat16* __restrict__ d_logits, size_t ld_d) {
+    const size_t t = blockIdx.x;
+    const size_t j0 = ((size_t)blockIdx.y * kGradThreads + threadIdx.x) * 8;
+    if (j0 >= v) return;
+    const T* row = logits + t * ld;
+    const bool vec_in = (reinterpret_cast<uintptr_t>(row) & (4 * sizeof(T) - 1)) == 0;
+    float x[2][4];
+    ld_logit4(row, j0, v, vec_in, x[0]);
+    ld_logit4(row, j0 + 4, v, vec_in, x[1]);
+    const uint32_t tg = targets[t];
+    const float mx = rmax[t], inv = rinv[t];
+    const bool counted = tg < v;
+    uint32_t pk[4];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        float g[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const size_t j = j0 + e + h;
+            float gr = 0.0f;
+            if (counted && j < v) {
+                const float p = __expf(x[(e + h) >> 2][(e + h) & 3] - mx) * inv;
+                gr = (j == tg ? p - 1.0f : p) * d_scale;
+            }
+            g[h] = gr;
+        }
+        const __nv_bfloat162 b2 = __floats2bfloat162_rn(g[0], g[1]);
+        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
     }
-    __syncthreads();
-    for (int i = ty; i < kTile; i += 4) {
-        const size_t c = c0 + i, r = r0 + tx;
-        if (c < cols && r < rows) out[c * ld_out + r] = tile[tx][i];
+    __nv_bfloat16* dst = d_logits + t * ld_d + j0;
+    if (j0 + 8 <= v && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    } else {
+        for (int e = 0; e < 8 && j0 + e < v; ++e) dst[e] = __ushort_as_bfloat16((unsigned short)(pk[e >> 1] >> (16 * (e & 1))));
     }
 }
 
@@ -197,40 +236,30 @@ transpose16_kernel(const uint16_t* __restrict__ in, size_t rows, size_t cols, si
 int abk_cross_entropy(ab_ctx* ctx, const void* logits, int dtype, size_t ld, const uint32_t* targets, size_t m, size_t v,
                       float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t) {
     if (m == 0 || v == 0) return AB_OK;
-    if ((m + kTok - 1) / kTok > 65535) return AB_ERR_UNSUPPORTED;
+    if ((m + kGTok - 1) / kGTok > 65535 || (v + kGradThreads * 8 - 1) / (kGradThreads * 8) > 65535) return AB_ERR_UNSUPPORTED;
     void* stats = nullptr;   // [max per row][1 / sum per row]
     int st = ab_ctx_scratch(ctx, 2 * m * sizeof(float), &stats);
     if (st) return st;
     float* rmax = static_cast<float*>(stats);
     float* rinv = rmax + m;
-    const bool grad = d_logits || d_logits_t;
-    dim3 ggrid((unsigned)((v + kGradCols - 1) / kGradCols), (unsigned)((m + kTok - 1) / kTok));
-    if (dtype == AB_BF16) {
-        ce_row_stats_kernel<__nv_bfloat16><<<(unsigned)m, kStatThreads, 0, ctx->stream>>>((const __nv_bfloat16*)logits, ld, targets, v, rmax, rinv, loss);
-        AB_LAUNCH_CHECK(ctx);
-        if (grad) {
-            ce_grad_kernel<__nv_bfloat16><<<ggrid, kGradThreads, 0, ctx->stream>>>((const __nv_bfloat16*)logits, ld, targets, m, v, d_scale, rmax, rinv,
-                                                                                  (__nv_bfloat16*)d_logits, ld_d, (__nv_bfloat16*)d_logits_t, ld_t);
-            AB_LAUNCH_CHECK(ctx);
-        }
-    } else {
-        ce_row_stats_kernel<float><<<(unsigned)m, kStatThreads, 0, ctx->stream>>>((const float*)logits, ld, targets, v, rmax, rinv, loss);
-        AB_LAUNCH_CHECK(ctx);
-        if (grad) {
-            ce_grad_kernel<float><<<ggrid, kGradThreads, 0, ctx->stream>>>((const float*)logits, ld, targets, m, v, d_scale, rmax, rinv,
-                                                                          (__nv_bfloat16*)d_logits, ld_d, (__nv_bfloat16*)d_logits_t, ld_t);
-            AB_LAUNCH_CHECK(ctx);
-        }
-    }
-    return AB_OK;
-}
-
-int abk_transpose16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out) {
-    if (rows == 0 || cols == 0) return AB_OK;
-    const size_t gx = (cols + kTile - 1) / kTile, gy = (rows + kTile - 1) / kTile;
-    if (gy > 65535) return AB_ERR_UNSUPPORTED;
-    dim3 grid((unsigned)gx, (unsigned)gy);
-    transpose16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)in, rows, cols, ld_in, (uint16_t*)out, ld_out);
-    AB_LAUNCH_CHECK(ctx);
+    dim3 bgrid((unsigned)((v + kGVoc - 1) / kGVoc), (unsigned)((m + kGTok - 1) / kGTok));
+    dim3 ngrid((unsigned)m, (unsigned)((v + kGradThreads * 8 - 1) / (kGradThreads * 8)));
+#define AB_CE(T)                                                                                                                   \
+    do {                                                                                                                           \
+        ce_row_stats_kernel<T><<<(unsigned)m, kStatThreads, 0, ctx->stream>>>((const T*)logits, ld, targets, v, rmax, rinv, loss); \
+        AB_LAUNCH_CHECK(ctx);                                                                                                      \
+        if (d_logits_t) {                                                                                                          \
+            ce_grad_both_kernel<T><<<bgrid, kGradThreads, 0, ctx->stream>>>((const T*)logits, ld, targets, m, v, d_scale, rmax, rinv, \
+                                                                          (__nv_bfloat16*)d_logits, ld_d, (__nv_bfloat16*)d_logits_t, ld_t); \
+            AB_LAUNCH_CHECK(ctx);                                                                                                  \
+        } else if (d_logits) {                                                                                                     \
+            ce_grad_kernel<T><<<ngrid, kGradThreads, 0, ctx->stream>>>((const T*)logits, ld, targets, v, d_scale, rmax, rinv,      \
+                                                                     (__nv_bfloat16*)d_logits, ld_d);                             \
+            AB_LAUNCH_CHECK(ctx);                                                                                                  \
+        }                                                                                                                          \
+    } while (0)
+    if (dtype == AB_BF16) AB_CE(__nv_bfloat16);
+    else AB_CE(float);
+#undef AB_CE
     return AB_OK;
 }

@@ -14,7 +14,8 @@
 // 16-row stages reach 14.5 us, 32-row stages 12.8.  Per-block time stamps then showed where the rest went: any memory
 // access made while the rings are full waits behind ~200 KB of queued code requests per SM (1.7 us for the vector, as
 // much again for a result exchanged through memory), so the vector is requested BEFORE the first codes, nothing on the
-// critical path goes through global memory twice.  (Handing the units out on demand from a ticket counter was tried and
+// critical path goes through global memory twice.  (Requesting the codes even earlier, before the wait for the launch in
+// front, was measured and is slower for the same reason: 18.3 against 16.7 us.)  (Handing the units out on demand from a ticket counter was tried and
 // was slower: a ticket's round trip waits in the same queue.)
 //
 // Work units.  K is cut into chunks (grid.y), whose digits a block keeps in shared memory; a unit is one 32-row group x
@@ -170,6 +171,31 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
+    // ---- This warp's producer (state in lane 0).  The warp's units are my_first, my_first + warps_total, ...; the
+    // request cursor runs up to `stages` spans ahead of the consumer.
+    int req_seq = 0, req_sp = 0, req_len = 0, req_x = 0, iss_st = 0;
+    size_t req_row = 0;
+    bool req_open = false, req_done = false;
+    auto issue_one = [&]() -> bool {  // lane 0: request the next span of this warp's stream; false when the stream has ended
+        if (req_done) return false;
+        if (!req_open || req_sp == req_len) {
+            if (req_open) ++req_seq;
+            const unsigned long long u = (unsigned long long)my_first + (unsigned long long)req_seq * warps_total;
+            if (u >= units) { req_done = true; return false; }
+            const unsigned int grp = (unsigned int)u / subs, sub = (unsigned int)u - grp * subs;
+            req_row = (size_t)grp * kJobRows;
+            req_x = (span0 + (int)sub * p.unit_spans) * (kSpan / 4);
+            const int left = spans - (int)sub * p.unit_spans;
+            req_len = left < p.unit_spans ? left : p.unit_spans;
+            req_sp = 0;
+            req_open = true;
+        }
+        mbar_expect_tx(bar_u32 + 8 * iss_st, kStageBytes);
+        tma_load_2d(ring_u32 + iss_st * kStageBytes, &tm, bar_u32 + 8 * iss_st, req_x + req_sp * (kSpan / 4), (int)req_row);
+        ++req_sp;
+        if (++iss_st == stages) iss_st = 0;
+        return true;
+    };
     // everything below reads or writes memory an earlier kernel in the stream may still be producing
     asm volatile("griddepcontrol.wait;" ::: "memory");
     AB_MV_STAMP(1);
@@ -219,31 +245,6 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         }
     }
 
-    // ---- This warp's producer (state in lane 0).  The warp's units are my_first, my_first + warps_total, ...; the
-    // request cursor runs up to `stages` spans ahead of the consumer.
-    int req_seq = 0, req_sp = 0, req_len = 0, req_x = 0, iss_st = 0;
-    size_t req_row = 0;
-    bool req_open = false, req_done = false;
-    auto issue_one = [&]() -> bool {  // lane 0: request the next span of this warp's stream; false when the stream has ended
-        if (req_done) return false;
-        if (!req_open || req_sp == req_len) {
-            if (req_open) ++req_seq;
-            const unsigned long long u = (unsigned long long)my_first + (unsigned long long)req_seq * warps_total;
-            if (u >= units) { req_done = true; return false; }
-            const unsigned int grp = (unsigned int)u / subs, sub = (unsigned int)u - grp * subs;
-            req_row = (size_t)grp * kJobRows;
-            req_x = (span0 + (int)sub * p.unit_spans) * (kSpan / 4);
-            const int left = spans - (int)sub * p.unit_spans;
-            req_len = left < p.unit_spans ? left : p.unit_spans;
-            req_sp = 0;
-            req_open = true;
-        }
-        mbar_expect_tx(bar_u32 + 8 * iss_st, kStageBytes);
-        tma_load_2d(ring_u32 + iss_st * kStageBytes, &tm, bar_u32 + 8 * iss_st, req_x + req_sp * (kSpan / 4), (int)req_row);
-        ++req_sp;
-        if (++iss_st == stages) iss_st = 0;
-        return true;
-    };
     if (lane == 0)
         for (int s = 0; s < stages; ++s)
             if (!issue_one()) break;

@@ -22,7 +22,6 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRegChunks = 8;   // 8 x 8 elements x 256 threads = rows up to 16384 stay in registers
 
 template <typename T> struct Vec8;
 template <> struct Vec8<__nv_bfloat16> {
@@ -80,46 +79,51 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
     return __fdiv_rn(1.0f, __fadd_rn(1.0f, __uint_as_float(bits)));
 }
 
-template <typename V>
-__device__ __forceinline__ V block_reduce(V v, V* smem /*[8]*/, bool is_max) {
+template <int THREADS, typename V>
+__device__ __forceinline__ V block_reduce(V v, V* smem /*[THREADS / 32]*/, bool is_max) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (int o = 16; o > 0; o >>= 1) {
         V other = __shfl_xor_sync(0xffffffffu, v, o);
         v = is_max ? (other > v ? other : v) : v + other;
     }
+    if (THREADS == 32) return v;   // one warp per row: the shuffles are the whole reduction
     __syncthreads();   // smem may still be read from the previous reduction
     if (lane == 0) smem[wid] = v;
     __syncthreads();
     V r = smem[0];
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) r = is_max ? (smem[i] > r ? smem[i] : r) : r + smem[i];
+    for (int i = 1; i < THREADS / 32; ++i) r = is_max ? (smem[i] > r ? smem[i] : r) : r + smem[i];
     return r;
 }
 
 // MODE 0: RMSNorm of x (weight w);  MODE 1: SwiGLU of (x = gate, x2 = up).  The row's result goes to `y` (optional, TY)
-// and, quantised per token, to xq / scales / rowsums (optional).
-template <int MODE, typename T, typename TY>
-__global__ void __launch_bounds__(kThreads)
+// and, quantised per token, to xq / scales / rowsums (optional).  One block of THREADS threads per row; a thread keeps up
+// to CH chunks of 8 results in registers between the abs-max pass and the rounding pass (rows longer than
+// THREADS * CH * 8 recompute instead).  Short rows take few threads and many chunks (more rows in flight per SM, cheap
+// reductions), long rows many threads and few chunks (low register count, full occupancy: SwiGLU's exp and divide make
+// that kernel issue-bound).
+template <int MODE, typename T, typename TY, int THREADS, int CH>
+__global__ void __launch_bounds__(THREADS)
 row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const float* __restrict__ w, size_t m, size_t k,
                         size_t ld_x, float eps, TY* __restrict__ y, size_t ld_y, int8_t* __restrict__ xq, size_t ld_xq,
                         float* __restrict__ scales, int32_t* __restrict__ rowsums, int vec_ok) {
-    __shared__ double s_d[kThreads / 32];
-    __shared__ float s_f[kThreads / 32];
-    __shared__ int s_i[kThreads / 32];
+    __shared__ double s_d[THREADS / 32];
+    __shared__ float s_f[THREADS / 32];
+    __shared__ int s_i[THREADS / 32];
     const size_t t = blockIdx.x;
     const T* row = x + t * ld_x;
     const T* row2 = MODE == 1 ? x2 + t * ld_x : nullptr;
     const size_t k8 = vec_ok ? k / 8 : 0;
-    const bool in_regs = k8 <= (size_t)kRegChunks * kThreads;
-    float cache[kRegChunks][8];
+    const bool in_regs = k8 <= (size_t)CH * THREADS;
+    float cache[CH][8];
 
     float mul = 1.0f;   // RMSNorm: inv_rms
     if (MODE == 0) {
         double ss = 0.0;
         if (in_regs) {
 #pragma unroll
-            for (int c = 0; c < kRegChunks; ++c) {
-                const size_t g = (size_t)c * kThreads + threadIdx.x;
+            for (int c = 0; c < CH; ++c) {
+                const size_t g = (size_t)c * THREADS + threadIdx.x;
                 if (g < k8) {
                     Vec8<T>::load(row + g * 8, cache[c]);
 #pragma unroll
@@ -127,18 +131,18 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
                 }
             }
         } else {
-            for (size_t g = threadIdx.x; g < k8; g += kThreads) {
+            for (size_t g = threadIdx.x; g < k8; g += THREADS) {
                 float v[8];
                 Vec8<T>::load(row + g * 8, v);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) ss += (double)v[i] * (double)v[i];
             }
         }
-        for (size_t i = k8 * 8 + threadIdx.x; i < k; i += kThreads) {
+        for (size_t i = k8 * 8 + threadIdx.x; i < k; i += THREADS) {
             const double v = (double)Vec8<T>::one(row + i);
             ss += v * v;
         }
-        ss = block_reduce<double>(ss, s_d, false);
+        ss = block_reduce<THREADS, double>(ss, s_d, false);
         mul = __fdiv_rn(1.0f, (float)sqrt(ss / (double)k + (double)eps));
     }
     // value of element i of the row after the operation, from the raw inputs
@@ -149,8 +153,8 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
     float amax = 0.0f;
     if (in_regs) {
 #pragma unroll
-        for (int c = 0; c < kRegChunks; ++c) {
-            const size_t g = (size_t)c * kThreads + threadIdx.x;
+        for (int c = 0; c < CH; ++c) {
+            const size_t g = (size_t)c * THREADS + threadIdx.x;
             if (g < k8) {
                 float b[8];
                 if (MODE == 1) {
@@ -166,7 +170,7 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
             }
         }
     } else {
-        for (size_t g = threadIdx.x; g < k8; g += kThreads) {
+        for (size_t g = threadIdx.x; g < k8; g += THREADS) {
             float a[8], b[8];
             Vec8<T>::load(row + g * 8, a);
             if (MODE == 1) Vec8<T>::load(row2 + g * 8, b);
@@ -178,13 +182,13 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
             if (y) Vec8<TY>::store(y + t * ld_y + g * 8, a);
         }
     }
-    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += kThreads) {
+    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += THREADS) {
         const float v = value(Vec8<T>::one(row + i), MODE == 1 ? Vec8<T>::one(row2 + i) : 0.0f, i);
         amax = fmaxf(amax, fabsf(v));
         if (y) Vec8<TY>::store_one(y + t * ld_y + i, v);
     }
     if (!xq) return;
-    amax = block_reduce<float>(amax, s_f, true);
+    amax = block_reduce<THREADS, float>(amax, s_f, true);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     int8_t* orow = xq + t * ld_xq;
     int sum = 0;
@@ -199,12 +203,12 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
     };
     if (in_regs) {
 #pragma unroll
-        for (int c = 0; c < kRegChunks; ++c) {
-            const size_t g = (size_t)c * kThreads + threadIdx.x;
+        for (int c = 0; c < CH; ++c) {
+            const size_t g = (size_t)c * THREADS + threadIdx.x;
             if (g < k8) emit8(cache[c], g);
         }
     } else {
-        for (size_t g = threadIdx.x; g < k8; g += kThreads) {
+        for (size_t g = threadIdx.x; g < k8; g += THREADS) {
             float a[8], b[8];
             Vec8<T>::load(row + g * 8, a);
             if (MODE == 1) Vec8<T>::load(row2 + g * 8, b);
@@ -213,13 +217,13 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
             emit8(a, g);
         }
     }
-    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += kThreads) {
+    for (size_t i = k8 * 8 + threadIdx.x; i < k; i += THREADS) {
         const int q = quant1(value(Vec8<T>::one(row + i), MODE == 1 ? Vec8<T>::one(row2 + i) : 0.0f, i), inv);
         sum += q;
         orow[i] = (int8_t)q;
     }
-    for (size_t i = k + threadIdx.x; i < ld_xq; i += kThreads) orow[i] = 0;   // padded pitch never feeds garbage to the GEMM
-    sum = block_reduce<int>(sum, s_i, false);
+    for (size_t i = k + threadIdx.x; i < ld_xq; i += THREADS) orow[i] = 0;   // padded pitch never feeds garbage to the GEMM
+    sum = block_reduce<THREADS, int>(sum, s_i, false);
     if (threadIdx.x == 0) {
         scales[t] = amax;
         if (rowsums) rowsums[t] = sum;
@@ -246,8 +250,8 @@ rmsnorm_backward_kernel(const float* __restrict__ dy, const float* __restrict__ 
             ss += (double)xv * (double)xv;
             dsum = __fadd_rn(dsum, __fmul_rn(__fmul_rn(dr[d], w[d]), xv));
         }
-        ss = block_reduce<double>(ss, s_d, false);
-        dsum = block_reduce<float>(dsum, s_f, false);
+        ss = block_reduce<kThreads, double>(ss, s_d, false);
+        dsum = block_reduce<kThreads, float>(dsum, s_f, false);
         const float inv_rms = (float)(1.0 / sqrt(ss / (double)dim + (double)eps));
         const float inv_rms3 = __fmul_rn(__fmul_rn(inv_rms, inv_rms), inv_rms);
         const float dimf = (float)dim;
@@ -307,9 +311,21 @@ int launch_row_op(ab_ctx* ctx, const void* x, const void* x2, int x_dtype, const
                  (!x2 || (reinterpret_cast<uintptr_t>(x2) & 15) == 0) &&
                  (!y || (((reinterpret_cast<uintptr_t>(y) & 15) == 0) && ((ld_y * ysz) % 16 == 0))) &&
                  (!xq || (((reinterpret_cast<uintptr_t>(xq) & 7) == 0) && (ld_xq % 8 == 0)));
-#define AB_ROW(T, TY)                                                                                                        \
-    row_op_act_quant_kernel<MODE, T, TY><<<(unsigned)m, kThreads, 0, ctx->stream>>>(                                         \
-        (const T*)x, (const T*)x2, w, m, k, ld_x, eps, (TY*)y, ld_y, xq, ld_xq, scales, rowsums, vec_ok)
+    // block shape by row length (in chunks of 8 elements)
+    const size_t k8 = vec_ok ? k / 8 : 0;
+    const int shape = k8 <= 64 * 8 ? 0 : (k8 <= 512 * 4 ? 1 : 2);
+#define AB_ROW(T, TY)                                                                                                          \
+    do {                                                                                                                       \
+        if (shape == 0)                                                                                                        \
+            row_op_act_quant_kernel<MODE, T, TY, 64, 8><<<(unsigned)m, 64, 0, ctx->stream>>>(                                  \
+                (const T*)x, (const T*)x2, w, m, k, ld_x, eps, (TY*)y, ld_y, xq, ld_xq, scales, rowsums, vec_ok);              \
+        else if (shape == 1)                                                                                                   \
+            row_op_act_quant_kernel<MODE, T, TY, 512, 4><<<(unsigned)m, 512, 0, ctx->stream>>>(                                \
+                (const T*)x, (const T*)x2, w, m, k, ld_x, eps, (TY*)y, ld_y, xq, ld_xq, scales, rowsums, vec_ok);              \
+        else                                                                                                                   \
+            row_op_act_quant_kernel<MODE, T, TY, 512, 8><<<(unsigned)m, 512, 0, ctx->stream>>>(                                \
+                (const T*)x, (const T*)x2, w, m, k, ld_x, eps, (TY*)y, ld_y, xq, ld_xq, scales, rowsums, vec_ok);              \
+    } while (0)
     if (x_dtype == AB_BF16) {
         if (y_dtype == AB_BF16) AB_ROW(__nv_bfloat16, __nv_bfloat16);
         else AB_ROW(__nv_bfloat16, float);

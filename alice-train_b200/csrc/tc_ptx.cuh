@@ -11,7 +11,11 @@ namespace tc {
 constexpr uint32_t WAIT_HINT_NS = 20000;   // one hardware suspension
 constexpr int WAIT_LIMIT_TRIES = 100000;    // x 20 us = 2 s, then the kernel gives up
 
-enum Mode { FWD = 0, DX = 1, DW = 2 };
+// FWD / DX take the B operand from 2-bit codes expanded in shared memory; DW, NT, NN are dense bf16 x bf16 with both
+// operands brought by TMA: DW = A^T B (both operands contract over their ROW index), NT = A B^T (both over their
+// column index), NN = A B (A over columns, B over rows).
+enum Mode { FWD = 0, DX = 1, DW = 2, NT = 3, NN = 4 };
+__host__ __device__ constexpr bool has_expanders(int mode) { return mode == FWD || mode == DX; }
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

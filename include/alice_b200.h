@@ -102,7 +102,8 @@ AB_API int ab_ctx_destroy(ab_ctx* ctx);
  *   AB_OPT_ASYNC_HOST_STEP     1: ab_bitlinear_step_host returns as soon as its copies and kernels are queued; the host
  *                                 buffers of a call may be read (y, dx) or reused (x, dy) after the next ab_ctx_sync().
  *                                 Consecutive calls then overlap: the copies in of one run beside the GEMMs and the
- *                                 copies out of the one before. */
+ *                                 copies out of the one before.
+ */
 typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2, AB_OPT_HOST_INTEGER_MATVEC = 3 } ab_option;
 AB_API int ab_ctx_set_option(ab_ctx* ctx, int option, int value);
 /* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
@@ -284,34 +285,36 @@ AB_API int ab_bitlinear_backward_host(ab_ctx* ctx, const ab_weights* w, const fl
                                       float* dx, size_t dx_len, float* d_bias, size_t d_bias_len);
 AB_API int ab_ste_weight_grad_host(ab_ctx* ctx, const float* x, size_t x_len, const float* dy,
                                    size_t dy_len, float* dW, size_t dw_len);
+/* blas::ternary_swiglu_ffn (src/blas.rs:462-494) with its own argument list: the three packed matrices have row stride
+ * ceil(k/4); output, gate_buf and up_buf are overwritten (gate_buf ends up holding SiLU(gate) * up).  Blocking. */
+AB_API int ab_ternary_swiglu_ffn_host(ab_ctx* ctx, const float* input, const uint8_t* gate_packed, float gate_scale,
+                                      const uint8_t* up_packed, float up_scale, const uint8_t* down_packed, float down_scale,
+                                      float* output, float* gate_buf, float* up_buf, size_t seq_len, size_t hidden_dim,
+                                      size_t intermediate_dim);
 AB_API int ab_ternary_matmul_bt_host(ab_ctx* ctx, const float* a, const uint8_t* packed_b,
                                      float scale, float* c, size_t m, size_t n, size_t k);
 
 /* ------------------------------------------------- output head: dense logits and cross-entropy
  * The reference keeps the output projection unquantised (src/bin/train_qat_70b.rs:1024-1031) and runs, per micro-batch,
  * logits = h W^T (matmul_bt_inplace), cross_entropy_loss per token (src/bin/train_qat_70b.rs:98-112), d_hidden =
- * d_logits W (matmul_nn_inplace, :1094-1101) and the weight gradient d_logits^T h.  Device pointers, bf16 operands, f32
- * accumulation and f32 results.  The products contract over the ROW index of both operands, so the forward takes the
- * weight matrix transposed ([hidden x vocab]; ab_transpose_bf16 makes that copy once per optimizer step) and the
- * backward takes the gradient of the logits in both orientations, which ab_cross_entropy writes in one pass. */
-AB_API int ab_transpose_bf16(ab_ctx* ctx, const void* in, size_t rows, size_t cols, size_t ld_in, void* out, size_t ld_out);
-/* logits[m x vocab] (f32) = h[m x hidden] (bf16) . W^T, with w_t = W^T stored [hidden x vocab] (bf16). */
-AB_API int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w_t, size_t ld_wt, size_t m, size_t hidden,
-                             size_t vocab, float* logits, size_t ld_logits);
+ * d_logits W (matmul_nn_inplace, :1094-1101) and the weight gradient d_logits^T h.  Device pointers, bf16 operands as
+ * they lie in memory (nothing is transposed), f32 accumulation. */
+/* logits[m x vocab] (f32 or bf16) = h[m x hidden] . w[vocab x hidden]^T, both bf16. */
+AB_API int ab_lm_head_logits(ab_ctx* ctx, const void* h, size_t ld_h, const void* w, size_t ld_w, size_t m, size_t hidden,
+                             size_t vocab, void* logits, int logits_dtype, size_t ld_logits);
 /* Softmax cross-entropy of every token row and its gradient, cross_entropy_loss (src/bin/train_qat_70b.rs:98-112):
  *   p = exp(x - max) / sum exp(x - max);  loss[t] = -ln(max(p[target_t], 1e-10));  d = (p - onehot(target_t)) * d_scale
  * logits are f32 or bf16 [m x vocab].  A target >= vocab marks a token that does not count: loss 0, gradient row 0 (the
  * reference's loop skips it, :1068-1072); d_scale is the caller's 1 / (counted tokens * accumulation steps) (:1080-1083).
- * loss (f32 [m]), d_logits (bf16 [m x vocab]) and d_logits_t (bf16 [vocab x m], the same values transposed) may each be
- * NULL. */
+ * loss (f32 [m]), d_logits (bf16 [m x vocab]) and d_logits_t (bf16 [vocab x m], the same values transposed, for callers
+ * that want the gradient vocabulary-major) may each be NULL. */
 AB_API int ab_cross_entropy(ab_ctx* ctx, const void* logits, int logits_dtype, size_t ld, const uint32_t* targets, size_t m,
                             size_t vocab, float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t);
-/* d_hidden[m x hidden] (f32, overwritten; NULL to skip) = d_logits . W from d_logits_t [vocab x m] and w [vocab x hidden];
- * dW[vocab x hidden] (f32; dw_beta 0 overwrites, 1 accumulates; NULL to skip) = d_logits^T . h from d_logits [m x vocab]
- * and h [m x hidden].  All operands bf16. */
-AB_API int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* d_logits_t, size_t ld_t, const void* w,
-                               size_t ld_w, const void* h, size_t ld_h, size_t m, size_t hidden, size_t vocab, float* d_hidden,
-                               size_t ld_dh, float* dW, size_t ld_dw, float dw_beta);
+/* d_hidden[m x hidden] (f32, overwritten; NULL to skip) = d_logits . w;  dW[vocab x hidden] (f32; dw_beta 0 overwrites,
+ * 1 accumulates; NULL to skip) = d_logits^T . h.  d_logits [m x vocab], w [vocab x hidden], h [m x hidden], all bf16. */
+AB_API int ab_lm_head_backward(ab_ctx* ctx, const void* d_logits, size_t ld_d, const void* w, size_t ld_w, const void* h,
+                               size_t ld_h, size_t m, size_t hidden, size_t vocab, float* d_hidden, size_t ld_dh, float* dW,
+                               size_t ld_dw, float dw_beta);
 /* Host-slice forms of CudaMatmul::matmul_bt_inplace / matmul_nn_inplace (src/cuda_matmul.rs:1149-1258) for a DENSE B:
  * C[m x n] = A[m x k] . B[n x k]^T and C[m x n] = A[m x k] . B[k x n]; f32 slices, operands rounded to bf16 on the
  * device, f32 accumulation, blocking.  AB_ERR_SHAPE where the reference's length assertions would panic. */

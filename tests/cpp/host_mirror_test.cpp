@@ -290,6 +290,24 @@ static void cuda_matmul_cases() {
         threw = true;
     }
     expect(threw, "src/cuda_matmul.rs:1161", "matmul_bt with a short slice");
+    // blas::ternary_swiglu_ffn (src/blas.rs:462-494): hidden 4, intermediate 8, one row, all scales 0.5
+    {
+        const size_t hd = 4, it = 8;
+        std::vector<int8_t> gc(it * hd), uc(it * hd), dc(hd * it);
+        for (size_t i = 0; i < gc.size(); ++i) { gc[i] = int8_t(int(i * 7 % 3) - 1); uc[i] = int8_t(int(i * 5 % 3) - 1); dc[i] = int8_t(int(i * 11 % 3) - 1); }
+        std::vector<float> in = {1.f, -2.f, 0.5f, 3.f}, out(hd, 9.f), gb(it, 9.f), ub(it, 9.f), want(hd, 0.f), g(it, 0.f), u(it, 0.f);
+        for (size_t j = 0; j < it; ++j) {
+            for (size_t p = 0; p < hd; ++p) { g[j] += float(gc[j * hd + p]) * in[p]; u[j] += float(uc[j * hd + p]) * in[p]; }
+            g[j] *= 0.5f; u[j] *= 0.5f;
+            g[j] = g[j] / (1.0f + std::exp(-g[j])) * u[j];
+        }
+        for (size_t j = 0; j < hd; ++j) {
+            for (size_t p = 0; p < it; ++p) want[j] += float(dc[j * it + p]) * g[p];
+            want[j] *= 0.5f;
+        }
+        blas::ternary_swiglu_ffn(in, pack_ternary(gc), 0.5f, pack_ternary(uc), 0.5f, pack_ternary(dc), 0.5f, out, gb, ub, 1, hd, it);
+        expect(close_to(out, want, 1e-5f) && close_to(gb, g, 1e-5f) && close_to(ub, u, 1e-5f), "src/blas.rs:462-494", "ternary_swiglu_ffn");
+    }
     GpuBackwardEngine eng(GpuContext::global());
     auto tw = TernaryWeightKernel::from_ternary({1, -1, 0, 1}, 2, 2);
     std::vector<float> gi(2, 9.f);

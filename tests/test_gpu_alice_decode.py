@@ -210,3 +210,20 @@ def test_matvec_ex_row_scales_and_accumulation(env, orc, out, inn):
     want = orc.ternary_matmul_bt(x, packed, g, y0.copy(), 1, out, inn).reshape(-1)
     assert rel_err(y.cpu().numpy(), want) <= RTOL
     w.close()
+
+
+@pytest.mark.parametrize("seq,hidden,inter", [(1, 8, 12), (3, 64, 96), (5, 1024, 1536)])
+def test_ternary_swiglu_ffn_host_form(env, orc, seq, hidden, inter):
+    """blas::ternary_swiglu_ffn with the reference's argument list (src/blas.rs:462-494), host slices in and out."""
+    at, ctx, torch = env
+    from alice_train import blas
+    gq = [orc.quantize_and_pack(normal_f32(90 + i, shp, 0.02)) for i, shp in enumerate([(inter, hidden), (inter, hidden), (hidden, inter)])]
+    x = normal_f32(95, (seq, hidden))
+    out = np.full(seq * hidden, 7.0, np.float32)          # the reference zero-fills all three before it accumulates
+    gbuf = np.full(seq * inter, 7.0, np.float32)
+    ubuf = np.full(seq * inter, 7.0, np.float32)
+    blas.ternary_swiglu_ffn(x, gq[0][2], gq[0][0], gq[1][2], gq[1][0], gq[2][2], gq[2][0], out, gbuf, ubuf, seq, hidden, inter, ctx)
+    want, mid = orc.ternary_swiglu_ffn(x, gq[0][2], gq[0][0], gq[1][2], gq[1][0], gq[2][2], gq[2][0], seq, hidden, inter)
+    up_ref = orc.ternary_matmul_bt(x, gq[1][2], gq[1][0], np.zeros(seq * inter, np.float32), seq, inter, hidden)
+    assert rel_err(out.reshape(seq, hidden), want) <= RTOL
+    assert rel_err(gbuf.reshape(seq, inter), mid) <= RTOL and rel_err(ubuf.reshape(seq, inter), up_ref) <= RTOL
