@@ -66,8 +66,6 @@ struct ab_ctx {
     uint64_t launches = 0;
     // true while the most recent kernel this context launched was a streaming matvec (kernels that never write codes):
     // the next one may then request its codes before the previous kernel has completed.  Every other launch clears it.
-    bool matvec_chain = false;
-    int vec_turn = 0;              // which of the two converted-vector buffers the next matvec uses
     std::string last_error;
 };
 
@@ -108,7 +106,6 @@ struct ab_weights {
 #define AB_LAUNCH_CHECK(ctx)                                                                  \
     do {                                                                                      \
         (ctx)->launches++;                                                                    \
-        (ctx)->matvec_chain = false;                                                          \
         cudaError_t _e = cudaGetLastError();                                                  \
         if (_e != cudaSuccess) {                                                              \
             (ctx)->last_error = std::string("kernel launch: ") + cudaGetErrorString(_e);      \

@@ -715,7 +715,6 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, ta, tb, p));
     ctx->launches++;
-    ctx->matvec_chain = false;
     return AB_OK;
 }
 

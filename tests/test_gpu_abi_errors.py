@@ -216,3 +216,61 @@ def test_bounded_wait_runs_out_and_the_context_recovers(env):
     assert b"timed out" in lib.ab_ctx_last_error(h)
     assert lib.ab_ctx_sync(h) == OK          # cleared by the report
     _still_works(env)
+
+
+def test_output_head_and_decode_family(env):
+    """Bad arguments and empty shapes of the output-head, cross-entropy and decode-chain entry points."""
+    torch, lib, h, ffi, at = env["torch"], env["lib"], env["h"], env["ffi"], env["at"]
+    m, hid, v = 8, 16, 40
+    hb = torch.zeros((m, hid), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((v, hid), dtype=torch.bfloat16, device="cuda")
+    lg = torch.zeros((m, v), dtype=torch.float32, device="cuda")
+    tg = torch.zeros(m, dtype=torch.int32, device="cuda")
+    d = torch.zeros((m, v), dtype=torch.bfloat16, device="cuda")
+    dh = torch.zeros((m, hid), dtype=torch.float32, device="cuda")
+    dW = torch.zeros((v, hid), dtype=torch.float32, device="cuda")
+    loss = torch.zeros(m, dtype=torch.float32, device="cuda")
+    # logits
+    assert lib.ab_lm_head_logits(None, _vp(hb), hid, _vp(w), hid, m, hid, v, _vp(lg), ffi.AB_F32, v) == NULL
+    assert lib.ab_lm_head_logits(h, None, hid, _vp(w), hid, m, hid, v, _vp(lg), ffi.AB_F32, v) == NULL
+    assert lib.ab_lm_head_logits(h, _vp(hb), hid, _vp(w), hid, m, hid, v, None, ffi.AB_F32, v) == NULL
+    assert lib.ab_lm_head_logits(h, _vp(hb), hid - 1, _vp(w), hid, m, hid, v, _vp(lg), ffi.AB_F32, v) == SHAPE
+    assert lib.ab_lm_head_logits(h, _vp(hb), hid, _vp(w), hid, m, hid, v, _vp(lg), ffi.AB_F32, v - 1) == SHAPE
+    assert lib.ab_lm_head_logits(h, _vp(hb), hid, _vp(w), hid, m, hid, v, _vp(lg), 7, v) == UNSUPPORTED
+    assert lib.ab_lm_head_logits(h, None, hid, None, hid, 0, hid, v, None, ffi.AB_F32, v) == OK          # no tokens: nothing to do
+    # cross-entropy
+    assert lib.ab_cross_entropy(h, None, ffi.AB_F32, v, _vp(tg), m, v, 1.0, _vp(loss), _vp(d), v, None, m) == NULL
+    assert lib.ab_cross_entropy(h, _vp(lg), ffi.AB_F32, v, None, m, v, 1.0, _vp(loss), _vp(d), v, None, m) == NULL
+    assert lib.ab_cross_entropy(h, _vp(lg), ffi.AB_F32, v - 1, _vp(tg), m, v, 1.0, _vp(loss), _vp(d), v, None, m) == SHAPE
+    assert lib.ab_cross_entropy(h, _vp(lg), ffi.AB_F32, v, _vp(tg), m, v, 1.0, _vp(loss), _vp(d), v - 1, None, m) == SHAPE
+    assert lib.ab_cross_entropy(h, _vp(lg), 5, v, _vp(tg), m, v, 1.0, _vp(loss), _vp(d), v, None, m) == UNSUPPORTED
+    assert lib.ab_cross_entropy(h, None, ffi.AB_F32, v, None, 0, v, 1.0, None, None, v, None, 0) == OK
+    assert lib.ab_cross_entropy(h, _vp(lg), ffi.AB_F32, v, _vp(tg), m, v, 1.0, None, None, v, None, m) == OK   # statistics only
+    # backward
+    assert lib.ab_lm_head_backward(h, None, v, _vp(w), hid, _vp(hb), hid, m, hid, v, _vp(dh), hid, _vp(dW), hid, 0.0) == NULL
+    assert lib.ab_lm_head_backward(h, _vp(d), v, None, hid, _vp(hb), hid, m, hid, v, _vp(dh), hid, None, hid, 0.0) == NULL
+    assert lib.ab_lm_head_backward(h, _vp(d), v, _vp(w), hid, None, hid, m, hid, v, None, hid, _vp(dW), hid, 0.0) == NULL
+    assert lib.ab_lm_head_backward(h, _vp(d), v, _vp(w), hid, _vp(hb), hid, m, hid, v, _vp(dh), hid, _vp(dW), hid, 0.5) == UNSUPPORTED
+    assert lib.ab_lm_head_backward(h, _vp(d), v - 1, _vp(w), hid, _vp(hb), hid, m, hid, v, _vp(dh), hid, _vp(dW), hid, 0.0) == SHAPE
+    assert lib.ab_lm_head_backward(h, _vp(d), v, _vp(w), hid, _vp(hb), hid, m, hid, v, _vp(dh), hid - 1, None, hid, 0.0) == SHAPE
+    assert lib.ab_lm_head_backward(h, _vp(d), v, _vp(w), hid, _vp(hb), hid, m, hid, v, None, hid, None, hid, 0.0) == OK       # nothing asked for
+    # dense host products: the reference's length assertions
+    a = np.zeros(m * hid, np.float32); b = np.zeros(v * hid, np.float32); c = np.zeros(m * v, np.float32)
+    assert lib.ab_matmul_bt_dense_host(h, _np(a), m * hid, _np(b), v * hid, _np(c), m * v + 1, m, v, hid) == SHAPE
+    assert lib.ab_matmul_bt_dense_host(h, None, m * hid, _np(b), v * hid, _np(c), m * v, m, v, hid) == NULL
+    assert lib.ab_matmul_nn_dense_host(h, _np(a), m * hid, _np(b), v * hid - 1, _np(c), m * v, m, v, hid) == SHAPE
+    assert lib.ab_matmul_bt_dense_host(h, _np(a), 0, _np(b), 0, _np(c), m * v, m, v, 0) == OK and not c.any()             # k = 0: zeros
+    # decode chain: matvec with per-row scales, the feed-forward block
+    tw = at.TernaryWeightKernel.from_ternary(np.ones(hid * 4, np.int8), 4, hid, ctx=env["ctx"])
+    td = at.TernaryWeightKernel.from_ternary(np.ones(hid * 4, np.int8), hid, 4, ctx=env["ctx"])
+    x = torch.zeros(hid, device="cuda"); y = torch.zeros(4, device="cuda")
+    assert lib.ab_ternary_matvec_ex(h, None, _vp(x), _vp(y), 1.0, None, 0) == NULL
+    assert lib.ab_ternary_matvec_ex(h, tw.handle, None, _vp(y), 1.0, None, 0) == NULL
+    assert lib.ab_ternary_matvec_ex(h, tw.handle, _vp(x), None, 1.0, None, 0) == NULL
+    g = torch.zeros(4, device="cuda"); u = torch.zeros(4, device="cuda"); o = torch.zeros(hid, device="cuda")
+    assert lib.ab_ternary_swiglu_ffn(h, _vp(x), tw.handle, 1.0, tw.handle, 1.0, tw.handle, 1.0, _vp(o), _vp(g), _vp(u), 1) == SHAPE   # down is not [hidden x inter]
+    assert lib.ab_ternary_swiglu_ffn(h, _vp(x), tw.handle, 1.0, tw.handle, 1.0, td.handle, 1.0, None, _vp(g), _vp(u), 1) == NULL
+    assert lib.ab_ternary_swiglu_ffn(h, None, tw.handle, 1.0, tw.handle, 1.0, td.handle, 1.0, None, None, None, 0) == OK
+    assert lib.ab_ternary_swiglu_ffn(h, _vp(x), tw.handle, 1.0, tw.handle, 1.0, td.handle, 1.0, _vp(o), _vp(g), _vp(u), 1) == OK
+    tw.close(); td.close()
+    _still_works(env)
