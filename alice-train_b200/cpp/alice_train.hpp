@@ -87,6 +87,20 @@ public:
                                             const GpuContext& ctx = GpuContext::global()) {
         return from_ternary(values.data(), values.size(), out_features, in_features, ctx);
     }
+    // flat 2-bit codes (src/export.rs:117-153), the encoding of a projection inside a .alice file
+    static TernaryWeightKernel from_packed(const uint8_t* packed, size_t bytes, size_t out_features, size_t in_features, float gamma,
+                                           const GpuContext& ctx = GpuContext::global()) {
+        TernaryWeightKernel w(out_features, in_features, ctx);
+        int st = ab_weights_set_packed2b(w.h_.get(), packed, bytes, gamma);
+        if (st == AB_ERR_SHAPE) throw AssertionError("packed.len() == ceil(out_features * in_features / 4)");
+        ctx.check(st);
+        return w;
+    }
+    std::vector<int8_t> to_ternary() const {
+        std::vector<int8_t> v(out_features() * in_features());
+        ctx_.check(ab_weights_get_ternary(h_.get(), v.data(), v.size()));
+        return v;
+    }
     size_t out_features() const { return ab_weights_out_features(h_.get()); }
     size_t in_features() const { return ab_weights_in_features(h_.get()); }
     size_t words_per_row() const { return ab_weights_words_per_row(h_.get()); }

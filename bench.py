@@ -688,6 +688,44 @@ def hbm_block(env, full: bool = True):
             nb = 4096 * 14336 * 5 + 12 * 4096
             res["swiglu_act_quant"] = {"us": t * 1e6, "gbs": nb / t / 1e9, "frac": nb / t / 1e9 / pk["hbm_gbs"]}
             del xn, gate
+            # the forward of one Llama-3-8B MLP block on 4096 tokens, RMSNorm in front: fused (the norm and SwiGLU hand int8
+            # activations straight to the GEMMs) against the same chain with the activations written as bf16 and quantised
+            # by separate act-quant launches
+            hid, inter, tok = 4096, 14336, 4096
+            xin = torch.randn((tok, hid), generator=gen, device=dev).to(torch.bfloat16)
+            nw_ = torch.ones(hid, device=dev)
+            wg, wu, wd = (bl.BitLinearWeights(o, i, ctx).quantize_(torch.randn((o, i), generator=gen, device=dev) * 0.02)
+                          for o, i in ((inter, hid), (inter, hid), (hid, inter)))
+            g_out = torch.empty((tok, inter), dtype=torch.bfloat16, device=dev)
+            u_out = torch.empty((tok, inter), dtype=torch.bfloat16, device=dev)
+            y_out = torch.empty((tok, hid), dtype=torch.bfloat16, device=dev)
+            xn_bf = torch.empty((tok, hid), dtype=torch.bfloat16, device=dev)
+            mid_bf = torch.empty((tok, inter), dtype=torch.bfloat16, device=dev)
+            _, q_in = bl.rmsnorm_act_quant(ctx, xin, nw_, 1e-5)
+            _, q_mid = bl.swiglu_act_quant(ctx, g_out, u_out)
+
+            def fused(_w):
+                bl.rmsnorm_act_quant(ctx, xin, nw_, 1e-5, None, q_in)
+                bl.bitlinear_fwd(wg, q_in, g_out)
+                bl.bitlinear_fwd(wu, q_in, u_out)
+                bl.swiglu_act_quant(ctx, g_out, u_out, None, q_mid)
+                bl.bitlinear_fwd(wd, q_mid, y_out)
+
+            def unfused(_w):
+                bl.rmsnorm_act_quant(ctx, xin, nw_, 1e-5, xn_bf, None, quantize=False)
+                bl.act_quant_int8(ctx, xn_bf, q_in)
+                bl.bitlinear_fwd(wg, q_in, g_out)
+                bl.bitlinear_fwd(wu, q_in, u_out)
+                bl.swiglu_act_quant(ctx, g_out, u_out, mid_bf, None, quantize=False)
+                bl.act_quant_int8(ctx, mid_bf, q_mid)
+                bl.bitlinear_fwd(wd, q_mid, y_out)
+
+            tf, tu = timeit(fused, 6, False), timeit(unfused, 6, False)
+            res["mlp_forward_chain"] = {"tokens": tok, "fused_us": tf * 1e6, "unfused_us": tu * 1e6, "tokens_per_s_fused": tok / tf,
+                                        "note": "rmsnorm -> gate, up -> swiglu -> down; fused = norm and SwiGLU emit the int8 activations themselves"}
+            for hnd in (wg, wu, wd):
+                hnd.close()
+            del xin, g_out, u_out, y_out, xn_bf, mid_bf
         # the CPU-runnable configuration: one 2048 x 2048 layer, batch 1 (1 MiB of codes: latency, not bandwidth)
         g1 = torch.randn((2048, 2048), generator=gen, device=dev) * 0.02
         h1 = bl.BitLinearWeights(2048, 2048, ctx).quantize_(g1)

@@ -7,6 +7,7 @@
 #include <string>
 #include <vector>
 
+#include "alice_file.hpp"
 #include "alice_train.hpp"
 
 using namespace alice_train;
@@ -315,6 +316,107 @@ static void cuda_matmul_cases() {
     expect(close_to(gi, {1.f, 0.f}, 1e-6f), "src/gpu_backward.rs:327-345", "GpuBackwardEngine::ternary_matvec_backward");
 }
 
+// A two-layer .alice file assembled by hand (src/export.rs:379-425 order) and read back through the C++ container.
+static std::vector<uint8_t> tiny_alice_file(const Qwen35Config& c, bool tied, std::vector<std::vector<int8_t>>* codes_out) {
+    std::string js = "{\"version\":1,\"config\":{\"vocab_size\":" + std::to_string(c.vocab_size) + ",\"hidden_size\":" + std::to_string(c.hidden_size) +
+                     ",\"intermediate_size\":" + std::to_string(c.intermediate_size) + ",\"num_hidden_layers\":" + std::to_string(c.num_hidden_layers) +
+                     ",\"rms_norm_eps\":1e-6,\"num_attention_heads\":" + std::to_string(c.num_attention_heads) + ",\"num_key_value_heads\":" +
+                     std::to_string(c.num_key_value_heads) + ",\"head_dim\":" + std::to_string(c.head_dim) +
+                     ",\"rope_theta\":10000.0,\"partial_rotary_factor\":0.25,\"linear_key_head_dim\":" + std::to_string(c.linear_key_head_dim) +
+                     ",\"linear_num_key_heads\":" + std::to_string(c.linear_num_key_heads) + ",\"linear_value_head_dim\":" +
+                     std::to_string(c.linear_value_head_dim) + ",\"linear_num_value_heads\":" + std::to_string(c.linear_num_value_heads) +
+                     ",\"linear_conv_kernel_dim\":" + std::to_string(c.linear_conv_kernel_dim) + ",\"full_attention_interval\":2,\"layer_types\":["
+                     "\"LinearAttention\",\"FullAttention\"]},\"quantization\":\"ternary_1_58bit\",\"tied_embeddings\":" + (tied ? "true" : "false") +
+                     ",\"quantized_params\":100,\"non_quantized_params\":50,\"total_params\":150,\"source_step\":1000,\"source_loss\":5.0,"
+                     "\"layer_scales\":[{\"layer_idx\":0,\"layer_type\":\"deltanet\",\"scales\":[[\"in_proj_qkv\",0.125],[\"in_proj_z\",0.25]]}]}";
+    std::vector<uint8_t> f;
+    auto put = [&](const void* p, size_t n) { const uint8_t* b = static_cast<const uint8_t*>(p); f.insert(f.end(), b, b + n); };
+    put("ALICEMOD", 8);
+    uint32_t ver = 1;
+    uint64_t hl = js.size();
+    put(&ver, 4); put(&hl, 8); put(js.data(), js.size());
+    std::vector<uint16_t> emb(c.vocab_size * c.hidden_size, 0x3F80);   // bf16 1.0
+    put(emb.data(), emb.size() * 2);
+    std::vector<float> norm(c.hidden_size, 1.5f);
+    put(norm.data(), norm.size() * 4);
+    if (!tied) put(emb.data(), emb.size() * 2);
+    for (size_t i = 0; i < c.num_hidden_layers; ++i) {
+        int pj = 0;
+        for (const auto& s : c.projection_shapes(i)) {
+            std::vector<int8_t> t(s.out_features * s.in_features);
+            for (size_t e = 0; e < t.size(); ++e) t[e] = int8_t(int((e * 7 + i * 3 + pj) % 3) - 1);
+            std::vector<uint8_t> pk((t.size() + 3) / 4, 0);
+            for (size_t e = 0; e < t.size(); ++e) pk[e / 4] |= uint8_t((t[e] == 1 ? 1 : (t[e] == -1 ? 2 : 0)) << (2 * (e % 4)));
+            float scale = 0.5f + 0.25f * float(pj);
+            put(&scale, 4); put(pk.data(), pk.size());
+            codes_out->push_back(std::move(t));
+            ++pj;
+        }
+        for (const auto& s : c.fp32_shapes(i)) {
+            std::vector<float> v(s.second, float(i) + 0.5f);
+            put(v.data(), v.size() * 4);
+        }
+    }
+    return f;
+}
+
+static Qwen35Config tiny_config() {
+    Qwen35Config c;
+    c.vocab_size = 5; c.hidden_size = 8; c.intermediate_size = 12; c.num_hidden_layers = 2; c.rms_norm_eps = 1e-6f;
+    c.num_attention_heads = 2; c.num_key_value_heads = 1; c.head_dim = 4; c.rope_theta = 10000.f; c.partial_rotary_factor = 0.25f;
+    c.linear_key_head_dim = 2; c.linear_num_key_heads = 2; c.linear_value_head_dim = 4; c.linear_num_value_heads = 2;
+    c.linear_conv_kernel_dim = 4; c.full_attention_interval = 2;
+    return c;
+}
+
+// no device needed: metadata, index, error behaviour (src/export.rs:877-933, src/inference.rs:1067-1113)
+static void alice_file_host_cases() {
+    std::vector<std::vector<int8_t>> codes;
+    const Qwen35Config c = tiny_config();
+    for (bool tied : {true, false}) {
+        codes.clear();
+        std::vector<uint8_t> bytes = tiny_alice_file(c, tied, &codes);
+        AliceModelMeta m = parse_alice_meta(bytes.data(), bytes.size());
+        expect(m.version == 1 && m.source_step == 1000 && std::fabs(m.source_loss - 5.0f) < 1e-6f && m.tied_embeddings == tied,
+               "src/export.rs:898-925", "read_alice_meta");
+        expect(m.config.hidden_size == 8 && m.config.layer_types.size() == 2 && !m.config.full_attention(0) && m.config.full_attention(1) &&
+                   m.layer_scales.size() == 1 && m.layer_scales[0].scales[1].first == "in_proj_z" && m.layer_scales[0].scales[1].second == 0.25f,
+               "src/export.rs:49-83", "metadata fields");
+        AliceIndex ix = build_alice_index(m);
+        expect(ix.end == bytes.size() && ix.layers.size() == 2 && ix.layers[0].packed.size() == 8 && ix.layers[1].packed.size() == 7 &&
+                   ix.layers[0].fp32.size() == 6 && ix.layers[1].fp32.size() == 4 && (ix.lm_head_off == 0) == tied,
+               "src/inference.rs:1067-1113", "layer index covers the file");
+        const PackedRef& r = ix.layers[0].packed[0];
+        expect(r.name == "in_proj_qkv" && r.out_features == 16 && r.in_features == 8 && r.packed_off == r.scale_off + 4 &&
+                   r.packed_len == 32 && ix.layers[0].packed[1].scale_off == r.packed_off + r.packed_len,
+               "src/inference.rs:1004-1011", "PackedRef offsets");
+    }
+    std::vector<uint8_t> bad = {'B', 'A', 'D', 'M', 'A', 'G', 'I', 'C', 1, 0, 0, 0};
+    bool threw = false;
+    try { parse_alice_meta(bad.data(), bad.size()); } catch (const std::runtime_error&) { threw = true; }
+    expect(threw, "src/export.rs:927-933", "read_alice_meta rejects a bad magic");
+    Qwen35Config q = Qwen35Config::qwen35_9b();
+    expect(q.linear_key_dim() == 2048 && q.linear_value_dim() == 4096 && q.conv_dim() == 8192 && q.projection_shapes(0)[0].out_features == 8192 &&
+               q.projection_shapes(3)[1].out_features == 1024 && q.fp32_shapes(0)[4].second == 8192 * 4,
+           "src/qwen35.rs:67-164", "Qwen3.5-9B shapes");
+}
+
+// on a device: the packed projections of the file become weight handles holding the file's codes and scales
+static void alice_file_device_cases() {
+    std::vector<std::vector<int8_t>> codes;
+    AliceFile f(tiny_alice_file(tiny_config(), true, &codes));
+    size_t n = 0;
+    bool same = true;
+    for (const LayerIndex& L : f.index().layers)
+        for (const PackedRef& r : L.packed) {
+            TernaryWeightKernel w = f.load_projection(r);
+            same = same && w.to_ternary() == codes[n] && w.gamma() == f.scale(r) && w.out_features() == r.out_features;
+            ++n;
+        }
+    expect(same && n == 15, "src/inference.rs:1029-1139", "projections load as packed codes with their scales");
+    expect(f.f32(f.index().layers[1].fp32[2]) == std::vector<float>(4, 1.5f), "src/export.rs:661-664", "f32 tensors of a layer");
+}
+
 int main(int argc, char** argv) {
     if (argc > 1 && std::strcmp(argv[1], "--no-device") == 0) {
         auto c = GpuContext::new_blocking(0);
@@ -328,6 +430,11 @@ int main(int argc, char** argv) {
         } catch (const Error& e) {
             threw = e.status == AB_ERR_NO_DEVICE;
         }
+        alice_file_host_cases();
+        if (g_fail) {
+            std::printf("%d checks, %d failed\n", g_run, g_fail);
+            return 1;
+        }
         std::printf(threw ? "no-device ok\n" : "global() did not fail without a device\n");
         return threw ? 0 : 1;
     }
@@ -339,6 +446,8 @@ int main(int argc, char** argv) {
         qat_cases();
         export_cases();
         cuda_matmul_cases();
+        alice_file_host_cases();
+        alice_file_device_cases();
     } catch (const std::exception& e) {
         std::printf("unexpected exception: %s\n", e.what());
         return 3;
