@@ -288,3 +288,55 @@ def test_norm_activation_optimizer_vectors(golden, orc):
         w = orc.sgd_update(np.array(g["w"], np.float32), np.array(g["grad"], np.float32), g["lr"], g["wd"])
         for got, want in zip(w, g["expect"]):
             assert abs(got - want) < g["tol"]
+
+
+def test_output_head_and_decode_oracles_against_float64(orc):
+    """The oracle's cross-entropy and packed decode chain have no reference vectors (their reference code is private to a
+    binary / has no unit test); they are held against independent float64 numpy restatements instead."""
+    r = np.random.default_rng(11)
+    m, v = 9, 57
+    x = (r.standard_normal((m, v)) * 3).astype(np.float32)
+    tg = r.integers(0, v, m).astype(np.uint32)
+    tg[4] = v + 3                                       # not counted
+    loss, d, n = orc.cross_entropy(x, tg, 0.25)
+    assert n == m - 1
+    x64 = x.astype(np.float64)
+    lse = np.log(np.exp(x64 - x64.max(1, keepdims=True)).sum(1)) + x64.max(1)
+    p = np.exp(x64 - lse[:, None])
+    for t in range(m):
+        if tg[t] >= v:
+            assert loss[t] == 0.0 and not d[t].any()
+            continue
+        assert abs(loss[t] - (lse[t] - x64[t, tg[t]])) < 1e-5
+        want = p[t].copy()
+        want[tg[t]] -= 1.0
+        assert np.abs(d[t] - 0.25 * want).max() < 1e-6
+        assert abs(d[t].sum()) < 1e-6
+    # ternary_swiglu_ffn and one layer of the decode chain
+    hidden, inter = 16, 24
+    def q(shape, seed):
+        w = (np.random.default_rng(seed).standard_normal(shape) * 0.02).astype(np.float32)
+        g, codes, packed = orc.quantize_and_pack(w)
+        return g, codes.reshape(shape).astype(np.float64), packed
+    (gg, gc, gp), (ug, uc, up), (dg, dc, dp) = q((inter, hidden), 1), q((inter, hidden), 2), q((hidden, inter), 3)
+    xs = r.standard_normal((2, hidden)).astype(np.float32)
+    out, mid = orc.ternary_swiglu_ffn(xs, gp, gg, up, ug, dp, dg, 2, hidden, inter)
+    g64 = xs.astype(np.float64) @ gc.T * gg
+    u64 = xs.astype(np.float64) @ uc.T * ug
+    mid64 = g64 / (1.0 + np.exp(-g64)) * u64
+    assert np.abs(mid - mid64).max() <= 1e-6 * max(1.0, np.abs(mid64).max())
+    assert np.abs(out - mid64 @ dc.T * dg).max() <= 1e-6 * max(1.0, np.abs(out).max())
+    (qg, qc, qp), (og, oc, op_) = q((2 * hidden, hidden), 4), q((hidden, hidden), 5)
+    nw1, nw2 = (1.0 + 0.1 * r.standard_normal(hidden)).astype(np.float32), (1.0 + 0.1 * r.standard_normal(hidden)).astype(np.float32)
+    layer = {"attn": [("qkv", qp, qg, 2 * hidden, hidden)], "out": (op_, og, hidden, hidden), "gate": (gp, gg, inter, hidden),
+             "up": (up, ug, inter, hidden), "down": (dp, dg, hidden, inter), "input_layernorm": nw1, "post_attn_layernorm": nw2}
+    h0 = r.standard_normal(hidden).astype(np.float32)
+    got = orc.decode_linears(h0, [layer], 1e-6, lambda outs, width: outs["qkv"][:width])
+    h = h0.astype(np.float64)
+    rms = lambda a, w: a / np.sqrt((a * a).mean() + 1e-6) * w
+    xa = rms(h, nw1)
+    h = h + (oc @ ((qc @ xa) * qg)[:hidden]) * og
+    xb = rms(h, nw2)
+    g2, u2 = (gc @ xb) * gg, (uc @ xb) * ug
+    h = h + (dc @ (g2 / (1.0 + np.exp(-g2)) * u2)) * dg
+    assert np.abs(got - h).max() <= 1e-5 * np.abs(h).max()
