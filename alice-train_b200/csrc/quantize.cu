@@ -312,18 +312,19 @@ quantize_pack_vec_kernel(const float* w, uint32_t nchunks /* of 32 float4 */, ui
             if (c0 + u * total_warps >= nchunks) break;  // warp-uniform
             const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
             float qv[4];
-            uint32_t cbits = 0, fbits = 0;
+            uint32_t cbits = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float scaled = __fmul_rn(x[i], inv);
-                const uint32_t pl = scaled >= 0.5f, mi = scaled <= -0.5f;
-                cbits |= (pl | (mi << 1)) << (2 * i);
-                fbits |= (1u + pl - mi) << (8 * i);  // offset binary w+1
-                n_thr += ((__float_as_uint(scaled) & 0x7fffffffu) - 0x3EFFFFFFu) <= 2u;  // |s| within 1 ulp of 0.5
+                // on the bits of s: |s| in [0.5, Inf] (NaN excluded) is one unsigned compare, the code is sign + 1
+                const uint32_t b = __float_as_uint(scaled), mag = b & 0x7fffffffu;
+                const uint32_t c = (mag - 0x3F000000u) <= 0x40800000u ? (b >> 31) + 1u : 0u;   // 1 = +1, 2 = -1
+                cbits += c << (2 * i);
+                n_thr += (mag - 0x3EFFFFFFu) <= 2u;  // |s| within 1 ulp of 0.5
                 if (WANT_FQ || WANT_STATS) {
                     // c * gamma as the reference forms it: NaN stays NaN, a rounded-to-zero value keeps its sign
                     qv[i] = scaled != scaled ? scaled
-                                             : (pl ? gamma : (mi ? -gamma : __uint_as_float(__float_as_uint(scaled) & 0x80000000u)));
+                                             : (c == 1u ? gamma : (c == 2u ? -gamma : __uint_as_float(b & 0x80000000u)));
                 }
                 if (WANT_STATS) {
                     double wd = (double)x[i], qd = (double)qv[i];
@@ -335,6 +336,11 @@ quantize_pack_vec_kernel(const float* w, uint32_t nchunks /* of 32 float4 */, ui
                     vmax = fmaxf(vmax, x[i]);
                 }
             }
+            // offset-binary copy (w + 1) of the four codes, one byte each: per 2-bit field 0 -> 1, 1 -> 2, 2 -> 0, then the
+            // fields move from bit 2i to bit 8i (two multiplies spread the even and the odd fields without overlap)
+            const uint32_t lo = cbits & 0x55u, hi = (cbits >> 1) & 0x55u;
+            const uint32_t fp = (~(lo | hi) & 0x55u) | (lo << 1);
+            const uint32_t fbits = (((fp & 0x33u) * 0x1001u) & 0x00030003u) | (((fp & 0xCCu) * 0x40040u) & 0x03000300u);
             // element e = 4*sub + i of the group: bit 2e in the canonical word, bit 8*(e%4) + 2*(e/4) in the operand copy
             uint32_t cpart = cbits << (8 * sub), fpart = fbits << (2 * sub);
             cpart |= __shfl_xor_sync(0xffffffffu, cpart, 1);
