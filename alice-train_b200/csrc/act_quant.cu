@@ -42,9 +42,12 @@ template <> struct Vec8<float> {
 };
 
 __device__ __forceinline__ int quant1(float x, float inv) {
-    float r = roundf(__fmul_rn(x, inv));
-    r = r < -127.0f ? -127.0f : (r > 127.0f ? 127.0f : r);
-    return (int)r;
+    // round half away from zero, as f32::round: for every float |y| <= 256 (checked exhaustively on the host)
+    // trunc(y + copysign(0.49999997f, y)) == roundf(y); beyond that both land outside +-127 and clamp to the same value;
+    // NaN converts to 0 in both forms
+    const float y = __fmul_rn(x, inv);
+    const int q = __float2int_rz(__fadd_rn(y, copysignf(0.49999997f, y)));
+    return q < -127 ? -127 : (q > 127 ? 127 : q);
 }
 
 // TPR threads share one token row; a block of 256 threads holds 256/TPR rows, so short rows still
