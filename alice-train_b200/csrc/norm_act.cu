@@ -113,6 +113,10 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
     __shared__ double s_d[THREADS / 32];
     __shared__ float s_f[THREADS / 32];
     __shared__ int s_i[THREADS / 32];
+    // A batch-1 matvec queued behind this kernel (the decode chain: norm -> projections, SiLU * up -> down) may set up
+    // its barriers while this kernel runs; it reads this kernel's output only after its own griddepcontrol.wait, which
+    // waits for this grid to complete.  Without such a dependent this is a no-op.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t t = blockIdx.x;
     const T* row = x + t * ld_x;
     const T* row2 = MODE == 1 ? x2 + t * ld_x : nullptr;
@@ -316,7 +320,8 @@ int launch_row_op(ab_ctx* ctx, const void* x, const void* x2, int x_dtype, const
                  (!xq || (((reinterpret_cast<uintptr_t>(xq) & 7) == 0) && (ld_xq % 8 == 0)));
     // block shape by row length (in chunks of 8 elements)
     const size_t k8 = vec_ok ? k / 8 : 0;
-    const int shape = k8 <= 64 * 8 ? 0 : (k8 <= 512 * 4 ? 1 : 2);
+    // few rows (the decode chain has one): the row's latency is what counts, so spread it over many threads
+    const int shape = (k8 <= 64 * 8 && m >= 64) ? 0 : (k8 <= 512 * 4 ? 1 : 2);
 #define AB_ROW(T, TY)                                                                                                          \
     do {                                                                                                                       \
         if (shape == 0)                                                                                                        \
