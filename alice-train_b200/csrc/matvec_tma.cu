@@ -488,6 +488,14 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
         double cost = (double)per_block * (double)span_per * (1.0 + 0.01 * (double)s);
         cost *= 1.0 + 0.5 / (double)span_per;                                // a group's epilogue is paid once per chunk
         if (per_block < 12) cost *= 1.0 + 0.03 * (double)(12 - per_block);   // too few warps on an SM to keep its pipes busy
+        // Small matrices are bound by round trips, not bandwidth: a warp has at most ~3 stages in flight, so a unit of
+        // more stages than that costs a further memory round trip (~14 stage times) per ring refill.  Cutting K finer
+        // spreads the same stages over more warps, at one more atomic per row and chunk.
+        const size_t nw_est = per_block < 4 ? 4 : (per_block > (size_t)kMaxWarps ? (size_t)kMaxWarps : per_block);
+        const size_t units_per_warp = (per_block + nw_est - 1) / nw_est;
+        const double round_trips = (double)((units_per_warp * span_per + 2) / 3);
+        const double latency_cost = 14.0 * round_trips * (1.0 + 0.02 * (double)s);
+        if (latency_cost > cost) cost = latency_cost;
         if (chunks == 0 || cost < best_cost) { best_cost = cost; chunks = s; chunk_spans = span_per; }
     }
     if (chunks == 0) return abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
