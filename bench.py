@@ -1263,7 +1263,7 @@ def main():
     ap.add_argument("--dw-exchange", default="switch", choices=["switch", "nccl"],
                     help="sum of dW / all-gather / reduce-scatter: the library's in-switch kernels (default) or NCCL")
     ap.add_argument("--exchange-ctas", type=int, default=0, help="CTAs of the in-switch exchange kernel (0 = library default)")
-    ap.add_argument("--partitioned-ctas", type=int, default=0, help="the same for the decoder workloads, whose exchange is much larger per unit of compute (0 = 32 at 2 GPUs, 16 beyond: measured)")
+    ap.add_argument("--partitioned-ctas", type=int, default=0, help="the same for the decoder workloads, whose exchange is much larger per unit of compute (0 = 32 at 2 GPUs, 16 at 4, 8 at 8: measured)")
     ap.add_argument("--partitioned-steps", type=int, default=5, help="timed steps of each partitioned workload inside the default run")
     ap.add_argument("--check-linears", type=int, default=12, help="dW buffers per decoder workload whose in-switch sum is checked against NCCL (0 = all)")
     ap.add_argument("--head-tokens", type=int, default=8192, help="tokens of the lm-head workload (a small value gives a case a profiler can capture)")
@@ -1272,7 +1272,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (no hbm_kernels / partitioned blocks)")
     args = ap.parse_args()
     if args.partitioned_ctas == 0:
-        args.partitioned_ctas = 32 if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else 16
+        ws = int(os.environ.get("WORLD_SIZE", "1"))
+        args.partitioned_ctas = 32 if ws <= 2 else (16 if ws <= 4 else 8)
     if args.impl == "reference":
         return run_reference(args)
     return run_native(args)
