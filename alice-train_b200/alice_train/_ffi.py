@@ -93,7 +93,6 @@ SIGNATURES = {
     "ab_lm_head_backward": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _f]),
     "ab_matmul_bt_dense_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz]),
     "ab_matmul_nn_dense_host": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _sz, _sz, _sz]),
-    "ab_rmsnorm_ternary_matvec": (_i, [_vp, _vp, _vp, _vp, _f, _vp, _f, _vp, _i]),
     "ab_ternary_matvec_ex": (_i, [_vp, _vp, _vp, _vp, _f, _vp, _i]),
     "ab_ternary_swiglu_ffn_host": (_i, [_vp, _vp, _vp, _f, _vp, _f, _vp, _f, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ab_ternary_swiglu_ffn": (_i, [_vp, _vp, _vp, _f, _vp, _f, _vp, _f, _vp, _vp, _vp, _sz]),

@@ -184,53 +184,46 @@ class StreamingAliceModel:
                                                   C.c_void_p(row_scale.data_ptr()) if row_scale is not None else None, 1 if accumulate else 0),
                    self.ctx.handle)
 
-    def _norm_matvec(self, w, h, norm_weight, y, scale=1.0, row_scale=None):
-        _ffi.check(self._lib.ab_rmsnorm_ternary_matvec(self.ctx.handle, w.handle, C.c_void_p(h.data_ptr()), C.c_void_p(norm_weight.data_ptr()),
-                                                       float(self.meta.config.rms_norm_eps), C.c_void_p(y.data_ptr()), float(scale),
-                                                       C.c_void_p(row_scale.data_ptr()) if row_scale is not None else None, 0), self.ctx.handle)
-
-    def _project(self, L, group, names, h, norm_weight, key):
-        """Outputs of the projections `names`, all of which read rmsnorm(h): one stacked launch with the norm inside it
-        where the file allowed stacking, else the norm once and one launch per projection."""
+    def _project(self, L, group, names, x, key):
+        """Outputs of the projections `names`, all of which read x: one stacked launch where the file allowed it."""
         import torch
         b = self._buffers()
         W = L["w"]
         if group in L["stacked"]:
             w, row_scale, parts = L["stacked"][group]
             if key not in b["proj"]:
-                b["proj"][key] = torch.empty(w.out_features(), device=h.device)
+                b["proj"][key] = torch.empty(w.out_features(), device=x.device)
             y = b["proj"][key]
-            self._norm_matvec(w, h, norm_weight, y, 1.0, row_scale)
+            self._matvec(w, x, y, 1.0, row_scale)
             outs, off = {}, 0
             for name, n in parts:
                 outs[name] = y[off:off + n]
                 off += n
             return outs
-        x = b["x"]
-        self._rmsnorm(h, norm_weight, x)
         outs = {}
         for name in names:
             k2 = key + (name,)
             if k2 not in b["proj"]:
-                b["proj"][k2] = torch.empty(W[name].out_features(), device=h.device)
+                b["proj"][k2] = torch.empty(W[name].out_features(), device=x.device)
             self._matvec(W[name], x, b["proj"][k2], W[name].scale)
             outs[name] = b["proj"][k2]
         return outs
 
     def decode_linears(self, hidden, mix=default_mix):
         """One token through every layer's linear chain, in place on `hidden` (f32 CUDA tensor of hidden_size
-        elements).  All work is queued on the context's stream; nothing is copied to the host.  Five launches per
-        layer: the stacked input projections and gate|up (each with its layer norm inside), the output projection,
-        SiLU * up, down."""
+        elements).  All work is queued on the context's stream; nothing is copied to the host.  Seven launches per
+        layer: two norms, the stacked input projections, the output projection, gate|up, SiLU * up, down."""
         b = self._buffers()
         h = hidden.view(1, -1)
         for L in self.layers:
             W, F = L["w"], L["f32"]
             out_name = "out_proj" if L["type"] == "LinearAttention" else "o_proj"
-            outs = self._project(L, "in", _ATTN_INPUTS[L["type"]], h, F["input_layernorm"], (L["type"], "in"))
+            self._rmsnorm(h, F["input_layernorm"], b["x"])
+            outs = self._project(L, "in", _ATTN_INPUTS[L["type"]], b["x"], (L["type"], "in"))
             m = mix(outs, W[out_name].in_features())
             self._matvec(W[out_name], m, h, W[out_name].scale, None, True)          # accumulates: the residual addition
-            gu = self._project(L, "gate_up", ("gate_proj", "up_proj"), h, F["post_attn_layernorm"], ("gate_up",))
+            self._rmsnorm(h, F["post_attn_layernorm"], b["x"])
+            gu = self._project(L, "gate_up", ("gate_proj", "up_proj"), b["x"], ("gate_up",))
             g, u = gu["gate_proj"].view(1, -1), gu["up_proj"].view(1, -1)
             _ffi.check(self._lib.ab_swiglu_act_quant(self.ctx.handle, C.c_void_p(g.data_ptr()), C.c_void_p(u.data_ptr()),
                                                      _ffi.AB_F32, 1, g.numel(), g.numel(), C.c_void_p(b["inter"].data_ptr()),

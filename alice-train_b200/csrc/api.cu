@@ -758,15 +758,6 @@ int ab_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float
     return abk_ternary_matvec_ex(ctx, w, x, y, scale, row_scale, accumulate ? 1 : 0);
 }
 
-int ab_rmsnorm_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, const float* norm_weight, float eps, float* y, float scale,
-                              const float* row_scale, int accumulate) {
-    AB_TRY(bind(ctx));
-    AB_TRY(check_w(ctx, w));
-    if (w->out) AB_REQUIRE(y, AB_ERR_NULL);
-    if (w->out * w->in) AB_REQUIRE(x && norm_weight, AB_ERR_NULL);
-    return abk_rmsnorm_ternary_matvec(ctx, w, x, norm_weight, eps, y, scale, row_scale, accumulate ? 1 : 0);
-}
-
 int ab_ternary_swiglu_ffn(ab_ctx* ctx, const float* input, const ab_weights* gate, float gate_scale, const ab_weights* up,
                           float up_scale, const ab_weights* down, float down_scale, float* output, float* gate_buf,
                           float* up_buf, size_t seq_len) {

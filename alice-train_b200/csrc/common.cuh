@@ -62,8 +62,6 @@ struct ab_ctx {
     bool async_host_step = false;  // AB_OPT_ASYNC_HOST_STEP
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     bool host_integer_matvec = false;  // AB_OPT_HOST_INTEGER_MATVEC: the host-slice forms may take the integer path too
-    const float* vec_norm_weight = nullptr;   // set for the duration of ab_rmsnorm_ternary_matvec: the vector is RMS-normalised on the fly
-    float vec_norm_eps = 0.0f;
     const float* row_scale = nullptr;   // set for the duration of ab_ternary_matvec_ex: y_j is scaled by row_scale[j] instead of one scale
     uint64_t launches = 0;
     // true while the most recent kernel this context launched was a streaming matvec (kernels that never write codes):
@@ -164,10 +162,6 @@ int abk_gemm_nn(ab_ctx* ctx, const void* a, size_t ld_a, const void* b, size_t l
                 size_t ld_c, float beta);
 int abk_cross_entropy(ab_ctx* ctx, const void* logits, int dtype, size_t ld, const uint32_t* targets, size_t m, size_t v,
                       float d_scale, float* loss, void* d_logits, size_t ld_d, void* d_logits_t, size_t ld_t);
-// internal answer of the streaming matvec when it cannot take a call with the norm fused in (the caller then normalises first)
-constexpr int AB_MATVEC_NO_FUSED_NORM = -1000;
-int abk_rmsnorm_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, const float* norm_weight, float eps, float* y, float scale,
-                               const float* row_scale, int accumulate);
 int abk_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale, const float* row_scale,
                           int accumulate);
 int abk_silu_mul_inplace(ab_ctx* ctx, float* gate, const float* up, size_t n);

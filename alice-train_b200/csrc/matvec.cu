@@ -350,29 +350,6 @@ int abk_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, floa
     return st;
 }
 
-// y (+)= s_j * (W . rmsnorm(x; norm_weight, eps))_j.  On the streaming integer path the norm is part of the matvec's own
-// prologue (the weight goes onto the elements as they are converted, 1 / rms onto the result); elsewhere the vector is
-// normalised by the row kernel first.
-int abk_rmsnorm_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, const float* norm_weight, float eps, float* y, float scale,
-                               const float* row_scale, int accumulate) {
-    if (w->out == 0) return AB_OK;
-    if (use_mma(ctx, w, false)) {
-        ctx->row_scale = row_scale;
-        ctx->vec_norm_weight = norm_weight;
-        ctx->vec_norm_eps = eps;
-        const int st = abk_matvec_mma(ctx, w->codes_fwd, w->pitch, w->out, w->in, x, y, scale, accumulate, 1);
-        ctx->row_scale = nullptr;
-        ctx->vec_norm_weight = nullptr;
-        if (st != AB_MATVEC_NO_FUSED_NORM) return st;
-    }
-    void* xn = nullptr;
-    int st = ab_ctx_stage(ctx, 12, (w->in ? w->in : 1) * sizeof(float), &xn);
-    if (st) return st;
-    st = abk_rmsnorm_act_quant(ctx, x, AB_F32, norm_weight, 1, w->in, w->in, eps, xn, AB_F32, w->in, nullptr, w->in, nullptr, nullptr);
-    if (st) return st;
-    return abk_ternary_matvec_ex(ctx, w, (const float*)xn, y, scale, row_scale, accumulate);
-}
-
 int abk_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w, float scale, float* c, size_t m) {
     if (w->out == 0 || m == 0) return AB_OK;
     // The decode loop's shape (src/inference.rs:1305-1472 calls this with m = 1): a few rows of A against a matrix that

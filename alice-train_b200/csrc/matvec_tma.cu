@@ -118,8 +118,6 @@ struct Params {
     float* y;
     float scale;
     const float* row_scale;    // per-row scale (used instead of `scale` when not null)
-    const float* vw;           // RMSNorm weight: the vector used is v * vw / rms(v) (not null), or v itself
-    float veps;
     int accumulate, use_scale, stages;
     int* status;
     unsigned long long* trace;   // trace builds only
@@ -143,7 +141,6 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ long long s_span_sum[kMaxChunkSpans];
     __shared__ unsigned int s_wmax[kMaxWarps];
-    __shared__ double s_wss[kMaxWarps];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int nwarps = (int)(blockDim.x >> 5);
     const int stages = p.stages;
@@ -222,22 +219,10 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) f[r][e] = base + e < p.k ? p.v[base + e] : 0.0f;
             }
-            if (p.vw) {   // the norm's weight goes onto the element now, its 1 / rms (one number) onto the result at the end
-#pragma unroll
-                for (int e = 0; e < 16; ++e) f[r][e] = base + e < p.k ? __fmul_rn(f[r][e], __ldg(p.vw + base + e)) : 0.0f;
-            }
         }
     }
     unsigned int m = 0u;
-    double ss = 0.0;   // RMSNorm: sum of squares of the raw vector (f64, as the reference's blas_rmsnorm, src/blas.rs:381-390)
-    if (p.vw) {
-        for (size_t j = threadIdx.x; j < p.k; j += blockDim.x) {
-            const float x = __ldg(p.v + j);
-            ss += (double)x * (double)x;
-            const unsigned int b = __float_as_uint(__fmul_rn(x, __ldg(p.vw + j))) & 0x7fffffffu;
-            m = b > m ? b : m;
-        }
-    } else if ((reinterpret_cast<uintptr_t>(p.v) & 15) == 0) {
+    if ((reinterpret_cast<uintptr_t>(p.v) & 15) == 0) {
         const size_t n4 = p.k / 4;
         const float4* v4 = reinterpret_cast<const float4*>(p.v);
         size_t i = threadIdx.x;
@@ -275,19 +260,11 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             }
         }
     m = __reduce_max_sync(0xffffffffu, m);
-    if (p.vw)
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) { s_wmax[wid] = m; s_wss[wid] = ss; }
+    if (lane == 0) s_wmax[wid] = m;
     __syncthreads();
     AB_MV_STAMP(2);
     m = 0u;
     for (int w = 0; w < nwarps; ++w) m = s_wmax[w] > m ? s_wmax[w] : m;
-    float inv_rms = 1.0f;
-    if (p.vw) {   // every block (of the same shape) adds the same partial sums in the same order: one value for the launch
-        double tot = 0.0;
-        for (int w = 0; w < nwarps; ++w) tot += s_wss[w];
-        inv_rms = __fdiv_rn(1.0f, (float)sqrt(tot / (double)p.k + (double)p.veps));
-    }
     const bool bad = m >= 0x7f800000u;                 // Inf or NaN somewhere
     const bool live = m >= 0x00800000u && !bad;        // a subnormal maximum counts as zero
     // 2^shift puts the largest magnitude into [2^29, 2^30); elements whose scaled exponent would leave the normal range
@@ -362,7 +339,6 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             const long long total = (long long)(pend_seen[j] - (arrived << 56));
             p.acc[row] = 0ull;               // ready for the next launch
             float val = bad ? nanf_ : (float)scalbn((double)total, -shift);
-            if (p.vw) val = __fmul_rn(val, inv_rms);
             if (p.use_scale) val = __fmul_rn(val, p.row_scale ? p.row_scale[row] : p.scale);
             p.y[row] = p.accumulate ? __fadd_rn(p.y[row], val) : val;
         }
@@ -457,7 +433,6 @@ matvec_tma_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
                 const size_t row = row0 + (j >> 1) * 16 + (j & 1) * 8 + g;
                 if (row >= p.rows) continue;
                 float val = bad ? nanf_ : (float)scalbn((double)res[j], -shift);
-                if (p.vw) val = __fmul_rn(val, inv_rms);
                 if (p.use_scale) val = __fmul_rn(val, p.row_scale ? p.row_scale[row] : p.scale);
                 p.y[row] = p.accumulate ? __fadd_rn(p.y[row], val) : val;
             }
@@ -493,7 +468,7 @@ int abk_matvec_ldg(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
 int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows, size_t k, const float* v, float* y, float scale,
                    int accumulate, int use_scale) {
     if (!tma_path_enabled() || pitch % 16 != 0 || (reinterpret_cast<uintptr_t>(codes) & 15) != 0)
-        return ctx->vec_norm_weight ? AB_MATVEC_NO_FUSED_NORM : abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
+        return abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
     static const int pdl = env_int("AB_MATVEC_PDL", 1);
     const size_t k_pad = ab_round_up(k, kSpan), total_spans = k_pad / kSpan;
     const size_t groups = (rows + kJobRows - 1) / kJobRows;
@@ -523,7 +498,7 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
         if (latency_cost > cost) cost = latency_cost;
         if (chunks == 0 || cost < best_cost) { best_cost = cost; chunks = s; chunk_spans = span_per; }
     }
-    if (chunks == 0) return ctx->vec_norm_weight ? AB_MATVEC_NO_FUSED_NORM : abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
+    if (chunks == 0) return abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
     const size_t unit_spans = chunk_spans, units = groups;   // one unit per row group and chunk
     size_t gx = sms / chunks < groups ? sms / chunks : groups;
     if (gx < 1) gx = 1;
@@ -549,7 +524,7 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
         --nw;
         stages = budget / (nw * (kStageBytes + 8));
     }
-    if (stages < 2 || nw * kConv < chunk_spans) return ctx->vec_norm_weight ? AB_MATVEC_NO_FUSED_NORM : abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
+    if (stages < 2 || nw * kConv < chunk_spans) return abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
     if (stages > (size_t)kMaxStages) stages = kMaxStages;
     const size_t smem = digit_bytes + nw * stages * (kStageBytes + 8) + 8 * chunk_spans;
     static std::mutex mu;
@@ -567,7 +542,6 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
     Params p{};
     p.rows = rows; p.k = k; p.chunk_spans = (int)chunk_spans; p.unit_spans = (int)unit_spans; p.arrivals = (int)arrivals;
     p.v = v; p.acc = acc; p.y = y; p.scale = scale; p.row_scale = ctx->row_scale;
-    p.vw = ctx->vec_norm_weight; p.veps = ctx->vec_norm_eps;
     p.accumulate = accumulate; p.use_scale = use_scale; p.stages = (int)stages; p.status = ctx->dev_status;
 #ifdef AB_MV_TRACE
     p.trace = reinterpret_cast<unsigned long long*>(ctx->stage[14]);   // reserved by ab_debug_mv_trace

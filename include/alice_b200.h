@@ -263,13 +263,6 @@ AB_API int ab_ternary_matmul_bt(ab_ctx* ctx, const float* a, const ab_weights* w
  * matrix and one launch, each keeping its own gamma.  Device pointers.  Same two arithmetic paths as ab_ternary_matvec. */
 AB_API int ab_ternary_matvec_ex(ab_ctx* ctx, const ab_weights* w, const float* x, float* y, float scale,
                                 const float* row_scale, int accumulate);
-/* The same with the vector RMS-normalised on the way in: y_j (+)= s_j * (W . rmsnorm(x))_j, rmsnorm as blas_rmsnorm
- * (src/blas.rs:381-390: f64 sum of squares, x * (1 / sqrt(ss / in + eps)) * norm_weight).  In the decode step every layer
- * norm is followed by projections of its result (src/inference.rs:1300-1317, 1415-1422); on the integer matvec path the
- * norm costs no launch and no pass of its own (its weight is applied as the vector is converted, 1 / rms to the result,
- * which moves the result by one rounding against normalising first).  x and norm_weight: in_features floats. */
-AB_API int ab_rmsnorm_ternary_matvec(ab_ctx* ctx, const ab_weights* w, const float* x, const float* norm_weight, float eps,
-                                     float* y, float scale, const float* row_scale, int accumulate);
 /* The packed decode step's feed-forward block, blas::ternary_swiglu_ffn (src/blas.rs:462-494), on device pointers:
  *   gate_buf = gate_scale * input gate^T ; up_buf = up_scale * input up^T ; gate_buf = gate_buf / (1 + exp(-gate_buf)) * up_buf ;
  *   output = down_scale * gate_buf down^T

@@ -267,10 +267,6 @@ def test_output_head_and_decode_family(env):
     assert lib.ab_ternary_matvec_ex(h, None, _vp(x), _vp(y), 1.0, None, 0) == NULL
     assert lib.ab_ternary_matvec_ex(h, tw.handle, None, _vp(y), 1.0, None, 0) == NULL
     assert lib.ab_ternary_matvec_ex(h, tw.handle, _vp(x), None, 1.0, None, 0) == NULL
-    assert lib.ab_rmsnorm_ternary_matvec(h, tw.handle, _vp(x), None, 1e-6, _vp(y), 1.0, None, 0) == NULL
-    assert lib.ab_rmsnorm_ternary_matvec(h, tw.handle, None, _vp(x), 1e-6, _vp(y), 1.0, None, 0) == NULL
-    assert lib.ab_rmsnorm_ternary_matvec(h, None, _vp(x), _vp(x), 1e-6, _vp(y), 1.0, None, 0) == NULL
-    assert lib.ab_rmsnorm_ternary_matvec(h, tw.handle, _vp(x), _vp(x), 1e-6, _vp(y), 1.0, None, 0) == OK
     g = torch.zeros(4, device="cuda"); u = torch.zeros(4, device="cuda"); o = torch.zeros(hid, device="cuda")
     assert lib.ab_ternary_swiglu_ffn(h, _vp(x), tw.handle, 1.0, tw.handle, 1.0, tw.handle, 1.0, _vp(o), _vp(g), _vp(u), 1) == SHAPE   # down is not [hidden x inter]
     assert lib.ab_ternary_swiglu_ffn(h, _vp(x), tw.handle, 1.0, tw.handle, 1.0, td.handle, 1.0, None, _vp(g), _vp(u), 1) == NULL

@@ -227,31 +227,3 @@ def test_ternary_swiglu_ffn_host_form(env, orc, seq, hidden, inter):
     up_ref = orc.ternary_matmul_bt(x, gq[1][2], gq[1][0], np.zeros(seq * inter, np.float32), seq, inter, hidden)
     assert rel_err(out.reshape(seq, hidden), want) <= RTOL
     assert rel_err(gbuf.reshape(seq, inter), mid) <= RTOL and rel_err(ubuf.reshape(seq, inter), up_ref) <= RTOL
-
-
-@pytest.mark.parametrize("out,inn", [(40, 96), (1500, 1024), (512, 4096)])
-def test_rmsnorm_fused_into_the_matvec(env, orc, out, inn):
-    """y_j (+)= s_j (W rmsnorm(x))_j against blas_rmsnorm (src/blas.rs:381-390) followed by ternary_matmul_bt; the small
-    shape takes the f32 kernels (norm first), the others the integer matvec with the norm inside."""
-    import ctypes as C
-    at, ctx, torch = env
-    lib = at._ffi.load()
-    g, codes, packed = orc.quantize_and_pack(normal_f32(70, (out, inn), 0.02))
-    w = at.TernaryWeightKernel.from_packed(packed, out, inn, g, ctx)
-    x = normal_f32(71, inn) * np.float32(3.0)
-    nw = (1.0 + 0.2 * normal_f32(72, inn)).astype(np.float32)
-    y0 = normal_f32(73, out)
-    xn = orc.rmsnorm(x.reshape(1, inn), nw, 1e-6).reshape(-1)
-    vp = lambda t: C.c_void_p(t.data_ptr())
-    xt, nwt = torch.from_numpy(x).cuda(), torch.from_numpy(nw).cuda()
-    rs = torch.full((out,), 0.5, device="cuda")
-    for accumulate, row_scale, scale in ((0, None, g), (1, None, g), (0, rs, 1.0)):
-        y = torch.from_numpy(y0.copy()).cuda()
-        at._ffi.check(lib.ab_rmsnorm_ternary_matvec(ctx.handle, w.handle, vp(xt), vp(nwt), 1e-6, vp(y), scale,
-                                                    vp(row_scale) if row_scale is not None else None, accumulate), ctx.handle)
-        ctx.sync()
-        s_eff = 0.5 if row_scale is not None else g
-        want = orc.ternary_matmul_bt(xn, packed, s_eff, y0.copy() if accumulate else np.zeros(out, np.float32), 1, out, inn).reshape(-1)
-        assert rel_err(y.cpu().numpy(), want) <= RTOL
-    assert torch.equal(xt.cpu(), torch.from_numpy(x))          # the input is not normalised in place
-    w.close()
