@@ -7,6 +7,8 @@
 //   code   = clamp(round_half_away(w * inv_gamma), -1, 1)          src/qwen35.rs:230, src/export.rs:107
 //   pack   = element i -> byte i/4, shift 2*(i%4); 01=+1 10=-1     src/export.rs:117-133
 //   planes = word j*wpr + k/32, bit k%32                           shaders/ternary_backward.wgsl:5-7
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -276,85 +278,81 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
     }
 }
 
-// Fast path of pass B (rows that are multiples of 128 elements, 16-byte aligned tensors, fewer
-// than 2^33 elements): every lane loads ONE float4 so that a warp reads 512 contiguous bytes per
-// instruction, four loads in flight per lane; the four lanes that share a 16-element group merge
-// their 2-bit fields with two shuffles and one of them stores the canonical word, another the
-// forward-operand word.  Row pitch equals the row length here, so code word i simply holds
-// elements 16i..16i+15 of the flat tensor.  512-byte chunks are walked from the end of the
-// tensor (see above).  clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff s <= -0.5 and
-// 0 otherwise (NaN -> 0), so the codes take two compares per element instead of a software roundf.
+// Fast path of pass B (rows that are multiples of 128 elements, 16-byte aligned tensors): row pitch equals the row
+// length, so code word i simply holds elements 16i..16i+15 of the flat tensor.  Lane L of a warp owns word L of a 32-word
+// block (four 128-bit loads at a 64-byte lane stride: the four loads of a warp together cover 2 KB exactly, the later
+// ones hit the lines the first brought in), so the word is assembled in the lane's own registers and both copies leave
+// as one coalesced 128-byte store per warp each.  Blocks are walked from the END of the tensor: pass A has just read it
+// front to back, so its tail is what the L2 still holds.  clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff
+// s <= -0.5 and 0 otherwise (NaN -> 0): on the bits of s that is one unsigned compare of |s| against [0.5, Inf] and the
+// sign.  (A form with one 128-bit load per lane and the word merged by shuffles among four lanes took 63 us for
+// 14336 x 4096 against 48 us; more than one block in flight per warp did not help: 91.0 / 92.5 / 101.4 us for the
+// whole quantiser at 1 / 2 / 4.)
 template <bool WANT_FQ, bool WANT_STATS>
 __global__ void __launch_bounds__(kThreads)
-quantize_pack_vec_kernel(const float* w, uint32_t nchunks /* of 32 float4 */, uint32_t* __restrict__ codes,
-                         uint32_t* __restrict__ codes_fwd, float* fq_out, ab_fq_dev_report* __restrict__ rep) {
-    const int lane = threadIdx.x & 31, sub = lane & 3;
+quantize_pack_word_kernel(const float* w, uint32_t nwords, uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, float* fq_out,
+                          ab_fq_dev_report* __restrict__ rep) {
+    const int lane = threadIdx.x & 31;
     const uint32_t total_warps = gridDim.x * (kThreads / 32);
     const uint32_t warp_global = (blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const uint32_t nblocks = (nwords + 31) / 32;
     const float gamma = rep->gamma, inv = rep->inv_gamma;
     const float4* w4 = reinterpret_cast<const float4*>(w);
     float4* q4 = reinterpret_cast<float4*>(fq_out);
     unsigned int n_plus = 0, n_minus = 0, n_thr = 0;
     double s_err = 0, s_wq = 0, s_ww = 0, s_qq = 0;
     float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
-    constexpr int U = 4;
-    for (uint32_t c0 = warp_global; c0 < nchunks; c0 += U * total_warps) {
-        float4 v[U];
-        uint32_t g[U];
+    constexpr int U = 1;
+    for (uint32_t b0 = warp_global; b0 < nblocks; b0 += U * total_warps) {
+        float4 v[U][4];
+        uint32_t word[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t c = c0 + u * total_warps;
-            g[u] = (nchunks - 1 - (c < nchunks ? c : c0)) * 32 + lane;  // an out-of-range slot re-reads chunk c0
-            v[u] = WANT_FQ ? w4[g[u]] : __ldg(w4 + g[u]);               // fq_out may alias w
+            const uint32_t b = b0 + u * total_warps;
+            word[u] = (nblocks - 1 - (b < nblocks ? b : b0)) * 32 + lane;      // blocks are walked from the end of the tensor
+            const uint32_t wl = word[u] < nwords ? word[u] : nwords - 1;      // a lane past the end re-reads the last word
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[u][q] = WANT_FQ ? w4[(size_t)wl * 4 + q] : __ldg(w4 + (size_t)wl * 4 + q);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (c0 + u * total_warps >= nchunks) break;  // warp-uniform
-            const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-            float qv[4];
-            uint32_t cbits = 0;
+            if (b0 + u * total_warps >= nblocks) break;   // warp-uniform
+            if (word[u] >= nwords) continue;
+            uint32_t cword = 0, fword = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float scaled = __fmul_rn(x[i], inv);
-                // on the bits of s: |s| in [0.5, Inf] (NaN excluded) is one unsigned compare, the code is sign + 1
-                const uint32_t b = __float_as_uint(scaled), mag = b & 0x7fffffffu;
-                const uint32_t c = (mag - 0x3F000000u) <= 0x40800000u ? (b >> 31) + 1u : 0u;   // 1 = +1, 2 = -1
-                cbits += c << (2 * i);
-                n_thr += (mag - 0x3EFFFFFFu) <= 2u;  // |s| within 1 ulp of 0.5
-                if (WANT_FQ || WANT_STATS) {
-                    // c * gamma as the reference forms it: NaN stays NaN, a rounded-to-zero value keeps its sign
-                    qv[i] = scaled != scaled ? scaled
-                                             : (c == 1u ? gamma : (c == 2u ? -gamma : __uint_as_float(b & 0x80000000u)));
+            for (int q = 0; q < 4; ++q) {
+                const float x[4] = {v[u][q].x, v[u][q].y, v[u][q].z, v[u][q].w};
+                float qv[4];
+                uint32_t cb = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float scaled = __fmul_rn(x[i], inv);
+                    const uint32_t bits = __float_as_uint(scaled), mag = bits & 0x7fffffffu;
+                    const uint32_t c = (mag - 0x3F000000u) <= 0x40800000u ? (bits >> 31) + 1u : 0u;   // 1 = +1, 2 = -1
+                    cb += c << (2 * i);
+                    n_thr += (mag - 0x3EFFFFFFu) <= 2u;
+                    if (WANT_FQ || WANT_STATS)
+                        qv[i] = scaled != scaled ? scaled : (c == 1u ? gamma : (c == 2u ? -gamma : __uint_as_float(bits & 0x80000000u)));
+                    if (WANT_STATS) {
+                        double wd = (double)x[i], qd = (double)qv[i];
+                        s_err += fabs(wd - qd);
+                        s_wq += wd * qd;
+                        s_ww += wd * wd;
+                        s_qq += qd * qd;
+                        vmin = fminf(vmin, x[i]);
+                        vmax = fmaxf(vmax, x[i]);
+                    }
                 }
-                if (WANT_STATS) {
-                    double wd = (double)x[i], qd = (double)qv[i];
-                    s_err += fabs(wd - qd);
-                    s_wq += wd * qd;
-                    s_ww += wd * wd;
-                    s_qq += qd * qd;
-                    vmin = fminf(vmin, x[i]);
-                    vmax = fmaxf(vmax, x[i]);
-                }
+                cword |= cb << (8 * q);                                  // element e = 4q + i at bit 2e
+                const uint32_t lo = cb & 0x55u, hi = (cb >> 1) & 0x55u;
+                const uint32_t fp = (~(lo | hi) & 0x55u) | (lo << 1);    // w + 1 per field: 0 -> 1, 1 -> 2, 2 -> 0
+                fword |= ((((fp & 0x33u) * 0x1001u) & 0x00030003u) | (((fp & 0xCCu) * 0x40040u) & 0x03000300u)) << (2 * q);   // bit 8i + 2q
+                if (WANT_FQ) q4[(size_t)word[u] * 4 + q] = make_float4(qv[0], qv[1], qv[2], qv[3]);
             }
-            // offset-binary copy (w + 1) of the four codes, one byte each: per 2-bit field 0 -> 1, 1 -> 2, 2 -> 0, then the
-            // fields move from bit 2i to bit 8i (two multiplies spread the even and the odd fields without overlap)
-            const uint32_t lo = cbits & 0x55u, hi = (cbits >> 1) & 0x55u;
-            const uint32_t fp = (~(lo | hi) & 0x55u) | (lo << 1);
-            const uint32_t fbits = (((fp & 0x33u) * 0x1001u) & 0x00030003u) | (((fp & 0xCCu) * 0x40040u) & 0x03000300u);
-            // element e = 4*sub + i of the group: bit 2e in the canonical word, bit 8*(e%4) + 2*(e/4) in the operand copy
-            uint32_t cpart = cbits << (8 * sub), fpart = fbits << (2 * sub);
-            cpart |= __shfl_xor_sync(0xffffffffu, cpart, 1);
-            fpart |= __shfl_xor_sync(0xffffffffu, fpart, 1);
-            cpart |= __shfl_xor_sync(0xffffffffu, cpart, 2);
-            fpart |= __shfl_xor_sync(0xffffffffu, fpart, 2);
-            const uint32_t word = g[u] >> 2;
-            if (sub == 0) {
-                codes[word] = cpart;
-                n_plus += __popc(cpart & 0x55555555u);
-                n_minus += __popc(cpart & 0xAAAAAAAAu);
-            }
-            if (sub == 1 && codes_fwd) codes_fwd[word] = fpart;
-            if (WANT_FQ) q4[g[u]] = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            codes[word[u]] = cword;
+            if (codes_fwd) codes_fwd[word[u]] = fword;
+            n_plus += __popc(cword & 0x55555555u);
+            n_minus += __popc(cword & 0xAAAAAAAAu);
         }
     }
     __shared__ unsigned int sc[3];
@@ -731,17 +729,17 @@ static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float*
         const bool vec = (w->in % 128 == 0) && n < (size_t(1) << 33) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
                          (!fq_out || (reinterpret_cast<uintptr_t>(fq_out) & 15) == 0);
         if (vec) {
-            const uint32_t chunks = (uint32_t)(n / 128);
-            size_t want = ((size_t)chunks + (kThreads / 32) * 4 - 1) / ((kThreads / 32) * 4);
+            const uint32_t nwords = (uint32_t)(n / 16);
+            size_t want = ((size_t)(nwords + 31) / 32 + (kThreads / 32) - 1) / (kThreads / 32);
             unsigned int grid = (unsigned int)(want < (size_t)ctx->sm_count * 8 ? (want ? want : 1) : (size_t)ctx->sm_count * 8);
             if (fq_out && want_stats)
-                quantize_pack_vec_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, fq_out, w->report_dev);
+                quantize_pack_word_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, nwords, c, f, fq_out, w->report_dev);
             else if (fq_out)
-                quantize_pack_vec_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, fq_out, w->report_dev);
+                quantize_pack_word_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, nwords, c, f, fq_out, w->report_dev);
             else if (want_stats)
-                quantize_pack_vec_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, nullptr, w->report_dev);
+                quantize_pack_word_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, nwords, c, f, nullptr, w->report_dev);
             else
-                quantize_pack_vec_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, chunks, c, f, nullptr, w->report_dev);
+                quantize_pack_word_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, nwords, c, f, nullptr, w->report_dev);
         } else {
             unsigned int grid = grid_for(words, kThreads);
             if (fq_out && want_stats)
