@@ -68,6 +68,19 @@ __device__ __forceinline__ int quant1(float x, float inv) {
     const int q = __float2int_rz(__fadd_rn(y, copysignf(0.49999997f, y)));
     return q < -127 ? -127 : (q > 127 ? 127 : q);
 }
+// The same without the clamp, for values that go through pack4_sat (which saturates): |x * inv| <= 127 (1 + 2^-22) whenever
+// |x| <= the row's maximum, so the clamp never acts on finite rows anyway.
+__device__ __forceinline__ int quant1_raw(float x, float inv) {
+    const float y = __fmul_rn(x, inv);
+    return __float2int_rz(__fadd_rn(y, copysignf(0.49999997f, y)));
+}
+// four s32 -> four saturated s8 in one word (byte i = q_i): two cvt.pack, each packing a pair and merging the other half
+__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(q1), "r"(q0), "r"(hi));
+    return d;
+}
 __device__ __forceinline__ float silu_mul(float g, float u) {
     const float silu_g = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
     return __fmul_rn(silu_g, u);
@@ -202,10 +215,12 @@ row_op_act_quant_kernel(const T* __restrict__ x, const T* __restrict__ x2, const
     auto emit8 = [&](const float* v, size_t g) {
         int q[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { q[i] = quant1(v[i], inv); sum += q[i]; }
+        for (int i = 0; i < 8; ++i) q[i] = quant1_raw(v[i], inv);
         uint2 pk;
-        pk.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-        pk.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+        pk.x = pack4_sat(q[0], q[1], q[2], q[3]);
+        pk.y = pack4_sat(q[4], q[5], q[6], q[7]);
+        sum = __dp4a((int)pk.x, 0x01010101, sum);      // the row sum, from the bytes that are stored
+        sum = __dp4a((int)pk.y, 0x01010101, sum);
         *reinterpret_cast<uint2*>(orow + g * 8) = pk;
     };
     if (in_regs) {
