@@ -476,7 +476,7 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
     // Cut K into chunks (grid.y) so that every SM gets the same amount of work: among the cuts whose chunks fit the
     // digit buffer, take the one with the smallest per-SM load (row groups per block x spans per chunk), biased
     // towards fewer chunks (each costs an atomic per row), longer chunks and a dozen warps per SM.
-    size_t chunks = 0, chunk_spans = 0;
+    size_t chunks = 0, chunk_spans = 0, best_nw = 0;
     double best_cost = 0.0;
     for (size_t s = 1; s <= total_spans && s <= sms; ++s) {
         const size_t span_per = (total_spans + s - 1) / s;
@@ -496,7 +496,13 @@ int abk_matvec_mma(ab_ctx* ctx, const uint8_t* codes, size_t pitch, size_t rows,
         const double round_trips = (double)((units_per_warp * span_per + 2) / 3);
         const double latency_cost = 14.0 * round_trips * (1.0 + 0.02 * (double)s);
         if (latency_cost > cost) cost = latency_cost;
-        if (chunks == 0 || cost < best_cost) { best_cost = cost; chunks = s; chunk_spans = span_per; }
+        // near-ties go to the cut that puts more warps (more stages in flight) on an SM: measured at 8192 x 28672, 8 chunks
+        // of 15 warps 17.8 us against 7 chunks of 13 warps 18.4 us at model costs 2.8 % apart
+        // (only among bandwidth-bound cuts of a dozen warps or more; nw_bal = warps once the passes are evened out)
+        const size_t nw_bal = per_block >= 12 ? (per_block + units_per_warp - 1) / units_per_warp : 0;
+        const bool better = chunks == 0 || cost < 0.96 * best_cost || (cost < 1.04 * best_cost && nw_bal > best_nw) ||
+                            (cost < best_cost && nw_bal >= best_nw);
+        if (better) { best_cost = cost; chunks = s; chunk_spans = span_per; best_nw = nw_bal; }
     }
     if (chunks == 0) return abk_matvec_ldg(ctx, codes, pitch, rows, k, v, y, scale, accumulate, use_scale);
     const size_t unit_spans = chunk_spans, units = groups;   // one unit per row group and chunk
