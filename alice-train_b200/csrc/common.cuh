@@ -77,7 +77,7 @@ struct ab_fq_dev_report {  // written by the quantiser kernels
     float inv_gamma;
     float w_min, w_max;
     unsigned int blocks_done;
-    unsigned int pad;
+    unsigned int tile_next;   // next tile of the tiled pack pass; cleared by the pass that sets gamma
 };
 
 struct ab_weights {

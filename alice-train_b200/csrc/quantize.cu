@@ -9,6 +9,8 @@
 //   planes = word j*wpr + k/32, bit k%32                           shaders/ternary_backward.wgsl:5-7
 #include <stdlib.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -70,22 +72,57 @@ struct OptArgs {
     float lr, wd, beta1, beta2, eps, bc1, bc2;
 };
 
+// One element of the update from values already in registers; m and v are updated in place (AdamW).
 template <int OPT>
-__device__ __forceinline__ float opt_update(float w, size_t i, const OptArgs& o) {
+__device__ __forceinline__ float opt_update_value(float w, float g, float& m, float& v, const OptArgs& o) {
     if (OPT == OPT_SGD) {
         // w -= lr * (g + wd * w)
-        return __fsub_rn(w, __fmul_rn(o.lr, __fadd_rn(o.grad[i], __fmul_rn(o.wd, w))));
+        return __fsub_rn(w, __fmul_rn(o.lr, __fadd_rn(g, __fmul_rn(o.wd, w))));
     } else if (OPT == OPT_ADAMW) {
-        const float g = o.grad[i];
-        const float mi = __fadd_rn(__fmul_rn(o.beta1, o.m[i]), __fmul_rn(__fsub_rn(1.0f, o.beta1), g));
-        const float vi = __fadd_rn(__fmul_rn(o.beta2, o.v[i]), __fmul_rn(__fmul_rn(__fsub_rn(1.0f, o.beta2), g), g));
-        o.m[i] = mi;
-        o.v[i] = vi;
-        const float m_hat = __fdiv_rn(mi, o.bc1), v_hat = __fdiv_rn(vi, o.bc2);
+        m = __fadd_rn(__fmul_rn(o.beta1, m), __fmul_rn(__fsub_rn(1.0f, o.beta1), g));
+        v = __fadd_rn(__fmul_rn(o.beta2, v), __fmul_rn(__fmul_rn(__fsub_rn(1.0f, o.beta2), g), g));
+        const float m_hat = __fdiv_rn(m, o.bc1), v_hat = __fdiv_rn(v, o.bc2);
         const float step = __fadd_rn(__fdiv_rn(m_hat, __fadd_rn(__fsqrt_rn(v_hat), o.eps)), __fmul_rn(o.wd, w));
         return __fsub_rn(w, __fmul_rn(o.lr, step));
     }
     return w;
+}
+
+template <int OPT>
+__device__ __forceinline__ float opt_update(float w, size_t i, const OptArgs& o) {
+    float m = 0.0f, v = 0.0f;
+    if (OPT == OPT_ADAMW) { m = o.m[i]; v = o.v[i]; }
+    const float r = opt_update_value<OPT>(w, OPT == OPT_NONE ? 0.0f : o.grad[i], m, v, o);
+    if (OPT == OPT_ADAMW) { o.m[i] = m; o.v[i] = v; }
+    return r;
+}
+
+// Four consecutive elements: the gradient and both moments move as 128-bit words like the weights themselves (`wide` =
+// all three tensors are 16-byte aligned; scalar accesses otherwise).  Same arithmetic per element either way.
+template <int OPT>
+__device__ __forceinline__ void opt_update4(float4& w, size_t i4, const OptArgs& o, bool wide) {
+    if (OPT == OPT_NONE) return;
+    if (!wide) {
+        w.x = opt_update<OPT>(w.x, 4 * i4, o);
+        w.y = opt_update<OPT>(w.y, 4 * i4 + 1, o);
+        w.z = opt_update<OPT>(w.z, 4 * i4 + 2, o);
+        w.w = opt_update<OPT>(w.w, 4 * i4 + 3, o);
+        return;
+    }
+    const float4 g = __ldg(reinterpret_cast<const float4*>(o.grad) + i4);
+    float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+    if (OPT == OPT_ADAMW) {
+        m = reinterpret_cast<const float4*>(o.m)[i4];
+        v = reinterpret_cast<const float4*>(o.v)[i4];
+    }
+    w.x = opt_update_value<OPT>(w.x, g.x, m.x, v.x, o);
+    w.y = opt_update_value<OPT>(w.y, g.y, m.y, v.y, o);
+    w.z = opt_update_value<OPT>(w.z, g.z, m.z, v.z, o);
+    w.w = opt_update_value<OPT>(w.w, g.w, m.w, v.w, o);
+    if (OPT == OPT_ADAMW) {
+        reinterpret_cast<float4*>(o.m)[i4] = m;
+        reinterpret_cast<float4*>(o.v)[i4] = v;
+    }
 }
 
 template <int OPT>
@@ -101,13 +138,12 @@ absmean_reduce_kernel(float* __restrict__ w, size_t n, double* __restrict__ part
     if ((reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         size_t n4 = n / 4;
         float4* w4 = reinterpret_cast<float4*>(w);
+        const bool wide = OPT != OPT_NONE && (reinterpret_cast<uintptr_t>(opt.grad) & 15) == 0 &&
+                          (OPT != OPT_ADAMW || ((reinterpret_cast<uintptr_t>(opt.m) | reinterpret_cast<uintptr_t>(opt.v)) & 15) == 0);
         for (size_t i = tid; i < n4; i += stride) {
             float4 v = OPT == OPT_NONE ? __ldg(w4 + i) : w4[i];
             if (OPT != OPT_NONE) {
-                v.x = opt_update<OPT>(v.x, 4 * i, opt);
-                v.y = opt_update<OPT>(v.y, 4 * i + 1, opt);
-                v.z = opt_update<OPT>(v.z, 4 * i + 2, opt);
-                v.w = opt_update<OPT>(v.w, 4 * i + 3, opt);
+                opt_update4<OPT>(v, i, opt, wide);
                 w4[i] = v;
             }
             acc += (double)fabsf(v.x);
@@ -163,6 +199,7 @@ absmean_reduce_kernel(float* __restrict__ w, size_t n, double* __restrict__ part
         rep->w_min = __uint_as_float(0xffffffffu);  // holds keys until read back
         rep->w_max = __uint_as_float(0u);
         rep->blocks_done = 0u;
+        rep->tile_next = 0u;
         *gamma_out = gamma;
     }
 }
@@ -218,8 +255,8 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
                 n_plus += c > 0;
                 n_minus += c < 0;
                 float a = fabsf(scaled);
-                n_thr += (a >= 0.49999997f && a <= 0.50000006f);
                 if (WANT_STATS) {
+                    n_thr += (a >= 0.49999997f && a <= 0.50000006f);
                     double wd = (double)v[e], qd = (double)qv[e];
                     s_err += fabs(wd - qd);
                     s_wq += wd * qd;
@@ -278,16 +315,45 @@ quantize_pack_kernel(const float* w, size_t out, size_t in, size_t words_per_row
     }
 }
 
+// One element of the fast pack passes.  clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff s <= -0.5 and 0
+// otherwise (NaN compares false twice -> 0; +-Inf -> +-1), so each element is a multiply, two compares and, for the one
+// weight in three that is non-zero, adds of constants: the canonical word takes 01 or 10 at bit 2e, the forward operand
+// word starts as 0x55555555 (every field w + 1 = 1) and takes +1 or -1 at its field's bit `fbit`.  Returns the
+// fake-quantised value where a caller wants it.  The census of elements within one ulp of a threshold and the
+// CalibrationStats sums are taken only when statistics were requested.
+template <bool WANT_FQ, bool WANT_STATS>
+__device__ __forceinline__ float pack_element(float x, float inv, float gamma, int e, int fbit, uint32_t& cword, uint32_t& fword,
+                                              unsigned int& n_thr, double& s_err, double& s_wq, double& s_ww, double& s_qq,
+                                              float& vmin, float& vmax) {
+    const float scaled = __fmul_rn(x, inv);
+    const bool plus = scaled >= 0.5f, minus = scaled <= -0.5f;
+    if (plus) { cword += 1u << (2 * e); fword += 1u << fbit; }
+    if (minus) { cword += 2u << (2 * e); fword -= 1u << fbit; }
+    float qv = 0.0f;
+    if (WANT_FQ || WANT_STATS)
+        qv = scaled != scaled ? scaled : (plus ? gamma : (minus ? -gamma : __uint_as_float(__float_as_uint(scaled) & 0x80000000u)));
+    if (WANT_STATS) {
+        n_thr += ((__float_as_uint(scaled) & 0x7fffffffu) - 0x3EFFFFFFu) <= 2u;
+        const double wd = (double)x, qd = (double)qv;
+        s_err += fabs(wd - qd);
+        s_wq += wd * qd;
+        s_ww += wd * wd;
+        s_qq += qd * qd;
+        vmin = fminf(vmin, x);
+        vmax = fmaxf(vmax, x);
+    }
+    return qv;
+}
+
 // Fast path of pass B (rows that are multiples of 128 elements, 16-byte aligned tensors): row pitch equals the row
 // length, so code word i simply holds elements 16i..16i+15 of the flat tensor.  Lane L of a warp owns word L of a 32-word
 // block (four 128-bit loads at a 64-byte lane stride: the four loads of a warp together cover 2 KB exactly, the later
 // ones hit the lines the first brought in), so the word is assembled in the lane's own registers and both copies leave
 // as one coalesced 128-byte store per warp each.  Blocks are walked from the END of the tensor: pass A has just read it
-// front to back, so its tail is what the L2 still holds.  clamp(round_half_away(s), -1, 1) is +1 iff s >= 0.5, -1 iff
-// s <= -0.5 and 0 otherwise (NaN -> 0): on the bits of s that is one unsigned compare of |s| against [0.5, Inf] and the
-// sign.  (A form with one 128-bit load per lane and the word merged by shuffles among four lanes took 63 us for
-// 14336 x 4096 against 48 us; more than one block in flight per warp did not help: 91.0 / 92.5 / 101.4 us for the
-// whole quantiser at 1 / 2 / 4.)
+// front to back, so its tail is what the L2 still holds.  This is the pass for handles that carry no transposed copy;
+// those that do take quantize_pack_tile_kernel below.  (A form with one 128-bit load per lane and the word merged by
+// shuffles among four lanes took 63 us for 14336 x 4096 against 48 us; more than one block in flight per warp did not
+// help: 91.0 / 92.5 / 101.4 us for the whole quantiser at 1 / 2 / 4.)
 template <bool WANT_FQ, bool WANT_STATS>
 __global__ void __launch_bounds__(kThreads)
 quantize_pack_word_kernel(const float* w, uint32_t nwords, uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd, float* fq_out,
@@ -318,41 +384,141 @@ quantize_pack_word_kernel(const float* w, uint32_t nwords, uint32_t* __restrict_
         for (int u = 0; u < U; ++u) {
             if (b0 + u * total_warps >= nblocks) break;   // warp-uniform
             if (word[u] >= nwords) continue;
-            uint32_t cword = 0, fword = 0;
+            uint32_t cword = 0, fword = 0x55555555u;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float x[4] = {v[u][q].x, v[u][q].y, v[u][q].z, v[u][q].w};
                 float qv[4];
-                uint32_t cb = 0;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float scaled = __fmul_rn(x[i], inv);
-                    const uint32_t bits = __float_as_uint(scaled), mag = bits & 0x7fffffffu;
-                    const uint32_t c = (mag - 0x3F000000u) <= 0x40800000u ? (bits >> 31) + 1u : 0u;   // 1 = +1, 2 = -1
-                    cb += c << (2 * i);
-                    n_thr += (mag - 0x3EFFFFFFu) <= 2u;
-                    if (WANT_FQ || WANT_STATS)
-                        qv[i] = scaled != scaled ? scaled : (c == 1u ? gamma : (c == 2u ? -gamma : __uint_as_float(bits & 0x80000000u)));
-                    if (WANT_STATS) {
-                        double wd = (double)x[i], qd = (double)qv[i];
-                        s_err += fabs(wd - qd);
-                        s_wq += wd * qd;
-                        s_ww += wd * wd;
-                        s_qq += qd * qd;
-                        vmin = fminf(vmin, x[i]);
-                        vmax = fmaxf(vmax, x[i]);
-                    }
-                }
-                cword |= cb << (8 * q);                                  // element e = 4q + i at bit 2e
-                const uint32_t lo = cb & 0x55u, hi = (cb >> 1) & 0x55u;
-                const uint32_t fp = (~(lo | hi) & 0x55u) | (lo << 1);    // w + 1 per field: 0 -> 1, 1 -> 2, 2 -> 0
-                fword |= ((((fp & 0x33u) * 0x1001u) & 0x00030003u) | (((fp & 0xCCu) * 0x40040u) & 0x03000300u)) << (2 * q);   // bit 8i + 2q
+                for (int i = 0; i < 4; ++i) qv[i] = pack_element<WANT_FQ, WANT_STATS>(x[i], inv, gamma, 4 * q + i, 8 * i + 2 * q, cword, fword, n_thr,
+                                                                                  s_err, s_wq, s_ww, s_qq, vmin, vmax);
                 if (WANT_FQ) q4[(size_t)word[u] * 4 + q] = make_float4(qv[0], qv[1], qv[2], qv[3]);
             }
             codes[word[u]] = cword;
             if (codes_fwd) codes_fwd[word[u]] = fword;
             n_plus += __popc(cword & 0x55555555u);
             n_minus += __popc(cword & 0xAAAAAAAAu);
+        }
+    }
+    __shared__ unsigned int sc[3];
+    __shared__ double sd[32];
+    if (threadIdx.x < 3) sc[threadIdx.x] = 0;
+    __syncthreads();
+    n_plus = __reduce_add_sync(0xffffffffu, n_plus);
+    n_minus = __reduce_add_sync(0xffffffffu, n_minus);
+    n_thr = __reduce_add_sync(0xffffffffu, n_thr);
+    if (lane == 0) {
+        atomicAdd(&sc[0], n_plus);
+        atomicAdd(&sc[1], n_minus);
+        atomicAdd(&sc[2], n_thr);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (sc[0]) atomicAdd(&rep->n_plus, (unsigned long long)sc[0]);
+        if (sc[1]) atomicAdd(&rep->n_minus, (unsigned long long)sc[1]);
+        if (sc[2]) atomicAdd(&rep->n_threshold, (unsigned long long)sc[2]);
+    }
+    if (WANT_STATS) {
+        double b;
+        b = block_sum(s_err, sd); if (threadIdx.x == 0) atomicAdd(&rep->sum_err, b);
+        b = block_sum(s_wq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_wq, b);
+        b = block_sum(s_ww, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_ww, b);
+        b = block_sum(s_qq, sd);  if (threadIdx.x == 0) atomicAdd(&rep->dot_qq, b);
+        unsigned int kmin = __reduce_min_sync(0xffffffffu, float_key(vmin));
+        unsigned int kmax = __reduce_max_sync(0xffffffffu, float_key(vmax));
+        if (lane == 0) {
+            atomicMin(reinterpret_cast<unsigned int*>(&rep->w_min), kmin);
+            atomicMax(reinterpret_cast<unsigned int*>(&rep->w_max), kmax);
+        }
+    }
+}
+
+// Pass B with the transposed operand copy made in the same pass (tensors that qualify for the word kernel and carry a
+// transposed copy).  A block takes tiles of 128 rows x 128 columns: the smallest tile whose row-major code words (8 per
+// row) and whose transposed words (8 row groups per column) both leave as whole 32-byte sectors.  Warp i owns row group i of
+// the tile; a lane computes four code words one after the other (rows 4p + lane/8, column word lane%8; four 128-bit loads each), stores
+// them row-major from its registers and drops the canonical word into a 4 KB shared tile; after one barrier two warps
+// transpose the tile's 64 blocks of 16 x 16 fields in registers (the word-level butterfly of transpose_codes_kernel) and
+// write codes_t, while the others already load the next tile into the second shared buffer.  Tiles are handed out by a
+// counter in the report block (cleared by pass A), from the END of the tensor, which is what pass A left in the L2.
+template <bool WANT_FQ, bool WANT_STATS>
+__global__ void __launch_bounds__(kThreads, WANT_STATS ? 4 : 6)
+quantize_pack_tile_kernel(const float* w, uint32_t out, uint32_t in, uint32_t* __restrict__ codes, uint32_t* __restrict__ codes_fwd,
+                          uint32_t* __restrict__ codes_t, uint32_t twpr, float* fq_out, ab_fq_dev_report* rep) {
+    constexpr int kTileWords = 128 * 8 + 8 * 4;   // row group i starts 4 words late: the transposing reads hit 32 banks
+    __shared__ uint32_t tile_s[2][kTileWords];
+    __shared__ uint32_t s_next[2];
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    const int r4 = lane >> 3, cw = lane & 7;
+    const uint32_t wpr = in / 16, col_tiles = in / 128, bands = (twpr + 7) / 8, ntiles = bands * col_tiles;
+    const float gamma = rep->gamma, inv = rep->inv_gamma;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4* q4 = reinterpret_cast<float4*>(fq_out);
+    unsigned int n_plus = 0, n_minus = 0, n_thr = 0;
+    double s_err = 0, s_wq = 0, s_ww = 0, s_qq = 0;
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    if (threadIdx.x == 0) s_next[0] = atomicAdd(&rep->tile_next, 1u);
+    __syncthreads();
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t t = s_next[it & 1];
+        if (t >= ntiles) break;                                                       // block-uniform
+        if (threadIdx.x == 0) s_next[(it + 1) & 1] = atomicAdd(&rep->tile_next, 1u);  // read after this iteration's barrier
+        const uint32_t tr = ntiles - 1 - t, band = tr / col_tiles, ct = tr % col_tiles;
+        const uint32_t row0 = (band * 8 + wi) * 16 + r4;
+        uint32_t* ts = tile_s[it & 1];
+#pragma unroll 1
+        for (int p = 0; p < 4; ++p) {   // one row at a time: 40 registers, six blocks per SM (two or four rows in flight: 87.5 / 95.4 us against 86.5)
+            const uint32_t row = row0 + 4 * p;
+            uint32_t cword = 0, fword = 0x55555555u;
+            if (row < out) {
+                const size_t base = ((size_t)row * in + (size_t)ct * 128 + (size_t)cw * 16) / 4;
+                float4 vp[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) vp[q] = WANT_FQ ? w4[base + q] : __ldg(w4 + base + q);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float x[4] = {vp[q].x, vp[q].y, vp[q].z, vp[q].w};
+                    float qv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) qv[i] = pack_element<WANT_FQ, WANT_STATS>(x[i], inv, gamma, 4 * q + i, 8 * i + 2 * q, cword, fword, n_thr,
+                                                                                      s_err, s_wq, s_ww, s_qq, vmin, vmax);
+                    if (WANT_FQ) q4[base + q] = make_float4(qv[0], qv[1], qv[2], qv[3]);
+                }
+                const uint32_t wi_glob = row * wpr + ct * 8 + cw;
+                codes[wi_glob] = cword;
+                if (codes_fwd) codes_fwd[wi_glob] = fword;
+                n_plus += __popc(cword & 0x55555555u);
+                n_minus += __popc(cword & 0xAAAAAAAAu);
+            }
+            ts[(wi * 16 + 4 * p + r4) * 8 + cw + wi * 4] = cword;
+        }
+        __syncthreads();
+        if (threadIdx.x < 64) {
+            const int jl = threadIdx.x & 7, cwt = threadIdx.x >> 3;
+            uint32_t x[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) x[4 * (e & 3) + (e >> 2)] = ts[(jl * 16 + e) * 8 + cwt + jl * 4];
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+                const int jj = 8 >> st;
+                const uint32_t m = st == 0 ? 0x0000FFFFu : (st == 1 ? 0x00FF00FFu : (st == 2 ? 0x0F0F0F0Fu : 0x33333333u));
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    if (k & jj) continue;
+                    const uint32_t tt = ((x[k] >> (2 * jj)) ^ x[k + jj]) & m;
+                    x[k] ^= tt << (2 * jj);
+                    x[k + jj] ^= tt;
+                }
+            }
+            const uint32_t jg = band * 8 + jl;
+            if (jg < twpr) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const size_t i = (size_t)ct * 128 + (size_t)cwt * 16 + c;
+                    const uint32_t plus = x[c] & 0x55555555u, minus = (x[c] >> 1) & 0x55555555u;
+                    codes_t[i * twpr + jg] = (plus << 1) | (~(plus | minus) & 0x55555555u);
+                }
+            }
         }
     }
     __shared__ unsigned int sc[3];
@@ -693,6 +859,7 @@ __global__ void shard_gamma_kernel(ab_fq_dev_report* rep, float* gamma_out, cons
     rep->n_plus = rep->n_minus = rep->n_threshold = 0ull;
     rep->w_min = __uint_as_float(0xffffffffu);
     rep->w_max = __uint_as_float(0u);
+    rep->tile_next = 0u;
     *gamma_out = gamma;
 }
 
@@ -719,6 +886,11 @@ int abk_fq_shard_pack(ab_ctx* ctx, const float* w_latent, ab_weights* w, const d
     return pack_launch(ctx, w_latent, w, fq_out, want_stats);
 }
 
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e && *e ? atoi(e) : dflt;
+}
+
 static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float* fq_out, int want_stats) {
     const size_t n = w->out * w->in;
     const size_t wpr = w->pitch / 4;
@@ -728,6 +900,26 @@ static int pack_launch(ab_ctx* ctx, const float* w_latent, ab_weights* w, float*
         uint32_t* f = reinterpret_cast<uint32_t*>(w->codes_fwd);
         const bool vec = (w->in % 128 == 0) && n < (size_t(1) << 33) && ((reinterpret_cast<uintptr_t>(w_latent) & 15) == 0) &&
                          (!fq_out || (reinterpret_cast<uintptr_t>(fq_out) & 15) == 0);
+        static const int tile_ok = env_int("AB_FQ_TILE", 1);   // measurement aid: 0 = word kernel + separate transposition
+        if (vec && w->codes_t && tile_ok) {
+            const uint32_t twpr = (uint32_t)(w->tpitch / 4), o32 = (uint32_t)w->out, i32 = (uint32_t)w->in;
+            uint32_t* tc = reinterpret_cast<uint32_t*>(w->codes_t);
+            const size_t ntiles = (size_t)((twpr + 7) / 8) * (i32 / 128);
+            const size_t resident = (size_t)ctx->sm_count * (want_stats ? 4 : 6);   // what the register budget of each form admits
+            const unsigned int grid = (unsigned int)(ntiles < resident ? ntiles : resident);
+            if (fq_out && want_stats)
+                quantize_pack_tile_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, o32, i32, c, f, tc, twpr, fq_out, w->report_dev);
+            else if (fq_out)
+                quantize_pack_tile_kernel<true, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, o32, i32, c, f, tc, twpr, fq_out, w->report_dev);
+            else if (want_stats)
+                quantize_pack_tile_kernel<false, true><<<grid, kThreads, 0, ctx->stream>>>(w_latent, o32, i32, c, f, tc, twpr, nullptr, w->report_dev);
+            else
+                quantize_pack_tile_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(w_latent, o32, i32, c, f, tc, twpr, nullptr, w->report_dev);
+            AB_LAUNCH_CHECK(ctx);
+            w->has_data = true;
+            w->has_report = true;
+            return AB_OK;
+        }
         if (vec) {
             const uint32_t nwords = (uint32_t)(n / 16);
             size_t want = ((size_t)(nwords + 31) / 32 + (kThreads / 32) - 1) / (kThreads / 32);

@@ -65,9 +65,10 @@ typedef struct ab_fq_report {
     uint64_t n;             /* elements quantised                                               */
     uint64_t n_plus;        /* codes equal to +1                                                */
     uint64_t n_minus;       /* codes equal to -1                                                */
+    /* The rest is filled only when stats were requested (zero otherwise).                      */
     uint64_t n_threshold;   /* elements with |w*inv_gamma| within 1 ulp of 0.5 (could flip
                                under a differently rounded gamma); reported, not an error      */
-    /* CalibrationStats inputs (src/qat.rs:270-310), f64; zero unless stats were requested     */
+    /* CalibrationStats inputs (src/qat.rs:270-310), f64                                        */
     double sum_err, dot_wq, dot_ww, dot_qq;
     float w_min, w_max;
 } ab_fq_report;

@@ -113,7 +113,7 @@ def test_forward_bf16_vs_matmul_bt_oracle(env, orc, m, out, inn):
 
 
 @pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 64, 256), (100, 304, 264), (1, 4096, 256),
-                                       (130, 48, 8), (257, 2000, 1000), (4, 4, 4), (3, 7, 5)])
+                                       (130, 48, 8), (257, 2000, 1000), (4, 4, 4), (3, 7, 5), (64, 200, 512)])
 def test_dx_vs_oracle(env, orc, m, out, inn):
     at, bl, ctx, torch = env
     h, g, codes = _weights(env, orc, out, inn, 50)

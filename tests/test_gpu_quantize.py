@@ -67,6 +67,39 @@ def test_fq_absmean_pack_bit_exact(ctx, orc, shape, seed):
     h.close()
 
 
+@pytest.mark.parametrize("shape,seed", [((200, 512), 31), ((72, 640), 32), ((1000, 1024), 33), ((2064, 768), 34),
+                                        ((128, 128), 35), ((4096, 2048), 36)])
+def test_quantiser_operand_copies(ctx, at, orc, shape, seed):
+    """The quantiser writes three layouts of the same codes: canonical (checked above), the forward operand copy and the
+    transposed copy.  Rows of a multiple of 128 elements take the tiled pack pass, which makes all three in one kernel;
+    row counts that are no multiple of 16 or of 128 end in partial row groups and partial tiles.  The two operand copies
+    are checked through the products that read them, y = W x and dx = W^T dy on the integer path, which are exact on
+    integer vectors (every sum is below 2^24)."""
+    import ctypes as C
+    import torch
+    from alice_train import _ffi
+    out, inn = shape
+    w = normal_f32(seed, shape, 0.02)
+    h, _ = _quantize_dev(ctx, w)
+    _, codes_ref, _ = orc.quantize_and_pack(w)
+    codes = codes_ref.reshape(out, inn).astype(np.int64)
+    assert np.array_equal(h.to_ternary().reshape(-1), codes_ref)
+    rng = np.random.Generator(np.random.Philox(seed))
+    x = rng.integers(-1000, 1001, size=inn).astype(np.float32)
+    dy = rng.integers(-1000, 1001, size=out).astype(np.float32)
+    xt, dyt = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+    y = torch.full((out,), 7.0, dtype=torch.float32, device="cuda")
+    dx = torch.full((inn,), 7.0, dtype=torch.float32, device="cuda")
+    lib = _ffi.load()
+    ctx.set_exact_matvec(False)
+    _ffi.check(lib.ab_ternary_matvec(ctx.handle, h.handle, C.c_void_p(xt.data_ptr()), C.c_void_p(y.data_ptr())), ctx.handle)
+    _ffi.check(lib.ab_ternary_matvec_backward(ctx.handle, h.handle, C.c_void_p(dyt.data_ptr()), C.c_void_p(dx.data_ptr())), ctx.handle)
+    ctx.sync()
+    assert np.array_equal(y.cpu().numpy(), (codes @ x.astype(np.int64)).astype(np.float32))
+    assert np.array_equal(dx.cpu().numpy(), (codes.T @ dy.astype(np.int64)).astype(np.float32))
+    h.close()
+
+
 def test_fq_edge_cases(ctx, orc):
     # all-zero tensor: inv_gamma = 0 -> all codes 0 (src/qwen35.rs:736-740)
     h, fq = _quantize_dev(ctx, np.zeros((4, 8), np.float32), want_fq=True)
