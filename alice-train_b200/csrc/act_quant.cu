@@ -65,7 +65,7 @@ __device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
 
 // TPR threads share one token row; a block of 256 threads holds 256/TPR rows, so short rows still
 // put whole 128-bit loads of many rows in flight per SM instead of one small row per block.
-template <typename T, int TPR>
+template <typename T, int TPR, int CH = kRegChunks>
 __global__ void __launch_bounds__(kThreads)
 act_quant_kernel(const T* __restrict__ x, size_t m, size_t k, size_t ld_x, int8_t* __restrict__ xq, size_t ld_xq,
                  float* __restrict__ scales, int32_t* __restrict__ rowsums, int vec_ok) {
@@ -80,14 +80,14 @@ act_quant_kernel(const T* __restrict__ x, size_t m, size_t k, size_t ld_x, int8_
     const T* row = x + (row_ok ? t : 0) * ld_x;
     int8_t* orow = xq + (row_ok ? t : 0) * ld_xq;
     const size_t k8 = vec_ok ? k / 8 : 0;  // 8-element groups handled with vector accesses
-    const bool in_regs = k8 <= (size_t)kRegChunks * TPR;
+    const bool in_regs = k8 <= (size_t)CH * TPR;
 
-    float cache[kRegChunks][8];
+    float cache[CH][8];
     float amax = 0.0f;
     if (row_ok) {
         if (in_regs) {
 #pragma unroll
-            for (int c = 0; c < kRegChunks; ++c) {
+            for (int c = 0; c < CH; ++c) {
                 size_t g = (size_t)c * TPR + tr;
                 if (g < k8) {
                     Vec8<T>::load(row + g * 8, cache[c]);
@@ -130,7 +130,7 @@ act_quant_kernel(const T* __restrict__ x, size_t m, size_t k, size_t ld_x, int8_
     if (row_ok) {
         if (in_regs) {
 #pragma unroll
-            for (int c = 0; c < kRegChunks; ++c) {
+            for (int c = 0; c < CH; ++c) {
                 size_t g = (size_t)c * TPR + tr;
                 if (g < k8) emit8(cache[c], g);
             }
@@ -172,7 +172,8 @@ static void launch_act_quant(ab_ctx* ctx, const T* x, size_t m, size_t k, size_t
     act_quant_kernel<T, TPR><<<(unsigned)((m + (kThreads / TPR) - 1) / (kThreads / TPR)), kThreads, 0, ctx->stream>>>( \
         x, m, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok)
     if (k <= per_thread_cap * 32) AB_AQ(32);
-    else if (k <= per_thread_cap * 64) AB_AQ(64);
+    else if (k <= per_thread_cap * 64)   // 128 threads x 4 chunks: half the registers of 64 x 8, twice the rows' warps resident
+        act_quant_kernel<T, 128, 4><<<(unsigned)((m + 1) / 2), kThreads, 0, ctx->stream>>>(x, m, k, ld_x, xq, ld_xq, scales, rowsums, vec_ok);
     else if (k <= per_thread_cap * 128) AB_AQ(128);
     else AB_AQ(256);
 #undef AB_AQ

@@ -336,11 +336,11 @@ int launch_row_op(ab_ctx* ctx, const void* x, const void* x2, int x_dtype, const
     // block shape by row length (in chunks of 8 elements)
     const size_t k8 = vec_ok ? k / 8 : 0;
     // few rows (the decode chain has one): the row's latency is what counts, so spread it over many threads
-    const int shape = (k8 <= 64 * 8 && m >= 64) ? 0 : (k8 <= 512 * 4 ? 1 : 2);
+    const int shape = (k8 <= 128 * 4 && m >= 64) ? 0 : (k8 <= 512 * 4 ? 1 : 2);
 #define AB_ROW(T, TY)                                                                                                          \
     do {                                                                                                                       \
         if (shape == 0)                                                                                                        \
-            row_op_act_quant_kernel<MODE, T, TY, 64, 8><<<(unsigned)m, 64, 0, ctx->stream>>>(                                  \
+            row_op_act_quant_kernel<MODE, T, TY, 128, 4><<<(unsigned)m, 128, 0, ctx->stream>>>(                                \
                 (const T*)x, (const T*)x2, w, m, k, ld_x, eps, (TY*)y, ld_y, xq, ld_xq, scales, rowsums, vec_ok);              \
         else if (shape == 1)                                                                                                   \
             row_op_act_quant_kernel<MODE, T, TY, 512, 4><<<(unsigned)m, 512, 0, ctx->stream>>>(                                \
