@@ -33,6 +33,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import numpy as np
@@ -93,14 +94,50 @@ def compact(o, digits=5):
 
 # ------------------------------------------------------------------------------ clocks
 class ClockSampler:
+    """SM clock, power and clock-event reasons of one GPU while a timed region runs.  Reads NVML from a thread every few
+    milliseconds (the region is some tens of milliseconds long; `nvidia-smi -lms` starts too slowly to land samples in
+    it) and keeps the samples taken between mark_begin() and mark_end(); falls back to an `nvidia-smi -lms 50` child
+    process when NVML cannot be loaded.  Nothing is set, only read."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu, self.proc, self.path = gpu_index, None, None
+        self.thread, self.stop_flag, self.samples, self.t_begin, self.t_end, self.nvml = None, None, [], None, None, None
+
+    def _nvml_handle(self):
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+
+    def _loop(self, nv, h):
+        while not self.stop_flag.is_set():
+            try:
+                t = time.time()
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append((t, float(sm), pw, int(rs)))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            nv, h = self._nvml_handle()
+            self.nvml = (nv, h, float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)))
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -110,7 +147,26 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            nv, _, mx = self.nvml
+            inside = [x for x in self.samples if (self.t_begin is None or x[0] >= self.t_begin) and (self.t_end is None or x[0] <= self.t_end)]
+            use = inside if inside else self.samples
+            names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap))
+            reasons = sorted({n for _, _, _, r in use for n, bit in names if r & bit})
+            return {"sm_mhz": statistics.median([x[1] for x in use]) if use else None, "sm_max_mhz": mx,
+                    "power_w_max": max([x[2] for x in use]) if use else None, "samples": len(use),
+                    "sampled": "NVML every ~2 ms inside the timed region" if inside else "NVML, no sample fell inside the timed region",
+                    "reasons": reasons}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -137,7 +193,8 @@ class ClockSampler:
         except OSError:
             pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "sampled": "nvidia-smi -lms 50 around the timed region",
+                "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------- reference (CPU) arm
@@ -391,11 +448,13 @@ def run_main(env, args):
     env.fence()
     launches0 = ctx.launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     t0.record()
     for _ in range(args.steps):
         step(True)
     t1.record()
     env.fence()
+    sampler.mark_end()
     launches = ctx.launch_count() - launches0
     ms_total = env.max_over_ranks(t0.elapsed_time(t1))
     clocks = sampler.stop() if rank == 0 else None
