@@ -17,7 +17,7 @@ AB_ERR_DEVICE_TIMEOUT, AB_ERR_UNSUPPORTED, AB_ERR_NO_DEVICE, AB_ERR_STATE = 5, 6
 AB_F32, AB_BF16 = 0, 1
 AB_TERNARY, AB_BINARY2, AB_INT4, AB_INT8 = 0, 1, 2, 3
 AB_GUARD_INV_ZERO, AB_GUARD_FLOOR = 0, 1
-AB_OPT_EXACT_MATVEC, AB_OPT_ASYNC_HOST_STEP, AB_OPT_HOST_INTEGER_MATVEC = 1, 2, 3
+AB_OPT_EXACT_MATVEC, AB_OPT_ASYNC_HOST_STEP, AB_OPT_HOST_INTEGER_MATVEC, AB_OPT_GEMM_OPERAND_FORM = 1, 2, 3, 4
 AB_XCHG_ALLREDUCE_F32, AB_XCHG_ALLGATHER, AB_XCHG_REDUCESCATTER_BF16 = 0, 1, 2
 
 

@@ -55,6 +55,12 @@ class GpuContext:
         tensor-core path like the device-pointer entry points."""
         _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_HOST_INTEGER_MATVEC, int(bool(on))), self._h)
 
+    def set_gemm_operand_form(self, form: int):
+        """0 (default): the batched forward and dx products choose by shape between the form with the expanded weights
+        in tensor memory and the one with them in shared memory; 1: tensor memory always; 2: shared memory always.
+        The results are identical."""
+        _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_GEMM_OPERAND_FORM, int(form)), self._h)
+
     def set_async_host_step(self, on: bool):
         """True: ab_bitlinear_step_host only queues its work; sync() before touching the host buffers."""
         _ffi.check(self._lib.ab_ctx_set_option(self._h, _ffi.AB_OPT_ASYNC_HOST_STEP, int(bool(on))), self._h)

@@ -63,6 +63,7 @@ public:
     void sync() const { check(ab_ctx_sync(h_.get())); }
     // true: batch-1 kernels add in f32 like the reference's loops; false (default): integer tensor-core path
     void set_exact_matvec(bool on) const { check(ab_ctx_set_option(h_.get(), AB_OPT_EXACT_MATVEC, on ? 1 : 0)); }
+    void set_gemm_operand_form(int form) const { check(ab_ctx_set_option(h_.get(), AB_OPT_GEMM_OPERAND_FORM, form)); }
     void check(int st) const {
         if (st != AB_OK) throw Error(st, ab_ctx_last_error(h_.get()));
     }

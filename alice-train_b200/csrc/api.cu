@@ -195,6 +195,11 @@ int ab_ctx_set_option(ab_ctx* ctx, int option, int value) {
         ctx->async_host_step = value != 0;
         return AB_OK;
     }
+    if (option == AB_OPT_GEMM_OPERAND_FORM) {
+        AB_REQUIRE(value >= 0 && value <= 2, AB_ERR_UNSUPPORTED);
+        ctx->gemm_operand_form = value;
+        return AB_OK;
+    }
     return AB_ERR_UNSUPPORTED;
 }
 

@@ -62,6 +62,7 @@ struct ab_ctx {
     bool async_host_step = false;  // AB_OPT_ASYNC_HOST_STEP
     bool exact_matvec = false;  // AB_OPT_EXACT_MATVEC: batch-1 kernels add in f32 like the reference
     bool host_integer_matvec = false;  // AB_OPT_HOST_INTEGER_MATVEC: the host-slice forms may take the integer path too
+    int gemm_operand_form = 0;  // AB_OPT_GEMM_OPERAND_FORM: 0 by shape, 1 weights in tensor memory, 2 weights in shared memory
     const float* row_scale = nullptr;   // set for the duration of ab_ternary_matvec_ex: y_j is scaled by row_scale[j] instead of one scale
     uint64_t launches = 0;
     // true while the most recent kernel this context launched was a streaming matvec (kernels that never write codes):

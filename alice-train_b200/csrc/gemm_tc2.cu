@@ -42,9 +42,22 @@ constexpr int TMEM_COLS = 512;
 constexpr int NUM_EXP_WARPS = 8;
 constexpr int kWarpsDW = 6;
 constexpr int kWarpsExp = 16;      // ids 0..15; 9 and 13 stay idle (they share the MMA warp's scheduler)
+// FWT / DXT: warps 0, 1 producer and MMA issuer, 2..9 epilogue (two per lane quarter of tensor memory, half the token
+// columns each), then the expanders: 8 for int8 (two per quarter, half of a stage's K each), 16 for bf16, whose byte
+// permutes are several times the work (two sets of 8 that take alternate stages).
+__host__ __device__ constexpr int ta_epi_warps() { return 8; }
+__host__ __device__ constexpr int ta_exp_warps(int mode) { return is_i8(mode) ? 8 : 16; }
+__host__ __device__ constexpr int block_warps(int mode) {
+    return tmem_a(mode) ? 2 + ta_epi_warps() + ta_exp_warps(mode) : (has_expanders(mode) ? kWarpsExp : kWarpsDW);
+}
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's leader
 
-template <int MODE> struct Cfg { static constexpr int STAGES = has_expanders(MODE) ? 6 : 7; };
+// FWT / DXT need no shared-memory stage for the expanded operand (it goes to tensor memory), so their ring is deeper;
+// their tensor memory holds ONE 256-column accumulator and the ring of expanded stages, 32 columns each.
+template <int MODE> struct Cfg { static constexpr int STAGES = tmem_a(MODE) ? 8 : (has_expanders(MODE) ? 6 : 7); };
+constexpr int TA_ACOL0 = 256;      // first tensor-memory column of the expanded-operand ring (FWT / DXT)
+constexpr int TA_STAGE_COLS = 32;  // 128 bytes of K per row
+constexpr int TOK_TAB_BYTES = 4 * 256 * 8;   // FWT: one table of (scale / 127, row sum) per token for each epilogue warp
 
 struct Params {
     int M, N, K;
@@ -215,6 +228,30 @@ __device__ __forceinline__ void umma_pair_x4(uint32_t tmem_d, uint32_t a_lo, uin
 #undef AB_MMA4
 }
 
+// The same for an A operand in tensor memory: its address advances 8 columns (32 bytes of K per row) per MMA, the
+// shared-memory descriptor of B by 32 bytes.
+template <bool I8>
+__device__ __forceinline__ void umma_pair_x4_ta(uint32_t tmem_d, uint32_t a_taddr, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                uint32_t first_acc) {
+#define AB_MMA4T(KIND)                                                                             \
+    asm volatile(                                                                                  \
+        "{\n\t.reg .pred p, pt;\n\t.reg .b64 db;\n\t.reg .b32 at, bl;\n\t"                        \
+        "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, %5, %5;\n\t"                                     \
+        "mov.b64 db, {%2, %3};\n\t"                                                                \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [%1], db, %4, p;\n\t"                       \
+        "add.u32 at, %1, 8;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 db, {bl, %3};\n\t"                    \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [at], db, %4, pt;\n\t"                      \
+        "add.u32 at, %1, 16;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 db, {bl, %3};\n\t"                   \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [at], db, %4, pt;\n\t"                      \
+        "add.u32 at, %1, 24;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 db, {bl, %3};\n\t"                   \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], [at], db, %4, pt;\n\t}"                     \
+        ::"r"(tmem_d), "r"(a_taddr), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first_acc)              \
+        : "memory")
+    if (I8) AB_MMA4T("i8");
+    else AB_MMA4T("f16");
+#undef AB_MMA4T
+}
+
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0) {
     if (p.n_fast) {
         n0 = (tile % p.tiles_n) * BN;
@@ -226,15 +263,19 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, 
 }
 
 template <int MODE>
-__global__ void __launch_bounds__((has_expanders(MODE) ? kWarpsExp : kWarpsDW) * 32, 1)
+__global__ void __launch_bounds__(block_warps(MODE) * 32, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_a = smem;
+    constexpr bool TA = tmem_a(MODE);      // expanded operand in tensor memory, roles of the operands swapped
+    constexpr bool I8 = is_i8(MODE);
+    constexpr int NACC = TA ? 1 : 2;       // accumulators in tensor memory
     uint8_t* s_b = s_a + STAGES * A_BYTES;
-    uint8_t* s_p = s_b + STAGES * B_BYTES;
+    uint8_t* s_p = s_b + (TA ? 0 : STAGES * B_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + (has_expanders(MODE) ? STAGES * P_BYTES : 0));
+    float2* tok_tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(bars) + 512);   // FWT: per token (scale / 127, row sum)
     // LEADER: "operands of the stage are ready in both CTAs".  FWD/DX: 16 expander-warp arrivals
     // (B halves written) plus the bytes of both A tiles; DW: one arrival plus the bytes of both
     // CTAs' A and B boxes.  One barrier, so the MMA thread waits once per stage.
@@ -254,7 +295,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t rank = cluster_ctarank();  // 0 = leader
     const int num_clusters = gridDim.x >> 1;
     // consumers of a published tile: the peer's producer, the MMA thread, 2 x 4 epilogue warps, 2 x 8 expander warps
-    constexpr uint32_t SCHED_CONSUMERS = has_expanders(MODE) ? 10 + 2 * NUM_EXP_WARPS : 10;
+    constexpr uint32_t SCHED_CONSUMERS = tmem_a(MODE) ? 2 + 2 * (ta_epi_warps() + ta_exp_warps(MODE)) : (has_expanders(MODE) ? 10 + 2 * NUM_EXP_WARPS : 10);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -265,7 +306,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(tmem_full + a), 1);
-            mbar_init(smem_u32(tmem_empty + a), 8);
+            mbar_init(smem_u32(tmem_empty + a), tmem_a(MODE) ? 2 * ta_epi_warps() : 8);
         }
         for (int q = 0; q < SCHED_SLOTS; ++q) {
             mbar_init(smem_u32(sched_full + q), 1);
@@ -325,7 +366,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             // bytes counted on the leader's barrier per stage: both CTAs' A tiles (+ DW: both B halves)
             constexpr uint32_t TX_LEADER = has_expanders(MODE) ? 2 * A_BYTES : 2 * (A_BYTES + B_BYTES);
-            constexpr uint32_t TX_P = MODE == FWD ? 128 * 32 : 128 * 16;
+            constexpr uint32_t TX_P = I8 ? 128 * 32 : 128 * 16;
             bool ok = true;
             int gi = 0;
             while (ok && tile < num_tiles) {
@@ -344,11 +385,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         if (has_expanders(MODE)) mbar_expect_tx_only(smem_u32(full + stage), TX_LEADER);
                         else mbar_expect_tx(smem_u32(full + stage), TX_LEADER);
                     }
-                    if (MODE == FWD) {
+                    if (I8) {
                         mbar_expect_tx(smem_u32(full_p + stage), TX_P);
                         tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 32, n0);
                         tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 128, m0);
-                    } else if (MODE == DX) {
+                    } else if (MODE == DX || MODE == DXT) {
                         mbar_expect_tx(smem_u32(full_p + stage), TX_P);
                         tma_load_2d(smem_u32(s_p + stage * P_BYTES), &tm_b, smem_u32(full_p + stage), kb * 16, n0);
                         tma_load_2d_pair(smem_u32(s_a + stage * A_BYTES), &tm_a, lbar, kb * 64, m0);
@@ -391,7 +432,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ---------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
             constexpr bool A_MN = MODE == DW, B_MN = MODE == DW || MODE == NN;   // operand stored with its M / N index contiguous
-            constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN) : make_idesc(1, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            // FWD: A = int8 activations (s8), B = weights + 1 (u8); FWT: the other way round
+            constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN)
+                                     : MODE == FWT ? make_idesc(2, 0, 1, 0, 0, BM, BN)
+                                                   : make_idesc(1, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
             const uint64_t da0 = A_MN ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
             const uint64_t db0 = B_MN ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
             constexpr int KSTEP = (A_MN ? 2048 : 32) >> 4, KSTEP_B = (B_MN ? 2048 : 32) >> 4;   // descriptor advance per K = 16
@@ -418,26 +462,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     AB_TRACE2(gi, 2);
                     tc_fence_after();
                     ready = mbar_try_cluster(full0 + 8 * ((s + 1) % STAGES), s + 1 == STAGES ? phase ^ 1 : phase);
-                    umma_pair_x4<MODE, KSTEP, KSTEP_B>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
-                                              first_acc);
+                    if (TA)   // A: this stage's columns of tensor memory; B: the activations' tile, staged where A is otherwise
+                        umma_pair_x4_ta<I8>(d_tmem, tmem_base + TA_ACOL0 + s * TA_STAGE_COLS, a_lo + s * (A_BYTES >> 4), a_hi, idesc, first_acc);
+                    else
+                        umma_pair_x4<MODE, KSTEP, KSTEP_B>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
+                                                  first_acc);
                     umma_commit_pair(empty0 + 8 * s);
                     AB_TRACE2(gi, 3);
                     ++gi;
                     first_acc = 1;
                     if (--kb_left == 0) {
-                        umma_commit_pair(tfull0 + 8 * (it & 1));
+                        umma_commit_pair(tfull0 + 8 * (it % NACC));
                         if (feed_next(feed, false, true, abort_flag) >= num_tiles) { ok = false; break; }
                         ++it;
                         kb_left = p.num_kb;
                         first_acc = 0;
-                        if (!(ok = mbar_wait_mma(tempty0 + 8 * (it & 1), ((it >> 1) & 1) ^ 1, abort_flag, 2))) break;
-                        d_tmem = tmem_base + (it & 1) * BN;
+                        if (!(ok = mbar_wait_mma(tempty0 + 8 * (it % NACC), ((it / NACC) & 1) ^ 1, abort_flag, 2))) break;
+                        d_tmem = tmem_base + (it % NACC) * BN;
                     }
                 }
                 phase ^= 1;
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < (TA ? 2 + ta_epi_warps() : 6)) {
         // ---------------------------------------------------------------------- epilogue
         const int quad = warp & 3;
         int it = 0;
@@ -447,9 +494,89 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
              tile = feed_next(feed, true, lane == 0, abort_flag), ++it) {
             int m0, n0;
             tile_coords(p, tile, m0, n0);
+            const int acc = it % NACC;
+            const uint32_t acc_phase = (it / NACC) & 1;
+            if (TA) {
+                // Transposed tile: lane = output feature (a row of W), column = token.  For every column the warp's 32
+                // lanes store 32 consecutive output features of one token: 128 contiguous bytes (f32) or 64 (bf16).
+                const int ch = (warp - 2) >> 2;               // which half of the tile's 256 token columns
+                const int mt = m0 + ch * 128;                 // first token of this warp's columns
+                float2* tab = tok_tab + (warp - 2) * 128;
+                if (I8) {   // the per-token factors of this warp's columns, fetched while the main loop still runs
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int tok = mt + j * 32 + lane;
+                        float2 e = make_float2(0.0f, 0.0f);
+                        if (tok < p.M) e = make_float2(__fdiv_rn(p.scales[tok], 127.0f), __int_as_float(p.rowsums[tok]));
+                        tab[j * 32 + lane] = e;
+                    }
+                    __syncwarp();
+                }
+                if (!(ok = mbar_wait(smem_u32(tmem_full + acc), acc_phase, abort_flag, 5))) break;
+                tc_fence_after();
+                const int wrow = n0 + 128 * (int)rank + quad * 32 + lane;
+                const bool w_ok = wrow < p.N;
+                const uint32_t taddr_t = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + ch * 128;
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t v[16];
+                    __syncwarp();
+                    tmem_ld16(taddr_t + c * 16, v);
+                    const int tok0 = mt + c * 16;
+                    if (tok0 >= p.M || !w_ok) continue;
+                    const int nt = p.M - tok0 < 16 ? p.M - tok0 : 16;   // tokens of this chunk (warp-uniform)
+                    // all 16 results first (independent loads and arithmetic), then the stores
+                    if (I8) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = (uint32_t)((int)v[i] - __float_as_int(tab[c * 16 + i].y));
+                        if (p.acc_out) {
+                            int32_t* d = p.acc_out + (long long)tok0 * p.N + wrow;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (i < nt) d[(long long)i * p.N] = (int32_t)v[i];
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            v[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)(int)v[i], tab[c * 16 + i].x), gamma));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__fmul_rn(__uint_as_float(v[i]), gamma));
+                    }
+                    if (p.out_dtype == AB_F32) {
+                        float* d = reinterpret_cast<float*>(p.out) + (long long)tok0 * p.ld_out + wrow;
+                        if (nt == 16 && p.beta == 0.0f) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) d[(long long)i * p.ld_out] = __uint_as_float(v[i]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (i < nt) {
+                                    float* q = d + (long long)i * p.ld_out;
+                                    *q = p.beta != 0.0f ? __fadd_rn(__uint_as_float(v[i]), *q) : __uint_as_float(v[i]);
+                                }
+                        }
+                    } else {
+                        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)tok0 * p.ld_out + wrow;
+                        if (nt == 16 && p.beta == 0.0f) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) d[(long long)i * p.ld_out] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (i < nt) {
+                                    __nv_bfloat16* q = d + (long long)i * p.ld_out;
+                                    *q = __float2bfloat16_rn(p.beta != 0.0f ? __fadd_rn(__uint_as_float(v[i]), __bfloat162float(*q)) : __uint_as_float(v[i]));
+                                }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + acc) & PEER_MASK);
+                continue;
+            }
             m0 += 128 * (int)rank;
-            const int acc = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
             if (!(ok = mbar_wait(smem_u32(tmem_full + acc), acc_phase, abort_flag, 5))) break;
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;
@@ -543,7 +670,50 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + acc) & PEER_MASK);
         }
-    } else if (has_expanders(MODE) && (warp & 3) != 1) {
+    } else if (TA) {
+        // ------------------------------------------------- expanders into tensor memory
+        // A warp reaches only the 32 lanes of its own quarter (warp % 4).  A set of 8 warps covers a stage: two per
+        // quarter, each expanding half of the stage's 128 bytes of K for the quarter's 32 rows of W (lane = row) and
+        // writing its 16 columns with one tcgen05.st.  bf16 has two such sets, which take alternate stages.
+        constexpr int EXP0 = 2 + ta_epi_warps(), SETS = ta_exp_warps(MODE) / 8;
+        const int xw = warp - EXP0;
+        const int q = warp & 3, h = (xw >> 2) & 1, set = xw >> 3;
+        const int row = q * 32 + lane;
+        const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + TA_ACOL0 + h * 16;
+        int stage = 0, gi = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = feed_next(feed, true, lane == 0, abort_flag); ok && tile < num_tiles;
+             tile = feed_next(feed, true, lane == 0, abort_flag)) {
+            for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
+                if (SETS == 1 || (gi & (SETS - 1)) == set) {
+                    if (!(ok = mbar_wait(smem_u32(full_p + stage), phase, abort_flag, 6))) break;
+                    {
+                        uint32_t o[16];
+                        if (I8) {
+                            const uint4 pk = *reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + row * 32 + h * 16);
+                            const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const uint4 x = expand_u8(w[c]);
+                                o[4 * c] = x.x; o[4 * c + 1] = x.y; o[4 * c + 2] = x.z; o[4 * c + 3] = x.w;
+                            }
+                        } else {
+                            const uint2 pk = *reinterpret_cast<const uint2*>(s_p + stage * P_BYTES + row * 16 + h * 8);
+                            expand_bf16(pk.x, o);
+                            expand_bf16(pk.y, o + 8);
+                        }
+                        __syncwarp();
+                        tmem_st16(a_taddr + stage * TA_STAGE_COLS, o);
+                        tc_fence_before();
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(smem_u32(full + stage) & PEER_MASK);
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (!TA && has_expanders(MODE) && (warp & 3) != 1) {
         // --------------------------------------------------------------------- expanders
         // Warp slots 6,7,8,10,11,12,14,15 -> expander index 0..7; two threads per row of this CTA's
         // 128-row B half, four 16-byte chunks each.
@@ -562,7 +732,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (!(ok = mbar_wait(smem_u32(full_p + stage), phase, abort_flag, 6))) break;
                     if (threadIdx.x == 6 * 32) AB_TRACE2(gi, 4);
                     uint8_t* brow = s_b + stage * B_BYTES + r * 128;
-                    if (MODE == FWD) {
+                    if (I8) {
                         const uint4 pk = *reinterpret_cast<const uint4*>(s_p + stage * P_BYTES + e * 16);
                         const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
@@ -660,7 +830,9 @@ __global__ void __launch_bounds__(128, 1) mma_pair_peak_kernel(int iters, int* s
 template <int MODE>
 static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
     constexpr int STAGES = Cfg<MODE>::STAGES;
-    constexpr size_t smem = 1024 + STAGES * (A_BYTES + B_BYTES + (has_expanders(MODE) ? P_BYTES : 0)) + 512;
+    constexpr size_t smem = 1024 + STAGES * (A_BYTES + (tmem_a(MODE) ? 0 : B_BYTES) + (has_expanders(MODE) ? P_BYTES : 0)) + 512 +
+                            (tmem_a(MODE) ? TOK_TAB_BYTES : 0);
+    static_assert(!tmem_a(MODE) || TA_ACOL0 + STAGES * TA_STAGE_COLS <= TMEM_COLS, "tensor memory: accumulator + operand ring");
     static_assert((4 * STAGES + 4 + 2 * SCHED_SLOTS) * 8 + 16 + 4 * SCHED_SLOTS <= 512, "barrier block");
     // per-device launch facts, looked up once; contexts on several host threads share them
     static std::mutex cache_mu;
@@ -676,7 +848,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     }
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
-    constexpr int KB = MODE == FWD ? 128 : 64;
+    constexpr int KB = is_i8(MODE) ? 128 : 64;
     p.num_kb = (p.K + KB - 1) / KB;
     p.status = ctx->dev_status;
     p.tile_counter = ctx->dev_status + 8;  // zero between launches: the last CTA pair of a launch resets it
@@ -685,7 +857,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     p.debug_flags = getenv("AB_TRACE_NOLOAD") ? 1 : 0;
 #endif
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3((has_expanders(MODE) ? kWarpsExp : kWarpsDW) * 32, 1, 1);
+    cfg.blockDim = dim3(block_warps(MODE) * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -750,6 +922,16 @@ int abk_tensor_peak_probe(ab_ctx* ctx, int kind_i8, int iters, double* ops_out) 
 int ab_make_tmap(ab_ctx* ctx, CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1,
                  uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle sw);
 
+// Which form a product takes (AB_OPT_GEMM_OPERAND_FORM; 0 = by shape).  Measured on 11 shapes from 1024 to 8192 tokens
+// and 512 to 14336 features: dx is 11-18 % faster with the weights in tensor memory at every shape; the forward
+// product, whose tiles are short when in_features is small (the accumulator is single-buffered in that form, so a
+// tile's epilogue is not hidden behind the next tile), gains 2-5 % from 8192 input features up and loses 3-9 % below.
+static bool weights_in_tensor_memory(const ab_ctx* ctx, bool forward_int8, size_t k) {
+    if (ctx->gemm_operand_form == 1) return true;
+    if (ctx->gemm_operand_form == 2) return false;
+    return forward_int8 ? k >= 8192 : true;
+}
+
 int abk_gemm2_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
                   const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {
     CUtensorMap ta, tb;
@@ -763,7 +945,7 @@ int abk_gemm2_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_
     p.gamma = w->gamma_dev; p.scales = scales; p.rowsums = rowsums;
     p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.acc_out = acc_out; p.beta = 0.0f;
     p.n_fast = 1;
-    return tc2::launch<tc::FWD>(ctx, ta, tb, p);
+    return weights_in_tensor_memory(ctx, true, w->in) ? tc2::launch<tc::FWT>(ctx, ta, tb, p) : tc2::launch<tc::FWD>(ctx, ta, tb, p);
 }
 
 int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx, int dx_dtype,
@@ -778,7 +960,7 @@ int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy,
     p.M = (int)m; p.N = (int)w->in; p.K = (int)w->out;
     p.gamma = w->gamma_dev; p.out = dx; p.out_dtype = dx_dtype; p.ld_out = (long long)ld_dx; p.beta = beta;
     p.n_fast = 1;
-    return tc2::launch<tc::DX>(ctx, ta, tb, p);
+    return weights_in_tensor_memory(ctx, false, (size_t)p.K) ? tc2::launch<tc::DXT>(ctx, ta, tb, p) : tc2::launch<tc::DX>(ctx, ta, tb, p);
 }
 
 // y = (beta * y +) gamma * x . codes^T with bf16 activations and f32 accumulation: the same kernel as dx (bf16 A operand
@@ -796,7 +978,7 @@ int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t l
     p.M = (int)m; p.N = (int)w->out; p.K = (int)w->in;
     p.gamma = w->gamma_dev; p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.beta = beta;
     p.n_fast = 1;
-    return tc2::launch<tc::DX>(ctx, ta, tb, p);
+    return weights_in_tensor_memory(ctx, false, (size_t)p.K) ? tc2::launch<tc::DXT>(ctx, ta, tb, p) : tc2::launch<tc::DX>(ctx, ta, tb, p);
 }
 
 int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,

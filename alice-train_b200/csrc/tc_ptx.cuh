@@ -14,8 +14,13 @@ constexpr int WAIT_LIMIT_TRIES = 100000;    // x 20 us = 2 s, then the kernel gi
 // FWD / DX take the B operand from 2-bit codes expanded in shared memory; DW, NT, NN are dense bf16 x bf16 with both
 // operands brought by TMA: DW = A^T B (both operands contract over their ROW index), NT = A B^T (both over their
 // column index), NN = A B (A over columns, B over rows).
-enum Mode { FWD = 0, DX = 1, DW = 2, NT = 3, NN = 4 };
-__host__ __device__ constexpr bool has_expanders(int mode) { return mode == FWD || mode == DX; }
+// FWT / DXT compute the same products as FWD / DX with the operand roles swapped: the expanded weights are the A operand
+// and live in TENSOR memory (written by the expander warps with tcgen05.st), the activations are the B operand in shared
+// memory, and the accumulator holds the output tile transposed (lane = output feature, column = token).
+enum Mode { FWD = 0, DX = 1, DW = 2, NT = 3, NN = 4, FWT = 5, DXT = 6 };
+__host__ __device__ constexpr bool has_expanders(int mode) { return mode == FWD || mode == DX || mode == FWT || mode == DXT; }
+__host__ __device__ constexpr bool tmem_a(int mode) { return mode == FWT || mode == DXT; }
+__host__ __device__ constexpr bool is_i8(int mode) { return mode == FWD || mode == FWT; }
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -95,6 +100,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 16 consecutive 32-bit columns of this warp's 32 lanes of tensor memory (lane = thread), then wait for the store
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
 // in 16-byte units, descriptor version 1 at bit 46, 128-byte swizzle (layout type 2) at bit 61.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {

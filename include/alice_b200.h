@@ -104,8 +104,16 @@ AB_API int ab_ctx_destroy(ab_ctx* ctx);
  *                                 buffers of a call may be read (y, dx) or reused (x, dy) after the next ab_ctx_sync().
  *                                 Consecutive calls then overlap: the copies in of one run beside the GEMMs and the
  *                                 copies out of the one before.
+ *   AB_OPT_GEMM_OPERAND_FORM   which of two forms of the same tensor-core kernel the batched forward and dx products
+ *                              take (identical results; a tuning and test switch).  In one the expanded weights are
+ *                              the B operand in shared memory, in the other the A operand in tensor memory (the
+ *                              output tile is then held transposed and stored token by token).
+ *                              0: chosen by shape (dx: tensor memory; forward: tensor memory when in_features >= 8192).
+ *                              1: tensor memory always.  2: shared memory always.
  */
-typedef enum ab_option { AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2, AB_OPT_HOST_INTEGER_MATVEC = 3 } ab_option;
+typedef enum ab_option {
+    AB_OPT_EXACT_MATVEC = 1, AB_OPT_ASYNC_HOST_STEP = 2, AB_OPT_HOST_INTEGER_MATVEC = 3, AB_OPT_GEMM_OPERAND_FORM = 4
+} ab_option;
 AB_API int ab_ctx_set_option(ab_ctx* ctx, int option, int value);
 /* Blocks until the stream is idle; also reports AB_ERR_DEVICE_TIMEOUT raised by a kernel. */
 AB_API int ab_ctx_sync(ab_ctx* ctx);

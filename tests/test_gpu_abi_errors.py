@@ -49,6 +49,8 @@ def test_context_family(env):
     assert lib.ab_ctx_create(99, None, C.byref(out)) == NO_DEVICE and not out.value
     assert lib.ab_ctx_create(-1, None, C.byref(out)) == NO_DEVICE
     assert lib.ab_ctx_set_option(h, 99, 1) == UNSUPPORTED
+    assert lib.ab_ctx_set_option(h, 4, 7) == UNSUPPORTED    # AB_OPT_GEMM_OPERAND_FORM takes 0, 1 or 2
+    assert lib.ab_ctx_set_option(h, 4, 0) == 0
     assert lib.ab_ctx_set_option(None, 1, 1) == NULL
     assert lib.ab_ctx_sync(None) == NULL and lib.ab_ctx_destroy(None) == NULL
     assert lib.ab_ctx_launch_count(None) == 0 and lib.ab_ctx_stream(None) is None

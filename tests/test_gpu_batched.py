@@ -55,9 +55,18 @@ def test_act_quant_bit_exact(env, orc, m, k, dtype):
     assert np.array_equal(qa.rowsums.cpu().numpy(), xq_ref.astype(np.int32).sum(axis=1))
 
 
+@pytest.fixture(params=[1, 2], ids=["weights-in-tensor-memory", "weights-in-shared-memory"])
+def operand_form(request, env):
+    """Both forms of the tensor-core forward / dx kernels (AB_OPT_GEMM_OPERAND_FORM), whatever the shape rule would pick."""
+    ctx = env[2]
+    ctx.set_gemm_operand_form(request.param)
+    yield request.param
+    ctx.set_gemm_operand_form(0)
+
+
 @pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 256, 128), (100, 300, 272), (1, 256, 4096),
-                                       (130, 8, 48), (257, 1000, 2000), (4, 4, 4), (3, 5, 7)])
-def test_forward_accumulators_bit_exact(env, orc, m, out, inn):
+                                       (130, 8, 48), (257, 1000, 2000), (4, 4, 4), (3, 5, 7), (300, 520, 8192)])
+def test_forward_accumulators_bit_exact(env, orc, operand_form, m, out, inn):
     at, bl, ctx, torch = env
     h, g, codes = _weights(env, orc, out, inn, 40)
     x = normal_f32(41, (m, inn))
@@ -78,7 +87,7 @@ def test_forward_accumulators_bit_exact(env, orc, m, out, inn):
 
 @pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 256, 128), (100, 300, 272), (1, 256, 4096), (130, 8, 48),
                                        (257, 1000, 2000), (4, 4, 4), (3, 5, 7), (512, 32, 4096), (1024, 14336, 4096)])
-def test_forward_bf16_vs_matmul_bt_oracle(env, orc, m, out, inn):
+def test_forward_bf16_vs_matmul_bt_oracle(env, orc, operand_form, m, out, inn):
     """The forward without activation quantisation, C = A B^T on fake-quantised weights: against orc_matmul_bt
     (src/llama_forward.rs:43-55, an fmaf chain in ascending k) on bf16-rounded x, 1e-5 of the largest output; the
     largest shape against a seeded sample of single-output chains."""
@@ -114,7 +123,7 @@ def test_forward_bf16_vs_matmul_bt_oracle(env, orc, m, out, inn):
 
 @pytest.mark.parametrize("m,out,inn", [(256, 512, 1024), (128, 64, 256), (100, 304, 264), (1, 4096, 256),
                                        (130, 48, 8), (257, 2000, 1000), (4, 4, 4), (3, 7, 5), (64, 200, 512)])
-def test_dx_vs_oracle(env, orc, m, out, inn):
+def test_dx_vs_oracle(env, orc, operand_form, m, out, inn):
     at, bl, ctx, torch = env
     h, g, codes = _weights(env, orc, out, inn, 50)
     dy = normal_f32(51, (m, out), 1e-2)
@@ -133,6 +142,30 @@ def test_dx_vs_oracle(env, orc, m, out, inn):
     bl.bitlinear_dx(h, dyt, dx=acc, beta=1.0)
     ctx.sync()
     assert rel_err(acc.cpu().numpy(), ref + base) <= RTOL_F32
+    h.close()
+
+
+def test_operand_forms_agree(env, orc):
+    """The two forms of the forward and dx kernels on the same inputs: the int8 forward bit for bit (integer sums, the same
+    three f32 operations behind them), dx to 1e-6 of its largest element (f32 accumulation inside the tensor core)."""
+    at, bl, ctx, torch = env
+    m, out, inn = 700, 1100, 8192
+    h, g, codes = _weights(env, orc, out, inn, 60)
+    xt, _ = to_bf16_tensor(orc, normal_f32(61, (m, inn)), "cuda")
+    dyt, _ = to_bf16_tensor(orc, normal_f32(62, (m, out), 1e-2), "cuda")
+    qa = bl.act_quant_int8(ctx, xt)
+    res = {}
+    try:
+        for form in (1, 2, 0):
+            ctx.set_gemm_operand_form(form)
+            y = bl.bitlinear_fwd(h, qa, dtype=torch.float32)
+            dx = bl.bitlinear_dx(h, dyt, dtype=torch.float32)
+            ctx.sync()
+            res[form] = (y.cpu().numpy(), dx.cpu().numpy())
+    finally:
+        ctx.set_gemm_operand_form(0)
+    assert np.array_equal(res[1][0], res[2][0]) and np.array_equal(res[0][0], res[1][0])
+    assert rel_err(res[1][1], res[2][1]) <= 1e-6 and np.array_equal(res[0][1], res[1][1])
     h.close()
 
 
