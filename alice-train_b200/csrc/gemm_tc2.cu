@@ -54,9 +54,10 @@ constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a sha
 
 // FWT / DXT need no shared-memory stage for the expanded operand (it goes to tensor memory), so their ring is deeper;
 // their tensor memory holds ONE 256-column accumulator and the ring of expanded stages, 32 columns each.
-template <int MODE> struct Cfg { static constexpr int STAGES = tmem_a(MODE) ? 8 : (has_expanders(MODE) ? 6 : 7); };
-constexpr int TA_ACOL0 = 256;      // first tensor-memory column of the expanded-operand ring (FWT / DXT)
-constexpr int TA_STAGE_COLS = 32;  // 128 bytes of K per row
+__host__ __device__ constexpr int ta_nacc(int tt) { return 2 * tt + 4 * 32 <= 512 ? 2 : 1; }
+__host__ __device__ constexpr int ta_stages(int tt) { return (512 - ta_nacc(tt) * tt) / 32 < 8 ? (512 - ta_nacc(tt) * tt) / 32 : 8; }
+template <int MODE, int TT = 256> struct Cfg { static constexpr int STAGES = tmem_a(MODE) ? ta_stages(TT) : (has_expanders(MODE) ? 6 : 7); };
+constexpr int TA_STAGE_COLS = 32;  // an expanded stage in tensor memory: 128 bytes of K per row
 constexpr int TOK_TAB_BYTES = 4 * 256 * 8;   // FWT: one table of (scale / 127, row sum) per token for each epilogue warp
 
 struct Params {
@@ -252,26 +253,36 @@ __device__ __forceinline__ void umma_pair_x4_ta(uint32_t tmem_d, uint32_t a_tadd
 #undef AB_MMA4T
 }
 
-__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0) {
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m0, int& n0, int bm = BM) {
     if (p.n_fast) {
         n0 = (tile % p.tiles_n) * BN;
-        m0 = (tile / p.tiles_n) * BM;
+        m0 = (tile / p.tiles_n) * bm;
     } else {
-        m0 = (tile % p.tiles_m) * BM;
+        m0 = (tile % p.tiles_m) * bm;
         n0 = (tile / p.tiles_m) * BN;
     }
 }
 
-template <int MODE>
+// TT (FWT / DXT only): tokens per tile = the N extent of the MMA.  256 leaves tensor memory for ONE accumulator and an
+// 8-stage ring of expanded weights.  Narrower tiles make room for two accumulators, so that a tile's epilogue overlaps
+// the next tile's main loop, but every one measured slower: 192 tokens (4-stage ring: too short for the expanders'
+// latency) +14 to +40 %, 160 (6 stages) and 128 (8 stages; shared-memory traffic per MMA clock back at its limit)
+// +15 to +50 %.  Only 256 is instantiated.
+template <int MODE, int TT = 256>
 __global__ void __launch_bounds__(block_warps(MODE) * 32, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
-    constexpr int STAGES = Cfg<MODE>::STAGES;
+    constexpr int STAGES = Cfg<MODE, TT>::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_a = smem;
     constexpr bool TA = tmem_a(MODE);      // expanded operand in tensor memory, roles of the operands swapped
     constexpr bool I8 = is_i8(MODE);
-    constexpr int NACC = TA ? 1 : 2;       // accumulators in tensor memory
+    constexpr int NACC = TA ? ta_nacc(TT) : 2;                        // accumulators in tensor memory
+    constexpr int TN = TA ? TT : BN;                                  // columns of one accumulator
+    constexpr int ACOL0 = NACC * TN;                                  // TA: first column of the expanded-operand ring
+    constexpr int A_RING = TA ? ((TMEM_COLS - ACOL0) / TA_STAGE_COLS < STAGES ? (TMEM_COLS - ACOL0) / TA_STAGE_COLS : STAGES) : STAGES;
+    static_assert(!TA || (STAGES % A_RING == 0 && A_RING >= 4 && TT % 32 == 0 && TT <= 256), "operand ring must divide the stage ring");
+    constexpr int BMT = TA ? TT : BM;                                 // extent of a tile along p.M
     uint8_t* s_b = s_a + STAGES * A_BYTES;
     uint8_t* s_p = s_b + (TA ? 0 : STAGES * B_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + (has_expanders(MODE) ? STAGES * P_BYTES : 0));
@@ -365,15 +376,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             // bytes counted on the leader's barrier per stage: both CTAs' A tiles (+ DW: both B halves)
-            constexpr uint32_t TX_LEADER = has_expanders(MODE) ? 2 * A_BYTES : 2 * (A_BYTES + B_BYTES);
+            constexpr uint32_t TX_LEADER = TA ? 2 * (TT / 2) * 128 : (has_expanders(MODE) ? 2 * A_BYTES : 2 * (A_BYTES + B_BYTES));
             constexpr uint32_t TX_P = I8 ? 128 * 32 : 128 * 16;
             bool ok = true;
             int gi = 0;
             while (ok && tile < num_tiles) {
                 int m0, n0;
-                tile_coords(p, tile, m0, n0);
-                m0 += 128 * (int)rank;  // this CTA's rows of A
-                n0 += 128 * (int)rank;  // and its half of B
+                tile_coords(p, tile, m0, n0, BMT);
+                m0 += (BMT / 2) * (int)rank;  // this CTA's rows of A (TA: its half of the tile's tokens)
+                n0 += 128 * (int)rank;        // and its half of B (TA: its rows of W)
                 for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                     if (!(ok = mbar_wait(smem_u32(empty + stage), phase ^ 1, abort_flag, 1))) break;
                     AB_TRACE2(gi, 0);
@@ -434,7 +445,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr bool A_MN = MODE == DW, B_MN = MODE == DW || MODE == NN;   // operand stored with its M / N index contiguous
             // FWD: A = int8 activations (s8), B = weights + 1 (u8); FWT: the other way round
             constexpr uint32_t idesc = MODE == FWD ? make_idesc(2, 1, 0, 0, 0, BM, BN)
-                                     : MODE == FWT ? make_idesc(2, 0, 1, 0, 0, BM, BN)
+                                     : MODE == FWT ? make_idesc(2, 0, 1, 0, 0, BM, TT)
+                                     : MODE == DXT ? make_idesc(1, 1, 1, 0, 0, BM, TT)
                                                    : make_idesc(1, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
             const uint64_t da0 = A_MN ? make_desc(smem_u32(s_a), 8192, 1024) : make_desc(smem_u32(s_a), 16, 1024);
             const uint64_t db0 = B_MN ? make_desc(smem_u32(s_b), 8192, 1024) : make_desc(smem_u32(s_b), 16, 1024);
@@ -463,7 +475,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     tc_fence_after();
                     ready = mbar_try_cluster(full0 + 8 * ((s + 1) % STAGES), s + 1 == STAGES ? phase ^ 1 : phase);
                     if (TA)   // A: this stage's columns of tensor memory; B: the activations' tile, staged where A is otherwise
-                        umma_pair_x4_ta<I8>(d_tmem, tmem_base + TA_ACOL0 + s * TA_STAGE_COLS, a_lo + s * (A_BYTES >> 4), a_hi, idesc, first_acc);
+                        umma_pair_x4_ta<I8>(d_tmem, tmem_base + ACOL0 + (s % A_RING) * TA_STAGE_COLS, a_lo + s * (A_BYTES >> 4), a_hi, idesc, first_acc);
                     else
                         umma_pair_x4<MODE, KSTEP, KSTEP_B>(d_tmem, a_lo + s * (A_BYTES >> 4), a_hi, b_lo + s * (B_BYTES >> 4), b_hi, idesc,
                                                   first_acc);
@@ -478,7 +490,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         kb_left = p.num_kb;
                         first_acc = 0;
                         if (!(ok = mbar_wait_mma(tempty0 + 8 * (it % NACC), ((it / NACC) & 1) ^ 1, abort_flag, 2))) break;
-                        d_tmem = tmem_base + (it % NACC) * BN;
+                        d_tmem = tmem_base + (it % NACC) * TN;
                     }
                 }
                 phase ^= 1;
@@ -493,23 +505,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int tile = feed_next(feed, true, lane == 0, abort_flag); ok && tile < num_tiles;
              tile = feed_next(feed, true, lane == 0, abort_flag), ++it) {
             int m0, n0;
-            tile_coords(p, tile, m0, n0);
+            tile_coords(p, tile, m0, n0, BMT);
             const int acc = it % NACC;
             const uint32_t acc_phase = (it / NACC) & 1;
             if (TA) {
                 // Transposed tile: lane = output feature (a row of W), column = token.  For every column the warp's 32
                 // lanes store 32 consecutive output features of one token: 128 contiguous bytes (f32) or 64 (bf16).
-                const int ch = (warp - 2) >> 2;               // which half of the tile's 256 token columns
-                const int mt = m0 + ch * 128;                 // first token of this warp's columns
+                constexpr int HC = TT / 2;                    // token columns of this warp
+                const int ch = (warp - 2) >> 2;               // which half of the tile's token columns
+                const int mt = m0 + ch * HC;                  // first token of this warp's columns
                 float2* tab = tok_tab + (warp - 2) * 128;
                 if (I8) {   // the per-token factors of this warp's columns, fetched while the main loop still runs
                     __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int tok = mt + j * 32 + lane;
+                    for (int j = 0; j < (HC + 31) / 32; ++j) {
+                        const int idx = j * 32 + lane, tok = mt + idx;
                         float2 e = make_float2(0.0f, 0.0f);
-                        if (tok < p.M) e = make_float2(__fdiv_rn(p.scales[tok], 127.0f), __int_as_float(p.rowsums[tok]));
-                        tab[j * 32 + lane] = e;
+                        if (idx < HC && tok < p.M) e = make_float2(__fdiv_rn(p.scales[tok], 127.0f), __int_as_float(p.rowsums[tok]));
+                        if (idx < 128) tab[idx] = e;
                     }
                     __syncwarp();
                 }
@@ -517,9 +530,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 tc_fence_after();
                 const int wrow = n0 + 128 * (int)rank + quad * 32 + lane;
                 const bool w_ok = wrow < p.N;
-                const uint32_t taddr_t = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + ch * 128;
+                const uint32_t taddr_t = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * TN + ch * HC;
 #pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < HC / 16; ++c) {
                     uint32_t v[16];
                     __syncwarp();
                     tmem_ld16(taddr_t + c * 16, v);
@@ -679,7 +692,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int xw = warp - EXP0;
         const int q = warp & 3, h = (xw >> 2) & 1, set = xw >> 3;
         const int row = q * 32 + lane;
-        const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + TA_ACOL0 + h * 16;
+        const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ACOL0 + h * 16;
         int stage = 0, gi = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -688,6 +701,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int kb = 0; kb < p.num_kb; ++kb, ++gi) {
                 if (SETS == 1 || (gi & (SETS - 1)) == set) {
                     if (!(ok = mbar_wait(smem_u32(full_p + stage), phase, abort_flag, 6))) break;
+                    // a ring of expanded stages shorter than the stage ring: the tensor-memory slot is free once the MMAs
+                    // of the stage that used it last (A_RING stages back) have retired
+                    if (A_RING < STAGES && gi >= A_RING)
+                        if (!(ok = mbar_wait(smem_u32(empty + (stage + STAGES - A_RING) % STAGES), ((gi - A_RING) / STAGES) & 1, abort_flag, 10))) break;
                     {
                         uint32_t o[16];
                         if (I8) {
@@ -704,7 +721,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             expand_bf16(pk.y, o + 8);
                         }
                         __syncwarp();
-                        tmem_st16(a_taddr + stage * TA_STAGE_COLS, o);
+                        tmem_st16(a_taddr + (stage % A_RING) * TA_STAGE_COLS, o);
                         tc_fence_before();
                     }
                     __syncwarp();
@@ -827,12 +844,11 @@ __global__ void __launch_bounds__(128, 1) mma_pair_peak_kernel(int iters, int* s
     }
 }
 
-template <int MODE>
+template <int MODE, int TT = 256>
 static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Params p) {
-    constexpr int STAGES = Cfg<MODE>::STAGES;
+    constexpr int STAGES = Cfg<MODE, TT>::STAGES;
     constexpr size_t smem = 1024 + STAGES * (A_BYTES + (tmem_a(MODE) ? 0 : B_BYTES) + (has_expanders(MODE) ? P_BYTES : 0)) + 512 +
                             (tmem_a(MODE) ? TOK_TAB_BYTES : 0);
-    static_assert(!tmem_a(MODE) || TA_ACOL0 + STAGES * TA_STAGE_COLS <= TMEM_COLS, "tensor memory: accumulator + operand ring");
     static_assert((4 * STAGES + 4 + 2 * SCHED_SLOTS) * 8 + 16 + 4 * SCHED_SLOTS <= 512, "barrier block");
     // per-device launch facts, looked up once; contexts on several host threads share them
     static std::mutex cache_mu;
@@ -842,11 +858,12 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     {
         std::lock_guard<std::mutex> lock(cache_mu);
         if (!attr_set[dev]) {
-            AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            AB_CUDA_CHECK(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set[dev] = true;
         }
     }
-    p.tiles_m = (p.M + BM - 1) / BM;
+    constexpr int BMT = tmem_a(MODE) ? TT : BM;
+    p.tiles_m = (p.M + BMT - 1) / BMT;
     p.tiles_n = (p.N + BN - 1) / BN;
     constexpr int KB = is_i8(MODE) ? 128 : 64;
     p.num_kb = (p.K + KB - 1) / KB;
@@ -874,7 +891,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
         if (max_clusters[dev] == 0) {
             cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1), 1, 1);
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg) != cudaSuccess || n <= 0) {
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE, TT>, &cfg) != cudaSuccess || n <= 0) {
                 cudaGetLastError();
                 n = ctx->sm_count / 2;
             }
@@ -885,7 +902,7 @@ static int launch(ab_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Par
     long long tiles = (long long)p.tiles_m * p.tiles_n;
     int clusters = (int)(tiles < max_pairs ? tiles : max_pairs);
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-    AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, ta, tb, p));
+    AB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE, TT>, ta, tb, p));
     ctx->launches++;
     return AB_OK;
 }
@@ -935,6 +952,7 @@ static bool weights_in_tensor_memory(const ab_ctx* ctx, bool forward_int8, size_
 int abk_gemm2_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_xq, const float* scales,
                   const int32_t* rowsums, size_t m, void* y, int y_dtype, size_t ld_y, int32_t* acc_out) {
     CUtensorMap ta, tb;
+    const bool tmem_form = weights_in_tensor_memory(ctx, true, w->in);
     int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, w->in, m, ld_xq, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st) return st;
     st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_fwd, w->pitch, w->out, w->pitch, 32, 128,
@@ -945,12 +963,14 @@ int abk_gemm2_fwd(ab_ctx* ctx, const ab_weights* w, const int8_t* xq, size_t ld_
     p.gamma = w->gamma_dev; p.scales = scales; p.rowsums = rowsums;
     p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.acc_out = acc_out; p.beta = 0.0f;
     p.n_fast = 1;
-    return weights_in_tensor_memory(ctx, true, w->in) ? tc2::launch<tc::FWT>(ctx, ta, tb, p) : tc2::launch<tc::FWD>(ctx, ta, tb, p);
+    if (!tmem_form) return tc2::launch<tc::FWD>(ctx, ta, tb, p);
+    return tc2::launch<tc::FWT>(ctx, ta, tb, p);
 }
 
 int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy, size_t m, void* dx, int dx_dtype,
                  size_t ld_dx, float beta) {
     CUtensorMap ta, tb;
+    const bool tmem_form = weights_in_tensor_memory(ctx, false, w->out);
     int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dy, w->out, m, ld_dy * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st) return st;
     st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_t, w->tpitch, w->in, w->tpitch, 16, 128,
@@ -960,7 +980,8 @@ int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy,
     p.M = (int)m; p.N = (int)w->in; p.K = (int)w->out;
     p.gamma = w->gamma_dev; p.out = dx; p.out_dtype = dx_dtype; p.ld_out = (long long)ld_dx; p.beta = beta;
     p.n_fast = 1;
-    return weights_in_tensor_memory(ctx, false, (size_t)p.K) ? tc2::launch<tc::DXT>(ctx, ta, tb, p) : tc2::launch<tc::DX>(ctx, ta, tb, p);
+    if (!tmem_form) return tc2::launch<tc::DX>(ctx, ta, tb, p);
+    return tc2::launch<tc::DXT>(ctx, ta, tb, p);
 }
 
 // y = (beta * y +) gamma * x . codes^T with bf16 activations and f32 accumulation: the same kernel as dx (bf16 A operand
@@ -969,6 +990,7 @@ int abk_gemm2_dx(ab_ctx* ctx, const ab_weights* w, const void* dy, size_t ld_dy,
 int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t ld_x, size_t m, void* y, int y_dtype,
                        size_t ld_y, float beta) {
     CUtensorMap ta, tb;
+    const bool tmem_form = weights_in_tensor_memory(ctx, false, w->in);
     int st = ab_make_tmap(ctx, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, w->in, m, ld_x * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st) return st;
     st = ab_make_tmap(ctx, &tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->codes_fwd, w->pitch, w->out, w->pitch, 16, 128,
@@ -978,7 +1000,8 @@ int abk_gemm2_fwd_bf16(ab_ctx* ctx, const ab_weights* w, const void* x, size_t l
     p.M = (int)m; p.N = (int)w->out; p.K = (int)w->in;
     p.gamma = w->gamma_dev; p.out = y; p.out_dtype = y_dtype; p.ld_out = (long long)ld_y; p.beta = beta;
     p.n_fast = 1;
-    return weights_in_tensor_memory(ctx, false, (size_t)p.K) ? tc2::launch<tc::DXT>(ctx, ta, tb, p) : tc2::launch<tc::DX>(ctx, ta, tb, p);
+    if (!tmem_form) return tc2::launch<tc::DX>(ctx, ta, tb, p);
+    return tc2::launch<tc::DXT>(ctx, ta, tb, p);
 }
 
 int abk_gemm2_dw(ab_ctx* ctx, const void* dy, size_t ld_dy, const void* x, size_t ld_x, size_t m, size_t out, size_t in,

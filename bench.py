@@ -500,7 +500,8 @@ def run_main(env, args):
         fr[c] = {"frac_burst": a / (mult * pk["bf16_tflops"]), "frac_sustained": a / (mult * pk["bf16_tflops_sustained"]),
                  "frac_probe": a / (probe["int8_tops"] if c == "fwd" else probe["bf16_tflops"])}
     dom = max(("fwd", "dx", "dw"), key=lambda c: per[c]["ms_total"])
-    kernel_names = {"fwd": "gemm_pair_kernel<FWD> int8 x ternary", "dx": "gemm_pair_kernel<DX> bf16 x ternary",
+    kernel_names = {"fwd": "gemm_pair_kernel<FWD / FWT> int8 x ternary (weights in tensor memory from 8192 input features)",
+                    "dx": "gemm_pair_kernel<DXT> bf16 x ternary (expanded weights in tensor memory)",
                     "dw": "gemm_pair_kernel<DW> bf16 x bf16"}
     peak = (2.0 if dom == "fwd" else 1.0) * bf16_peak
     roofline = {"bound": "tensor", "kernel": kernel_names[dom], "achieved": per[dom]["tops_avg"], "peak": peak, "unit": "TFLOP/s",
