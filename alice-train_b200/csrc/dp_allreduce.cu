@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int kArThreads = 256;
+constexpr int kArThreads = 128;   // half of the 256-thread unit the `ctas` arguments count in: two CTAs are launched per unit
 constexpr unsigned long long kSpinNs = 4000000000ull;  // 4 s: far beyond any skew between the GPUs' launches
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -81,8 +81,9 @@ __device__ __forceinline__ void mc_st_raw(void* mc, uint4 v) {
 //   ALLGATHER          : slice `rank` of the buffer holds this GPU's contribution: plain local load -> st to all GPUs
 //   REDUCESCATTER_BF16 : slice `rank` of the buffer: ld_reduce (bf16, f32 accumulation) -> plain store to `out_local`
 // flags (u32, in the multicast-mapped allocation): [0] start barrier, [1] end barrier, [2] CTAs of this GPU done.
-// The CTA is small on purpose (256 threads, no shared memory of its own, at most 64 registers a thread): it fits on
-// an SM beside a resident CTA of the pair GEMMs, so the exchange takes issue slots from them, not SMs.
+// The CTA is small on purpose (128 threads, no shared memory of its own, at most 64 registers a thread = 8192
+// registers): it fits on an SM beside a resident CTA of the pair GEMMs, the largest of which (dx with the weights in
+// tensor memory: 26 warps x 64 registers) leaves 12288 registers free, so the exchange takes issue slots from them, not SMs.
 enum { OP_ALLREDUCE_F32 = 0, OP_ALLGATHER = 1, OP_REDUCESCATTER_BF16 = 2 };
 
 template <int OP>
@@ -181,7 +182,7 @@ static int exchange_launch(ab_ctx* ctx, void* mc_buf, const void* local_buf, voi
     // the exchange starts once everything queued on the context's stream so far (the producing GEMM) has finished
     AB_CUDA_CHECK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
     AB_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
-    nvls_exchange_kernel<OP><<<ctas, kArThreads, 0, ctx->comm_stream>>>(
+    nvls_exchange_kernel<OP><<<2 * ctas, kArThreads, 0, ctx->comm_stream>>>(
         static_cast<uint4*>(mc_buf), static_cast<const uint4*>(local_buf), static_cast<uint4*>(out_local), bytes / 16, flags_local,
         flags_mc, rank, world, epoch * (unsigned int)world, ctx->dev_status);
     AB_LAUNCH_CHECK(ctx);

@@ -466,7 +466,8 @@ AB_API int ab_qat_linear_steps(ab_ctx* ctx, const ab_linear_step* steps, size_t 
  *                    call, on every GPU (then synchronise the GPUs)
  *   flags_multicast  the same 16 bytes in the multicast mapping
  *   epoch            1 for the first call on this buffer, then 2, 3, ...; equal on all GPUs
- *   ctas             CTAs to launch (256 threads each, small enough to share an SM with a GEMM CTA), 0 = default
+ *   ctas             units of 256 threads to launch (as two CTAs of 128 threads each, small enough to share an SM with
+ *                    a GEMM CTA), 0 = default
  *                    (16 for 2 GPUs, 12 for up to 4, 8 beyond: sized for a gradient exchange that overlaps GEMMs)
  * _start queues the exchange on a high-priority stream of the context behind the work already queued on the
  * context's stream and returns; _wait makes the context's stream wait for every exchange started so far.  Every
