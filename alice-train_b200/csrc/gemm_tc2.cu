@@ -8,6 +8,9 @@
 //   DW   dW = dy^T . x                          bf16 x bf16 (both MN-major), f32 in TMEM
 //   NT   C  = A . B^T                           bf16 x bf16 (both K-major): the dense output head's logits
 //   NN   C  = A . B                             bf16 x bf16 (A K-major, B MN-major): its d_hidden = d_logits . W
+//   FWT / DXT  the products of FWD / DX with the operand roles swapped: the expanded weights are the A operand and live
+//              in TENSOR memory (tcgen05.st by the expander warps), the activations are B, the output tile is held
+//              transposed.  Their warp roles differ from the list below: see block_warps() and the branches on TA.
 //
 // A cluster of two CTAs walks 256x256 tiles persistently.  Per CTA:
 //   warp 0   TMA producer.  A (and for DW the B half) is loaded with the cta_group::2 form so
