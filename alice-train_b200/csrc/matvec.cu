@@ -235,13 +235,40 @@ prenorm_finish_kernel(const float* __restrict__ x, size_t n, float eps, float* _
     __shared__ double s_a[32], s_b[32];
     __shared__ float s_inv, s_coef;
     // launched with programmatic stream serialisation behind the matvec that produces dx: its launch overlaps that
-    // kernel's tail, its reads wait here until the producer has completed
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // kernel's tail, its reads of dx wait below until the producer has completed.  x does not come from the producer: for
+    // vectors of up to 16 elements per thread it is read (and its squares summed) BEFORE the wait and kept in registers
+    // together with dx, so that after the wait only dx is read, once.  Same elements per thread in the same order as the
+    // strided loops, so the f64 sums are unchanged.  (Reading x early is safe whatever wrote it: the matvec in front lets
+    // its dependents start only after its own wait for ITS predecessors, so every earlier kernel of the stream has completed
+    // by the time this one runs at all.)
+    constexpr int R = 16;
+    const bool cached = n <= (size_t)R * blockDim.x;
+    float xr[R], dr[R];
     double ss = 0.0, dot = 0.0;
-    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
-        double xv = (double)x[i];
-        ss += xv * xv;
-        dot += xv * (double)dx[i];
+    if (cached) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const size_t i = threadIdx.x + (size_t)r * blockDim.x;
+            xr[r] = i < n ? x[i] : 0.0f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) ss += (double)xr[r] * (double)xr[r];
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (cached) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const size_t i = threadIdx.x + (size_t)r * blockDim.x;
+            dr[r] = i < n ? dx[i] : 0.0f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) dot += (double)xr[r] * (double)dr[r];
+    } else {
+        for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+            double xv = (double)x[i];
+            ss += xv * xv;
+            dot += xv * (double)dx[i];
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         ss += __shfl_down_sync(0xffffffffu, ss, o);
@@ -260,8 +287,16 @@ prenorm_finish_kernel(const float* __restrict__ x, size_t n, float eps, float* _
     }
     __syncthreads();
     const float inv = s_inv, coef = s_coef;
-    for (size_t i = threadIdx.x; i < n; i += blockDim.x)
-        dx[i] = __fsub_rn(__fmul_rn(dx[i], inv), __fmul_rn(coef, x[i]));
+    if (cached) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const size_t i = threadIdx.x + (size_t)r * blockDim.x;
+            if (i < n) dx[i] = __fsub_rn(__fmul_rn(dr[r], inv), __fmul_rn(coef, xr[r]));
+        }
+    } else {
+        for (size_t i = threadIdx.x; i < n; i += blockDim.x)
+            dx[i] = __fsub_rn(__fmul_rn(dx[i], inv), __fmul_rn(coef, x[i]));
+    }
 }
 
 // ------------------------------------------------------------------- STE rank-1 update
